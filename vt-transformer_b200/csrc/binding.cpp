@@ -1,0 +1,220 @@
+// Python bindings of the kernels: tensors in, checks of device, dtype, shape and layout,
+// then the plain-pointer launchers of kernels.h on the current stream.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "kernels.h"
+
+namespace {
+
+using torch::Tensor;
+
+int dtype_code(const Tensor& t, const char* name) {
+    if (t.scalar_type() == torch::kFloat32) return vtb::kF32;
+    if (t.scalar_type() == torch::kBFloat16) return vtb::kBF16;
+    TORCH_CHECK(false, name, ": dtype must be float32 or bfloat16, found ", t.scalar_type());
+}
+
+void check_cuda(const Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda(), name, ": must be a CUDA tensor (there is no CPU path)");
+    TORCH_CHECK(t.is_contiguous(), name, ": must be contiguous");
+}
+
+void check_i32(const Tensor& t, const char* name) {
+    check_cuda(t, name);
+    TORCH_CHECK(t.scalar_type() == torch::kInt32, name, ": must be int32");
+}
+
+void check_f32(const Tensor& t, const char* name) {
+    check_cuda(t, name);
+    TORCH_CHECK(t.scalar_type() == torch::kFloat32, name, ": must be float32");
+}
+
+void check_launch(cudaError_t e, const char* what) {
+    TORCH_CHECK(e == cudaSuccess, what, ": launch failed: ", cudaGetErrorString(e));
+}
+
+cudaStream_t stream_of(const Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
+
+int* status_ptr(const c10::optional<Tensor>& status) {
+    if (!status.has_value()) return nullptr;
+    check_i32(*status, "status");
+    TORCH_CHECK(status->numel() >= 2, "status: needs two ints");
+    return status->data_ptr<int>();
+}
+
+void embedding(const Tensor& table, const Tensor& ids, Tensor& out, c10::optional<Tensor> status) {
+    check_cuda(table, "table"); check_i32(ids, "ids"); check_f32(out, "out");
+    TORCH_CHECK(table.dim() == 2 && out.dim() == 2, "embedding: table and out must be 2-d");
+    const int hidden = table.size(1);
+    TORCH_CHECK(hidden % 8 == 0, "embedding: hidden size ", hidden, " must be a multiple of 8");
+    TORCH_CHECK(out.size(1) == hidden && out.size(0) == ids.numel(), "embedding: out must be [tokens, hidden]");
+    c10::cuda::CUDAGuard guard(table.device());
+    check_launch(vtb::launch_embedding(dtype_code(table, "table"), table.data_ptr(), ids.data_ptr<int>(),
+                                       out.data_ptr<float>(), ids.numel(), hidden, table.size(0),
+                                       status_ptr(status), stream_of(table)), "embedding");
+}
+
+void rmsnorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, double eps, Tensor& out,
+             c10::optional<Tensor> rows, c10::optional<Tensor> status) {
+    check_f32(x, "x"); check_f32(weight, "weight"); check_cuda(out, "out");
+    TORCH_CHECK(x.dim() == 2 && out.dim() == 2, "rmsnorm: x and out must be 2-d");
+    const int hidden = x.size(1);
+    TORCH_CHECK(hidden % 8 == 0, "rmsnorm: hidden size ", hidden, " must be a multiple of 8");
+    TORCH_CHECK(weight.numel() == hidden && out.size(1) == hidden, "rmsnorm: weight and out must match hidden size");
+    const int code = dtype_code(out, "out");
+    const void* dp = nullptr;
+    if (delta.has_value()) {
+        check_cuda(*delta, "delta");
+        TORCH_CHECK(delta->scalar_type() == out.scalar_type(), "rmsnorm: delta and out must have one dtype");
+        TORCH_CHECK(delta->sizes() == x.sizes(), "rmsnorm: delta must have the shape of x");
+        dp = delta->data_ptr();
+    }
+    const int* rp = nullptr;
+    int n_rows = x.size(0);
+    if (rows.has_value()) {
+        check_i32(*rows, "rows");
+        rp = rows->data_ptr<int>();
+        n_rows = rows->numel();
+    }
+    TORCH_CHECK(out.size(0) == n_rows, "rmsnorm: out must have one row for each normed row");
+    c10::cuda::CUDAGuard guard(x.device());
+    check_launch(vtb::launch_rmsnorm(code, x.data_ptr<float>(), dp, weight.data_ptr<float>(), (float)eps,
+                                     out.data_ptr(), rp, n_rows, x.size(0), hidden, status_ptr(status),
+                                     stream_of(x)), "rmsnorm");
+}
+
+void silu_mul(const Tensor& gu, Tensor& out) {
+    check_cuda(gu, "gu"); check_cuda(out, "out");
+    TORCH_CHECK(gu.dim() == 2 && out.dim() == 2 && gu.size(1) == 2 * out.size(1) && gu.size(0) == out.size(0),
+                "silu_mul: gu must be [tokens, 2 * inter] and out [tokens, inter]");
+    TORCH_CHECK(gu.scalar_type() == out.scalar_type(), "silu_mul: one dtype");
+    TORCH_CHECK(out.size(1) % 8 == 0, "silu_mul: intermediate size ", out.size(1), " must be a multiple of 8");
+    c10::cuda::CUDAGuard guard(gu.device());
+    check_launch(vtb::launch_silu_mul(dtype_code(gu, "gu"), gu.data_ptr(), out.data_ptr(), gu.size(0), out.size(1),
+                                      stream_of(gu)), "silu_mul");
+}
+
+void check_cache(const Tensor& k_cache, const Tensor& v_cache, const Tensor& ref, int kv_heads, int head_dim) {
+    check_cuda(k_cache, "k_cache"); check_cuda(v_cache, "v_cache");
+    TORCH_CHECK(k_cache.dim() == 4 && k_cache.sizes() == v_cache.sizes(),
+                "cache: k and v must be [pages, kv_heads, page_size, head_dim]");
+    TORCH_CHECK(k_cache.size(1) == kv_heads && k_cache.size(3) == head_dim, "cache: kv_heads or head_dim differ");
+    TORCH_CHECK(k_cache.scalar_type() == ref.scalar_type() && v_cache.scalar_type() == ref.scalar_type(),
+                "cache: dtype differs from the activations'");
+}
+
+void rope_store(Tensor& qkv, const Tensor& positions, c10::optional<Tensor> cos_sin, Tensor& k_cache, Tensor& v_cache,
+                const Tensor& token_seq, const Tensor& block_table, int64_t heads, int64_t kv_heads, int64_t head_dim,
+                bool store, c10::optional<Tensor> status) {
+    check_cuda(qkv, "qkv"); check_i32(positions, "positions"); check_i32(token_seq, "token_seq");
+    check_i32(block_table, "block_table");
+    TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) == (heads + 2 * kv_heads) * head_dim,
+                "rope_store: qkv must be [tokens, (heads + 2 kv_heads) * head_dim]");
+    TORCH_CHECK(head_dim % 2 == 0, "rope_store: head_dim must be even");
+    const int n = qkv.size(0);
+    TORCH_CHECK(positions.numel() == n && token_seq.numel() == n, "rope_store: one position and sequence a token");
+    TORCH_CHECK(block_table.dim() == 2, "rope_store: block_table must be [sequences, stride]");
+    check_cache(k_cache, v_cache, qkv, kv_heads, head_dim);
+    const float2* cs = nullptr;
+    int max_pos = 0;
+    if (cos_sin.has_value()) {
+        check_f32(*cos_sin, "cos_sin");
+        TORCH_CHECK(cos_sin->dim() == 3 && cos_sin->size(1) == head_dim / 2 && cos_sin->size(2) == 2,
+                    "rope_store: cos_sin must be [positions, head_dim / 2, 2]");
+        cs = reinterpret_cast<const float2*>(cos_sin->data_ptr<float>());
+        max_pos = cos_sin->size(0);
+    }
+    c10::cuda::CUDAGuard guard(qkv.device());
+    check_launch(vtb::launch_rope_store(dtype_code(qkv, "qkv"), qkv.data_ptr(), positions.data_ptr<int>(), cs, max_pos,
+                                        k_cache.data_ptr(), v_cache.data_ptr(), token_seq.data_ptr<int>(),
+                                        block_table.data_ptr<int>(), block_table.size(1), block_table.size(0),
+                                        k_cache.size(0), n, heads, kv_heads, head_dim, k_cache.size(2),
+                                        cs != nullptr, store, status_ptr(status), stream_of(qkv)), "rope_store");
+}
+
+void gemm_simt(const Tensor& a, const Tensor& w, c10::optional<Tensor> bias, Tensor& c) {
+    check_cuda(a, "a"); check_cuda(w, "w"); check_cuda(c, "c");
+    TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && c.dim() == 2, "gemm_simt: 2-d tensors");
+    TORCH_CHECK(a.scalar_type() == w.scalar_type(), "gemm_simt: a and w must have one dtype");
+    const int in_code = dtype_code(a, "a"), out_code = dtype_code(c, "c");
+    TORCH_CHECK(out_code == vtb::kF32 || out_code == in_code, "gemm_simt: out must be float32 or the dtype of a");
+    const int m = a.size(0), k = a.size(1), n = w.size(0);
+    TORCH_CHECK(w.size(1) == k && c.size(0) == m && c.size(1) == n, "gemm_simt: shapes [m,k] x [n,k] -> [m,n]");
+    TORCH_CHECK(k % 8 == 0, "gemm_simt: inner size ", k, " must be a multiple of 8");
+    const float* bp = nullptr;
+    if (bias.has_value()) {
+        check_f32(*bias, "bias");
+        TORCH_CHECK(bias->numel() == n, "gemm_simt: bias must have one entry for each output column");
+        bp = bias->data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(a.device());
+    check_launch(vtb::launch_gemm_simt(in_code, out_code, a.data_ptr(), w.data_ptr(), bp, c.data_ptr(), m, n, k,
+                                       stream_of(a)), "gemm_simt");
+}
+
+void attention_simt(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache,
+                    const Tensor& positions, const Tensor& token_seq, const Tensor& block_table, int64_t heads,
+                    int64_t kv_heads, int64_t head_dim, int64_t window, double scale, c10::optional<Tensor> status) {
+    check_cuda(qkv, "qkv"); check_cuda(out, "out"); check_i32(positions, "positions");
+    check_i32(token_seq, "token_seq"); check_i32(block_table, "block_table");
+    TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) >= heads * head_dim, "attention: qkv must hold the queries first");
+    TORCH_CHECK(out.dim() == 2 && out.size(0) == qkv.size(0) && out.size(1) == heads * head_dim,
+                "attention: out must be [tokens, heads * head_dim]");
+    TORCH_CHECK(out.scalar_type() == qkv.scalar_type(), "attention: one dtype");
+    TORCH_CHECK(head_dim <= 256, "attention: head_dim ", head_dim, " is above 256");
+    TORCH_CHECK(heads % kv_heads == 0, "attention: heads must be a multiple of kv_heads");
+    check_cache(k_cache, v_cache, qkv, kv_heads, head_dim);
+    const int n = qkv.size(0);
+    TORCH_CHECK(positions.numel() == n && token_seq.numel() == n, "attention: one position and sequence a token");
+    c10::cuda::CUDAGuard guard(qkv.device());
+    check_launch(vtb::launch_attention_simt(dtype_code(qkv, "qkv"), qkv.data_ptr(), qkv.size(1), out.data_ptr(),
+                                            k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr<int>(),
+                                            token_seq.data_ptr<int>(), block_table.data_ptr<int>(),
+                                            block_table.size(1), block_table.size(0), k_cache.size(0), n, heads,
+                                            kv_heads, head_dim, k_cache.size(2), window, (float)scale,
+                                            status_ptr(status), stream_of(qkv)), "attention_simt");
+}
+
+void argmax(const Tensor& logits, Tensor& out) {
+    check_f32(logits, "logits"); check_i32(out, "out");
+    TORCH_CHECK(logits.dim() == 2 && out.numel() == logits.size(0), "argmax: logits [rows, vocab], out [rows]");
+    c10::cuda::CUDAGuard guard(logits.device());
+    check_launch(vtb::launch_argmax(logits.data_ptr<float>(), out.data_ptr<int>(), logits.size(0), logits.size(1),
+                                    stream_of(logits)), "argmax");
+}
+
+void sample(const Tensor& logits, const Tensor& temperature, const Tensor& top_k, const Tensor& top_p, const Tensor& u,
+            Tensor& out) {
+    check_f32(logits, "logits"); check_f32(temperature, "temperature"); check_i32(top_k, "top_k");
+    check_f32(top_p, "top_p"); check_f32(u, "u"); check_i32(out, "out");
+    const int rows = logits.size(0);
+    TORCH_CHECK(logits.dim() == 2 && temperature.numel() == rows && top_k.numel() == rows && top_p.numel() == rows &&
+                    u.numel() == rows && out.numel() == rows,
+                "sample: one parameter of each kind for each row of logits");
+    c10::cuda::CUDAGuard guard(logits.device());
+    check_launch(vtb::launch_sample(logits.data_ptr<float>(), temperature.data_ptr<float>(), top_k.data_ptr<int>(),
+                                    top_p.data_ptr<float>(), u.data_ptr<float>(), out.data_ptr<int>(), rows,
+                                    logits.size(1), stream_of(logits)), "sample");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    namespace py = pybind11;
+    m.def("embedding", &embedding, py::arg("table"), py::arg("ids"), py::arg("out"), py::arg("status") = py::none());
+    m.def("rmsnorm", &rmsnorm, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("eps"), py::arg("out"),
+          py::arg("rows") = py::none(), py::arg("status") = py::none());
+    m.def("silu_mul", &silu_mul, py::arg("gu"), py::arg("out"));
+    m.def("rope_store", &rope_store, py::arg("qkv"), py::arg("positions"), py::arg("cos_sin"), py::arg("k_cache"),
+          py::arg("v_cache"), py::arg("token_seq"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),
+          py::arg("head_dim"), py::arg("store"), py::arg("status") = py::none());
+    m.def("gemm_simt", &gemm_simt, py::arg("a"), py::arg("w"), py::arg("bias"), py::arg("c"));
+    m.def("attention_simt", &attention_simt, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
+          py::arg("positions"), py::arg("token_seq"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),
+          py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("status") = py::none());
+    m.def("argmax", &argmax, py::arg("logits"), py::arg("out"));
+    m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"),
+          py::arg("u"), py::arg("out"));
+}

@@ -1,0 +1,233 @@
+// Embedding, RMS norm with the residual sum, SiLU * up, rotation with the cache store.
+//
+// Formulas after vt-transformer's kernels: v1/tensortype/cuda_kernels/rmsnorm.cu:20-47
+// (w * x * rsqrt(mean(x^2) + eps), all in 32-bit, one rounding),
+// v1/tensortype/cuda_kernels/rotary_embed.cu:19-29 (pairs (i, i + d/2)),
+// v1/tensortype/cuda_kernels/silu_product.cu:15-17 (act / (1 + exp(-act)) * in),
+// v1/tensortype/host_tensor.cpp:189-198 (the embedding is a copy of rows).
+// The launch shapes are this engine's: one block a token, 16-byte accesses, the residual
+// sum folded into the norm, and the keys and values written straight into their pages.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace vtb {
+
+// ------------------------------------------------------------------------- embedding
+
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+                                 int hidden, int vocab, int* status) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (size_t)t * hidden;
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0 && id >= vocab) set_status(status, kStatusBadTokenId, id);
+        // a negative id marks a padding token: its row is zero
+        for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+            float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            Vec8<float>::store(o + i, z);
+        }
+        return;
+    }
+    const T* row = table + (size_t)id * hidden;
+    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+        float f[8];
+        Vec8<T>::load(row + i, f);
+        Vec8<float>::store(o + i, f);
+    }
+}
+
+cudaError_t launch_embedding(int table_dtype, const void* table, const int* ids, float* out, int n_tokens,
+                             int hidden, int vocab, int* status, cudaStream_t stream) {
+    if (n_tokens == 0) return cudaSuccess;
+    int threads = min(256, max(32, ((hidden / 8 + 31) / 32) * 32));
+    if (table_dtype == kBF16)
+        embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
+    else
+        embedding_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab, status);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------- rmsnorm
+
+// One block a row.  Pass 1 forms v = x (+ delta) in 32-bit, writes it back when there is a
+// delta, and sums v^2; pass 2 reads v again (its own writes) and scales it.  The sum's order
+// depends on hidden and the block size only, never on the batch.
+template <typename T>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ weight,
+                               float eps, T* __restrict__ out, const int* __restrict__ rows, int n_tokens, int hidden,
+                               int* status) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int t = rows ? rows[r] : r;
+    T* o = out + (size_t)r * hidden;
+    if (t < 0 || t >= n_tokens) {
+        if (threadIdx.x == 0) set_status(status, kStatusBadRow, t);
+        return;
+    }
+    float* xr = x + (size_t)t * hidden;
+    const T* dr = delta ? delta + (size_t)t * hidden : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+        float v[8];
+        Vec8<float>::load(xr + i, v);
+        if (dr) {
+            float d[8];
+            Vec8<T>::load(dr + i, d);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] += d[j];
+            Vec8<float>::store(xr + i, v);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+    }
+    const float total = block_sum(ss, scratch);
+    const float rs = rsqrtf(total / (float)hidden + eps);
+    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+        float v[8], w[8], y[8];
+        Vec8<float>::load(xr + i, v);
+        Vec8<float>::load(weight + i, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[j] = w[j] * v[j] * rs;
+        Vec8<T>::store(o + i, y);
+    }
+}
+
+cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const float* weight, float eps,
+                           void* out, const int* rows, int n_rows, int n_tokens, int hidden, int* status,
+                           cudaStream_t stream) {
+    if (n_rows == 0) return cudaSuccess;
+    int threads = min(512, max(32, ((hidden / 8 + 31) / 32) * 32));
+    if (out_dtype == kBF16)
+        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, (const __nv_bfloat16*)delta, weight, eps,
+                                                                      (__nv_bfloat16*)out, rows, n_tokens, hidden, status);
+    else
+        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, (const float*)delta, weight, eps, (float*)out, rows,
+                                                              n_tokens, hidden, status);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------- silu * up
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tokens, int inter) {
+    const int per_row = inter / 8;
+    const size_t total = (size_t)n_tokens * per_row;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(e / per_row);
+        const int i = (int)(e % per_row) * 8;
+        float g[8], u[8], y[8];
+        Vec8<T>::load(gu + (size_t)t * 2 * inter + i, g);
+        Vec8<T>::load(gu + (size_t)t * 2 * inter + inter + i, u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[j] = g[j] / (1.f + expf(-g[j])) * u[j];
+        Vec8<T>::store(out + (size_t)t * inter + i, y);
+    }
+}
+
+cudaError_t launch_silu_mul(int dtype, const void* gu, void* out, int n_tokens, int inter, cudaStream_t stream) {
+    const size_t total = (size_t)n_tokens * (inter / 8);
+    if (total == 0) return cudaSuccess;
+    const int threads = 256;
+    const int blocks = (int)min((size_t)148 * 16, (total + threads - 1) / threads);
+    if (dtype == kBF16)
+        silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter);
+    else
+        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, n_tokens, inter);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------- rotation + cache store
+
+// One block a token.  The angle's cos and sin come from a table of float pairs built on the
+// host as vt-transformer builds its own (v1/tensortype/common.cpp:6-24); the rotation is done
+// in 32-bit with one rounding.  Keys are rotated on their way into the page, values are copied.
+template <typename T>
+__global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                  const float2* __restrict__ cos_sin, int max_pos, T* __restrict__ k_cache,
+                                  T* __restrict__ v_cache, const int* __restrict__ token_seq,
+                                  const int* __restrict__ block_table, int table_stride, int n_seqs, int n_pages,
+                                  int heads, int kv_heads, int head_dim, int page_size, int rotate, int store,
+                                  int* status) {
+    const int t = blockIdx.x;
+    const int seq = token_seq[t];
+    if (seq < 0) return;  // padding
+    if (seq >= n_seqs) {
+        if (threadIdx.x == 0) set_status(status, kStatusBadSequence, seq);
+        return;
+    }
+    const int pos = positions[t];
+    if (pos < 0 || (rotate && pos >= max_pos)) {
+        if (threadIdx.x == 0) set_status(status, kStatusBadPosition, pos);
+        return;
+    }
+    const int half = head_dim / 2;
+    const int q_dim = heads * head_dim, kv_dim = kv_heads * head_dim;
+    T* row = qkv + (size_t)t * (q_dim + 2 * kv_dim);
+    const float2* cs = cos_sin + (size_t)pos * half;
+
+    size_t page_base = 0;
+    int slot = 0;
+    if (store) {
+        const int page = block_table[(size_t)seq * table_stride + pos / page_size];
+        if (page < 0 || page >= n_pages) {
+            if (threadIdx.x == 0) set_status(status, kStatusBadPage, page);
+            store = 0;
+        }
+        page_base = (size_t)page * kv_heads * page_size * head_dim;
+        slot = pos % page_size;
+    }
+
+    // queries: rotate in place
+    if (rotate) {
+        for (int e = threadIdx.x; e < heads * half; e += blockDim.x) {
+            const int h = e / half, i = e % half;
+            const float2 c = cs[i];
+            T* p = row + h * head_dim;
+            const float a = to_float(p[i]), b = to_float(p[i + half]);
+            p[i] = from_float<T>(a * c.x - b * c.y);
+            p[i + half] = from_float<T>(b * c.x + a * c.y);
+        }
+    }
+    if (!store) return;
+    // keys: rotate into the page
+    for (int e = threadIdx.x; e < kv_heads * half; e += blockDim.x) {
+        const int h = e / half, i = e % half;
+        const T* p = row + q_dim + h * head_dim;
+        T* dst = k_cache + page_base + ((size_t)h * page_size + slot) * head_dim;
+        const float a = to_float(p[i]), b = to_float(p[i + half]);
+        if (rotate) {
+            const float2 c = cs[i];
+            dst[i] = from_float<T>(a * c.x - b * c.y);
+            dst[i + half] = from_float<T>(b * c.x + a * c.y);
+        } else {
+            dst[i] = p[i];
+            dst[i + half] = p[i + half];
+        }
+    }
+    // values: copy into the page
+    for (int e = threadIdx.x; e < kv_dim; e += blockDim.x) {
+        const int h = e / head_dim, i = e % head_dim;
+        v_cache[page_base + ((size_t)h * page_size + slot) * head_dim + i] = row[q_dim + kv_dim + e];
+    }
+}
+
+cudaError_t launch_rope_store(int dtype, void* qkv, const int* positions, const float2* cos_sin, int max_pos,
+                              void* k_cache, void* v_cache, const int* token_seq, const int* block_table,
+                              int table_stride, int n_seqs, int n_pages, int n_tokens, int heads, int kv_heads,
+                              int head_dim, int page_size, int rotate, int store, int* status, cudaStream_t stream) {
+    if (n_tokens == 0) return cudaSuccess;
+    const int work = max(heads * head_dim / 2, kv_heads * head_dim);
+    const int threads = min(512, max(32, ((work + 31) / 32) * 32));
+    if (dtype == kBF16)
+        rope_store_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+            (__nv_bfloat16*)qkv, positions, cos_sin, max_pos, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, token_seq,
+            block_table, table_stride, n_seqs, n_pages, heads, kv_heads, head_dim, page_size, rotate, store, status);
+    else
+        rope_store_kernel<float><<<n_tokens, threads, 0, stream>>>(
+            (float*)qkv, positions, cos_sin, max_pos, (float*)k_cache, (float*)v_cache, token_seq, block_table,
+            table_stride, n_seqs, n_pages, heads, kv_heads, head_dim, page_size, rotate, store, status);
+    return cudaGetLastError();
+}
+
+}  // namespace vtb

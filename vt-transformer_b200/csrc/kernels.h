@@ -1,0 +1,59 @@
+// Launchers of the hand-written kernels.  Plain pointers and sizes; every launcher
+// enqueues on `stream` and returns cudaGetLastError().  `status` points at two ints on
+// the device (code, detail), see common.cuh; it may be null.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace vtb {
+
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+// out[t, :] = float(table[ids[t], :]).  hidden % 8 == 0.
+cudaError_t launch_embedding(int table_dtype, const void* table, const int* ids, float* out, int n_tokens,
+                             int hidden, int vocab, int* status, cudaStream_t stream);
+
+// For r in 0..n_rows: t = rows ? rows[r] : r; v = x[t] (+ delta[t], written back to x[t]);
+// out[r] = weight * v * rsqrt(mean(v^2) + eps).  x float, weight float, delta/out of out_dtype.
+cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const float* weight, float eps,
+                           void* out, const int* rows, int n_rows, int n_tokens, int hidden, int* status,
+                           cudaStream_t stream);
+
+// out[t, i] = silu(gu[t, i]) * gu[t, inter + i].  inter % 8 == 0.
+cudaError_t launch_silu_mul(int dtype, const void* gu, void* out, int n_tokens, int inter, cudaStream_t stream);
+
+// Rotates q (in place) and k by the token's position and stores k and v into the pages.
+// qkv [n_tokens, (heads + 2 kv_heads) * head_dim]; cos_sin [max_pos, head_dim / 2] of (cos, sin);
+// k_cache, v_cache [pages, kv_heads, page_size, head_dim]; token_seq[t] < 0 marks padding.
+// store == 0 rotates q only.
+cudaError_t launch_rope_store(int dtype, void* qkv, const int* positions, const float2* cos_sin, int max_pos,
+                              void* k_cache, void* v_cache, const int* token_seq, const int* block_table,
+                              int table_stride, int n_seqs, int n_pages, int n_tokens, int heads, int kv_heads,
+                              int head_dim, int page_size, int rotate, int store, int* status, cudaStream_t stream);
+
+// C[M, N] = A[M, K] W[N, K]^T (+ bias[N]) with 32-bit multiply-adds in a fixed order (no tensor cores).
+// (in, out) dtypes: (float, float), (bfloat16, bfloat16), (bfloat16, float).  k % 4 == 0.
+cudaError_t launch_gemm_simt(int in_dtype, int out_dtype, const void* a, const void* w, const float* bias, void* c,
+                             int m, int n, int k, cudaStream_t stream);
+
+// Attention of every token over the paged keys of its sequence, one warp for a (token, head).
+// q is read from qkv [n_tokens, qkv_stride] at column head * head_dim; out [n_tokens, heads * head_dim].
+// Token t at position p of sequence s sees keys j with max(0, p - window + 1) <= j <= p (window <= 0: all).
+cudaError_t launch_attention_simt(int dtype, const void* qkv, int qkv_stride, void* out, const void* k_cache,
+                                  const void* v_cache, const int* positions, const int* token_seq,
+                                  const int* block_table, int table_stride, int n_seqs, int n_pages, int n_tokens,
+                                  int heads, int kv_heads, int head_dim, int page_size, int window, float scale,
+                                  int* status, cudaStream_t stream);
+
+// out[r] = index of the largest logit of row r (the lowest index among equals).
+cudaError_t launch_argmax(const float* logits, int* out, int n_rows, int vocab, cudaStream_t stream);
+
+// Sampling of one token for each row of float logits [n_rows, vocab]:
+// temperature[r] <= 0 or top_k[r] == 1: argmax.  Else p = softmax(logits / temperature) restricted to the
+// top_k[r] largest (top_k <= 0: all) and then to the smallest set of largest p whose sum reaches top_p[r];
+// the token is the first index, in index order, at which the running sum of the kept p exceeds u[r] * total.
+cudaError_t launch_sample(const float* logits, const float* temperature, const int* top_k, const float* top_p,
+                          const float* u, int* out, int n_rows, int vocab, cudaStream_t stream);
+
+}  // namespace vtb

@@ -1,0 +1,140 @@
+"""The step function: one batch of (request, its next tokens) in, logits at the wanted
+places out.
+
+It is the only way tokens go through the model: generation, the scheduler and the trace
+replay all call ``ModelRunner.step``.  A step runs only the tokens it is given, as one
+flat batch, against the keys and values that earlier steps left in the pages.  Like
+vt-transformer's forward (vt-transformer/core/vt_request.hpp:18-33) it writes the cache
+for exactly the new tokens; unlike it (vt-transformer/core/vt_engine.hpp:34-37) it returns
+logits and leaves sampling to the caller.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import ops as _ops
+from ..cache.manager import CacheManager
+from ..config.registry import get_architecture, load_config
+from ..models.base import DecoderModel
+from ..parts.base import Runtime
+from ..weights.loader import RandomSource, SafetensorsSource, WeightSource
+from .batch import StepContext, StepEntry, build_context
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+_STATUS_TEXT = {
+    1: "a token id lies outside the embedding table",
+    2: "a position lies outside the rotation table",
+    3: "a block-table entry lies outside the page pool",
+    4: "a token's sequence index lies outside the step",
+    5: "a row index lies outside its tensor",
+    6: "a bounded wait inside a kernel ran out",
+}
+
+
+class DeviceStatusError(RuntimeError):
+    """A kernel met an index it must not follow (it skipped the access and went on)."""
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"dtype must be 'bfloat16' or 'float32', found {dtype!r}") from None
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cache: CacheManager, rt: Runtime):
+        self.model, self.cache, self.rt = model, cache, rt
+        self.status = torch.zeros(2, dtype=torch.int32, device=rt.device)
+        self.steps = 0
+
+    # ---- construction --------------------------------------------------------------------
+    @classmethod
+    def build(cls, config, source_factory, *, dtype="bfloat16", device="cuda:0", page_size: int = 16,
+              num_pages: Optional[int] = None, max_tokens: Optional[int] = None, max_requests: int = 8,
+              max_seq_len: Optional[int] = None, ops=None) -> "ModelRunner":
+        """``source_factory(param_table)`` returns the ``WeightSource``.  The pool holds
+        ``num_pages`` pages in each group, or enough for ``max_tokens`` tokens."""
+        dt = parse_dtype(dtype)
+        rt = Runtime(device=torch.device(device), dtype=dt, ops=ops if ops is not None else _ops)
+        spec = get_architecture(config.architecture).model_spec(config)
+        model = DecoderModel(spec, rt)
+        source = source_factory(model.param_specs())
+        try:
+            model.load(source)
+        finally:
+            source.close()
+        limit = spec.max_positions or None
+        if max_seq_len is None:
+            max_seq_len = limit or 4096
+        if limit is not None and max_seq_len > limit:
+            raise ValueError(f"max_seq_len {max_seq_len} is above the model's {limit} positions")
+        if num_pages is None:
+            if max_tokens is None:
+                max_tokens = max_seq_len * max_requests
+            num_pages = -(-max_tokens // page_size)
+        cache = CacheManager(model.cache_slots(), page_size=page_size, num_pages=num_pages,
+                             max_requests=max_requests, max_seq_len=max_seq_len, dtype=dt, device=rt.device)
+        return cls(model, cache, rt)
+
+    @classmethod
+    def from_folder(cls, folder: str, **kw) -> "ModelRunner":
+        config = load_config(folder)
+        return cls.build(config, lambda table: SafetensorsSource(folder), **kw)
+
+    @classmethod
+    def from_random(cls, config, seed: int = 0, sigma: float = 0.02, **kw) -> "ModelRunner":
+        """Random weights made on the device, tensor by tensor (no folder is written)."""
+        device = kw.get("device", "cuda:0")
+        return cls.build(config, lambda table: RandomSource(table, seed, sigma, device=device), **kw)
+
+    # ---- requests --------------------------------------------------------------------------
+    def admit(self) -> int:
+        return self.cache.admit()
+
+    def release(self, row: int) -> None:
+        self.cache.release(row)
+
+    # ---- the step ----------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs the entries as one batch and returns float32 logits [wanted, vocab] on the
+        device, in the order of the entries and of their ``want``.  Raises ``OutOfPages``
+        (and changes nothing) if a group cannot cover the new tokens."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        vocab = self.model.spec.vocab
+        if not entries:
+            return torch.empty((0, vocab), dtype=torch.float32, device=self.rt.device)
+        seen = set()
+        for e in entries:
+            if e.row in seen:
+                raise ValueError(f"row {e.row} appears twice in one step")
+            seen.add(e.row)
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise ValueError(f"row {e.row}: wanted place {w} is outside its {len(e.tokens)} tokens")
+        self.cache.extend([(e.row, self.cache.length(e.row) + len(e.tokens)) for e in entries])
+        ctx = build_context(entries, self.cache, self.rt.device, status=self.status)
+        logits = self.model.forward(ctx, self.cache.views(ctx.block_tables))
+        for e in entries:
+            self.cache.commit(e.row, self.cache.length(e.row) + len(e.tokens))
+        self.steps += 1
+        if ctx.want_inverse is not None:
+            logits = logits[torch.as_tensor(ctx.want_inverse, device=logits.device)]
+        return logits
+
+    def check_status(self) -> None:
+        """Reads the kernels' status word (this waits for the device) and raises if a kernel
+        reported a bad index."""
+        code, detail = (int(v) for v in self.status.tolist())
+        if code:
+            self.status.zero_()
+            raise DeviceStatusError(f"{_STATUS_TEXT.get(code, 'unknown status')} (code {code}, value {detail})")
+
+    # ---- figures for the roofline ----------------------------------------------------------------
+    def weight_bytes(self, n_tokens: int = 1) -> int:
+        return self.model.weight_bytes(n_tokens)

@@ -1,0 +1,114 @@
+"""The kernels as Python functions over torch tensors.
+
+Every function runs a hand-written sm_100a kernel of ``csrc`` (or, for the bfloat16
+matrix products of large batches, the library product that vt-transformer's engine also
+uses: cuBLASLt, v1/tensortype/cuda_kernels/lt_sgemm.cu:55-126).  There is no CPU path and
+no fallback: if the extension cannot be loaded or built, the first call raises.
+
+``backend()`` returns the extension module.  Tests of the host-side logic may put an
+object with the same functions in its place (``use_backend``); nothing in the package
+does.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+_backend = None
+
+
+def backend():
+    global _backend
+    if _backend is None:
+        if not torch.cuda.is_available():
+            raise RuntimeError("vt_transformer_b200 runs on a CUDA device (B200, sm_100a) only; "
+                               "torch.cuda.is_available() is False and there is no CPU path")
+        from ..csrc import build
+        _backend = build.load()
+    return _backend
+
+
+def use_backend(obj) -> None:
+    """Replaces the kernel module (for tests of the host-side logic).  ``None`` restores
+    the real one at the next call."""
+    global _backend
+    _backend = obj
+
+
+# --------------------------------------------------------------------------- elementwise
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status=None) -> torch.Tensor:
+    backend().embedding(table, ids, out, status)
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None, status=None) -> torch.Tensor:
+    backend().rmsnorm(x, delta, weight, float(eps), out, rows, status)
+    return out
+
+
+def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    backend().silu_mul(gu, out)
+    return out
+
+
+def rope_store(qkv, positions, cos_sin, k_cache, v_cache, token_seq, block_table, heads: int, kv_heads: int,
+               head_dim: int, store: bool = True, status=None) -> None:
+    backend().rope_store(qkv, positions, cos_sin, k_cache, v_cache, token_seq, block_table, heads, kv_heads,
+                         head_dim, bool(store), status)
+
+
+# --------------------------------------------------------------------------- matrix products
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+    """out[T, N] = x[T, K] w[N, K]^T (+ bias).  ``out`` is float32 or the dtype of x.
+
+    float32 x and w: the 32-bit kernel (FFMA in a fixed order, no TF32).  A weight kept in
+    32-bit beside bfloat16 activations goes the same way, with x widened.  bfloat16: the
+    weight-streaming kernel for small batches, the tensor-core product for large ones.
+    """
+    be = backend()
+    if w.dtype == torch.float32:
+        xf = x if x.dtype == torch.float32 else x.float()
+        if out.dtype == torch.float32:
+            be.gemm_simt(xf, w, bias, out)
+        else:
+            tmp = torch.empty(out.shape, dtype=torch.float32, device=out.device)
+            be.gemm_simt(xf, w, bias, tmp)
+            out.copy_(tmp)
+        return out
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise TypeError(f"linear: unsupported dtypes x {x.dtype}, w {w.dtype}")
+    be.gemm_simt(x, w, bias, out)
+    return out
+
+
+# --------------------------------------------------------------------------- attention
+
+
+def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv_heads: int, head_dim: int,
+                    window: Optional[int], scale: float, status=None) -> torch.Tensor:
+    """Attention of the step's tokens over the paged keys and values of their sequences.
+    ``ctx`` is the step's ``StepContext`` (positions, token_seq and the tile lists)."""
+    be = backend()
+    w = int(window) if window else 0
+    be.attention_simt(qkv, out, k_cache, v_cache, ctx.positions, ctx.token_seq, block_table, heads, kv_heads,
+                      head_dim, w, float(scale), status)
+    return out
+
+
+# --------------------------------------------------------------------------- sampling
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    backend().argmax(logits, out)
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, u, out) -> torch.Tensor:
+    backend().sample(logits, temperature, top_k, top_p, u, out)
+    return out

@@ -1,0 +1,225 @@
+"""Interfaces of the parts a model is put together from, and their registry.
+
+Five categories: ``norm``, ``position``, ``mixer``, ``feed_forward``, ``block``.  A part is
+built from its spec (sizes and constants), the prefix of its tensor names and the
+``Runtime`` (device, compute dtype, kernels).  It says which tensors it wants
+(``param_specs``), takes them (``load``) and runs on the flat token batch of one step.
+No part knows which model it is in.
+
+What a mixer keeps between steps it declares with ``cache_spec``: pages of keys and
+values (``KVCacheSpec``), a block of fixed size for each request (``StateSpec``), or
+nothing.  The cache manager gives the mixer a ``CacheView`` of what it declared.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Mapping, Optional, Tuple
+
+import torch
+
+
+# ----------------------------------------------------------------------------- parameters
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    """A tensor a part reads from the weights.
+
+    ``role``: "matrix" and "vector" are floating point (stored in bfloat16 by the random
+    initialiser; a file may hold them in 32-bit); "table" is an integer table (int32).
+    ``init``: how the random initialiser fills it: "normal" is N(0, sigma),
+    "one_plus_normal" is 1 + N(0, sigma).
+    """
+    shape: Tuple[int, ...]
+    role: str = "matrix"
+    init: str = "normal"
+    optional: bool = False
+
+
+# ----------------------------------------------------------------------------- runtime
+
+
+@dataclass
+class Runtime:
+    """Where and in which precision a model runs.  ``dtype`` is torch.bfloat16 (the
+    serving path) or torch.float32 (everything in true 32-bit); ``ops`` is the kernel
+    module (``vt_transformer_b200.ops``)."""
+    device: torch.device
+    dtype: torch.dtype
+    ops: object
+
+    def param(self, t: torch.Tensor, role: str = "matrix") -> torch.Tensor:
+        """A stored tensor as the kernels read it.  Matrices are used in the compute
+        dtype (a bfloat16 tensor is widened exactly for the 32-bit path; a tensor stored
+        in 32-bit stays 32-bit and its products run through the 32-bit kernels).
+        Vectors are read in 32-bit by every kernel.  Tables are int32."""
+        if role == "table":
+            return t.to(device=self.device, dtype=torch.int32).contiguous()
+        if role == "vector":
+            return t.to(device=self.device, dtype=torch.float32).contiguous()
+        if self.dtype == torch.float32 or t.dtype == torch.float32:
+            return t.to(device=self.device, dtype=torch.float32).contiguous()
+        return t.to(device=self.device, dtype=self.dtype).contiguous()
+
+
+# ----------------------------------------------------------------------------- caches
+
+
+@dataclass(frozen=True)
+class KVCacheSpec:
+    """Keys and values in pages: ``kv_heads`` heads of ``head_dim`` for each token;
+    ``window`` None keeps all tokens, w keeps the last w."""
+    kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """A block of fixed size for each request, zero when the request is admitted."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class CacheView:
+    """What one run of a block sees of the cache.
+
+    For a ``KVCacheSpec`` slot: ``k`` and ``v`` are [pages, kv_heads, page_size, head_dim],
+    ``block_table`` is the int32 device table [sequences of this step, stride] of the slot's
+    group, ``page_size`` the tokens in a page.  For a ``StateSpec`` slot: ``state`` is
+    [request rows, *shape]; the step's ``rows`` index it.  ``writes`` is False for a run
+    that only reads another run's slot."""
+    spec: object = None
+    k: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None
+    block_table: Optional[torch.Tensor] = None
+    page_size: int = 0
+    state: Optional[torch.Tensor] = None
+    writes: bool = True
+
+
+# ----------------------------------------------------------------------------- parts
+
+
+class Part:
+    category = ""
+
+    def __init__(self, spec, prefix: str, rt: Runtime):
+        self.spec = spec
+        self.prefix = prefix
+        self.rt = rt
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        """Full tensor name -> what is expected under it."""
+        return {}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        """Takes the tensors named by ``param_specs`` (as stored) and keeps what the
+        kernels need on the device."""
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights one step reads (for the roofline)."""
+        return 0
+
+
+class Norm(Part):
+    """``__call__(x, delta=None, rows=None)``: x is the 32-bit residual stream [T, H].
+    With ``delta`` the sum x + delta is formed in 32-bit, written back to x, and normed.
+    With ``rows`` (int32 indices) only those rows are done, packed in that order.
+    Returns the normed rows in the compute dtype."""
+    category = "norm"
+
+    def __call__(self, x, delta=None, rows=None, status=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    category = "position"
+
+
+class Mixer(Part):
+    """``forward(h, ctx, cache)``: h [T, hidden] normed input in the compute dtype, ctx the
+    ``StepContext`` of the step, cache the ``CacheView`` of this run (None if
+    ``cache_spec`` is None).  Returns [T, hidden] in the compute dtype."""
+    category = "mixer"
+
+    def cache_spec(self):
+        return None
+
+    def forward(self, h, ctx, cache):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    """``forward(h, ctx)``: [T, hidden] -> [T, hidden] in the compute dtype."""
+    category = "feed_forward"
+
+    def forward(self, h, ctx):
+        raise NotImplementedError
+
+
+class Block(Part):
+    """``forward(stream, ctx, cache)`` runs the layer on the ``ResidualStream``."""
+    category = "block"
+
+    def cache_spec(self):
+        return None
+
+    def forward(self, stream, ctx, cache):
+        raise NotImplementedError
+
+
+class ResidualStream:
+    """The 32-bit residual stream [T, H] and a delta not yet added to it.
+
+    A block leaves the output of its last part in ``pending``; the next norm adds it
+    while it reads the stream (one pass over memory instead of two), so the sum is
+    formed in 32-bit whatever the compute dtype is."""
+
+    def __init__(self, x: torch.Tensor, status: Optional[torch.Tensor] = None):
+        self.x = x
+        self.status = status
+        self.pending: Optional[torch.Tensor] = None
+
+    def normed(self, norm: Norm, rows=None):
+        delta, self.pending = self.pending, None
+        return norm(self.x, delta=delta, rows=rows, status=self.status)
+
+    def add(self, delta: torch.Tensor) -> None:
+        if self.pending is not None:
+            raise RuntimeError("the residual stream holds a delta that no norm has added yet")
+        self.pending = delta
+
+
+# ----------------------------------------------------------------------------- registry
+
+_CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block")
+_PARTS: Dict[str, Dict[str, Callable]] = {c: {} for c in _CATEGORIES}
+
+
+def register_part(category: str, kind: str, factory: Callable = None, replace: bool = False):
+    """Registers ``factory(spec, prefix, rt)`` for specs of ``kind``.  Usable as a decorator."""
+    if category not in _PARTS:
+        raise ValueError(f"unknown category '{category}'; known: {', '.join(_CATEGORIES)}")
+
+    def _do(f):
+        if kind in _PARTS[category] and not replace:
+            raise ValueError(f"{category} '{kind}' is registered already")
+        _PARTS[category][kind] = f
+        return f
+
+    return _do if factory is None else _do(factory)
+
+
+def unregister_part(category: str, kind: str) -> None:
+    _PARTS[category].pop(kind, None)
+
+
+def build_part(category: str, spec, prefix: str, rt: Runtime) -> Part:
+    try:
+        factory = _PARTS[category][spec.kind]
+    except KeyError:
+        raise ValueError(f"no {category} of kind '{spec.kind}' is registered; known: "
+                         f"{', '.join(sorted(_PARTS[category])) or 'none'}") from None
+    return factory(spec, prefix, rt)

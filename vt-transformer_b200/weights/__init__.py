@@ -1,0 +1,4 @@
+from .loader import (DictSource, RandomSource, SafetensorsSource, WeightError, WeightSource, check_against,
+                     random_tensor)
+from .random_init import write_random_model
+from .safetensors_io import SafetensorsError

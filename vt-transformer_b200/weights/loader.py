@@ -1,0 +1,171 @@
+"""Weights by tensor name, checked as a whole against what the model expects.
+
+vt-transformer loads one raw file a tensor and asserts on its byte size
+(v1/models/qwen2-7b/inference_fp16.dag:87-142, v1/tensortype/cuda_tensor.cpp:102-111);
+a missing file is a panic (v1/tensortype/common.hpp:72-75).  Here the names and shapes
+of a folder are compared with the model's ``ParamSpec`` table before any data is read,
+and every difference is reported in one ``WeightError``: missing tensors, tensors the
+model does not know, wrong shapes and wrong kinds of dtype.
+
+Tensors are handed out as they are stored: bfloat16 stays bfloat16, a tensor stored in
+32-bit stays 32-bit; float16 and float64 (which no kernel reads) become bfloat16 and
+float32; integer tables become int32.
+"""
+from __future__ import annotations
+
+import hashlib
+from typing import Dict, Iterator, Mapping, Tuple
+
+import torch
+
+from ..parts.base import ParamSpec
+from . import safetensors_io as st
+
+_FLOATS = (torch.float32, torch.bfloat16, torch.float16, torch.float64)
+_INTS = (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8)
+
+
+class WeightError(ValueError):
+    """The tensors of a model folder do not fit the model.  ``missing``, ``unexpected``,
+    ``wrong_shape`` (name -> (expected, found)) and ``wrong_dtype`` (name -> (expected
+    kind, found dtype)) say how."""
+
+    def __init__(self, where: str, missing, unexpected, wrong_shape, wrong_dtype):
+        self.where = where
+        self.missing = sorted(missing)
+        self.unexpected = sorted(unexpected)
+        self.wrong_shape = dict(wrong_shape)
+        self.wrong_dtype = dict(wrong_dtype)
+        lines = [f"{where}: the tensors do not fit the model"]
+        if self.missing:
+            lines.append(f"  missing ({len(self.missing)}): " + ", ".join(self.missing))
+        if self.unexpected:
+            lines.append(f"  unexpected ({len(self.unexpected)}): " + ", ".join(self.unexpected))
+        for name, (want, got) in sorted(self.wrong_shape.items()):
+            lines.append(f"  wrong shape: {name} expected {list(want)}, found {list(got)}")
+        for name, (want, got) in sorted(self.wrong_dtype.items()):
+            lines.append(f"  wrong dtype: {name} expected {want}, found {got}")
+        super().__init__("\n".join(lines))
+
+
+class WeightSource:
+    """Where tensors come from: ``entries()`` gives name -> (dtype, shape) without reading
+    data, ``get(name)`` the tensor as stored."""
+
+    where = "weights"
+
+    def entries(self) -> Dict[str, Tuple[torch.dtype, Tuple[int, ...]]]:
+        raise NotImplementedError
+
+    def get(self, name: str) -> torch.Tensor:
+        raise NotImplementedError
+
+    def close(self) -> None:
+        pass
+
+
+class SafetensorsSource(WeightSource):
+    def __init__(self, folder: str):
+        self.where = folder
+        self.index = st.index_folder(folder)
+        self.files = st.MappedFiles()
+
+    def entries(self):
+        return {n: (e.dtype, e.shape) for n, e in self.index.items()}
+
+    def get(self, name: str) -> torch.Tensor:
+        return normalise_dtype(self.files.tensor(self.index[name]))
+
+    def close(self) -> None:
+        self.files.close()
+
+
+class DictSource(WeightSource):
+    def __init__(self, tensors: Mapping[str, torch.Tensor], where: str = "tensors"):
+        self.tensors = tensors
+        self.where = where
+
+    def entries(self):
+        return {n: (t.dtype, tuple(t.shape)) for n, t in self.tensors.items()}
+
+    def get(self, name: str) -> torch.Tensor:
+        return normalise_dtype(self.tensors[name])
+
+
+def normalise_dtype(t: torch.Tensor) -> torch.Tensor:
+    if t.dtype in (torch.bfloat16, torch.float32, torch.int32):
+        return t
+    if t.dtype == torch.float16:
+        return t.to(torch.bfloat16)
+    if t.dtype == torch.float64:
+        return t.to(torch.float32)
+    if t.dtype in _INTS:
+        return t.to(torch.int32)
+    raise TypeError(f"no kernel reads dtype {t.dtype}")
+
+
+def check_against(source: WeightSource, expected: Mapping[str, ParamSpec]) -> None:
+    """Raises one ``WeightError`` that lists every difference between the source and the
+    model's parameter table."""
+    found = source.entries()
+    missing = [n for n, s in expected.items() if n not in found and not s.optional]
+    unexpected = [n for n in found if n not in expected]
+    wrong_shape, wrong_dtype = {}, {}
+    for name, spec in expected.items():
+        if name not in found:
+            continue
+        dtype, shape = found[name]
+        if tuple(shape) != tuple(spec.shape):
+            wrong_shape[name] = (tuple(spec.shape), tuple(shape))
+        if spec.role == "table":
+            if dtype not in _INTS:
+                wrong_dtype[name] = ("an integer type", str(dtype))
+        elif dtype not in _FLOATS:
+            wrong_dtype[name] = ("a floating-point type", str(dtype))
+    if missing or unexpected or wrong_shape or wrong_dtype:
+        raise WeightError(source.where, missing, unexpected, wrong_shape, wrong_dtype)
+
+
+# ----------------------------------------------------------------------------- random weights
+
+
+def _tensor_seed(seed: int, name: str) -> int:
+    digest = hashlib.sha256(f"{seed}:{name}".encode()).digest()
+    return int.from_bytes(digest[:8], "little") & ((1 << 63) - 1)
+
+
+def random_tensor(name: str, spec: ParamSpec, seed: int, sigma: float, device="cpu") -> torch.Tensor:
+    """The tensor ``name`` of a random model: N(0, sigma) for matrices and vectors,
+    1 + N(0, sigma) for norm weights, stored in bfloat16; tables are zeros.  The numbers
+    depend on (seed, name) only, not on the order in which tensors are made."""
+    if spec.role == "table":
+        return torch.zeros(spec.shape, dtype=torch.int32, device=device)
+    g = torch.Generator(device=device)
+    g.manual_seed(_tensor_seed(seed, name))
+    t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device) * sigma
+    if spec.init == "one_plus_normal":
+        t = t + 1.0
+    elif spec.init != "normal":
+        raise ValueError(f"unknown initialiser '{spec.init}' for {name}")
+    return t.to(torch.bfloat16)
+
+
+class RandomSource(WeightSource):
+    """Seeded random weights made on demand (on ``device``), never all at once."""
+
+    def __init__(self, expected: Mapping[str, ParamSpec], seed: int, sigma: float, device="cpu"):
+        self.expected = {n: s for n, s in expected.items() if not s.optional}
+        self.seed, self.sigma, self.device = seed, sigma, device
+        self.where = f"random weights (seed {seed}, sigma {sigma})"
+
+    def entries(self):
+        return {n: (torch.int32 if s.role == "table" else torch.bfloat16, tuple(s.shape))
+                for n, s in self.expected.items()}
+
+    def get(self, name: str) -> torch.Tensor:
+        return random_tensor(name, self.expected[name], self.seed, self.sigma, self.device)
+
+
+def iter_source(source: WeightSource) -> Iterator[Tuple[str, torch.Tensor]]:
+    for name in source.entries():
+        yield name, source.get(name)
