@@ -1,0 +1,240 @@
+"""Tiny configurations, traces and comparisons shared by the tests."""
+from __future__ import annotations
+
+import json
+import os
+import random
+import subprocess
+import sys
+from typing import Dict, List, Sequence, Tuple
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# Three tiny configurations that differ in every size and option.  A and B are the two of the
+# task's description; C adds a window on the later layers, a head size that is no power of two,
+# a head_dim that is not hidden / heads, and a vocabulary and width that are no powers of two.
+CONFIGS: Dict[str, dict] = {
+    "A": dict(architectures=["Qwen2ForCausalLM"], vocab_size=256, hidden_size=64, intermediate_size=176,
+              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-6,
+              rope_theta=10000.0, max_position_embeddings=256, tie_word_embeddings=True),
+    "B": dict(architectures=["Qwen2ForCausalLM"], vocab_size=512, hidden_size=128, intermediate_size=344,
+              num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=1, head_dim=32, rms_norm_eps=1e-5,
+              rope_theta=1000000.0, max_position_embeddings=512, tie_word_embeddings=False),
+    "C": dict(architectures=["Qwen2ForCausalLM"], vocab_size=301, hidden_size=72, intermediate_size=136,
+              num_hidden_layers=4, num_attention_heads=6, num_key_value_heads=3, head_dim=48, rms_norm_eps=3e-5,
+              rope_theta=500000.0, max_position_embeddings=192, tie_word_embeddings=False,
+              use_sliding_window=True, sliding_window=20, max_window_layers=2),
+}
+SIGMA = {"A": 0.02, "B": 0.05, "C": 0.08}
+SEED = {"A": 11, "B": 22, "C": 33}
+# request lengths of the replay tests: a single token, page edges (16, 32), beyond 32 for the
+# one-by-one tail, several pages
+LENGTHS = {"A": [5, 17, 33, 70, 100], "B": [1, 8, 31, 70, 129], "C": [3, 16, 48, 81, 120]}
+
+# logits of the tiny models are of order 1; the 32-bit path differs from the plain
+# implementation by the order of its sums only, the bfloat16 path by the rounding of weights'
+# products and activations to 8 bits of mantissa at every part
+TOL = {"float32": 2e-5, "bfloat16": 6e-2}
+
+
+def make_config(name: str):
+    from vt_transformer_b200.config import config_from_dict
+    return config_from_dict(CONFIGS[name])
+
+
+def make_folder(name: str, folder: str) -> str:
+    from vt_transformer_b200.weights import write_random_model
+    return write_random_model(make_config(name), folder, seed=SEED[name], sigma=SIGMA[name])
+
+
+def prompts_for(name: str, seed: int = 0) -> List[List[int]]:
+    rng = random.Random(1000 + seed)
+    vocab = CONFIGS[name]["vocab_size"]
+    return [[rng.randrange(vocab) for _ in range(n)] for n in LENGTHS[name]]
+
+
+_plain_cache: Dict[Tuple[str, Tuple[int, ...]], torch.Tensor] = {}
+
+
+def plain_logits(folder: str, tokens: Sequence[int]) -> torch.Tensor:
+    """Logits [T, vocab] (float64) of the plain implementation for the whole sequence."""
+    from plain import qwen2_plain as plain
+    key = (folder, tuple(tokens))
+    if key not in _plain_cache:
+        cfg, w = plain.read_config(folder), _plain_weights(folder)
+        _plain_cache[key] = plain.forward(cfg, w, list(tokens))
+    return _plain_cache[key]
+
+
+_weights_cache: Dict[str, dict] = {}
+
+
+def _plain_weights(folder: str):
+    from plain import qwen2_plain as plain
+    if folder not in _weights_cache:
+        _weights_cache[folder] = plain.read_weights(folder)
+    return _weights_cache[folder]
+
+
+# ----------------------------------------------------------------------------- traces
+# A trace is a list of steps {"step", "entries": [{"id", "tokens", "want"}], "end"}; `expect`
+# lists for each step the (request, position) of every wanted row, in order.
+
+
+class Trace:
+    def __init__(self):
+        self.steps: List[dict] = []
+        self.expect: Dict[int, List[Tuple[int, int]]] = {}
+
+    def add(self, entries: List[Tuple[int, int, int]], prompts, end=(), want_all=True, tag=""):
+        """entries: (request index, first position, n tokens); wants every position."""
+        n = len(self.steps)
+        recs, exp = [], []
+        for r, a, k in entries:
+            want = list(range(k)) if want_all else [k - 1]
+            recs.append({"id": f"{tag}r{r}", "tokens": prompts[r][a:a + k], "want": want})
+            exp += [(r, a + w) for w in want]
+        self.steps.append({"step": n, "entries": recs, "end": [f"{tag}r{r}" for r in end]})
+        if exp:
+            self.expect[n] = exp
+
+    def extend(self, other: "Trace"):
+        base = len(self.steps)
+        for s in other.steps:
+            s = dict(s)
+            s["step"] += base
+            self.steps.append(s)
+        for k, v in other.expect.items():
+            self.expect[k + base] = v
+
+
+def trace_whole(prompts, tag="w") -> Trace:
+    t = Trace()
+    for r, p in enumerate(prompts):
+        t.add([(r, 0, len(p))], prompts, end=[r], tag=tag)
+    return t
+
+
+def trace_tail(prompts, tail=32, tag="t") -> Trace:
+    """Most of each request in one step, its last `tail` tokens one by one."""
+    t = Trace()
+    for r, p in enumerate(prompts):
+        head = max(1, len(p) - tail)
+        t.add([(r, 0, head)], prompts, tag=tag, end=[r] if head == len(p) else [])
+        for a in range(head, len(p)):
+            t.add([(r, a, 1)], prompts, end=[r] if a == len(p) - 1 else [], tag=tag)
+    return t
+
+
+def trace_portions(prompts, sizes=(2, 3, 5, 8, 13, 2, 21, 4), tag="p") -> Trace:
+    """Each request alone in portions of changing size, down to two tokens."""
+    t = Trace()
+    for r, p in enumerate(prompts):
+        a, i = 0, r
+        while a < len(p):
+            k = min(sizes[i % len(sizes)], len(p) - a)
+            t.add([(r, a, k)], prompts, end=[r] if a + k == len(p) else [], tag=tag)
+            a, i = a + k, i + 1
+    return t
+
+
+def trace_mixed(prompts, max_live=4, seed=0, tag="m", decode_tail=6) -> Trace:
+    """Up to `max_live` live requests: portions of some beside single tokens of others; a
+    request skips a step now and then; finished requests make room for the next."""
+    rng = random.Random(seed)
+    t = Trace()
+    order = list(range(len(prompts)))
+    rng.shuffle(order)
+    done = {r: 0 for r in order}
+    live: List[int] = []
+    while order or live:
+        while order and len(live) < max_live:
+            live.append(order.pop(0))
+        entries = []
+        for r in live:
+            left = len(prompts[r]) - done[r]
+            if len(live) > 1 and rng.random() < 0.2:
+                continue   # sits this step out
+            k = 1 if left <= decode_tail else min(left - decode_tail, rng.choice([2, 3, 7, 16, 25]))
+            entries.append((r, done[r], k))
+        if not entries:
+            r = live[0]
+            entries.append((r, done[r], 1))
+        ends = []
+        for r, a, k in entries:
+            done[r] += k
+            if done[r] == len(prompts[r]):
+                ends.append(r)
+                live.remove(r)
+        t.add(entries, prompts, end=ends, tag=tag)
+    return t
+
+
+def tokens_needed(trace: Trace, round_to: int = 64) -> int:
+    """The most tokens live requests hold at any time, each rounded up to `round_to`."""
+    held: Dict[str, int] = {}
+    most = 0
+    for s in trace.steps:
+        for e in s["entries"]:
+            held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
+        most = max(most, sum(-(-v // round_to) * round_to for v in held.values()))
+        for rid in s["end"]:
+            held.pop(rid, None)
+    return most
+
+
+def run_trace_cli(folder: str, trace: Trace, dtype: str, out_dir: str, max_tokens: int, extra=()) -> Dict[int, np.ndarray]:
+    """Replays the trace with bin/trace_run in a process of its own and reads the logits back."""
+    text = "".join(json.dumps(s) + "\n" for s in trace.steps)
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype, "--out", out_dir,
+           "--max-tokens", str(max_tokens), *extra]
+    res = subprocess.run(cmd, input=text, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, f"trace_run failed ({res.returncode}):\n{res.stdout[-2000:]}\n{res.stderr[-4000:]}"
+    done = [l for l in res.stdout.splitlines() if l.startswith("done ")]
+    assert [int(l.split()[1]) for l in done] == [s["step"] for s in trace.steps], "a `done` line is missing"
+    vocab = json.load(open(os.path.join(folder, "config.json")))["vocab_size"]
+    out = {}
+    for n in trace.expect:
+        arr = np.fromfile(os.path.join(out_dir, f"{n}.f32"), dtype="<f4")
+        out[n] = arr.reshape(-1, vocab)
+    return out
+
+
+def run_trace_inproc(runner, trace: Trace) -> Dict[int, np.ndarray]:
+    """Replays the trace on a ModelRunner in this process (the code path of bin/trace_run)."""
+    from vt_transformer_b200.engine.batch import StepEntry
+    rows, out = {}, {}
+    for s in trace.steps:
+        entries = []
+        for e in s["entries"]:
+            if e["id"] not in rows:
+                rows[e["id"]] = runner.admit()
+            entries.append(StepEntry(rows[e["id"]], e["tokens"], e["want"]))
+        logits = runner.step(entries)
+        runner.check_status()
+        if logits.shape[0]:
+            out[s["step"]] = logits.float().cpu().numpy()
+        for rid in s["end"]:
+            runner.release(rows.pop(rid))
+        runner.cache.check()
+    return out
+
+
+def compare_trace(folder: str, prompts, trace: Trace, got: Dict[int, np.ndarray], tol: float) -> float:
+    """Every wanted row against the plain implementation; returns the largest difference and
+    fails at the first row beyond `tol`, saying where it lies."""
+    worst = 0.0
+    for n in sorted(trace.expect):
+        exp = trace.expect[n]
+        assert got[n].shape[0] == len(exp), f"step {n}: {got[n].shape[0]} rows, {len(exp)} wanted"
+        for i, (r, pos) in enumerate(exp):
+            ref = plain_logits(folder, prompts[r])[pos].numpy()
+            d = float(np.abs(got[n][i].astype(np.float64) - ref).max())
+            assert np.isfinite(d) and d <= tol, (
+                f"step {n}, request {r} (length {len(prompts[r])}), position {pos}: |dlogit| {d:.3e} > {tol:.1e} "
+                f"(entries {[(e['id'], len(e['tokens'])) for e in trace.steps[n]['entries']]})")
+            worst = max(worst, d)
+    return worst

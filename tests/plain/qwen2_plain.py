@@ -236,23 +236,47 @@ def uniform_from_counter(seed: int, request: int, index: int) -> float:
     return (z >> 40) / float(1 << 24)
 
 
-def sample_temperature(logits: torch.Tensor, temperature: float, u: float) -> int:
-    """p = softmax(logits / temperature) over the whole vocabulary; the first index
-    whose running sum of p exceeds u (inverse CDF in index order)."""
-    p = torch.softmax(logits.double() / temperature, dim=-1)
+def kept_probabilities(logits: torch.Tensor, temperature: float, top_k: int = -1, top_p: float = 1.0) -> torch.Tensor:
+    """Probabilities [vocab] after temperature, top-k and top-p, zero outside the kept set.
+    The parameters are those of the front end (sglfront/sglfront/core.py:6-17).  The kept set:
+    the top_k largest logits (values equal to the k-th are all kept; top_k <= 0 keeps all),
+    then the smallest set of largest probabilities whose sum reaches top_p of the total (equal
+    values again kept together)."""
+    z = logits.double() / temperature
+    e = torch.exp(z - z.max())
+    if 0 < top_k < z.numel():
+        kth = torch.topk(z, top_k).values[-1]
+        e = torch.where(z >= kth, e, torch.zeros_like(e))
+    if top_p < 1.0:
+        vals = torch.sort(e[e > 0], descending=True).values
+        need = top_p * float(vals.sum())
+        c = torch.cumsum(vals, 0)
+        n = int((c < need).sum()) + 1                      # the shortest head whose sum reaches `need`
+        thr = vals[min(n, vals.numel()) - 1]
+        e = torch.where(e >= thr, e, torch.zeros_like(e))
+    return e / e.sum()
+
+
+def sample(logits: torch.Tensor, temperature: float, u: float, top_k: int = -1, top_p: float = 1.0) -> int:
+    """The first index, in index order, at which the running sum of the kept probabilities
+    exceeds u (inverse CDF).  temperature <= 0 or top_k == 1 is the argmax."""
+    if temperature <= 0 or top_k == 1:
+        return sample_greedy(logits)
+    p = kept_probabilities(logits, temperature, top_k, top_p)
     c = torch.cumsum(p, dim=-1)
     idx = int(torch.searchsorted(c, torch.tensor(u * float(c[-1]), dtype=torch.float64), right=True))
     return min(idx, logits.numel() - 1)
 
 
-def sample_top_k(logits: torch.Tensor, temperature: float, k: int, u: float) -> int:
-    """The reference's sampler with k = 3 (v1/tensortype/cuda_kernels/easy_sampling.cu:32-104):
-    logits / temperature, keep the k largest, softmax over those, walk them from the
-    smallest kept to the largest and stop when the running sum reaches u."""
-    vals, idxs = torch.topk(logits.double() / temperature, k)   # descending
+def sample_top3_reference(logits: torch.Tensor, temperature: float, u: float) -> int:
+    """vt-transformer's own sampler, literally (v1/tensortype/cuda_kernels/easy_sampling.cu:32-104):
+    logits / temperature, the three largest, softmax over those, then walk them from the
+    third to the first and stop when the running sum reaches u.  It draws from the same
+    distribution as ``sample(..., top_k=3)``; only the order of the walk differs."""
+    vals, idxs = torch.topk(logits.double() / temperature, 3)   # descending
     p = torch.softmax(vals, dim=-1)
     s = 0.0
-    for i in range(k - 1, -1, -1):
+    for i in range(2, -1, -1):
         s += float(p[i])
         if s >= u:
             return int(idxs[i])

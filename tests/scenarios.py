@@ -1,0 +1,281 @@
+"""Scenarios that run the engine against the plain implementation.  Each takes the device
+and dtype: the host-side tests run them on the CPU with the stand-in kernels
+(tests/fake_ops.py), the GPU tests run them on cuda:0 with the real ones."""
+from __future__ import annotations
+
+import copy
+import math
+import os
+import random
+from dataclasses import dataclass, replace
+from typing import List
+
+import numpy as np
+import torch
+
+import helpers
+from plain import qwen2_plain as plain
+
+
+def runner_for(folder, device, dtype, num_pages, max_requests=4, max_seq_len=None, page_size=16):
+    from vt_transformer_b200.engine.runner import ModelRunner
+    return ModelRunner.from_folder(folder, dtype=dtype, device=device, page_size=page_size, num_pages=num_pages,
+                                   max_requests=max_requests, max_seq_len=max_seq_len)
+
+
+# ----------------------------------------------------------------------------- the four ways of cutting
+
+
+def replay_family(folder, name, family, device, dtype):
+    prompts = helpers.prompts_for(name)
+    trace = {"whole": helpers.trace_whole, "tail": helpers.trace_tail, "portions": helpers.trace_portions,
+             "mixed": lambda p: helpers.trace_mixed(p, max_live=4, seed=3)}[family](prompts)
+    # so few pages that they are used again: what the live requests need at most, no more
+    pages = helpers.tokens_needed(trace, round_to=16) // 16
+    runner = runner_for(folder, device, dtype, num_pages=pages)
+    got = helpers.run_trace_inproc(runner, trace)
+    worst = helpers.compare_trace(folder, prompts, trace, got, helpers.TOL[dtype])
+    assert runner.cache.free_pages() == [g.pool.num_pages for g in runner.cache.groups]
+    return worst
+
+
+# ----------------------------------------------------------------------------- run order as data
+
+
+def register_order_architecture(order_name: str, order):
+    """An architecture that is Qwen2's parts in another run order (a test's own, never a model of
+    anyone's): ``order`` is a tuple of RunSpec."""
+    from vt_transformer_b200.config import Qwen2Config, register_architecture
+    from vt_transformer_b200.models.qwen2 import qwen2_model_spec
+
+    def spec(cfg):
+        return replace(qwen2_model_spec(cfg), order=tuple(order))
+
+    register_architecture(order_name, Qwen2Config, spec, replace=True)
+
+
+def run_order_case(tmp, device, dtype):
+    """Layer 1 runs twice (each run with a cache slot of its own) and a last run of layer 0
+    reads the keys and values that the first run stored."""
+    from vt_transformer_b200.config import config_from_dict, unregister_architecture
+    from vt_transformer_b200.parts import RunSpec
+    from vt_transformer_b200.weights import write_random_model
+    order = (RunSpec(0, 0), RunSpec(1, 1), RunSpec(1, 2), RunSpec(0, 0, writes=False))
+    register_order_architecture("OrderTestLM", order)
+    try:
+        d = copy.deepcopy(helpers.CONFIGS["A"])
+        d["architectures"] = ["OrderTestLM"]
+        folder = write_random_model(config_from_dict(d), os.path.join(tmp, "order"), seed=4, sigma=0.08)
+        cfg, w = plain.read_config(folder), plain.read_weights(folder)
+        ids = helpers.prompts_for("A")[3]
+        ref = plain.forward(cfg, w, ids, order=[0, 1, 1, (0, 0)])
+        runner = runner_for(folder, device, dtype, num_pages=6, max_requests=2)
+        assert sorted(runner.model.cache_slots()) == [0, 1, 2]
+        row = runner.admit()
+        got, a = [], 0
+        for k in (23, 1, 1, 30, 15):
+            got.append(runner.step([helpers_entry(row, ids[a:a + k])]).float().cpu())
+            a += k
+        runner.check_status()
+        err = float((torch.cat(got).double() - ref).abs().max())
+        assert err <= helpers.TOL[dtype], err
+        plain_default = plain.forward(cfg, w, ids)
+        assert float((ref - plain_default).abs().max()) > 100 * helpers.TOL[dtype]   # the order matters
+        return err
+    finally:
+        unregister_architecture("OrderTestLM")
+
+
+def helpers_entry(row, tokens):
+    from vt_transformer_b200.engine.batch import StepEntry
+    return StepEntry(row, list(tokens), list(range(len(tokens))))
+
+
+# ----------------------------------------------------------------------------- a toy mixer with state
+
+
+def define_toy_parts():
+    """A mixer that keeps state of fixed size for each request: the running mean of its inputs
+    over the request's tokens, times a matrix.  Defined here, in the tests, and registered
+    through the package's public registry; no file of the package knows it."""
+    from vt_transformer_b200.parts import Mixer, MixerSpec, ParamSpec, StateSpec, register_part
+
+    @dataclass(frozen=True)
+    class RunningMeanSpec(MixerSpec):
+        hidden: int = 0
+        kind: str = "toy_running_mean"
+
+    class RunningMean(Mixer):
+        def cache_spec(self):
+            return StateSpec((self.spec.hidden + 1,), torch.float32)     # sum of inputs, and their count
+
+        def param_specs(self):
+            return {self.prefix + "proj.weight": ParamSpec((self.spec.hidden, self.spec.hidden))}
+
+        def load(self, get):
+            self.w = self.rt.param(get(self.prefix + "proj.weight"))
+
+        def forward(self, h, ctx, cache):
+            out = torch.empty_like(h)
+            H = self.spec.hidden
+            for s in ctx.seqs:                                   # portions of a request come in order
+                x = h[s.offset:s.offset + s.length].float()
+                st = cache.state[s.row]
+                total = st[:H] + torch.cumsum(x, dim=0)
+                count = st[H] + torch.arange(1, s.length + 1, device=h.device, dtype=torch.float32)
+                out[s.offset:s.offset + s.length] = ((total / count[:, None]) @ self.w.float().t()).to(h.dtype)
+                st[:H] = total[-1]
+                st[H] = count[-1]
+            return out
+
+    register_part("mixer", "toy_running_mean", RunningMean, replace=True)
+    return RunningMeanSpec
+
+
+def toy_state_case(tmp, device, dtype):
+    """A model of three layers whose middle mixer is the toy: registered, built from a folder,
+    stepped in portions beside another request, with its rows used again."""
+    from vt_transformer_b200.config import Qwen2Config, config_from_dict, register_architecture, unregister_architecture
+    from vt_transformer_b200.models.qwen2 import qwen2_model_spec
+    from vt_transformer_b200.parts import unregister_part
+    from vt_transformer_b200.weights import write_random_model
+    Spec = define_toy_parts()
+
+    def spec(cfg):
+        base = qwen2_model_spec(cfg)
+        blocks = list(base.blocks)
+        blocks[1] = replace(blocks[1], mixer=Spec(hidden=cfg.hidden_size), mixer_prefix="mixer.")
+        return replace(base, blocks=tuple(blocks))
+
+    register_architecture("ToyStateLM", Qwen2Config, spec, replace=True)
+    try:
+        d = copy.deepcopy(helpers.CONFIGS["B"])
+        d["architectures"] = ["ToyStateLM"]
+        folder = write_random_model(config_from_dict(d), os.path.join(tmp, "toy"), seed=9, sigma=0.05)
+        cfg, w = plain.read_config(folder), plain.read_weights(folder)
+        assert "model.layers.1.mixer.proj.weight" in w and "model.layers.1.self_attn.q_proj.weight" not in w
+
+        def reference(ids):
+            cos, sin = plain.rotation_table(cfg.max_pos, cfg.head_dim, cfg.theta)
+            x = plain.embed(w["model.embed_tokens.weight"], ids)
+            x = plain.layer(cfg, w, 0, x, cos, sin)
+            h = plain.rms_norm(x, w["model.layers.1.input_layernorm.weight"], cfg.eps)
+            mean = torch.cumsum(h, 0) / torch.arange(1, len(ids) + 1, dtype=h.dtype)[:, None]
+            x = x + mean @ w["model.layers.1.mixer.proj.weight"].t()
+            h = plain.rms_norm(x, w["model.layers.1.post_attention_layernorm.weight"], cfg.eps)
+            x = x + plain.swiglu(h, w["model.layers.1.mlp.gate_proj.weight"], w["model.layers.1.mlp.up_proj.weight"],
+                                 w["model.layers.1.mlp.down_proj.weight"])
+            x = plain.layer(cfg, w, 2, x, cos, sin)
+            x = plain.rms_norm(x, w["model.norm.weight"], cfg.eps)
+            return plain.linear(x, w["lm_head.weight"])
+
+        runner = runner_for(folder, device, dtype, num_pages=8, max_requests=2)
+        slots = runner.model.cache_slots()
+        assert type(slots[1]).__name__ == "StateSpec" and type(slots[0]).__name__ == "KVCacheSpec"
+        prompts = helpers.prompts_for("B")
+        worst = 0.0
+        for first, second in ((prompts[3], prompts[2]), (prompts[2], prompts[1])):   # the second pair uses the rows again
+            rows = [runner.admit(), runner.admit()]
+            got = [[], []]
+            done = [0, 0]
+            sizes = [[9, 2, 30, 1, 1, 27], [5, 1, 1, 13, 11]]
+            for step in range(6):
+                entries = []
+                for i, ids in enumerate((first, second)):
+                    if step < len(sizes[i]) and done[i] < len(ids):
+                        k = min(sizes[i][step], len(ids) - done[i])
+                        entries.append((i, helpers_entry(rows[i], ids[done[i]:done[i] + k])))
+                        done[i] += k
+                logits = runner.step([e for _, e in entries]).float().cpu()
+                at = 0
+                for i, e in entries:
+                    got[i].append(logits[at:at + len(e.tokens)])
+                    at += len(e.tokens)
+            runner.check_status()
+            for i, ids in enumerate((first, second)):
+                assert done[i] == len(ids)
+                err = float((torch.cat(got[i]).double() - reference(ids)).abs().max())
+                assert err <= helpers.TOL[dtype], (i, err)
+                worst = max(worst, err)
+            for r in rows:
+                runner.release(r)
+        return worst
+    finally:
+        unregister_architecture("ToyStateLM")
+        unregister_part("mixer", "toy_running_mean")
+
+
+# ----------------------------------------------------------------------------- generation
+
+
+def plain_generate(folder, prompt, n, temperature=0.0, seed=0, top_k=-1, top_p=1.0) -> List[int]:
+    cfg, w = plain.read_config(folder), helpers._plain_weights(folder)
+    from vt_transformer_b200.sampling import uniform   # the draw's random number is part of the request, not of the model
+    ids = list(prompt)
+    for i in range(n):
+        logits = plain.forward(cfg, w, ids)[-1]
+        ids.append(plain.sample(logits, temperature, uniform(seed, i), top_k, top_p))
+    return ids[len(prompt):]
+
+
+def greedy_generation_case(folder, name, device, dtype, n_new=16):
+    """Greedy generation through the entry point.  In 32-bit the tokens are the plain
+    implementation's.  In bfloat16 two logits closer than the rounding may change places, so
+    each token is checked along the engine's own path: it is the plain argmax, or its plain
+    logit lies within the tolerance of the largest."""
+    from vt_transformer_b200 import LLM, SamplingParams
+    prompts = helpers.prompts_for(name)[:3]
+    llm = LLM(folder, dtype=dtype, device=device, max_running_reqs=3, num_pages=24, max_seq_len=160,
+              max_extend_tokens=48, chunk_size=24)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert len(o) == n_new
+        if dtype == "float32":
+            assert o == plain_generate(folder, p, n_new), (len(p), o)
+        else:
+            ref = helpers.plain_logits(folder, list(p) + o)
+            for i, tok in enumerate(o):
+                row = ref[len(p) - 1 + i]
+                assert float(row.max() - row[tok]) <= 2 * helpers.TOL[dtype], (len(p), i, tok)
+    llm.runner.cache.check()
+    assert llm.stats["free_pages"] == [24] * len(llm.runner.cache.groups)
+    return outs
+
+
+def temperature_generation_case(folder, name, device, dtype, n_new=24):
+    """Temperature sampling with a fixed seed under four settings of token budget, portion
+    size and pool, the last two with so few pages that requests are pre-empted.  In 32-bit
+    all settings give the plain implementation's tokens.  In bfloat16 every token is checked
+    along its own path against the plain probabilities: the draw's random number falls into
+    the token's interval of the plain cumulative distribution, give or take the tolerance."""
+    from vt_transformer_b200 import LLM, SamplingParams
+    from vt_transformer_b200.sampling import uniform
+    prompts = helpers.prompts_for(name)[:4]
+    params = SamplingParams(temperature=0.7, max_tokens=n_new, ignore_eos=True, seed=77)
+    results, preemptions = [], []
+    for kw in (dict(max_running_reqs=4, num_pages=40, max_extend_tokens=256, chunk_size=None),
+               dict(max_running_reqs=4, num_pages=40, max_extend_tokens=28, chunk_size=24),
+               dict(max_running_reqs=4, num_pages=11, max_extend_tokens=40, chunk_size=24),
+               dict(max_running_reqs=2, num_pages=9, max_extend_tokens=16, chunk_size=5)):
+        llm = LLM(folder, dtype=dtype, device=device, max_seq_len=160, **kw)
+        results.append(llm.generate(prompts, params))
+        preemptions.append(llm.stats["preemptions"])
+        llm.runner.cache.check()
+    assert max(preemptions) > 0, "no setting ran out of pages: the test does not test pre-emption"
+    if dtype == "float32":
+        for other in results[1:]:
+            assert other == results[0]
+        for i, (p, o) in enumerate(zip(prompts, results[0])):
+            assert o == plain_generate(folder, p, n_new, temperature=0.7, seed=77 + i), i
+    else:
+        slack = 4 * helpers.TOL[dtype]
+        for res in results:
+            for i, (p, o) in enumerate(zip(prompts, res)):
+                ref = helpers.plain_logits(folder, list(p) + o)
+                for j, tok in enumerate(o):
+                    c = torch.cumsum(plain.kept_probabilities(ref[len(p) - 1 + j], 0.7), 0)
+                    u = uniform(77 + i, j)
+                    lo = float(c[tok - 1]) if tok > 0 else 0.0
+                    assert lo - slack <= u <= float(c[tok]) + slack, (i, j, tok, u, lo, float(c[tok]))
+    assert len({tuple(o) for o in results[0]}) > 1
+    return results[0], preemptions

@@ -1,0 +1,75 @@
+"""The engine's host-side logic on the CPU: the step function, the cache manager and the
+scheduler drive stand-in kernels (tests/fake_ops.py) and are compared with the plain
+implementation.  The same scenarios run on the GPU with the real kernels in
+test_gpu_engine.py."""
+import pytest
+import torch
+
+import helpers
+import scenarios
+
+DEV, DT = "cpu", "float32"
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
+def test_cuts_equal_the_plain_implementation(fake_backend, folders, name, family):
+    scenarios.replay_family(folders(name), name, family, DEV, DT)
+
+
+def test_run_order_is_data(fake_backend, tmp_path):
+    scenarios.run_order_case(str(tmp_path), DEV, DT)
+
+
+def test_bad_run_orders_are_refused(fake_backend):
+    from dataclasses import replace
+    from vt_transformer_b200.models import DecoderModel
+    from vt_transformer_b200.models.qwen2 import qwen2_model_spec
+    from vt_transformer_b200.parts import RunSpec, Runtime
+    spec = qwen2_model_spec(helpers.make_config("A"))
+    rt = Runtime(torch.device("cpu"), torch.float32, None)
+    for order, word in (((RunSpec(0, 0), RunSpec(1, 0)), "written by an earlier run"),
+                        ((RunSpec(0, 0, writes=False),), "before any run wrote"),
+                        ((RunSpec(5, 0),), "names block 5"),
+                        ((RunSpec(0, None),), "names no slot")):
+        with pytest.raises(ValueError, match=word):
+            DecoderModel(replace(spec, order=order), rt)
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped(fake_backend, tmp_path):
+    scenarios.toy_state_case(str(tmp_path), DEV, DT)
+
+
+def test_step_refuses_bad_entries_and_leaves_the_cache_alone(fake_backend, folders):
+    from vt_transformer_b200.cache import OutOfPages
+    from vt_transformer_b200.engine import StepEntry
+    runner = scenarios.runner_for(folders("A"), DEV, DT, num_pages=2, max_requests=2, max_seq_len=64)
+    a, b = runner.admit(), runner.admit()
+    with pytest.raises(ValueError, match="twice"):
+        runner.step([StepEntry(a, [1, 2]), StepEntry(a, [3])])
+    with pytest.raises(ValueError, match="outside"):
+        runner.step([StepEntry(a, [1, 2], [2])])
+    with pytest.raises(OutOfPages):
+        runner.step([StepEntry(a, [1] * 20, [0]), StepEntry(b, [2] * 20, [0])])
+    assert runner.cache.free_pages() == [2] and runner.cache.length(a) == 0
+    out = runner.step([StepEntry(a, [1] * 20, [19, 0, 19])])      # a place may be wanted twice
+    assert out.shape == (3, 256) and torch.equal(out[0], out[2]) and not torch.equal(out[0], out[1])
+    assert runner.step([]).shape == (0, 256)
+    assert runner.step([StepEntry(a, [5], [])]).shape == (0, 256) and runner.cache.length(a) == 21
+
+
+def test_greedy_generation(fake_backend, folders):
+    scenarios.greedy_generation_case(folders("A"), "A", DEV, DT)
+
+
+def test_temperature_generation_survives_recutting_and_preemption(fake_backend, folders):
+    out, pre = scenarios.temperature_generation_case(folders("B"), "B", DEV, DT)
+    assert pre[0] == 0
+
+
+def test_missing_extension_fails_loudly():
+    from vt_transformer_b200 import ops
+    ops.use_backend(None)
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="no CPU path"):
+            ops.backend()

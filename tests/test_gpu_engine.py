@@ -1,0 +1,165 @@
+"""The engine on the GPU with the real kernels, in 32-bit and in bfloat16, against the plain
+implementation: every way of cutting, run orders, a toy mixer, generation."""
+import pytest
+import torch
+
+import helpers
+import scenarios
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = ["float32", "bfloat16"]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
+def test_cuts_equal_the_plain_implementation(folders, name, family, dtype):
+    scenarios.replay_family(folders(name), name, family, DEV, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_run_order_is_data(tmp_path, dtype):
+    scenarios.run_order_case(str(tmp_path), DEV, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
+    scenarios.toy_state_case(str(tmp_path), DEV, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_greedy_generation_through_the_entry_point(folders, name, dtype):
+    scenarios.greedy_generation_case(folders(name), name, DEV, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_temperature_generation_survives_recutting_and_preemption(folders, dtype):
+    scenarios.temperature_generation_case(folders("B"), "B", DEV, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens_of_a_sequence(folders, dtype):
+    """One token, two tokens, three: the first positions, where the cache is empty and a
+    portion is shorter than any tile."""
+    from vt_transformer_b200.engine import StepEntry
+    folder = folders("B")
+    ids = helpers.prompts_for("B")[3]
+    ref = helpers.plain_logits(folder, ids)
+    runner = scenarios.runner_for(folder, DEV, dtype, num_pages=4, max_requests=4)
+    for n in (1, 2, 3):
+        row = runner.admit()
+        got = runner.step([StepEntry(row, ids[:n], list(range(n)))]).double().cpu()
+        assert float((got - ref[:n]).abs().max()) <= helpers.TOL[dtype]
+        for t in range(n, n + 3):                            # and three single tokens after them
+            got = runner.step([StepEntry(row, ids[t:t + 1], [0])]).double().cpu()
+            assert float((got[0] - ref[t]).abs().max()) <= helpers.TOL[dtype], (n, t)
+        runner.release(row)
+    runner.check_status()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(folders, dtype):
+    """A short prompt and then 230 tokens one by one, beside a second request that joins late:
+    the cache grows over many pages, one token at a time."""
+    from vt_transformer_b200.engine import StepEntry
+    folder = folders("A")
+    rng_ids = helpers.prompts_for("A", seed=5)
+    ids = (rng_ids[4] + rng_ids[3] + rng_ids[2] + rng_ids[1] + rng_ids[0] + rng_ids[4])[:240]
+    other = rng_ids[3]
+    ref, ref_other = helpers.plain_logits(folder, ids), helpers.plain_logits(folder, other)
+    runner = scenarios.runner_for(folder, DEV, dtype, num_pages=21, max_requests=2)
+    a = runner.admit()
+    worst = float((runner.step([StepEntry(a, ids[:10], [9])]).double().cpu()[0] - ref[9]).abs().max())
+    b, done_b = None, 0
+    for t in range(10, 240):
+        entries = [StepEntry(a, ids[t:t + 1], [0])]
+        if t == 100:
+            b = runner.admit()
+        if b is not None and done_b < len(other):
+            k = min(7, len(other) - done_b)
+            entries.append(StepEntry(b, other[done_b:done_b + k], [k - 1]))
+        got = runner.step(entries).double().cpu()
+        worst = max(worst, float((got[0] - ref[t]).abs().max()))
+        if len(entries) == 2:
+            done_b += k
+            worst = max(worst, float((got[1] - ref_other[done_b - 1]).abs().max()))
+    runner.check_status()
+    assert worst <= helpers.TOL[dtype], worst
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_far_key_among_hundreds_is_found(tmp_path, dtype):
+    """Random weights give flat attention, which hides a key that is read from the wrong place.
+    Here the queries and keys of layer 0 are scaled up so that the scores are sharp and every
+    token attends to a few keys that differ from token to token: a key missed at a page's
+    edge, in a page that was used before, or far back, changes the logits by far more than
+    the tolerance."""
+    from safetensors import safe_open
+    from vt_transformer_b200.engine import StepEntry
+    from vt_transformer_b200.weights import SafetensorsSource, write_random_model
+    from vt_transformer_b200.weights import safetensors_io as st
+    import os
+    src_folder = write_random_model(helpers.make_config("B"), str(tmp_path / "src"), seed=41, sigma=0.05)
+    src = SafetensorsSource(src_folder)
+    tensors = {n: src.get(n).clone() for n in src.entries()}
+    for proj in ("q_proj", "k_proj"):
+        for kind in ("weight", "bias"):
+            name = f"model.layers.0.self_attn.{proj}.{kind}"
+            tensors[name] = (tensors[name].float() * 6.0).to(torch.bfloat16)
+    folder = str(tmp_path / "sharp")
+    os.makedirs(folder)
+    helpers.make_config("B").save(folder)
+    st.write_file(os.path.join(folder, "model.safetensors"), iter(tensors.items()),
+                  [(n, t.dtype, tuple(t.shape)) for n, t in tensors.items()])
+    ids = (helpers.prompts_for("B", seed=8)[4] * 3)[:380]
+    ref = helpers.plain_logits(folder, ids)
+    flat = helpers.plain_logits(src_folder, ids)
+    assert float((ref - flat).abs().max()) > 50 * helpers.TOL[dtype]       # the scaling matters
+    runner = scenarios.runner_for(folder, DEV, dtype, num_pages=26, max_requests=2)
+    # a first request fills and frees pages, so the long one lives in pages that were used before
+    warm = runner.admit()
+    runner.step([StepEntry(warm, ids[:200][::-1], [])])
+    runner.release(warm)
+    row = runner.admit()
+    got, a = [], 0
+    for k in (300, 17, 1, 1, 1, 30, 2, 28):
+        got.append(runner.step([StepEntry(row, ids[a:a + k], list(range(k)))]).double().cpu())
+        a += k
+    runner.check_status()
+    err = float((torch.cat(got) - ref).abs().max())
+    assert err <= helpers.TOL[dtype], err
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_window_edge(folders, dtype):
+    """Config C's late layers see 20 keys.  Positions around the edge (19, 20, 21), around the
+    pages' edges, and with the window cutting through a portion are compared one by one."""
+    from vt_transformer_b200.engine import StepEntry
+    folder = folders("C")
+    ids = helpers.prompts_for("C")[4]
+    ref = helpers.plain_logits(folder, ids)
+    runner = scenarios.runner_for(folder, DEV, dtype, num_pages=8, max_requests=2)
+    row = runner.admit()
+    got, a = [], 0
+    for k in (19, 1, 1, 1, 10, 16, 1, 31, 2, 38):
+        got.append(runner.step([StepEntry(row, ids[a:a + k], list(range(k)))]).double().cpu())
+        a += k
+        runner.cache.check()
+    assert a == len(ids)
+    win = [g for g in runner.cache.groups if g.spec.window][0]
+    assert win.pool.free >= win.pool.num_pages - 3               # pages behind the window went back
+    runner.check_status()
+    err = (torch.cat(got) - ref).abs().max(dim=1).values
+    assert float(err.max()) <= helpers.TOL[dtype], (int(err.argmax()), float(err.max()))
+
+
+def test_status_word_reports_a_bad_token_id(folders):
+    from vt_transformer_b200.engine import DeviceStatusError, StepEntry
+    runner = scenarios.runner_for(folders("A"), DEV, "float32", num_pages=2, max_requests=1)
+    row = runner.admit()
+    runner.step([StepEntry(row, [1, 2, 100000], [2])])
+    with pytest.raises(DeviceStatusError, match="token id"):
+        runner.check_status()
+    runner.check_status()                                        # the word was cleared

@@ -1,0 +1,257 @@
+"""Each kernel alone against a plain float64 computation of the same op (the plain
+implementation's functions where it has one), at sizes other than the engine's tests use."""
+import math
+import random
+
+import pytest
+import torch
+
+from plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    # one rounding of the result: 2^-24 relative in 32-bit (sums of a few hundred terms: 1e-5), 2^-9 in bfloat16
+    return (2e-5 if dtype == torch.float32 else 1.0 / 256) * scale
+
+
+def ops():
+    from vt_transformer_b200 import ops as o
+    return o
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(dtype):
+    torch.manual_seed(0)
+    table = torch.randn(1000, 200, device=DEV).to(dtype)
+    ids = torch.tensor([0, 999, 5, 5, 123, -1], dtype=torch.int32, device=DEV)
+    out = torch.full((6, 200), 7.0, device=DEV)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    ops().embedding(table, ids, out, status=status)
+    ref = plain.embed(table.cpu().double(), [0, 999, 5, 5, 123])
+    assert torch.equal(out[:5].cpu().double(), ref) and float(out[5].abs().sum()) == 0.0     # a negative id pads
+    assert status.tolist() == [0, 0]
+    ops().embedding(table, torch.tensor([1000], dtype=torch.int32, device=DEV), out[:1], status=status)
+    assert status.tolist() == [1, 1000]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [72, 1000, 3584, 8200])
+def test_rmsnorm_with_residual_sum_and_rows(dtype, hidden):
+    torch.manual_seed(1)
+    T = 37
+    x = torch.randn(T, hidden, device=DEV) * 3
+    delta = torch.randn(T, hidden, device=DEV).to(dtype)
+    w = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    ref_sum = x.cpu().double() + delta.cpu().double()
+    out = torch.empty(T, hidden, device=DEV, dtype=dtype)
+    x1 = x.clone()
+    ops().rmsnorm(x1, w, 1e-5, out)                                                   # plain norm
+    assert float((out.cpu().double() - plain.rms_norm(x.cpu().double(), w.cpu().double(), 1e-5)).abs().max()) <= tol(dtype, 8)
+    assert torch.equal(x1, x)
+    ops().rmsnorm(x1, w, 1e-5, out, delta=delta)                                      # with the sum
+    assert float((x1.cpu().double() - ref_sum).abs().max()) <= 1e-6                   # the stream holds the 32-bit sum
+    assert float((out.cpu().double() - plain.rms_norm(ref_sum, w.cpu().double(), 1e-5)).abs().max()) <= tol(dtype, 8)
+    rows = torch.tensor([36, 0, 17], dtype=torch.int32, device=DEV)                   # some rows only, in that order
+    x2, out2 = x.clone(), torch.empty(3, hidden, device=DEV, dtype=dtype)
+    ops().rmsnorm(x2, w, 1e-5, out2, delta=delta, rows=rows)
+    assert torch.equal(out2, out[rows.long()])
+    assert torch.equal(x2[1], x[1]) and torch.equal(x2[17], x1[17])                   # other rows are untouched
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    torch.manual_seed(2)
+    gu = (torch.randn(19, 2 * 344, device=DEV) * 4).to(dtype)
+    out = torch.empty(19, 344, device=DEV, dtype=dtype)
+    ops().silu_mul(gu, out)
+    g, u = gu[:, :344].cpu().double(), gu[:, 344:].cpu().double()
+    ref = g / (1 + torch.exp(-g)) * u
+    assert float((out.cpu().double() - ref).abs().max()) <= tol(dtype, 16)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 40, 64), (77, 130, 200), (64, 64, 16), (5, 301, 72), (200, 1000, 344)])
+def test_gemm_simt(dtype, m, n, k):
+    torch.manual_seed(3)
+    a = torch.randn(m, k, device=DEV).to(dtype)
+    w = torch.randn(n, k, device=DEV).to(dtype)
+    bias = torch.randn(n, device=DEV)
+    ref = plain.linear(a.cpu().double(), w.cpu().double(), bias.cpu().double())
+    for out_dtype in {dtype, torch.float32}:
+        c = torch.empty(m, n, device=DEV, dtype=out_dtype)
+        ops().linear(a, w, bias, c)
+        assert float((c.cpu().double() - ref).abs().max()) <= tol(out_dtype, 4 * math.sqrt(k))
+        ops().linear(a, w, None, c)
+        assert float((c.cpu().double() - (ref - bias.cpu().double())).abs().max()) <= tol(out_dtype, 4 * math.sqrt(k))
+
+
+def test_gemm_f32_is_a_true_32_bit_product_and_does_not_depend_on_the_batch():
+    torch.manual_seed(4)
+    a = torch.randn(50, 256, device=DEV)
+    w = torch.randn(96, 256, device=DEV)
+    c = torch.empty(50, 96, device=DEV)
+    ops().linear(a, w, None, c)
+    ref = a.cpu().double() @ w.cpu().double().t()
+    assert float((c.cpu().double() - ref).abs().max()) < 3e-5          # TF32 would be off by 1e-2 here
+    one = torch.empty(1, 96, device=DEV)
+    ops().linear(a[7:8].contiguous(), w, None, one)
+    assert torch.equal(one[0], c[7])                                   # bit for bit, alone or in a batch of 50
+
+
+def paged_cache(k, v, seq_lens, page_size, n_pages, dtype, seed=0):
+    """Scatters dense keys and values [sum(seq_lens), kv_heads, d] into shuffled pages.
+    Returns k_cache, v_cache [pages, kv_heads, page_size, d] and the block table."""
+    rng = random.Random(seed)
+    kv_heads, d = k.shape[1], k.shape[2]
+    kc = torch.full((n_pages, kv_heads, page_size, d), float("nan"), device=DEV).to(dtype)
+    vc = torch.full_like(kc, float("nan"))
+    free = list(range(n_pages))
+    rng.shuffle(free)
+    max_pages = max(-(-n // page_size) for n in seq_lens)
+    table = torch.full((len(seq_lens), max_pages), -1, dtype=torch.int32)
+    at = 0
+    for s, n in enumerate(seq_lens):
+        for p in range(-(-n // page_size)):
+            page = free.pop()
+            table[s, p] = page
+            cnt = min(page_size, n - p * page_size)
+            kc[page, :, :cnt] = k[at + p * page_size: at + p * page_size + cnt].transpose(0, 1).to(dtype)
+            vc[page, :, :cnt] = v[at + p * page_size: at + p * page_size + cnt].transpose(0, 1).to(dtype)
+        at += n
+    return kc, vc, table.to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,d,page_size,window", [(6, 2, 80, 32, None), (5, 5, 16, 16, 7), (8, 1, 128, 64, 50),
+                                                               (3, 3, 256, 16, None)])
+def test_attention_over_pages(dtype, heads, kv_heads, d, page_size, window):
+    """Three sequences in shuffled pages: whole ones and a tail of queries of a longer one."""
+    torch.manual_seed(5)
+    seq_lens = [70, 33, 150]
+    q_lens = [70, 1, 9]                       # the queries are the last q_len positions of each sequence
+    total = sum(seq_lens)
+    k = torch.randn(total, kv_heads, d, device=DEV).to(dtype)
+    v = torch.randn(total, kv_heads, d, device=DEV).to(dtype)
+    kc, vc, table = paged_cache(k, v, seq_lens, page_size, 12 * 64 // page_size, dtype)
+    T = sum(q_lens)
+    q = (torch.randn(T, heads, d, device=DEV) * 2).to(dtype)
+    qkv = torch.cat([q.view(T, -1), torch.zeros(T, 2 * kv_heads * d, device=DEV, dtype=dtype)], dim=1).contiguous()
+    positions, token_seq = [], []
+    for s, (n, ql) in enumerate(zip(seq_lens, q_lens)):
+        positions += list(range(n - ql, n))
+        token_seq += [s] * ql
+    class Ctx:
+        pass
+    ctx = Ctx()
+    ctx.positions = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    ctx.token_seq = torch.tensor(token_seq, dtype=torch.int32, device=DEV)
+    ctx.max_q_len, ctx.max_kv_len, ctx.n_seqs, ctx.n_tokens = max(q_lens), max(seq_lens), 3, T
+    ctx.extras = {}
+    out = torch.empty(T, heads * d, device=DEV, dtype=dtype)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    ops().paged_attention(qkv, out, kc, vc, ctx, table, heads, kv_heads, d, window, 1 / math.sqrt(d), status=status)
+    assert status.tolist() == [0, 0]
+    at_q = at_k = 0
+    for n, ql in zip(seq_lens, q_lens):
+        qq = torch.zeros(n, heads, d, dtype=torch.float64)
+        qq[n - ql:] = q[at_q:at_q + ql].cpu().double()
+        ref = plain.attention(qq, k[at_k:at_k + n].cpu().double(), v[at_k:at_k + n].cpu().double(), window)[n - ql:]
+        got = out[at_q:at_q + ql].view(ql, heads, d).cpu().double()
+        assert float((got - ref).abs().max()) <= tol(dtype, 4), (n, ql)
+        at_q, at_k = at_q + ql, at_k + n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,d,page_size", [(6, 2, 48, 16), (4, 4, 128, 32)])
+def test_rotation_and_cache_store(dtype, heads, kv_heads, d, page_size):
+    from vt_transformer_b200.parts.rope import rotation_table
+    torch.manual_seed(6)
+    table = rotation_table(300, d, 50000.0).to(DEV)
+    cos, sin = plain.rotation_table(300, d, 50000.0)
+    positions = [0, 1, 15, 16, 17, 250, 299, 3]
+    token_seq = [0, 0, 0, 0, 0, 1, 1, -1]                       # the last token is padding
+    T = len(positions)
+    qkv = torch.randn(T, (heads + 2 * kv_heads) * d, device=DEV).to(dtype)
+    before = qkv.clone()
+    n_pages = 30
+    kc = torch.zeros(n_pages, kv_heads, page_size, d, device=DEV, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    bt = torch.full((2, 300 // page_size + 1), -1, dtype=torch.int32)
+    bt[0, 0], bt[0, 1], bt[1, 250 // page_size], bt[1, 299 // page_size] = 7, 3, 11, 29
+    bt = bt.to(DEV)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    ops().rope_store(qkv, torch.tensor(positions, dtype=torch.int32, device=DEV), table, kc, vc,
+                     torch.tensor(token_seq, dtype=torch.int32, device=DEV), bt, heads, kv_heads, d, status=status)
+    assert status.tolist() == [0, 0]
+    qd, kd = heads * d, kv_heads * d
+    live = list(range(T - 1))
+    q_ref = plain.rotate(before[:, :qd].view(T, heads, d).cpu().double(), positions, cos, sin)
+    k_ref = plain.rotate(before[:, qd:qd + kd].view(T, kv_heads, d).cpu().double(), positions, cos, sin)
+    got_q = qkv[:, :qd].view(T, heads, d).cpu().double()
+    assert float((got_q[live] - q_ref[live]).abs().max()) <= tol(dtype, 8)
+    assert torch.equal(qkv[T - 1], before[T - 1])                       # padding is left alone
+    assert torch.equal(qkv[:, qd:], before[:, qd:])                     # k and v rows stay as they were
+    for t in live:
+        page = int(bt[token_seq[t], positions[t] // page_size])
+        slot = positions[t] % page_size
+        assert float((kc[page, :, slot].cpu().double() - k_ref[t]).abs().max()) <= tol(dtype, 8)
+        assert torch.equal(vc[page, :, slot], before[t, qd + kd:].view(kv_heads, d))
+    assert int((kc != 0).any(dim=-1).sum()) == len(live) * kv_heads     # nothing else was written
+    # a run that only reads another's cache rotates q and stores nothing
+    kc.zero_()
+    qkv2 = before.clone()
+    ops().rope_store(qkv2, torch.tensor(positions, dtype=torch.int32, device=DEV), table, kc, vc,
+                     torch.tensor(token_seq, dtype=torch.int32, device=DEV), bt, heads, kv_heads, d, store=False)
+    assert torch.equal(qkv2, qkv) and float(kc.abs().sum()) == 0.0
+    # a position beyond the table is reported, not followed
+    ops().rope_store(qkv2[:1], torch.tensor([300], dtype=torch.int32, device=DEV), table, kc, vc,
+                     torch.tensor([0], dtype=torch.int32, device=DEV), bt, heads, kv_heads, d, status=status)
+    assert status.tolist() == [2, 300]
+
+
+def test_argmax_takes_the_lowest_of_equals():
+    torch.manual_seed(7)
+    logits = torch.randn(5, 50257, device=DEV)
+    logits[1, 40000] = logits[1, 123] = 50.0
+    logits[2, 50256] = 60.0
+    logits[3, 0] = 70.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops().argmax(logits, out)
+    assert out.tolist() == [plain.sample_greedy(logits[r].cpu()) for r in range(5)]
+    assert out.tolist()[1:4] == [123, 50256, 0]
+
+
+@pytest.mark.parametrize("vocab", [1000, 50257])
+def test_sampling_kernel_draws_what_the_plain_sampler_draws(vocab):
+    from vt_transformer_b200.sampling import uniform
+    torch.manual_seed(8)
+    cases = [(0.0, -1, 1.0), (0.7, -1, 1.0), (1.3, -1, 1.0), (0.8, 3, 1.0), (1.0, 40, 1.0), (1.0, -1, 0.9),
+             (0.6, 50, 0.5), (1.0, 1, 1.0), (2.0, vocab, 0.999)]
+    rows = len(cases) * 8
+    logits = torch.randn(rows, vocab, device=DEV) * 3
+    params = [cases[r % len(cases)] for r in range(rows)]
+    us = [uniform(5, r) for r in range(rows)]
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops().sample(logits, torch.tensor([p[0] for p in params], device=DEV),
+                 torch.tensor([p[1] for p in params], dtype=torch.int32, device=DEV),
+                 torch.tensor([p[2] for p in params], device=DEV), torch.tensor(us, device=DEV), out)
+    host = logits.cpu()
+    want = [plain.sample(host[r], params[r][0], float(torch.tensor(us[r], dtype=torch.float32)), params[r][1], params[r][2])
+            for r in range(rows)]
+    assert out.tolist() == want
+    assert len(set(out.tolist())) > rows // 2
+
+
+def test_sampling_kernel_follows_the_distribution():
+    logits = torch.tensor([0.0, math.log(2.0), math.log(5.0), -40.0] + [-60.0] * 96, device=DEV).repeat(4000, 1)
+    n = logits.shape[0]
+    u = (torch.arange(n, device=DEV, dtype=torch.float32) + 0.5) / n
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops().sample(logits, torch.ones(n, device=DEV), torch.full((n,), -1, dtype=torch.int32, device=DEV),
+                 torch.ones(n, device=DEV), u, out)
+    freq = torch.bincount(out.long().cpu(), minlength=100)[:4].double() / n
+    assert float((freq - torch.tensor([1 / 8, 2 / 8, 5 / 8, 0.0], dtype=torch.float64)).abs().max()) < 1e-3

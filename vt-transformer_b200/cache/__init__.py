@@ -1,0 +1,1 @@
+from .manager import CacheManager, OutOfPages, OutOfRows, PagePool

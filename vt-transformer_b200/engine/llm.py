@@ -1,0 +1,111 @@
+"""The Python entry point: a model folder in, generated token ids out.
+
+vt-transformer's own entry points are the C++ chat loop (v1/models/qwen2-7b/chat.cpp:54-123:
+prompt ids in, one token a step, stop at the end token or after ``max_output``) and, in its
+second generation, the back end driven by ``FullScheduler::step`` with the front end's
+``SamplingParams`` (sglfront/sglfront/core.py:6-17).  ``LLM`` keeps those names:
+``SchedulerConfig`` fields for the engine, ``SamplingParams`` for a request, ``step()``
+returning ``ReqResult`` records.  Text is outside: prompts are token ids.
+"""
+from __future__ import annotations
+
+from dataclasses import replace
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..config.registry import load_config
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .runner import ModelRunner
+from .scheduler import ReqResult, Scheduler, SchedulerConfig, StepResult
+
+
+class LLM:
+    def __init__(self, model: str, dtype: str = "bfloat16", device: str = "cuda:0",
+                 max_running_reqs: int = 128, num_pages: Optional[int] = None, max_seq_len: int = 4096,
+                 page_size: int = 16, max_extend_tokens: int = 8192, default_max_output: int = 1024,
+                 chunk_size: Optional[int] = None, runner: Optional[ModelRunner] = None):
+        """``model``: a folder with config.json and model.safetensors.  ``num_pages`` None
+        sizes the pool for ``max_running_reqs`` requests of ``max_seq_len`` tokens, capped at
+        half a million tokens."""
+        if runner is None:
+            config = load_config(model)
+            limit = getattr(config, "max_position_embeddings", None)
+            if limit:
+                max_seq_len = min(max_seq_len, limit)
+            if num_pages is None:
+                num_pages = -(-min(max_running_reqs * max_seq_len, 1 << 19) // page_size)
+            runner = ModelRunner.from_folder(model, dtype=dtype, device=device, page_size=page_size,
+                                             num_pages=num_pages, max_requests=max_running_reqs,
+                                             max_seq_len=max_seq_len)
+        self.runner = runner
+        cache = runner.cache
+        self.config = SchedulerConfig(max_running_reqs=cache.max_requests, num_pages=cache.groups[0].pool.num_pages
+                                      if cache.groups else 0, max_seq_len=cache.max_seq_len,
+                                      page_size=cache.page_size, max_extend_tokens=max_extend_tokens,
+                                      default_max_output=default_max_output, chunk_size=chunk_size)
+        self.sampler = Sampler(runner.rt.ops, runner.rt.device)
+        eos = ()
+        try:
+            eos = load_config(model).eos_token_id or () if model else ()
+        except Exception:
+            eos = ()
+        self.scheduler = Scheduler(cache, self.config, self._run_step, eos_token_ids=eos)
+
+    # the scheduler's hook: run the batch, sample one token for each request that wants one
+    def _run_step(self, entries, wanting) -> List[int]:
+        logits = self.runner.step(entries)
+        if not wanting:
+            return []
+        tokens = self.sampler.sample(logits, [r.params for r in wanting], [len(r.output) for r in wanting])
+        host = tokens.tolist()          # waits for the step
+        self.runner.check_status()
+        return host
+
+    # ---- requests one by one ---------------------------------------------------------------
+    def add_request(self, prompt_token_ids: Sequence[int], sampling_params: Optional[SamplingParams] = None) -> int:
+        return self.scheduler.add_request(prompt_token_ids, sampling_params)
+
+    def abort(self, uid: int) -> bool:
+        return self.scheduler.abort(uid)
+
+    def step(self) -> StepResult:
+        return self.scheduler.step()
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ---- whole batches ---------------------------------------------------------------------------
+    def generate(self, prompt_token_ids: Sequence[Sequence[int]],
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[List[int]]:
+        """Generates for every prompt and returns the new token ids of each, in the order of
+        the prompts.  One ``SamplingParams`` stands for all prompts; prompt i then draws with
+        seed ``sampling_params.seed + i``."""
+        n = len(prompt_token_ids)
+        if sampling_params is None:
+            sampling_params = SamplingParams(max_tokens=self.config.default_max_output)
+        if isinstance(sampling_params, SamplingParams):
+            params = [replace(sampling_params, seed=sampling_params.seed + i) for i in range(n)]
+        else:
+            params = list(sampling_params)
+            if len(params) != n:
+                raise ValueError(f"{n} prompts but {len(params)} sampling parameters")
+        uids = [self.add_request(p, sp) for p, sp in zip(prompt_token_ids, params)]
+        while self.scheduler.has_work():
+            res = self.scheduler.step()
+            if not res.ran_batch and not res.n_preempted and self.scheduler.has_work():
+                raise RuntimeError("the scheduler can run nothing: the cache pool is too small for the waiting request")
+        out = []
+        for uid in uids:
+            req = self.scheduler.finished.pop(uid)
+            if req.finish_reason == "out_of_pages":
+                raise RuntimeError(f"request {uid} does not fit the cache pool even alone")
+            out.append(list(req.output))
+        return out
+
+    @property
+    def stats(self) -> Dict[str, int]:
+        s = dict(self.scheduler.stats)
+        s["free_pages"] = self.runner.cache.free_pages()
+        return s

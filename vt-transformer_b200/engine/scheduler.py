@@ -1,0 +1,272 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget, decodes,
+finishes and frees.
+
+After vt-transformer's ``FullScheduler`` (vt-transformer/core/vt_scheduler.cpp): two queues,
+waiting and running (``pending_``/``running_``, vt_scheduler.hpp:132-141); FIFO admission
+(:251-302); a token budget for a step (``max_extend_tokens``); a result for every request that
+produced a token, ``ReqResult{uid, next_token, finished}`` (vt_scheduler.hpp:94-98).  What is
+decided differently, because the reference leaves it open:
+
+* a step is mixed: every running request takes part, those that decode with one token,
+  those still in their prompt with a portion of it (the reference runs prompts or decodes,
+  never both, vt_scheduler.cpp:102-110, and never cuts a prompt, :277,:292-294);
+* admission reserves nothing for the future; when pages run out, the youngest running
+  request is pre-empted: its pages and row are given back, its tokens (prompt and what it
+  has generated) are kept, and it goes to the head of the waiting queue; when it is
+  admitted again its tokens are run again in portions and it goes on where it stopped,
+  with the same random numbers.  (The reference rolls a prompt batch back and otherwise
+  stalls, vt_scheduler.cpp:386-402, and never evicts.)  The oldest request always goes on;
+  a request that cannot fit the pool even alone is finished with reason "out_of_pages".
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence, Tuple
+
+from ..cache.manager import OutOfPages
+from ..sampling.params import SamplingParams
+from .batch import StepEntry
+
+
+@dataclass
+class SchedulerConfig:
+    """Names and defaults of vt-transformer/core/vt_scheduler.hpp:33-38, except
+    ``page_size`` (16 here: the attention kernels read keys in runs of 16) and
+    ``chunk_size`` (the longest portion of one prompt in a step; the reference has none)."""
+    max_running_reqs: int = 128
+    num_pages: int = 1024
+    max_seq_len: int = 4096
+    page_size: int = 16
+    max_extend_tokens: int = 8192
+    default_max_output: int = 1024
+    chunk_size: Optional[int] = None
+
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+
+
+@dataclass
+class Request:
+    uid: int
+    prompt: List[int]
+    params: SamplingParams
+    arrival: int
+    output: List[int] = field(default_factory=list)
+    state: str = WAITING
+    row: Optional[int] = None
+    cached: int = 0              # tokens whose keys and values are in the cache
+    preemptions: int = 0
+    finish_reason: Optional[str] = None
+
+    @property
+    def n_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    @property
+    def pending(self) -> int:
+        """Tokens that still have to run: the rest of the prompt, or the last sampled token."""
+        return self.n_tokens - self.cached
+
+    def token_slice(self, a: int, b: int) -> List[int]:
+        n = len(self.prompt)
+        if b <= n:
+            return self.prompt[a:b]
+        if a >= n:
+            return self.output[a - n:b - n]
+        return self.prompt[a:] + self.output[:b - n]
+
+
+@dataclass
+class ReqResult:
+    uid: int
+    next_token: int
+    finished: bool
+    finish_reason: Optional[str] = None
+
+
+@dataclass
+class StepResult:
+    ran_batch: bool
+    results: List[ReqResult]
+    n_tokens: int = 0
+    n_preempted: int = 0
+
+
+class Scheduler:
+    """``cache`` is the cache manager (pages and rows); ``run_step(entries)`` runs a batch and
+    returns one sampled token for each entry that wants logits, in order (the engine binds it
+    to ``ModelRunner.step`` plus the sampler; tests bind a fake)."""
+
+    def __init__(self, cache, config: SchedulerConfig, run_step, eos_token_ids: Sequence[int] = ()):
+        self.cache = cache
+        self.config = config
+        self.run_step = run_step
+        self.eos = tuple(eos_token_ids)
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []
+        self.finished: Dict[int, Request] = {}
+        self._next_uid = 0
+        self._arrivals = 0
+        self.stats = {"steps": 0, "tokens": 0, "preemptions": 0, "finished": 0}
+
+    # ---- requests ----------------------------------------------------------------------------
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    uid: Optional[int] = None) -> int:
+        params = params or SamplingParams(max_tokens=self.config.default_max_output)
+        params.validate()
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            raise ValueError("a request needs at least one prompt token")
+        if len(prompt) >= self.config.max_seq_len:
+            raise ValueError(f"the prompt has {len(prompt)} tokens; max_seq_len is {self.config.max_seq_len}")
+        if uid is None:
+            uid = self._next_uid
+        self._next_uid = max(self._next_uid, uid) + 1
+        req = Request(uid=uid, prompt=prompt, params=params, arrival=self._arrivals)
+        self._arrivals += 1
+        self.waiting.append(req)
+        return uid
+
+    def abort(self, uid: int) -> bool:
+        """Drops a request wherever it is; what it holds is given back at once."""
+        for req in list(self.waiting):
+            if req.uid == uid:
+                self.waiting.remove(req)
+                self._finish(req, "abort")
+                return True
+        for req in self.running:
+            if req.uid == uid:
+                self.running.remove(req)
+                self._finish(req, "abort")
+                return True
+        return False
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def _finish(self, req: Request, reason: str) -> None:
+        if req.row is not None:
+            self.cache.release(req.row)
+            req.row = None
+        req.state, req.finish_reason = FINISHED, reason
+        self.finished[req.uid] = req
+        self.stats["finished"] += 1
+
+    def _preempt(self, req: Request) -> None:
+        self.running.remove(req)
+        self.cache.release(req.row)
+        req.row, req.cached, req.state = None, 0, WAITING
+        req.preemptions += 1
+        self.waiting.appendleft(req)
+        self.stats["preemptions"] += 1
+
+    # ---- planning ------------------------------------------------------------------------------
+    def _portion(self, req: Request, budget: int) -> int:
+        n = min(req.pending, budget)
+        if self.config.chunk_size is not None and req.pending > 1:
+            n = min(n, self.config.chunk_size)
+        return n
+
+    def _plan_running(self) -> Tuple[List[Tuple[Request, int]], int]:
+        budget = self.config.max_extend_tokens
+        plan = []
+        for req in sorted(self.running, key=lambda r: (r.pending > 1, r.arrival)):
+            n = self._portion(req, budget)
+            if n > 0:
+                plan.append((req, n))
+                budget -= n
+        return plan, budget
+
+    def plan(self) -> Tuple[List[Tuple[Request, int]], int]:
+        """Decides the step: which requests run how many tokens.  Pre-empts and admits as
+        needed.  Returns the plan and the number of requests pre-empted."""
+        n_preempted = 0
+        while True:
+            plan, budget = self._plan_running()
+            need = self.cache.pages_needed([(r.row, r.cached + n) for r, n in plan])
+            free = self.cache.free_pages()
+            if all(n <= f for n, f in zip(need, free)):
+                break
+            if len(self.running) <= 1:
+                # alone and still too large for the pool: it can never go on
+                for req in list(self.running):
+                    self.running.remove(req)
+                    self._finish(req, "out_of_pages")
+                continue
+            self._preempt(max(self.running, key=lambda r: r.arrival))
+            n_preempted += 1
+        left = [f - n for f, n in zip(free, need)]
+        # admission, first come first served; nobody overtakes the head of the queue
+        while self.waiting and budget > 0 and n_preempted == 0:
+            if len(self.running) >= self.config.max_running_reqs or self.cache.free_rows == 0:
+                break
+            req = self.waiting[0]
+            n = self._portion(req, budget)
+            want = self.cache.pages_for_new(n)
+            reserve = len(self.running)          # a page of head-room for each running request
+            if any(w + (reserve if self.running else 0) > l for w, l in zip(want, left)):
+                if not self.running and not plan:
+                    # nothing else holds pages: shrink the portion to what fits, or give up
+                    fit = min(left) * self.cache.page_size if left else n
+                    if fit <= 0:
+                        self.waiting.popleft()
+                        self._finish(req, "out_of_pages")
+                        continue
+                    n = min(n, fit)
+                    want = self.cache.pages_for_new(n)
+                else:
+                    break
+            self.waiting.popleft()
+            req.row, req.state, req.cached = self.cache.admit(), RUNNING, 0
+            self.running.append(req)
+            plan.append((req, n))
+            budget -= n
+            left = [l - w for l, w in zip(left, want)]
+        return plan, n_preempted
+
+    # ---- the step ----------------------------------------------------------------------------------
+    def step(self) -> StepResult:
+        """One step: plan, run the batch, sample, finish and free."""
+        if not self.has_work():
+            return StepResult(False, [])
+        plan, n_preempted = self.plan()
+        if not plan:
+            return StepResult(False, [], n_preempted=n_preempted)
+        entries, wanting = [], []
+        for req, n in plan:
+            last = (n == req.pending)
+            entries.append(StepEntry(req.row, req.token_slice(req.cached, req.cached + n), [n - 1] if last else []))
+            if last:
+                wanting.append(req)
+        try:
+            tokens = self.run_step(entries, wanting)
+        except OutOfPages:
+            # the plan counted pages; a group can still be short when window groups hold pages of
+            # portions in flight.  Pre-empt the youngest and let the next step plan again.
+            if len(self.running) > 1:
+                self._preempt(max(self.running, key=lambda r: r.arrival))
+                return StepResult(False, [], n_preempted=n_preempted + 1)
+            raise
+        for req, n in plan:
+            req.cached += n
+        results = []
+        for req, tok in zip(wanting, tokens):
+            tok = int(tok)
+            req.output.append(tok)
+            reason = None
+            eos = req.params.eos_token_ids if req.params.eos_token_ids is not None else self.eos
+            if not req.params.ignore_eos and tok in eos:
+                reason = "stop"
+            elif len(req.output) >= req.params.max_tokens:
+                reason = "length"
+            elif req.n_tokens >= self.config.max_seq_len:
+                reason = "length"
+            if reason is not None:
+                self.running.remove(req)
+                self._finish(req, reason)
+            results.append(ReqResult(req.uid, tok, reason is not None, reason))
+        n_tok = sum(n for _, n in plan)
+        self.stats["steps"] += 1
+        self.stats["tokens"] += n_tok
+        return StepResult(True, results, n_tokens=n_tok, n_preempted=n_preempted)
