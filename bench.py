@@ -1,0 +1,256 @@
+"""Benchmark of the engine on one B200: decode and prefill throughput of Qwen2-7B layer sizes
+with random weights, with their roofline fractions.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step of a batch of 8 requests with 1,024-token prompts (the context grows
+from 1,024).  ``value`` is decoded tokens a second with the K steps timed on the device;
+``e2e`` is the same through the Python entry point (``LLM.step``), token ids crossing between
+host and device every step.  One JSON line is printed.  The engine runs on one GPU: for
+--gpus above 1 a line says so and the exit code is 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# layer sizes of Qwen2-7B (BASELINE.json configs[2]); weights are random, N(0, 0.02)
+MODEL = dict(architectures=["Qwen2ForCausalLM"], vocab_size=152064, hidden_size=3584, intermediate_size=18944,
+             num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, head_dim=128, rms_norm_eps=1e-6,
+             rope_theta=1000000.0, max_position_embeddings=32768, tie_word_embeddings=False,
+             sliding_window=131072, use_sliding_window=False, max_window_layers=28, torch_dtype="bfloat16")
+PROMPT_LEN, CONTEXT, PREFILL_TOKENS, PAGE = 1024, 4096, 2048, 16
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]),
+                    bf16_tflops_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm():
+    # viitrix/vt-transformer has no Python package at its root (no setup.py / pyproject.toml beside its
+    # C++ trees), so `pip install <checkout>` has nothing to install; its engine is a C++ program that
+    # needs cuDNN, a Rust tokenizer library and a per-tensor weight dump made with network access.
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "vt-transformer is a C++ program without a Python package to install offline; it needs cuDNN, "
+                      "a Rust tokenizer library and a weight dump that cannot be made here"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has (recorded in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the prefill")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(3, args.warmup)
+
+    import torch
+    from vt_transformer_b200 import LLM, SamplingParams, ops
+    from vt_transformer_b200.config import config_from_dict
+    from vt_transformer_b200.engine import ModelRunner, StepEntry
+
+    pk = peaks()
+    model = dict(MODEL)
+    layers_full = model["num_hidden_layers"]
+    if args.layers:
+        model["num_hidden_layers"] = args.layers
+    cfg = config_from_dict(model)
+    dev = "cuda:0"
+    max_batch = max(64, args.batch)
+    new_tokens = warmup + args.steps + 8
+    per_req = PROMPT_LEN + max(new_tokens, 256) + PAGE
+    pool_tokens = max_batch * per_req + PREFILL_TOKENS
+    t0 = time.time()
+    runner = ModelRunner.from_random(cfg, seed=0, sigma=0.02, dtype="bfloat16", device=dev, page_size=PAGE,
+                                     num_pages=-(-pool_tokens // PAGE), max_requests=max_batch, max_seq_len=CONTEXT)
+    torch.cuda.synchronize()
+    build_s = time.time() - t0
+    gen = torch.Generator().manual_seed(1)
+    vocab = cfg.vocab_size
+
+    def random_tokens(n):
+        return torch.randint(0, vocab, (n,), generator=gen).tolist()
+
+    def fill(batch):
+        """Admits `batch` requests and runs their 1,024-token prompts, two prompts a step."""
+        rows = [runner.admit() for _ in range(batch)]
+        for i in range(0, batch, 2):
+            runner.step([StepEntry(r, random_tokens(PROMPT_LEN), []) for r in rows[i:i + 2]])
+        return rows
+
+    def decode_run(batch, steps, warm, clocks=None):
+        rows = fill(batch)
+        out = torch.empty(batch, dtype=torch.int32, device=dev)
+        feeds = [[random_tokens(batch) for _ in range(steps + warm)]][0]
+
+        def one(i):
+            logits = runner.step([StepEntry(r, [feeds[i][j]], [0]) for j, r in enumerate(rows)])
+            ops.argmax(logits, out)
+
+        for i in range(warm):
+            one(i)
+        torch.cuda.synchronize()
+        if clocks:
+            clocks.start()
+        launches0 = ops.launches
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(warm, warm + steps):
+            one(i)
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end)
+        info = clocks.stop() if clocks else None
+        launched = ops.launches - launches0
+        ctx_mean = PROMPT_LEN + warm + (steps - 1) / 2.0 + 1
+        runner.check_status()
+        for r in rows:
+            runner.release(r)
+        return dict(tok_s=batch * steps / (ms / 1e3), ms_per_step=ms / steps, launches=launched, ctx_mean=ctx_mean,
+                    clocks=info)
+
+    main_run = decode_run(args.batch, args.steps, warmup, ClockSampler())
+    kv_bytes = runner.cache.bytes_per_token() * main_run["ctx_mean"] * args.batch
+    step_bytes = runner.weight_bytes(args.batch) + kv_bytes
+    achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
+
+    points, prefill = {}, None
+    if not args.skip_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(decode_run(b, min(args.steps, 64), 5)["tok_s"], 1)
+        # prefill of 2,048 tokens: one request, one step, logits of the last token
+        times = []
+        for i in range(3 + 5):
+            row = runner.admit()
+            toks = random_tokens(PREFILL_TOKENS)
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            runner.step([StepEntry(row, toks, [PREFILL_TOKENS - 1])])
+            e.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                times.append(s.elapsed_time(e))
+            runner.release(row)
+        runner.check_status()
+        ms = statistics.median(times)
+        T, H, I, L = PREFILL_TOKENS, cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers
+        per_layer = 2 * T * H * (cfg.q_dim + 2 * cfg.kv_dim) + 2 * T * cfg.q_dim * H + 2 * T * H * 2 * I + 2 * T * I * H
+        attn = 2 * 2 * (T * (T + 1) // 2) * cfg.head_dim * cfg.num_attention_heads
+        flops = L * (per_layer + attn) + 2 * H * vocab
+        prefill = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
+                   "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(flops / ms / 1e9, 1)}
+
+    # end to end: the Python entry point, token ids in from the host and out to the host every step
+    llm = LLM(None, runner=runner, max_extend_tokens=2048)
+    params = SamplingParams(temperature=0.0, max_tokens=new_tokens, ignore_eos=True)
+    for _ in range(args.batch):
+        llm.add_request(random_tokens(PROMPT_LEN), params)
+    while any(len(r.output) == 0 for r in llm.scheduler.running) or llm.scheduler.waiting:
+        llm.step()
+    for _ in range(warmup):
+        llm.step()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    produced = 0
+    for _ in range(args.steps):
+        produced += len(llm.step().results)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t1
+    h2d = llm.h2d_bytes_last_step
+    d2h = llm.d2h_bytes_last_step
+    for req in list(llm.scheduler.running):
+        llm.abort(req.uid)
+
+    clocks = main_run["clocks"] or {}
+    line = {
+        "metric": "decode tok/s at batch 8 (Qwen2-7B layer sizes, random weights, 1,024-token prompts)",
+        "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {"model": "Qwen2-7B sizes, random N(0,0.02)", "layers": cfg.num_hidden_layers, "layers_full": layers_full,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
+                   "mean_context": round(main_run["ctx_mean"], 1), "page_size": PAGE, "parallelism": "1 GPU",
+                   "l2": "inputs larger than L2 (every step reads all weights)", "peaks": pk["source"]},
+        "e2e": {"value": round(produced / e2e_s, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": main_run["launches"],
+        "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"), "reasons": clocks.get("reasons", [])},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
+        "points": points, "build_s": round(build_s, 1),
+    }
+    if prefill is not None:
+        line["prefill"] = prefill
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

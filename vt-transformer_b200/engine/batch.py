@@ -56,6 +56,7 @@ class StepContext:
     status: Optional[torch.Tensor] = None   # [2] int32 on the device: code, detail
     want_inverse: Optional[np.ndarray] = None   # set if wanted rows repeat: logits[want_inverse]
     extras: dict = field(default_factory=dict)  # per-step scratch of the kernels' wrappers
+    h2d_bytes: int = 0                          # bytes of the description copied to the device
 
 
 def _align4(n: int) -> int:
@@ -124,4 +125,5 @@ def build_context(entries: Sequence[StepEntry], cache, device, status=None) -> S
         n_tokens=T, n_seqs=n, seqs=seqs, token_ids=dseg(0), positions=dseg(1), token_seq=dseg(2), cu_q=dseg(3),
         q_start=dseg(4), kv_len=dseg(5), rows=dseg(6), want_rows=dseg(7),
         block_tables={g: dseg(8 + g).view(n, n_pages) for g in range(n_groups)},
-        max_q_len=max(lens, default=0), max_kv_len=max_kv, status=status, want_inverse=want_inverse)
+        max_q_len=max(lens, default=0), max_kv_len=max_kv, status=status, want_inverse=want_inverse,
+        h2d_bytes=total * 4)

@@ -46,6 +46,8 @@ class LLM:
                                       page_size=cache.page_size, max_extend_tokens=max_extend_tokens,
                                       default_max_output=default_max_output, chunk_size=chunk_size)
         self.sampler = Sampler(runner.rt.ops, runner.rt.device)
+        self.h2d_bytes_last_step = 0
+        self.d2h_bytes_last_step = 0
         eos = ()
         try:
             eos = load_config(model).eos_token_id or () if model else ()
@@ -56,11 +58,17 @@ class LLM:
     # the scheduler's hook: run the batch, sample one token for each request that wants one
     def _run_step(self, entries, wanting) -> List[int]:
         logits = self.runner.step(entries)
+        self.h2d_bytes_last_step = self.runner.last_h2d_bytes
+        self.d2h_bytes_last_step = 0
         if not wanting:
             return []
-        tokens = self.sampler.sample(logits, [r.params for r in wanting], [len(r.output) for r in wanting])
+        params = [r.params for r in wanting]
+        tokens = self.sampler.sample(logits, params, [len(r.output) for r in wanting])
+        if not all(p.is_greedy for p in params):
+            self.h2d_bytes_last_step += 16 * len(wanting)
         host = tokens.tolist()          # waits for the step
         self.runner.check_status()
+        self.d2h_bytes_last_step = 4 * len(host) + 8
         return host
 
     # ---- requests one by one ---------------------------------------------------------------

@@ -52,6 +52,7 @@ class ModelRunner:
         self.model, self.cache, self.rt = model, cache, rt
         self.status = torch.zeros(2, dtype=torch.int32, device=rt.device)
         self.steps = 0
+        self.last_h2d_bytes = 0
 
     # ---- construction --------------------------------------------------------------------
     @classmethod
@@ -119,6 +120,7 @@ class ModelRunner:
                     raise ValueError(f"row {e.row}: wanted place {w} is outside its {len(e.tokens)} tokens")
         self.cache.extend([(e.row, self.cache.length(e.row) + len(e.tokens)) for e in entries])
         ctx = build_context(entries, self.cache, self.rt.device, status=self.status)
+        self.last_h2d_bytes = ctx.h2d_bytes
         logits = self.model.forward(ctx, self.cache.views(ctx.block_tables))
         for e in entries:
             self.cache.commit(e.row, self.cache.length(e.row) + len(e.tokens))

@@ -16,6 +16,7 @@ from typing import Optional
 import torch
 
 _backend = None
+launches = 0          # kernels of this package enqueued so far (one for each call below)
 
 
 def backend():
@@ -112,3 +113,18 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 def sample(logits, temperature, top_k, top_p, u, out) -> torch.Tensor:
     backend().sample(logits, temperature, top_k, top_p, u, out)
     return out
+
+
+def _counted(fn):
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(*a, **k):
+        global launches
+        launches += 1
+        return fn(*a, **k)
+    return wrapper
+
+
+for _name in ("embedding", "rmsnorm", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):
+    globals()[_name] = _counted(globals()[_name])
