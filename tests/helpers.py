@@ -238,3 +238,21 @@ def compare_trace(folder: str, prompts, trace: Trace, got: Dict[int, np.ndarray]
                 f"(entries {[(e['id'], len(e['tokens'])) for e in trace.steps[n]['entries']]})")
             worst = max(worst, d)
     return worst
+
+
+def step_context(q_lens, starts, device, status=None):
+    """A StepContext for sequences whose new tokens are `q_lens` long and start at positions
+    `starts` (no block tables: tests of parts pass theirs in the cache view)."""
+    from vt_transformer_b200.engine.batch import SeqSlice, StepContext
+    seqs, off, pos, tseq = [], 0, [], []
+    for i, (n, s) in enumerate(zip(q_lens, starts)):
+        seqs.append(SeqSlice(i, s, n, off))
+        pos += list(range(s, s + n))
+        tseq += [i] * n
+        off += n
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+    return StepContext(n_tokens=off, n_seqs=len(q_lens), seqs=seqs, token_ids=t([0] * off), positions=t(pos),
+                       token_seq=t(tseq), cu_q=t([s.offset for s in seqs] + [off]), q_start=t(list(starts)),
+                       kv_len=t([s + n for s, n in zip(starts, q_lens)]), rows=t(list(range(len(q_lens)))),
+                       want_rows=t([]), block_tables={}, max_q_len=max(q_lens), max_kv_len=max(s + n for s, n in zip(starts, q_lens)),
+                       status=status)

@@ -92,9 +92,12 @@ def test_gemm_simt(dtype, m, n, k):
     for out_dtype in {dtype, torch.float32}:
         c = torch.empty(m, n, device=DEV, dtype=out_dtype)
         ops().linear(a, w, bias, c)
-        assert float((c.cpu().double() - ref).abs().max()) <= tol(out_dtype, 4 * math.sqrt(k))
+        close(c, ref, out_dtype, 3 if out_dtype == torch.bfloat16 else 40)
         ops().linear(a, w, None, c)
-        assert float((c.cpu().double() - (ref - bias.cpu().double())).abs().max()) <= tol(out_dtype, 4 * math.sqrt(k))
+        close(c, ref - bias.cpu().double(), out_dtype, 3 if out_dtype == torch.bfloat16 else 40)
+        if dtype == torch.bfloat16:                       # the plain twin itself, whatever `linear` picks
+            ops().backend().gemm_simt(a, w, bias, c)
+            close(c, ref, out_dtype, 2 if out_dtype == torch.bfloat16 else 40)
 
 
 def test_gemm_f32_is_a_true_32_bit_product_and_does_not_depend_on_the_batch():
@@ -135,7 +138,8 @@ def paged_cache(k, v, seq_lens, page_size, n_pages, dtype, seed=0):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,d,page_size,window", [(6, 2, 80, 32, None), (5, 5, 16, 16, 7), (8, 1, 128, 64, 50),
-                                                               (3, 3, 256, 16, None)])
+                                                               (3, 3, 256, 16, None), (28, 4, 128, 16, None), (14, 2, 64, 16, 90),
+                                                               (7, 7, 112, 16, None), (9, 3, 96, 48, 33)])
 def test_attention_over_pages(dtype, heads, kv_heads, d, page_size, window):
     """Three sequences in shuffled pages: whole ones and a tail of queries of a longer one."""
     torch.manual_seed(5)
@@ -148,17 +152,8 @@ def test_attention_over_pages(dtype, heads, kv_heads, d, page_size, window):
     T = sum(q_lens)
     q = (torch.randn(T, heads, d, device=DEV) * 2).to(dtype)
     qkv = torch.cat([q.view(T, -1), torch.zeros(T, 2 * kv_heads * d, device=DEV, dtype=dtype)], dim=1).contiguous()
-    positions, token_seq = [], []
-    for s, (n, ql) in enumerate(zip(seq_lens, q_lens)):
-        positions += list(range(n - ql, n))
-        token_seq += [s] * ql
-    class Ctx:
-        pass
-    ctx = Ctx()
-    ctx.positions = torch.tensor(positions, dtype=torch.int32, device=DEV)
-    ctx.token_seq = torch.tensor(token_seq, dtype=torch.int32, device=DEV)
-    ctx.max_q_len, ctx.max_kv_len, ctx.n_seqs, ctx.n_tokens = max(q_lens), max(seq_lens), 3, T
-    ctx.extras = {}
+    import helpers
+    ctx = helpers.step_context(q_lens, [n - ql for n, ql in zip(seq_lens, q_lens)], DEV)
     out = torch.empty(T, heads * d, device=DEV, dtype=dtype)
     status = torch.zeros(2, dtype=torch.int32, device=DEV)
     ops().paged_attention(qkv, out, kc, vc, ctx, table, heads, kv_heads, d, window, 1 / math.sqrt(d), status=status)
@@ -168,9 +163,76 @@ def test_attention_over_pages(dtype, heads, kv_heads, d, page_size, window):
         qq = torch.zeros(n, heads, d, dtype=torch.float64)
         qq[n - ql:] = q[at_q:at_q + ql].cpu().double()
         ref = plain.attention(qq, k[at_k:at_k + n].cpu().double(), v[at_k:at_k + n].cpu().double(), window)[n - ql:]
-        got = out[at_q:at_q + ql].view(ql, heads, d).cpu().double()
-        assert float((got - ref).abs().max()) <= tol(dtype, 4), (n, ql)
+        close(out[at_q:at_q + ql].view(ql, heads, d), ref, dtype, 4)
         at_q, at_k = at_q + ql, at_k + n
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,page_size,window", [(28, 4, 128, 16, None), (6, 2, 80, 32, None), (4, 4, 16, 16, 40),
+                                                               (16, 1, 64, 64, 100), (14, 2, 64, 16, None), (40, 2, 32, 16, None)])
+def test_single_token_steps_split_the_keys(heads, kv_heads, d, page_size, window):
+    """Every sequence brings one token (a decode step): the tensor-core kernel splits the keys of a
+    sequence over several CTAs and merges the parts.  Sequences of very different lengths, one of a
+    single token."""
+    import helpers
+    from vt_transformer_b200 import ops as o
+    dtype = torch.bfloat16
+    torch.manual_seed(9)
+    seq_lens = [1, 700, 64, 65, 333, 16]
+    total = sum(seq_lens)
+    k = torch.randn(total, kv_heads, d, device=DEV).to(dtype)
+    v = torch.randn(total, kv_heads, d, device=DEV).to(dtype)
+    kc, vc, table = paged_cache(k, v, seq_lens, page_size, 1300 // page_size + 8, dtype, seed=3)
+    T = len(seq_lens)
+    q = (torch.randn(T, heads, d, device=DEV) * 2).to(dtype)
+    qkv = torch.cat([q.view(T, -1), torch.zeros(T, 2 * kv_heads * d, device=DEV, dtype=dtype)], dim=1).contiguous()
+    ctx = helpers.step_context([1] * T, [n - 1 for n in seq_lens], DEV)
+    out = torch.empty(T, heads * d, device=DEV, dtype=dtype)
+    o.paged_attention(qkv, out, kc, vc, ctx, table, heads, kv_heads, d, window, 1 / math.sqrt(d))
+    plain_out = torch.empty_like(out)
+    o.ATTENTION_KERNEL = "simt"
+    try:
+        o.paged_attention(qkv, plain_out, kc, vc, ctx, table, heads, kv_heads, d, window, 1 / math.sqrt(d))
+    finally:
+        o.ATTENTION_KERNEL = "auto"
+    at = 0
+    for i, n in enumerate(seq_lens):
+        qq = torch.zeros(n, heads, d, dtype=torch.float64)
+        qq[n - 1] = q[i].cpu().double()
+        ref = plain.attention(qq, k[at:at + n].cpu().double(), v[at:at + n].cpu().double(), window)[n - 1]
+        close(out[i].view(heads, d), ref, dtype, 4)
+        close(plain_out[i].view(heads, d), ref, dtype, 4)
+        at += n
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("n,k", [(40, 64), (301, 72), (1000, 344), (4608, 3584), (100, 18944)])
+def test_weight_streaming_product(m, n, k):
+    torch.manual_seed(10)
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    bias = torch.randn(n, device=DEV)
+    ref = plain.linear(x.cpu().double(), w.cpu().double(), bias.cpu().double())
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.empty(m, n, device=DEV, dtype=out_dtype)
+        ops().backend().gemm_skinny(x, w, bias, out)
+        close(out, ref, out_dtype, 2 if out_dtype == torch.bfloat16 else 40)
+    out = torch.empty(m, n, device=DEV, dtype=torch.float32)
+    ops().backend().gemm_skinny(x, w, None, out)
+    close(out, ref - bias.cpu().double(), torch.float32, 40)
+
+
+@pytest.mark.parametrize("m", [65, 200, 1000])
+def test_large_batch_product(m):
+    torch.manual_seed(11)
+    n, k = 344, 136
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    bias = torch.randn(n, device=DEV)
+    ref = plain.linear(x.cpu().double(), w.cpu().double(), bias.cpu().double())
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.empty(m, n, device=DEV, dtype=out_dtype)
+        ops().linear(x, w, bias, out)
+        close(out, ref, out_dtype, 3 if out_dtype == torch.bfloat16 else 40)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

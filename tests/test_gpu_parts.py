@@ -82,14 +82,10 @@ def test_attention_part_in_two_portions(dtype, window):
                      block_table=torch.tensor([[4, 0, 2]], dtype=torch.int32, device=DEV), page_size=16)
     outs = []
     for a, b in ((0, 27), (27, 40)):
-        class Ctx:
-            positions = torch.arange(a, b, dtype=torch.int32, device=DEV)
-            token_seq = torch.zeros(b - a, dtype=torch.int32, device=DEV)
-            status = torch.zeros(2, dtype=torch.int32, device=DEV)
-            n_tokens, n_seqs, max_q_len, max_kv_len = b - a, 1, b - a, b
-            extras = {}
-        outs.append(part.forward(h[a:b].contiguous(), Ctx, view))
-        assert Ctx.status.tolist() == [0, 0]
+        import helpers
+        ctx = helpers.step_context([b - a], [a], DEV, status=torch.zeros(2, dtype=torch.int32, device=DEV))
+        outs.append(part.forward(h[a:b].contiguous(), ctx, view))
+        assert ctx.status.tolist() == [0, 0]
     hd = h.cpu().double()
     cos, sin = plain.rotation_table(64, 32, 7777.0)
     q = plain.linear(hd, w["att.q_proj.weight"].double(), w["att.q_proj.bias"].double()).view(T, 6, 32)
@@ -117,13 +113,8 @@ def test_block_part_and_the_residual_stream(dtype):
     kc = torch.zeros(2, 1, 16, 16, device=DEV, dtype=dtype)
     view = CacheView(spec=part.cache_spec(), k=kc, v=torch.zeros_like(kc),
                      block_table=torch.tensor([[1, 0]], dtype=torch.int32, device=DEV), page_size=16)
-    class Ctx:
-        positions = torch.arange(T, dtype=torch.int32, device=DEV)
-        token_seq = torch.zeros(T, dtype=torch.int32, device=DEV)
-        status = None
-        n_tokens, n_seqs, max_q_len, max_kv_len = T, 1, T, T
-        extras = {}
-    part.forward(stream, Ctx, view)
+    import helpers
+    part.forward(stream, helpers.step_context([T], [0], DEV), view)
     assert stream.x.dtype == torch.float32 and stream.pending is not None
     got = stream.x.cpu().double() + stream.pending.cpu().double()
     x = x0.cpu().double()

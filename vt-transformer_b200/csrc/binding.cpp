@@ -154,6 +154,77 @@ void gemm_simt(const Tensor& a, const Tensor& w, c10::optional<Tensor> bias, Ten
                                        stream_of(a)), "gemm_simt");
 }
 
+void gemm_skinny(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tensor& out) {
+    check_cuda(x, "x"); check_cuda(w, "w"); check_cuda(out, "out");
+    TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16,
+                "gemm_skinny: x and w must be bfloat16");
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm_skinny: 2-d tensors");
+    const int m = x.size(0), k = x.size(1), n = w.size(0);
+    TORCH_CHECK(w.size(1) == k && out.size(0) == m && out.size(1) == n, "gemm_skinny: shapes [m,k] x [n,k] -> [m,n]");
+    TORCH_CHECK(m <= 64, "gemm_skinny: at most 64 rows, found ", m);
+    TORCH_CHECK(k % 8 == 0, "gemm_skinny: inner size ", k, " must be a multiple of 8");
+    const float* bp = nullptr;
+    if (bias.has_value()) {
+        check_f32(*bias, "bias");
+        TORCH_CHECK(bias->numel() == n, "gemm_skinny: bias must have one entry for each output column");
+        bp = bias->data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    check_launch(vtb::launch_gemm_skinny(dtype_code(out, "out"), x.data_ptr(), w.data_ptr(), bp, out.data_ptr(), m, n, k,
+                                         stream_of(x)), "gemm_skinny");
+}
+
+bool attention_mma_supports(int64_t head_dim, int64_t heads, int64_t kv_heads, int64_t warps) {
+    return vtb::attention_mma_supports(head_dim, heads, kv_heads, warps);
+}
+
+void attention_mma(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache, const Tensor& cu_q,
+                   const Tensor& q_start, const Tensor& block_table, c10::optional<Tensor> tiles, int64_t heads,
+                   int64_t kv_heads, int64_t head_dim, int64_t window, double scale, int64_t warps, int64_t n_splits,
+                   c10::optional<Tensor> part_o, c10::optional<Tensor> part_ml, c10::optional<Tensor> status) {
+    check_cuda(qkv, "qkv"); check_cuda(out, "out"); check_i32(cu_q, "cu_q"); check_i32(q_start, "q_start");
+    check_i32(block_table, "block_table");
+    TORCH_CHECK(qkv.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16,
+                "attention_mma: bfloat16 only");
+    TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) >= heads * head_dim, "attention_mma: qkv must hold the queries first");
+    TORCH_CHECK(out.dim() == 2 && out.size(0) == qkv.size(0) && out.size(1) == heads * head_dim,
+                "attention_mma: out must be [tokens, heads * head_dim]");
+    TORCH_CHECK(heads % kv_heads == 0, "attention_mma: heads must be a multiple of kv_heads");
+    TORCH_CHECK(vtb::attention_mma_supports(head_dim, heads, kv_heads, warps),
+                "attention_mma: head_dim ", head_dim, " with ", heads / kv_heads, " heads in a group and ", warps,
+                " warps is not supported (head_dim a multiple of 16 up to 128, group <= 16 * warps)");
+    check_cache(k_cache, v_cache, qkv, kv_heads, head_dim);
+    TORCH_CHECK(k_cache.size(2) % 16 == 0, "attention_mma: page size must be a multiple of 16");
+    const int n_seqs = cu_q.numel() - 1;
+    TORCH_CHECK(q_start.numel() == n_seqs && block_table.dim() == 2 && block_table.size(0) == n_seqs,
+                "attention_mma: one q_start and one block-table row for each sequence");
+    const int* tp = nullptr;
+    int n_tiles = n_seqs;
+    if (tiles.has_value()) {
+        check_i32(*tiles, "tiles");
+        TORCH_CHECK(tiles->dim() == 2 && tiles->size(1) == 2, "attention_mma: tiles must be [n, 2]");
+        tp = tiles->data_ptr<int>();
+        n_tiles = tiles->size(0);
+    }
+    float *po = nullptr, *pm = nullptr;
+    const int n_tokens = qkv.size(0);
+    if (n_splits > 1) {
+        TORCH_CHECK(part_o.has_value() && part_ml.has_value(), "attention_mma: splits need scratch tensors");
+        check_f32(*part_o, "part_o"); check_f32(*part_ml, "part_ml");
+        TORCH_CHECK(part_o->numel() >= n_splits * n_tokens * heads * head_dim &&
+                        part_ml->numel() >= n_splits * n_tokens * heads * 2, "attention_mma: scratch too small");
+        po = part_o->data_ptr<float>();
+        pm = part_ml->data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(qkv.device());
+    check_launch(vtb::launch_attention_mma(qkv.data_ptr(), qkv.size(1), out.data_ptr(), k_cache.data_ptr(),
+                                           v_cache.data_ptr(), cu_q.data_ptr<int>(), q_start.data_ptr<int>(),
+                                           block_table.data_ptr<int>(), block_table.size(1), tp, n_tiles,
+                                           k_cache.size(0), n_tokens, heads, kv_heads, head_dim, k_cache.size(2), window,
+                                           (float)scale, warps, n_splits, po, pm, status_ptr(status), stream_of(qkv)),
+                 "attention_mma");
+}
+
 void attention_simt(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache,
                     const Tensor& positions, const Tensor& token_seq, const Tensor& block_table, int64_t heads,
                     int64_t kv_heads, int64_t head_dim, int64_t window, double scale, c10::optional<Tensor> status) {
@@ -214,6 +285,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("attention_simt", &attention_simt, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
           py::arg("positions"), py::arg("token_seq"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),
           py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("status") = py::none());
+    m.def("gemm_skinny", &gemm_skinny, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"));
+    m.def("attention_mma_supports", &attention_mma_supports);
+    m.def("attention_mma", &attention_mma, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
+          py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("tiles"), py::arg("heads"),
+          py::arg("kv_heads"), py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("warps"),
+          py::arg("n_splits"), py::arg("part_o") = py::none(), py::arg("part_ml") = py::none(),
+          py::arg("status") = py::none());
     m.def("argmax", &argmax, py::arg("logits"), py::arg("out"));
     m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"),
           py::arg("u"), py::arg("out"));

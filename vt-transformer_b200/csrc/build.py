@@ -25,6 +25,8 @@ SOURCES = [
     "elementwise.cu",
     "gemm_simt.cu",
     "attention_simt.cu",
+    "attention_mma.cu",
+    "gemm_skinny.cu",
     "sampling.cu",
 ]
 HEADERS = ["common.cuh", "kernels.h"]

@@ -46,6 +46,23 @@ cudaError_t launch_attention_simt(int dtype, const void* qkv, int qkv_stride, vo
                                   int heads, int kv_heads, int head_dim, int page_size, int window, float scale,
                                   int* status, cudaStream_t stream);
 
+// out[M, N] = x[M, K] w[N, K]^T (+ bias) for M <= 64 rows of bfloat16 x: the weight-streaming kernel.
+// out is bfloat16 or float.  k % 8 == 0.
+cudaError_t launch_gemm_skinny(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n,
+                               int k, cudaStream_t stream);
+
+// Tensor-core attention over the paged cache (bfloat16).  A tile is 16 * warps rows, row r being
+// (token r / group, head r % group); `tiles` lists (sequence, first token) pairs, or is null when
+// every sequence is one tile (single-token steps).  warps is 1 or 4.  With n_splits > 1 the keys of a
+// tile are cut into n_splits runs whose partial results go to part_o [splits, tokens, heads, head_dim]
+// and part_ml [splits, tokens, heads, 2] and are merged by a second kernel.
+bool attention_mma_supports(int head_dim, int heads, int kv_heads, int warps);
+cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, const void* k_cache, const void* v_cache,
+                                 const int* cu_q, const int* q_start, const int* block_table, int table_stride,
+                                 const int* tiles, int n_tiles, int n_pages, int n_tokens, int heads, int kv_heads,
+                                 int head_dim, int page_size, int window, float scale, int warps, int n_splits,
+                                 float* part_o, float* part_ml, int* status, cudaStream_t stream);
+
 // out[r] = index of the largest logit of row r (the lowest index among equals).
 cudaError_t launch_argmax(const float* logits, int* out, int n_rows, int vocab, cudaStream_t stream);
 

@@ -84,22 +84,77 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
         return out
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise TypeError(f"linear: unsupported dtypes x {x.dtype}, w {w.dtype}")
-    be.gemm_simt(x, w, bias, out)
+    m = x.shape[0]
+    if m <= SKINNY_MAX_ROWS:
+        be.gemm_skinny(x, w, bias, out)
+    elif out.dtype == torch.bfloat16 and m >= LIBRARY_MIN_ROWS:
+        # the library product, as in vt-transformer (cuBLASLt with 32-bit accumulation, then the bias,
+        # v1/tensortype/cuda_tensor.cpp:544-563)
+        torch.matmul(x, w.t(), out=out)
+        if bias is not None:
+            out.add_(bias.to(out.dtype))
+    else:
+        for a in range(0, m, SKINNY_MAX_ROWS):
+            be.gemm_skinny(x[a:a + SKINNY_MAX_ROWS], w, bias, out[a:a + SKINNY_MAX_ROWS])
     return out
+
+
+SKINNY_MAX_ROWS = 64        # rows of x up to which the weight-streaming kernel runs
+LIBRARY_MIN_ROWS = 65       # rows of x from which the tensor-core product for large batches runs
+ATTENTION_KERNEL = "auto"   # "auto", or "simt" to force the plain kernel (tests compare the two)
 
 
 # --------------------------------------------------------------------------- attention
 
 
+def _attention_tiles(ctx, tokens_per_tile: int, device):
+    """(sequence, first token) for every tile of the step: each sequence's new tokens in runs of
+    ``tokens_per_tile``.  Built once a step and kept in ``ctx.extras``."""
+    key = ("attention_tiles", tokens_per_tile)
+    tiles = ctx.extras.get(key)
+    if tiles is None:
+        pairs = [(i, a) for i, s in enumerate(ctx.seqs) for a in range(0, s.length, tokens_per_tile)]
+        host = torch.tensor(pairs, dtype=torch.int32).view(-1, 2)
+        if torch.device(device).type == "cuda":
+            host = host.pin_memory()
+        tiles = host.to(device, non_blocking=True)
+        ctx.extras[key] = tiles
+    return tiles
+
+
 def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv_heads: int, head_dim: int,
                     window: Optional[int], scale: float, status=None) -> torch.Tensor:
     """Attention of the step's tokens over the paged keys and values of their sequences.
-    ``ctx`` is the step's ``StepContext`` (positions, token_seq and the tile lists)."""
+    ``ctx`` is the step's ``StepContext``.  bfloat16 runs on the tensor cores where the kernel
+    takes the sizes (head_dim a multiple of 16 up to 128): single-token steps with the keys of a
+    sequence split over several CTAs, other steps in tiles of 64 rows of (token, head of the
+    group).  Everything else, and all of float32, runs the plain kernel."""
     be = backend()
     w = int(window) if window else 0
+    group = heads // kv_heads
+    if qkv.dtype == torch.bfloat16 and ATTENTION_KERNEL == "auto":
+        if ctx.max_q_len == 1 and be.attention_mma_supports(head_dim, heads, kv_heads, 1):
+            span = ctx.max_kv_len if not w else min(ctx.max_kv_len, w + 63)
+            n_blocks = max(1, -(-span // 64))
+            splits = max(1, min(n_blocks, -(-DECODE_TARGET_CTAS // (ctx.n_seqs * kv_heads)), 32))
+            part_o = part_ml = None
+            if splits > 1:
+                part_o = torch.empty((splits, ctx.n_tokens, heads, head_dim), dtype=torch.float32, device=qkv.device)
+                part_ml = torch.empty((splits, ctx.n_tokens, heads, 2), dtype=torch.float32, device=qkv.device)
+            be.attention_mma(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, None, heads, kv_heads,
+                             head_dim, w, float(scale), 1, splits, part_o, part_ml, status)
+            return out
+        if be.attention_mma_supports(head_dim, heads, kv_heads, 4):
+            tiles = _attention_tiles(ctx, 64 // group, qkv.device)
+            be.attention_mma(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, tiles, heads, kv_heads,
+                             head_dim, w, float(scale), 4, 1, None, None, status)
+            return out
     be.attention_simt(qkv, out, k_cache, v_cache, ctx.positions, ctx.token_seq, block_table, heads, kv_heads,
                       head_dim, w, float(scale), status)
     return out
+
+
+DECODE_TARGET_CTAS = 444    # three one-warp CTAs of the split-key kernel fit an SM (shared memory), 148 SMs
 
 
 # --------------------------------------------------------------------------- sampling
