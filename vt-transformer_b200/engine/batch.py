@@ -63,67 +63,100 @@ def _align4(n: int) -> int:
     return (n + 3) & ~3
 
 
-def build_context(entries: Sequence[StepEntry], cache, device, status=None) -> StepContext:
-    """Packs the description of a step into one int32 buffer, copies it to the device in
-    one transfer and returns views into it.  ``cache`` gives each row's cached length and
-    block-table rows; pages for the new tokens must have been allocated already."""
-    n = len(entries)
-    lens = [len(e.tokens) for e in entries]
-    T = sum(lens)
-    starts = [cache.length(e.row) for e in entries]
-    seqs, off = [], 0
-    for e, s, l in zip(entries, starts, lens):
-        seqs.append(SeqSlice(e.row, s, l, off))
-        off += l
-    want_flat = [sl.offset + int(w) for e, sl in zip(entries, seqs) for w in e.want]
-    want_inverse = None
-    if len(set(want_flat)) != len(want_flat):
-        uniq, inverse = np.unique(np.asarray(want_flat, dtype=np.int64), return_inverse=True)
-        want_flat, want_inverse = [int(u) for u in uniq], inverse
-    W = len(want_flat)
-    max_kv = max((s + l for s, l in zip(starts, lens)), default=0)
-    n_pages = max(1, -(-max_kv // cache.page_size))
-    n_groups = len(cache.groups)
+@dataclass
+class Layout:
+    """Where the arrays of a step lie in its one int32 buffer."""
+    T: int
+    n: int
+    W: int
+    n_pages: int
+    n_groups: int
+    offs: List[int]
+    sizes: List[int]
+    total: int
 
-    sizes = [T, T, T, n + 1, n, n, n, W] + [n * n_pages] * n_groups
-    offs, total = [], 0
-    for sz in sizes:
-        offs.append(total)
-        total += _align4(max(sz, 1))
-    host = np.empty(total, dtype=np.int32)
+    @staticmethod
+    def make(T: int, n: int, W: int, n_pages: int, n_groups: int) -> "Layout":
+        sizes = [T, T, T, n + 1, n, n, n, W] + [n * n_pages] * n_groups
+        offs, total = [], 0
+        for sz in sizes:
+            offs.append(total)
+            total += _align4(max(sz, 1))
+        return Layout(T, n, W, n_pages, n_groups, offs, sizes, total)
 
-    def seg(i):
-        return host[offs[i]:offs[i] + sizes[i]]
+    def seg(self, buf, i):
+        return buf[self.offs[i]:self.offs[i] + self.sizes[i]]
 
-    tok, pos, tseq = seg(0), seg(1), seg(2)
+
+def fill_host(host: np.ndarray, lay: Layout, entries: Sequence[StepEntry], seqs: List[SeqSlice], want_flat: List[int],
+              cache) -> None:
+    """Writes the step's arrays into ``host``.  The layout may be larger than the step (a fixed
+    layout of a captured graph): the rest is padding -- tokens of no sequence (id and sequence -1),
+    sequences without tokens, block-table entries -1, wanted rows that point at themselves."""
+    T, n = sum(s.length for s in seqs), len(seqs)
+    tok, pos, tseq = lay.seg(host, 0), lay.seg(host, 1), lay.seg(host, 2)
+    tok[T:], pos[T:], tseq[T:] = -1, 0, -1
     for i, (e, sl) in enumerate(zip(entries, seqs)):
         a, b = sl.offset, sl.offset + sl.length
         tok[a:b] = np.asarray(e.tokens, dtype=np.int32)
         pos[a:b] = np.arange(sl.start, sl.start + sl.length, dtype=np.int32)
         tseq[a:b] = i
-    seg(3)[:] = np.asarray([sl.offset for sl in seqs] + [T], dtype=np.int32)
-    seg(4)[:] = np.asarray(starts, dtype=np.int32)
-    seg(5)[:] = np.asarray([s + l for s, l in zip(starts, lens)], dtype=np.int32)
-    seg(6)[:] = np.asarray([e.row for e in entries], dtype=np.int32)
-    seg(7)[:] = np.asarray(want_flat, dtype=np.int32)
-    rows = [e.row for e in entries]
-    for g in range(n_groups):
-        seg(8 + g)[:] = cache.table_rows(g, rows, n_pages).reshape(-1)
+    cu = lay.seg(host, 3)
+    cu[:n] = [sl.offset for sl in seqs]
+    cu[n:] = T
+    q_start, kv_len, rows, want = lay.seg(host, 4), lay.seg(host, 5), lay.seg(host, 6), lay.seg(host, 7)
+    q_start[:n] = [sl.start for sl in seqs]
+    kv_len[:n] = [sl.start + sl.length for sl in seqs]
+    rows[:n] = [sl.row for sl in seqs]
+    q_start[n:], kv_len[n:], rows[n:] = 0, 0, 0
+    w = len(want_flat)
+    want[:w] = want_flat
+    want[w:] = np.arange(lay.T - (lay.W - w), lay.T, dtype=np.int32)   # padding rows want themselves
+    live = [sl.row for sl in seqs]
+    for g in range(lay.n_groups):
+        bt = lay.seg(host, 8 + g).reshape(lay.n, lay.n_pages)
+        bt[n:] = -1
+        bt[:n] = cache.table_rows(g, live, lay.n_pages)
 
+
+def context_from(buf: torch.Tensor, lay: Layout, seqs: List[SeqSlice], max_q_len: int, max_kv_len: int, status,
+                 want_inverse=None) -> StepContext:
+    return StepContext(
+        n_tokens=lay.T, n_seqs=lay.n, seqs=seqs, token_ids=lay.seg(buf, 0), positions=lay.seg(buf, 1),
+        token_seq=lay.seg(buf, 2), cu_q=lay.seg(buf, 3), q_start=lay.seg(buf, 4), kv_len=lay.seg(buf, 5),
+        rows=lay.seg(buf, 6), want_rows=lay.seg(buf, 7),
+        block_tables={g: lay.seg(buf, 8 + g).view(lay.n, lay.n_pages) for g in range(lay.n_groups)},
+        max_q_len=max_q_len, max_kv_len=max_kv_len, status=status, want_inverse=want_inverse, h2d_bytes=lay.total * 4)
+
+
+def slices_of(entries: Sequence[StepEntry], cache) -> List[SeqSlice]:
+    seqs, off = [], 0
+    for e in entries:
+        seqs.append(SeqSlice(e.row, cache.length(e.row), len(e.tokens), off))
+        off += len(e.tokens)
+    return seqs
+
+
+def build_context(entries: Sequence[StepEntry], cache, device, status=None) -> StepContext:
+    """Packs the description of a step into one int32 buffer, copies it to the device in
+    one transfer and returns views into it.  ``cache`` gives each row's cached length and
+    block-table rows; pages for the new tokens must have been allocated already."""
+    seqs = slices_of(entries, cache)
+    T = sum(s.length for s in seqs)
+    want_flat = [sl.offset + int(w) for e, sl in zip(entries, seqs) for w in e.want]
+    want_inverse = None
+    if len(set(want_flat)) != len(want_flat):
+        uniq, inverse = np.unique(np.asarray(want_flat, dtype=np.int64), return_inverse=True)
+        want_flat, want_inverse = [int(u) for u in uniq], inverse
+    max_kv = max((s.start + s.length for s in seqs), default=0)
+    lay = Layout.make(T, len(seqs), len(want_flat), max(1, -(-max_kv // cache.page_size)), len(cache.groups))
     dev = torch.device(device)
     if dev.type == "cuda":
-        pinned = torch.empty(total, dtype=torch.int32, pin_memory=True)
-        pinned.numpy()[:] = host
+        pinned = torch.empty(lay.total, dtype=torch.int32, pin_memory=True)
+        fill_host(pinned.numpy(), lay, entries, seqs, want_flat, cache)
         buf = pinned.to(dev, non_blocking=True)
     else:
-        buf = torch.from_numpy(host.copy()).to(dev)
-
-    def dseg(i):
-        return buf[offs[i]:offs[i] + sizes[i]]
-
-    return StepContext(
-        n_tokens=T, n_seqs=n, seqs=seqs, token_ids=dseg(0), positions=dseg(1), token_seq=dseg(2), cu_q=dseg(3),
-        q_start=dseg(4), kv_len=dseg(5), rows=dseg(6), want_rows=dseg(7),
-        block_tables={g: dseg(8 + g).view(n, n_pages) for g in range(n_groups)},
-        max_q_len=max(lens, default=0), max_kv_len=max_kv, status=status, want_inverse=want_inverse,
-        h2d_bytes=total * 4)
+        host = np.empty(lay.total, dtype=np.int32)
+        fill_host(host, lay, entries, seqs, want_flat, cache)
+        buf = torch.from_numpy(host).to(dev)
+    return context_from(buf, lay, seqs, max((s.length for s in seqs), default=0), max_kv, status, want_inverse)

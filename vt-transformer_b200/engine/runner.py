@@ -53,6 +53,10 @@ class ModelRunner:
         self.status = torch.zeros(2, dtype=torch.int32, device=rt.device)
         self.steps = 0
         self.last_h2d_bytes = 0
+        # single-token steps are replayed as CUDA graphs where every part allows it
+        self.use_graphs = rt.device.type == "cuda" and model.graph_safe()
+        self.max_graph_batch = 256
+        self._graphs = {}
 
     # ---- construction --------------------------------------------------------------------
     @classmethod
@@ -119,14 +123,34 @@ class ModelRunner:
                 if not 0 <= w < len(e.tokens):
                     raise ValueError(f"row {e.row}: wanted place {w} is outside its {len(e.tokens)} tokens")
         self.cache.extend([(e.row, self.cache.length(e.row) + len(e.tokens)) for e in entries])
-        ctx = build_context(entries, self.cache, self.rt.device, status=self.status)
-        self.last_h2d_bytes = ctx.h2d_bytes
-        logits = self.model.forward(ctx, self.cache.views(ctx.block_tables))
+        if self.use_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries):
+            logits = self._graph_step(entries)
+        else:
+            ctx = build_context(entries, self.cache, self.rt.device, status=self.status)
+            self.last_h2d_bytes = ctx.h2d_bytes
+            logits = self.model.forward(ctx, self.cache.views(ctx.block_tables))
+            if ctx.want_inverse is not None:
+                logits = logits[torch.as_tensor(ctx.want_inverse, device=logits.device)]
         for e in entries:
             self.cache.commit(e.row, self.cache.length(e.row) + len(e.tokens))
         self.steps += 1
-        if ctx.want_inverse is not None:
-            logits = logits[torch.as_tensor(ctx.want_inverse, device=logits.device)]
+        return logits
+
+    def _graph_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """A step of single tokens through a captured graph.  The logits lie in the graph's own
+        buffer: they are valid until the next step."""
+        from .graphs import DecodeGraph, batch_bucket, context_bucket
+        max_kv = max(self.cache.length(e.row) for e in entries) + 1
+        key = (batch_bucket(len(entries)), context_bucket(max_kv))
+        graph = self._graphs.get(key)
+        if graph is None:
+            graph = DecodeGraph(self, *key)
+            self._graphs[key] = graph
+        logits = graph.run(entries)
+        self.last_h2d_bytes = graph.layout.total * 4
+        wanted = [i for i, e in enumerate(entries) if len(e.want) > 0]
+        if len(wanted) != len(entries):
+            logits = logits[torch.as_tensor(wanted, dtype=torch.long, device=logits.device)]
         return logits
 
     def check_status(self) -> None:

@@ -55,6 +55,10 @@ class DecoderModel:
     def cache_slots(self) -> Dict[int, object]:
         return dict(self._slots)
 
+    def graph_safe(self) -> bool:
+        """True if a step of this model may be captured as a CUDA graph and replayed."""
+        return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+
     def param_specs(self) -> Dict[str, ParamSpec]:
         s = self.spec
         out = {s.embed_name: ParamSpec((s.vocab, s.hidden))}

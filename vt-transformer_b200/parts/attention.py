@@ -17,6 +17,8 @@ class PagedAttention(Mixer):
     softmax(q k^T / sqrt(d)) v over the keys the token may see (:307-318); then the o
     projection (:322).  All sizes come from the spec."""
 
+    graph_safe = True
+
     def __init__(self, spec, prefix, rt):
         super().__init__(spec, prefix, rt)
         self.position = build_part("position", spec.position, prefix, rt)

@@ -104,6 +104,10 @@ class CacheView:
 
 class Part:
     category = ""
+    # True if ``forward`` only enqueues kernels that read the step's description from device
+    # memory, so that a captured CUDA graph of it can be replayed for another step.  A part that
+    # loops over ``ctx.seqs`` on the host, or allocates by the step's contents, must leave it False.
+    graph_safe = False
 
     def __init__(self, spec, prefix: str, rt: Runtime):
         self.spec = spec

@@ -21,6 +21,10 @@ class PreNormBlock(Block):
     def cache_spec(self):
         return self.mixer.cache_spec()
 
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts)
+
     def param_specs(self):
         out = {}
         for p in self.parts:

@@ -13,6 +13,8 @@ class GatedMLP(FeedForward):
     v1/tensortype/cuda_kernels/silu_product.cu:15-17).  Gate and up are one product over
     the packed rows of the two matrices."""
 
+    graph_safe = True
+
     def __init__(self, spec, prefix, rt):
         super().__init__(spec, prefix, rt)
         if spec.activation != "silu":

@@ -13,6 +13,8 @@ class RMSNorm(Norm):
     (v1/tensortype/cuda_kernels/rmsnorm.cu:20-47).  ``prefix`` is the tensor's name
     without ".weight"."""
 
+    graph_safe = True
+
     def param_specs(self):
         return {self.prefix + ".weight": ParamSpec((self.spec.size,), role="vector", init="one_plus_normal")}
 
