@@ -101,6 +101,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has (recorded in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the prefill")
+    ap.add_argument("--skip-e2e", action="store_true", help="leave out the run through the Python entry point")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -206,6 +207,10 @@ def main() -> int:
         prefill = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
                    "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(flops / ms / 1e9, 1)}
 
+    if args.skip_e2e:
+        print(json.dumps({"value": round(main_run["tok_s"], 1), "ms_per_step": round(main_run["ms_per_step"], 4),
+                          "points": points, "prefill": prefill, "note": "partial run (--skip-e2e): not a bench line"}))
+        return 0
     # end to end: the Python entry point, token ids in from the host and out to the host every step
     llm = LLM(None, runner=runner, max_extend_tokens=2048)
     params = SamplingParams(temperature=0.0, max_tokens=new_tokens, ignore_eos=True)

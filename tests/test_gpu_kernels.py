@@ -221,18 +221,37 @@ def test_weight_streaming_product(m, n, k):
     close(out, ref - bias.cpu().double(), torch.float32, 40)
 
 
-@pytest.mark.parametrize("m", [65, 200, 1000])
-def test_large_batch_product(m):
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 33, 64, 65, 128, 129, 300, 1000])
+@pytest.mark.parametrize("n,k", [(40, 64), (301, 72), (344, 136), (1000, 344), (4608, 3584), (520, 18944)])
+def test_tcgen05_product(m, n, k):
+    """The tcgen05 kernel alone, in both orientations (w as the 128-row operand for up to 64 rows of x,
+    x beyond), with tiles that hang over every edge, k that is no multiple of 64, and k cut over a cluster."""
     torch.manual_seed(11)
-    n, k = 344, 136
     x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
     w = (torch.randn(n, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
     bias = torch.randn(n, device=DEV)
     ref = plain.linear(x.cpu().double(), w.cpu().double(), bias.cpu().double())
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
     for out_dtype in (torch.bfloat16, torch.float32):
-        out = torch.empty(m, n, device=DEV, dtype=out_dtype)
-        ops().linear(x, w, bias, out)
-        close(out, ref, out_dtype, 3 if out_dtype == torch.bfloat16 else 40)
+        out = torch.full((m, n), float("nan"), device=DEV, dtype=out_dtype)
+        ops().backend().gemm_tc(x, w, bias, out, status)
+        close(out, ref, out_dtype, 2 if out_dtype == torch.bfloat16 else 40)
+    out = torch.full((m, n), float("nan"), device=DEV, dtype=torch.float32)
+    ops().backend().gemm_tc(x, w, None, out, status)
+    close(out, ref - bias.cpu().double(), torch.float32, 40)
+    assert status.tolist() == [0, 0]
+
+
+def test_tcgen05_product_takes_each_element_once():
+    """x and w of small integers: every product and sum is exact in bfloat16 and float, so a tile read
+    from the wrong place, a k-block counted twice or dropped, shows as a wrong integer."""
+    torch.manual_seed(12)
+    for m, n, k in ((200, 300, 1096), (40, 700, 2056)):
+        x = torch.randint(-3, 4, (m, k), device=DEV).to(torch.bfloat16)
+        w = torch.randint(-3, 4, (n, k), device=DEV).to(torch.bfloat16)
+        out = torch.empty(m, n, device=DEV, dtype=torch.float32)
+        ops().backend().gemm_tc(x, w, None, out, None)
+        assert torch.equal(out.cpu().double(), x.cpu().double() @ w.cpu().double().t())
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -174,6 +174,26 @@ void gemm_skinny(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, T
                                          stream_of(x)), "gemm_skinny");
 }
 
+void gemm_tc(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tensor& out, c10::optional<Tensor> status) {
+    check_cuda(x, "x"); check_cuda(w, "w"); check_cuda(out, "out");
+    TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16, "gemm_tc: x and w must be bfloat16");
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm_tc: 2-d tensors");
+    const int m = x.size(0), k = x.size(1), n = w.size(0);
+    TORCH_CHECK(w.size(1) == k && out.size(0) == m && out.size(1) == n, "gemm_tc: shapes [m,k] x [n,k] -> [m,n]");
+    TORCH_CHECK(k % 8 == 0, "gemm_tc: inner size ", k, " must be a multiple of 8 (TMA rows start on 16-byte boundaries)");
+    TORCH_CHECK(((uintptr_t)x.data_ptr() & 15) == 0 && ((uintptr_t)w.data_ptr() & 15) == 0,
+                "gemm_tc: x and w must start on 16-byte boundaries");
+    const float* bp = nullptr;
+    if (bias.has_value()) {
+        check_f32(*bias, "bias");
+        TORCH_CHECK(bias->numel() == n, "gemm_tc: bias must have one entry for each output column");
+        bp = bias->data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    check_launch(vtb::launch_gemm_tc(dtype_code(out, "out"), x.data_ptr(), w.data_ptr(), bp, out.data_ptr(), m, n, k,
+                                     status_ptr(status), stream_of(x)), "gemm_tc");
+}
+
 bool attention_mma_supports(int64_t head_dim, int64_t heads, int64_t kv_heads, int64_t warps) {
     return vtb::attention_mma_supports(head_dim, heads, kv_heads, warps);
 }
@@ -286,6 +306,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("positions"), py::arg("token_seq"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),
           py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("status") = py::none());
     m.def("gemm_skinny", &gemm_skinny, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"));
+    m.def("gemm_tc", &gemm_tc, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"), py::arg("status") = py::none());
     m.def("attention_mma_supports", &attention_mma_supports);
     m.def("attention_mma", &attention_mma, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
           py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("tiles"), py::arg("heads"),

@@ -27,6 +27,7 @@ SOURCES = [
     "attention_simt.cu",
     "attention_mma.cu",
     "gemm_skinny.cu",
+    "gemm_tc.cu",
     "sampling.cu",
 ]
 HEADERS = ["common.cuh", "kernels.h"]

@@ -9,8 +9,18 @@
 // memory, and their partial sums meet in shared memory.  Which k of a block goes to which slot
 // of the operand does not matter for a dot product, as long as w and x agree: a thread's 8
 // consecutive elements serve two MMAs, and x is loaded the same way.
+//
+// A matrix with few rows (the o and down projections: 224 tiles of 16 rows for 148 SMs) would
+// leave most of the machine without loads in flight, so its k range is cut over the CTAs of a
+// thread-block cluster (up to 8); each CTA sums its share, and the shares are added in rank
+// order through distributed shared memory: no scratch in global memory, no atomics, the same
+// sum whatever the timing.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "kernels.h"
+
+namespace cg = cooperative_groups;
 
 namespace vtb {
 
@@ -40,8 +50,11 @@ __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    const float* __restrict__ bias, TOut* __restrict__ out, int m, int n, int k) {
     __shared__ float red[WARPS][NT][16][8 + 1];
+    __shared__ float tile[NT * 128];
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned rank = cluster.block_rank(), csize = cluster.num_blocks();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * 16;
+    const int n0 = blockIdx.y * 16;
     const int r0 = n0 + g, r1 = n0 + g + 8;
     const bool ok0 = r0 < n, ok1 = r1 < n;
     const __nv_bfloat16* w0 = w + (size_t)(ok0 ? r0 : 0) * k + 8 * t;
@@ -57,21 +70,25 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 #pragma unroll
     for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 
-    const int nkb = (k + 31) / 32;
+    const int nkb_all = (k + 31) / 32;
+    const int per_cta = (nkb_all + (int)csize - 1) / (int)csize;
+    const int kb_begin = (int)rank * per_cta;
+    const int nkb = min(nkb_all, kb_begin + per_cta);
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    for (int kb = warp; kb < nkb; kb += WARPS * UNROLL) {
+    for (int kb = kb_begin + warp; kb < nkb; kb += WARPS * UNROLL) {
         uint4 a[UNROLL], b[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int kk = (kb + u * WARPS) * 32;
-            const bool in = kk + 8 * t + 8 <= k;      // k % 8 == 0: a thread's piece lies inside or outside as a whole
+            // k % 8 == 0: a thread's piece lies inside or outside as a whole
+            const bool in = (kb + u * WARPS) < nkb && kk + 8 * t + 8 <= k;
             a[u] = (in && ok0) ? load_stream(reinterpret_cast<const uint4*>(w0 + kk)) : zero;
             b[u] = (in && ok1) ? load_stream(reinterpret_cast<const uint4*>(w1 + kk)) : zero;
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int kk = (kb + u * WARPS) * 32;
-            const bool in = kk + 8 * t + 8 <= k;
+            const bool in = (kb + u * WARPS) < nkb && kk + 8 * t + 8 <= k;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const uint4 xv = (in && xok[j]) ? __ldg(reinterpret_cast<const uint4*>(xr[j] + kk)) : zero;
@@ -89,28 +106,59 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         red[warp][j][g + 8][2 * t + 1] = acc[j][3];
     }
     __syncthreads();
+    // this CTA's share of every output of the tile: e = (j, x column, w row)
     for (int e = threadIdx.x; e < NT * 128; e += WARPS * 32) {
+        const int row = e & 15, col = (e >> 4) & 7, j = e >> 7;
+        float s = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < WARPS; ++wv) s += red[wv][j][row][col];
+        tile[e] = s;
+    }
+    cluster.sync();
+    // the CTAs of the cluster share out the outputs; each adds the shares in rank order
+    for (int e = (int)rank * (WARPS * 32) + threadIdx.x; e < NT * 128; e += (int)csize * WARPS * 32) {
         const int row = e & 15, col = (e >> 4) & 7, j = e >> 7;
         const int mm = j * 8 + col, nn = n0 + row;
         if (mm >= m || nn >= n) continue;
         float s = 0.f;
-#pragma unroll
-        for (int wv = 0; wv < WARPS; ++wv) s += red[wv][j][row][col];
+        for (unsigned r = 0; r < csize; ++r) s += cluster.map_shared_rank(tile, r)[e];
         if (bias) s += bias[nn];
         out[(size_t)mm * n + nn] = from_float<TOut>(s);
     }
+    cluster.sync();   // nobody leaves while its shared memory is still being read
+}
+
+template <int NT, typename TOut>
+cudaError_t launch_nt(const __nv_bfloat16* x, const __nv_bfloat16* w, const float* bias, TOut* out, int m, int n, int k,
+                      int ksplit, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ksplit, (n + 15) / 16, 1);
+    cfg.blockDim = dim3(WARPS * 32, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ksplit;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NT, TOut>, x, w, bias, out, m, n, k);
 }
 
 template <typename TOut>
 cudaError_t launch_t(const __nv_bfloat16* x, const __nv_bfloat16* w, const float* bias, TOut* out, int m, int n, int k,
                      cudaStream_t stream) {
-    const int grid = (n + 15) / 16;
-    if (m <= 8) gemm_skinny_kernel<1, TOut><<<grid, WARPS * 32, 0, stream>>>(x, w, bias, out, m, n, k);
-    else if (m <= 16) gemm_skinny_kernel<2, TOut><<<grid, WARPS * 32, 0, stream>>>(x, w, bias, out, m, n, k);
-    else if (m <= 32) gemm_skinny_kernel<4, TOut><<<grid, WARPS * 32, 0, stream>>>(x, w, bias, out, m, n, k);
-    else if (m <= 64) gemm_skinny_kernel<8, TOut><<<grid, WARPS * 32, 0, stream>>>(x, w, bias, out, m, n, k);
-    else return cudaErrorInvalidValue;
-    return cudaGetLastError();
+    // enough CTAs to keep loads in flight on all 148 SMs: cut k over a cluster when the rows are few,
+    // but leave every warp at least one unrolled round of k-blocks
+    const int tiles = (n + 15) / 16, nkb = (k + 31) / 32;
+    int ksplit = 1;
+    while (ksplit < 8 && tiles * ksplit < 1184 && nkb / (ksplit * 2) >= WARPS * UNROLL / 2) ksplit *= 2;
+    if (m <= 8) return launch_nt<1, TOut>(x, w, bias, out, m, n, k, ksplit, stream);
+    if (m <= 16) return launch_nt<2, TOut>(x, w, bias, out, m, n, k, ksplit, stream);
+    if (m <= 32) return launch_nt<4, TOut>(x, w, bias, out, m, n, k, ksplit, stream);
+    if (m <= 64) return launch_nt<8, TOut>(x, w, bias, out, m, n, k, ksplit, stream);
+    return cudaErrorInvalidValue;
 }
 
 }  // namespace

@@ -1,0 +1,368 @@
+// out = x w^T (+ bias) on the 5th-generation tensor cores: TMA -> shared memory -> tcgen05.mma ->
+// tensor memory -> registers -> global memory.  bfloat16 operands, 32-bit accumulation, one
+// rounding at the end (the bias is added in 32-bit before it).
+//
+// vt-transformer calls cuBLASLt for these products and adds the bias in a second pass that rounds
+// again (v1/tensortype/cuda_kernels/lt_sgemm.cu:55-126, v1/tensortype/cuda_tensor.cpp:544-563).
+// Here both x [M, K] and w [N, K] are K-major, so either can be the 128-row operand of the MMA:
+//   * many rows of x (prompt portions): a tile is 128 rows of x by BN rows of w, D[token, feature];
+//   * few rows of x (decode): "swapped": a tile is 128 rows of w by all rows of x (BN = 16..64),
+//     D[feature, token], so a weight is read once and the small batch rides along.  The k range of a
+//     matrix with few tiles is cut over a thread-block cluster and the shares are added in rank
+//     order through distributed shared memory.
+//
+// One CTA computes one tile.  Warp 0 issues the TMA loads (one elected thread), warp 1 owns the
+// tensor memory and issues the MMAs (one elected thread), warps 2..5 read the accumulator back
+// (tcgen05.ld, each warp its quarter of the 128 lanes) and store.  A ring of STAGES stages of 64 k
+// (128-byte rows, 128-byte swizzle) lies between them, with a full and an empty mbarrier a stage.
+// TMA fills what lies outside a matrix with zeros, so any M, N and K (K % 8 == 0) is taken.
+// Every wait on a barrier is bounded by a clock limit; a wait that runs out records it in the status
+// word and the CTA winds down: tensor memory is freed and the kernel returns.
+#include <cooperative_groups.h>
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace cg = cooperative_groups;
+
+namespace vtb {
+
+namespace {
+
+constexpr int BM = 128;                  // rows of the 128-lane operand in a tile
+constexpr int BK = 64;                   // k in a stage: 64 bfloat16 = one 128-byte swizzled row
+constexpr int A_STAGE = BM * BK * 2;     // 16 KB
+constexpr int THREADS = 192;
+constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Waits for the phase with the given parity; false if the clock limit ran out first.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if (clock64() - t0 > WAIT_CYCLES) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(
+            smem_u32(smem)),
+        "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// Shared-memory descriptor of a K-major operand tile with 128-byte rows and 128-byte swizzle:
+// start address, leading byte offset 1 (unused with a swizzle), stride byte offset 1024 (eight rows),
+// descriptor version 1, layout type 2 (SWIZZLE_128B); addresses and offsets without their 4 low bits.
+__device__ __forceinline__ uint64_t smem_desc(const void* tile) {
+    uint64_t d = (uint64_t)((smem_u32(tile) >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor: D float (1 at bit 4), A and B bfloat16 (1 at bits 7 and 10), both K-major,
+// N / 8 at bit 17, M / 16 at bit 24.
+__device__ __forceinline__ uint32_t instr_desc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <typename T> __device__ __forceinline__ void store8(T* p, const float* v);
+template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float* v) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+template <> __device__ __forceinline__ void store8<float>(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+// BN: rows of the other operand in a tile (columns of the accumulator).  SWAP: the 128-row operand is w.
+template <int BN, int STAGES, bool SWAP, typename TOut>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo, int* status) {
+    constexpr int B_STAGE = BN * BK * 2;
+    constexpr int COLS = BN < 32 ? 32 : BN;          // tensor-memory columns: a power of two, at least 32
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* a_s = smem;
+    unsigned char* b_s = smem + STAGES * A_STAGE;
+    uint64_t* full = reinterpret_cast<uint64_t*>(b_s + STAGES * B_STAGE);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_done = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int ksplit = (int)cluster.num_blocks(), krank = (int)cluster.block_rank();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // consecutive CTAs take consecutive tiles of the 128-row operand and share the other operand's tile:
+    // for prompt portions the weights' tile is fetched from HBM once and then found in L2
+    const int a_row0 = blockIdx.x * BM, b_row0 = blockIdx.y * BN;
+    const int nkb_all = (k + BK - 1) / BK;
+    const int per = (nkb_all + ksplit - 1) / ksplit;
+    const int kb0 = krank * per, kb1 = min(nkb_all, kb0 + per);
+    const int nkb = max(0, kb1 - kb0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    bool timed_out = false;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int it = 0; it < nkb; ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) { timed_out = true; break; }
+                mbar_expect_tx(&full[s], A_STAGE + B_STAGE);
+                tma_load_2d(a_s + s * A_STAGE, &map_a, (kb0 + it) * BK, a_row0, &full[s]);
+                tma_load_2d(b_s + s * B_STAGE, &map_b, (kb0 + it) * BK, b_row0, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(BM, BN);
+            for (int it = 0; it < nkb; ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(&full[s], (it / STAGES) & 1)) { timed_out = true; break; }
+                tc_fence_after();
+                const uint64_t ad = smem_desc(a_s + s * A_STAGE), bd = smem_desc(b_s + s * B_STAGE);
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; ++kk)   // 16 k = 32 bytes further along the swizzled row
+                    tc_mma(tmem, ad + 2 * kk, bd + 2 * kk, idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                tc_commit(&empty[s]);                  // the stage is free when these MMAs have read it
+            }
+            tc_commit(acc_done);                       // the accumulator is whole when all MMAs are done
+        }
+    }
+    __syncwarp();
+
+    // ---- epilogue: warps 2..5, each its quarter of the lanes --------------------------------------
+    float* share = reinterpret_cast<float*>(smem);     // [BN][128] floats, over the stages, when k is split
+    if (warp >= 2) {
+        const int q = warp & 3;
+        const int r = q * 32 + lane;                   // lane of the accumulator = row of the 128-row operand
+        bool ok = true;
+        if (nkb > 0) ok = mbar_wait(acc_done, 0);
+        if (!ok) timed_out = true;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+            float v[16];
+            if (nkb > 0 && ok) {
+                uint32_t raw[16];
+                tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, raw);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(raw[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = 0.f;
+            }
+            if (ksplit > 1) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) share[(c0 + i) * BM + r] = v[i];
+                continue;
+            }
+            if (SWAP) {
+                const int n = a_row0 + r;              // feature
+                if (n < rows_a) {
+                    const float b = bias ? bias[n] : 0.f;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int m = b_row0 + c0 + i; // token
+                        if (m < rows_b) out[(size_t)m * ldo + n] = from_float<TOut>(v[i] + b);
+                    }
+                }
+            } else {
+                const int m = a_row0 + r;              // token
+                if (m < rows_a) {
+                    const int n0 = b_row0 + c0;        // feature of v[0]
+                    TOut* o = out + (size_t)m * ldo + n0;
+                    if (bias) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] += (n0 + i < rows_b) ? bias[n0 + i] : 0.f;
+                    }
+                    if ((ldo & 7) == 0 && n0 + 16 <= rows_b) {
+                        store8<TOut>(o, v);
+                        store8<TOut>(o + 8, v + 8);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (n0 + i < rows_b) o[i] = from_float<TOut>(v[i]);
+                    }
+                }
+            }
+        }
+    }
+    if (ksplit > 1) {
+        // all MMAs of this CTA are done (acc_done), so the stages may be overwritten by the shares
+        cluster.sync();
+        if (warp >= 2 && SWAP) {
+            const int r = (warp & 3) * 32 + lane;
+            const int n = a_row0 + r;
+            for (int c = krank; c < BN; c += ksplit) {
+                const int m = b_row0 + c;
+                if (m >= rows_b || n >= rows_a) continue;
+                float s = 0.f;
+                for (int rk = 0; rk < ksplit; ++rk) s += cluster.map_shared_rank(share, rk)[c * BM + r];
+                if (bias) s += bias[n];
+                out[(size_t)m * ldo + n] = from_float<TOut>(s);
+            }
+        }
+        cluster.sync();
+    }
+    if (timed_out && status) set_status(status, kStatusWaitTimeout, blockIdx.x + blockIdx.y * gridDim.x);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(COLS));
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encoder() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(p);
+    }
+    return fn;
+}
+
+// A [rows, k] bfloat16 row-major matrix seen in boxes of box_rows rows by 64 k, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int k, int box_rows) {
+    EncodeTiled enc = encoder();
+    if (enc == nullptr) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, bool SWAP, typename TOut>
+cudaError_t launch_cfg(const void* a, int rows_a, const void* b, int rows_b, int k, const float* bias, TOut* out, int ldo,
+                       int ksplit, int* status, cudaStream_t stream) {
+    CUtensorMap map_a, map_b;
+    if (!make_map(&map_a, a, rows_a, k, BM) || !make_map(&map_b, b, rows_b, k, BN)) return cudaErrorInvalidValue;
+    constexpr int smem = STAGES * (A_STAGE + BN * BK * 2) + 1024 + 256;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((rows_a + BM - 1) / BM, (rows_b + BN - 1) / BN, ksplit);
+    cfg.blockDim = dim3(THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = ksplit;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, SWAP, TOut>, map_a, map_b, bias, out, rows_a, rows_b, k, ldo, status);
+}
+
+template <typename TOut>
+cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* out, int m, int n, int k, int* status,
+                         cudaStream_t stream) {
+    if (m <= 64) {
+        // swapped: w is the 128-row operand; cut k over a cluster while the tiles are fewer than the SMs
+        const int tiles = (n + BM - 1) / BM, nkb = (k + BK - 1) / BK;
+        int ksplit = 1;
+        while (ksplit < 8 && tiles * ksplit < 148 && nkb / (ksplit * 2) >= 4) ksplit *= 2;
+        if (m <= 16) return launch_cfg<16, 8, true, TOut>(w, n, x, m, k, bias, out, n, ksplit, status, stream);
+        if (m <= 32) return launch_cfg<32, 8, true, TOut>(w, n, x, m, k, bias, out, n, ksplit, status, stream);
+        return launch_cfg<64, 6, true, TOut>(w, n, x, m, k, bias, out, n, ksplit, status, stream);
+    }
+    if (n <= 128 || m <= 128) return launch_cfg<128, 4, false, TOut>(x, m, w, n, k, bias, out, n, 1, status, stream);
+    return launch_cfg<256, 4, false, TOut>(x, m, w, n, k, bias, out, n, 1, status, stream);
+}
+
+}  // namespace
+
+cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n, int k,
+                           int* status, cudaStream_t stream) {
+    if (m == 0 || n == 0) return cudaSuccess;
+    if (k % 8 != 0 || k < 8) return cudaErrorInvalidValue;
+    if (out_dtype == kBF16) return launch_typed<__nv_bfloat16>(x, w, bias, (__nv_bfloat16*)out, m, n, k, status, stream);
+    if (out_dtype == kF32) return launch_typed<float>(x, w, bias, (float*)out, m, n, k, status, stream);
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace vtb

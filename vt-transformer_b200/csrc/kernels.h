@@ -51,6 +51,12 @@ cudaError_t launch_attention_simt(int dtype, const void* qkv, int qkv_stride, vo
 cudaError_t launch_gemm_skinny(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n,
                                int k, cudaStream_t stream);
 
+// out[M, N] = x[M, K] w[N, K]^T (+ bias) with tcgen05.mma fed by TMA, accumulators in tensor memory.
+// bfloat16 x and w, out bfloat16 or float, any M and N, k % 8 == 0.  status receives kStatusWaitTimeout
+// if a bounded wait inside the kernel runs out.
+cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n, int k,
+                           int* status, cudaStream_t stream);
+
 // Tensor-core attention over the paged cache (bfloat16).  A tile is 16 * warps rows, row r being
 // (token r / group, head r % group); `tiles` lists (sequence, first token) pairs, or is null when
 // every sequence is one tile (single-token steps).  warps is 1 or 4.  With n_splits > 1 the keys of a

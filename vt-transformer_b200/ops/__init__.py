@@ -65,12 +65,13 @@ def rope_store(qkv, positions, cos_sin, k_cache, v_cache, token_seq, block_table
 # --------------------------------------------------------------------------- matrix products
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, status=None) -> torch.Tensor:
     """out[T, N] = x[T, K] w[N, K]^T (+ bias).  ``out`` is float32 or the dtype of x.
 
     float32 x and w: the 32-bit kernel (FFMA in a fixed order, no TF32).  A weight kept in
     32-bit beside bfloat16 activations goes the same way, with x widened.  bfloat16: the
-    weight-streaming kernel for small batches, the tensor-core product for large ones.
+    weight-streaming kernel for up to 64 rows of x, the tcgen05 kernel (TMA, tensor memory)
+    beyond.
     """
     be = backend()
     if w.dtype == torch.float32:
@@ -85,22 +86,18 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise TypeError(f"linear: unsupported dtypes x {x.dtype}, w {w.dtype}")
     m = x.shape[0]
-    if m <= SKINNY_MAX_ROWS:
+    if m <= SKINNY_MAX_ROWS and SMALL_BATCH_KERNEL == "skinny":
         be.gemm_skinny(x, w, bias, out)
-    elif out.dtype == torch.bfloat16 and m >= LIBRARY_MIN_ROWS:
-        # the library product, as in vt-transformer (cuBLASLt with 32-bit accumulation, then the bias,
-        # v1/tensortype/cuda_tensor.cpp:544-563)
-        torch.matmul(x, w.t(), out=out)
-        if bias is not None:
-            out.add_(bias.to(out.dtype))
     else:
-        for a in range(0, m, SKINNY_MAX_ROWS):
-            be.gemm_skinny(x[a:a + SKINNY_MAX_ROWS], w, bias, out[a:a + SKINNY_MAX_ROWS])
+        be.gemm_tc(x, w, bias, out, status)
     return out
 
 
-SKINNY_MAX_ROWS = 64        # rows of x up to which the weight-streaming kernel runs
-LIBRARY_MIN_ROWS = 65       # rows of x from which the tensor-core product for large batches runs
+SKINNY_MAX_ROWS = 64            # rows of x up to which the small-batch kernel may run
+# "skinny": mma.sync weight streaming; "tc": the tcgen05 kernel with w as the 128-row operand.
+# The environment variable VTB200_SMALL_BATCH_KERNEL overrides it (for measurements).
+import os as _os
+SMALL_BATCH_KERNEL = _os.environ.get("VTB200_SMALL_BATCH_KERNEL", "skinny")
 ATTENTION_KERNEL = "auto"   # "auto", or "simt" to force the plain kernel (tests compare the two)
 
 
