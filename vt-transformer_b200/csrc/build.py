@@ -28,9 +28,10 @@ SOURCES = [
     "attention_mma.cu",
     "gemm_skinny.cu",
     "gemm_tc.cu",
+    "attention_noalloc.cu",
     "sampling.cu",
 ]
-HEADERS = ["common.cuh", "kernels.h"]
+HEADERS = ["common.cuh", "kernels.h", "attention_noalloc.h"]
 
 CUDA_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
