@@ -143,4 +143,13 @@ def _compile(name: str, verbose: bool) -> str:
     if not os.path.isfile(path):
         raise RuntimeError(f"the build finished but {path} is missing")
     print(f"[vt_transformer_b200] compiled in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+    _remove_stale(os.path.dirname(build_dir), name)
     return path
+
+
+def _remove_stale(root: str, keep: str) -> None:
+    """Deletes the builds of earlier sources beside the one just made."""
+    import shutil
+    for entry in os.listdir(root):
+        if entry.startswith("vtb200_ext_") and entry != keep:
+            shutil.rmtree(os.path.join(root, entry), ignore_errors=True)

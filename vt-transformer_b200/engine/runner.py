@@ -66,6 +66,9 @@ class ModelRunner:
         """``source_factory(param_table)`` returns the ``WeightSource``.  The pool holds
         ``num_pages`` pages in each group, or enough for ``max_tokens`` tokens."""
         dt = parse_dtype(dtype)
+        if torch.device(device).type == "cuda" and not torch.cuda.is_available():
+            raise RuntimeError("vt_transformer_b200 runs on a CUDA device (B200, sm_100a) only; "
+                               "torch.cuda.is_available() is False and there is no CPU path")
         rt = Runtime(device=torch.device(device), dtype=dt, ops=ops if ops is not None else _ops)
         spec = get_architecture(config.architecture).model_spec(config)
         model = DecoderModel(spec, rt)
