@@ -102,6 +102,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the prefill")
     ap.add_argument("--skip-e2e", action="store_true", help="leave out the run through the Python entry point")
+    ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prefill only (for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -175,18 +176,22 @@ def main() -> int:
         return dict(tok_s=batch * steps / (ms / 1e3), ms_per_step=ms / steps, launches=launched, ctx_mean=ctx_mean,
                     clocks=info)
 
-    main_run = decode_run(args.batch, args.steps, warmup, ClockSampler())
+    if args.only_prefill:
+        main_run = dict(tok_s=0.0, ms_per_step=1.0, launches=0, ctx_mean=0.0, clocks=None)
+        args.skip_e2e = True
+    else:
+        main_run = decode_run(args.batch, args.steps, warmup, ClockSampler())
     kv_bytes = runner.cache.bytes_per_token() * main_run["ctx_mean"] * args.batch
     step_bytes = runner.weight_bytes(args.batch) + kv_bytes
     achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
 
     points, prefill = {}, None
     if not args.skip_points:
-        for b in (1, 64):
+        for b in (() if args.only_prefill else (1, 64)):
             points[f"decode_b{b}"] = round(decode_run(b, min(args.steps, 64), 5)["tok_s"], 1)
         # prefill of 2,048 tokens: one request, one step, logits of the last token
         times = []
-        for i in range(3 + 5):
+        for i in range((1 + 1) if args.only_prefill else (3 + 5)):
             row = runner.admit()
             toks = random_tokens(PREFILL_TOKENS)
             torch.cuda.synchronize()
@@ -195,7 +200,7 @@ def main() -> int:
             runner.step([StepEntry(row, toks, [PREFILL_TOKENS - 1])])
             e.record()
             torch.cuda.synchronize()
-            if i >= 3:
+            if i >= (1 if args.only_prefill else 3):
                 times.append(s.elapsed_time(e))
             runner.release(row)
         runner.check_status()

@@ -222,7 +222,7 @@ def test_weight_streaming_product(m, n, k):
 
 
 @pytest.mark.parametrize("m", [1, 8, 16, 17, 33, 64, 65, 128, 129, 300, 1000])
-@pytest.mark.parametrize("n,k", [(40, 64), (301, 72), (344, 136), (1000, 344), (4608, 3584), (520, 18944)])
+@pytest.mark.parametrize("n,k", [(40, 64), (301, 72), (344, 136), (1000, 344), (4608, 3584), (520, 18944), (3584, 3584)])
 def test_tcgen05_product(m, n, k):
     """The tcgen05 kernel alone, in both orientations (w as the 128-row operand for up to 64 rows of x,
     x beyond), with tiles that hang over every edge, k that is no multiple of 64, and k cut over a cluster."""
@@ -232,14 +232,19 @@ def test_tcgen05_product(m, n, k):
     bias = torch.randn(n, device=DEV)
     ref = plain.linear(x.cpu().double(), w.cpu().double(), bias.cpu().double())
     status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    scratch, counters = ops()._split_workspace(torch.device(DEV))
     for out_dtype in (torch.bfloat16, torch.float32):
         out = torch.full((m, n), float("nan"), device=DEV, dtype=out_dtype)
-        ops().backend().gemm_tc(x, w, bias, out, status)
+        ops().backend().gemm_tc(x, w, bias, out, status)                       # k in one piece
         close(out, ref, out_dtype, 2 if out_dtype == torch.bfloat16 else 40)
+        for _ in range(2):                                                     # k cut over CTAs where that pays; twice:
+            out.fill_(float("nan"))                                            # the counters must be back at zero
+            ops().backend().gemm_tc(x, w, bias, out, status, scratch, counters)
+            close(out, ref, out_dtype, 2 if out_dtype == torch.bfloat16 else 40)
     out = torch.full((m, n), float("nan"), device=DEV, dtype=torch.float32)
-    ops().backend().gemm_tc(x, w, None, out, status)
+    ops().backend().gemm_tc(x, w, None, out, status, scratch, counters)
     close(out, ref - bias.cpu().double(), torch.float32, 40)
-    assert status.tolist() == [0, 0]
+    assert status.tolist() == [0, 0] and int(counters.abs().sum()) == 0
 
 
 def test_tcgen05_product_takes_each_element_once():
@@ -250,7 +255,7 @@ def test_tcgen05_product_takes_each_element_once():
         x = torch.randint(-3, 4, (m, k), device=DEV).to(torch.bfloat16)
         w = torch.randint(-3, 4, (n, k), device=DEV).to(torch.bfloat16)
         out = torch.empty(m, n, device=DEV, dtype=torch.float32)
-        ops().backend().gemm_tc(x, w, None, out, None)
+        ops().backend().gemm_tc(x, w, None, out, None, *ops()._split_workspace(torch.device(DEV)))
         assert torch.equal(out.cpu().double(), x.cpu().double() @ w.cpu().double().t())
 
 

@@ -15,6 +15,7 @@
 // (page_size % 16 == 0).  S = Q K^T and O += P V are mma.sync m16n8k16 (P rounded to bfloat16).
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace vtb {
 
@@ -79,6 +80,8 @@ attention_mma_kernel(const AttnParams p) {
     __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [2][KB][LD]
     __nv_bfloat16* vs = ks + 2 * KB * LD;                             // [2][KB][LD]
 
+    pdl_launch();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
     const int kvh = blockIdx.y, split = blockIdx.z;
     int seq, tok0;
@@ -288,6 +291,8 @@ template <int D>
 __global__ void __launch_bounds__(128)
 attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                          __nv_bfloat16* __restrict__ out, int n_tokens, int heads, int n_splits) {
+    pdl_launch();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const long long pair = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (pair >= (long long)n_tokens * heads) return;
@@ -330,14 +335,12 @@ cudaError_t launch_one(const AttnParams& p, int n_tiles, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(n_tiles, p.kv_heads, p.n_splits);
-    attention_mma_kernel<D, WARPS><<<grid, WARPS * 32, smem, stream>>>(p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch(attention_mma_kernel<D, WARPS>, grid, WARPS * 32, smem, stream, p);
     if (e != cudaSuccess) return e;
     if (p.n_splits > 1) {
         const long long pairs = (long long)p.n_tokens * p.heads;
-        attention_combine_kernel<D><<<(int)((pairs + 3) / 4), 128, 0, stream>>>(p.part_o, p.part_ml, p.out, p.n_tokens,
-                                                                                p.heads, p.n_splits);
-        e = cudaGetLastError();
+        e = launch(attention_combine_kernel<D>, (int)((pairs + 3) / 4), 128, 0, stream, (const float*)p.part_o,
+                   (const float*)p.part_ml, p.out, p.n_tokens, p.heads, p.n_splits);
     }
     return e;
 }

@@ -11,6 +11,7 @@
 // running maximum and sum in 32-bit.  The result for a token depends on its own keys only.
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace vtb {
 
@@ -25,6 +26,8 @@ attention_simt_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restrict__
                       const int* __restrict__ token_seq, const int* __restrict__ block_table, int table_stride,
                       int n_seqs, int n_pages, int n_tokens, int heads, int kv_heads, int head_dim, int page_size,
                       int window, float scale, int* status) {
+    pdl_launch();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const long long pair = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (pair >= (long long)n_tokens * heads) return;
@@ -96,16 +99,14 @@ cudaError_t launch_attention_simt(int dtype, const void* qkv, int qkv_stride, vo
     const long long pairs = (long long)n_tokens * heads;
     const int blocks = (int)((pairs + 3) / 4);
     if (dtype == kBF16)
-        attention_simt_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(
+        return launch(attention_simt_kernel<__nv_bfloat16>, blocks, 128, 0, stream,
             (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
             (const __nv_bfloat16*)v_cache, positions, token_seq, block_table, table_stride, n_seqs, n_pages, n_tokens,
             heads, kv_heads, head_dim, page_size, window, scale, status);
-    else
-        attention_simt_kernel<float><<<blocks, 128, 0, stream>>>(
+    return launch(attention_simt_kernel<float>, blocks, 128, 0, stream,
             (const float*)qkv, qkv_stride, (float*)out, (const float*)k_cache, (const float*)v_cache, positions,
             token_seq, block_table, table_stride, n_seqs, n_pages, n_tokens, heads, kv_heads, head_dim, page_size,
             window, scale, status);
-    return cudaGetLastError();
 }
 
 }  // namespace vtb

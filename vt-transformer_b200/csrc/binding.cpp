@@ -174,7 +174,8 @@ void gemm_skinny(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, T
                                          stream_of(x)), "gemm_skinny");
 }
 
-void gemm_tc(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tensor& out, c10::optional<Tensor> status) {
+void gemm_tc(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tensor& out, c10::optional<Tensor> status,
+             c10::optional<Tensor> scratch, c10::optional<Tensor> counters) {
     check_cuda(x, "x"); check_cuda(w, "w"); check_cuda(out, "out");
     TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16, "gemm_tc: x and w must be bfloat16");
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm_tc: 2-d tensors");
@@ -189,9 +190,20 @@ void gemm_tc(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tenso
         TORCH_CHECK(bias->numel() == n, "gemm_tc: bias must have one entry for each output column");
         bp = bias->data_ptr<float>();
     }
+    float* sp = nullptr;
+    int* cp = nullptr;
+    long long sn = 0;
+    int cn = 0;
+    if (scratch.has_value() && counters.has_value()) {
+        check_f32(*scratch, "scratch"); check_i32(*counters, "counters");
+        sp = scratch->data_ptr<float>();
+        sn = scratch->numel();
+        cp = counters->data_ptr<int>();
+        cn = counters->numel();
+    }
     c10::cuda::CUDAGuard guard(x.device());
-    check_launch(vtb::launch_gemm_tc(dtype_code(out, "out"), x.data_ptr(), w.data_ptr(), bp, out.data_ptr(), m, n, k,
-                                     status_ptr(status), stream_of(x)), "gemm_tc");
+    check_launch(vtb::launch_gemm_tc(dtype_code(out, "out"), x.data_ptr(), w.data_ptr(), bp, out.data_ptr(), m, n, k, sp, sn,
+                                     cp, cn, status_ptr(status), stream_of(x)), "gemm_tc");
 }
 
 bool attention_mma_supports(int64_t head_dim, int64_t heads, int64_t kv_heads, int64_t warps) {
@@ -306,7 +318,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("positions"), py::arg("token_seq"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),
           py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("status") = py::none());
     m.def("gemm_skinny", &gemm_skinny, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"));
-    m.def("gemm_tc", &gemm_tc, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"), py::arg("status") = py::none());
+    m.def("gemm_tc", &gemm_tc, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"), py::arg("status") = py::none(),
+          py::arg("scratch") = py::none(), py::arg("counters") = py::none());
     m.def("attention_mma_supports", &attention_mma_supports);
     m.def("attention_mma", &attention_mma, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
           py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("tiles"), py::arg("heads"),

@@ -31,7 +31,7 @@ SOURCES = [
     "attention_noalloc.cu",
     "sampling.cu",
 ]
-HEADERS = ["common.cuh", "kernels.h", "attention_noalloc.h"]
+HEADERS = ["common.cuh", "kernels.h", "launch.cuh", "attention_noalloc.h"]
 
 CUDA_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

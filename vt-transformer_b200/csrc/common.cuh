@@ -25,6 +25,14 @@ __device__ __forceinline__ void set_status(int* status, int code, int detail) {
     }
 }
 
+// Programmatic dependent launch: every kernel of this library is launched so that it may start
+// while the kernel before it in the stream is still running.  `pdl_launch` lets the next kernel's
+// CTAs be scheduled as soon as there is room; `pdl_wait` returns when the kernels before have
+// completed and their writes are visible.  A kernel calls both at its top, before it reads or
+// writes global memory, so only set-up that touches no global data overlaps.
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
 template <typename T> __device__ __forceinline__ float to_float(T v);
 template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -9,6 +9,7 @@
 // sum folded into the norm, and the keys and values written straight into their pages.
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace vtb {
 
@@ -17,6 +18,8 @@ namespace vtb {
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                                  int hidden, int vocab, int* status) {
+    pdl_launch();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * hidden;
@@ -42,10 +45,8 @@ cudaError_t launch_embedding(int table_dtype, const void* table, const int* ids,
     if (n_tokens == 0) return cudaSuccess;
     int threads = min(256, max(32, ((hidden / 8 + 31) / 32) * 32));
     if (table_dtype == kBF16)
-        embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
-    else
-        embedding_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab, status);
-    return cudaGetLastError();
+        return launch(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
+    return launch(embedding_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab, status);
 }
 
 // ------------------------------------------------------------------------- rmsnorm
@@ -58,6 +59,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
                                float eps, T* __restrict__ out, const int* __restrict__ rows, int n_tokens, int hidden,
                                int* status) {
     __shared__ float scratch[32];
+    pdl_launch();
+    pdl_wait();
     const int r = blockIdx.x;
     const int t = rows ? rows[r] : r;
     T* o = out + (size_t)r * hidden;
@@ -99,18 +102,18 @@ cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const flo
     if (n_rows == 0) return cudaSuccess;
     int threads = min(512, max(32, ((hidden / 8 + 31) / 32) * 32));
     if (out_dtype == kBF16)
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, (const __nv_bfloat16*)delta, weight, eps,
-                                                                      (__nv_bfloat16*)out, rows, n_tokens, hidden, status);
-    else
-        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, (const float*)delta, weight, eps, (float*)out, rows,
-                                                              n_tokens, hidden, status);
-    return cudaGetLastError();
+        return launch(rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, (const __nv_bfloat16*)delta, weight, eps,
+                      (__nv_bfloat16*)out, rows, n_tokens, hidden, status);
+    return launch(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, (const float*)delta, weight, eps, (float*)out, rows, n_tokens,
+                  hidden, status);
 }
 
 // ------------------------------------------------------------------------- silu * up
 
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tokens, int inter) {
+    pdl_launch();
+    pdl_wait();
     const int per_row = inter / 8;
     const size_t total = (size_t)n_tokens * per_row;
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
@@ -131,10 +134,8 @@ cudaError_t launch_silu_mul(int dtype, const void* gu, void* out, int n_tokens, 
     const int threads = 256;
     const int blocks = (int)min((size_t)148 * 16, (total + threads - 1) / threads);
     if (dtype == kBF16)
-        silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter);
-    else
-        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, n_tokens, inter);
-    return cudaGetLastError();
+        return launch(silu_mul_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter);
+    return launch(silu_mul_kernel<float>, blocks, threads, 0, stream, (const float*)gu, (float*)out, n_tokens, inter);
 }
 
 // ------------------------------------------------------------------------- rotation + cache store
@@ -149,6 +150,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   const int* __restrict__ block_table, int table_stride, int n_seqs, int n_pages,
                                   int heads, int kv_heads, int head_dim, int page_size, int rotate, int store,
                                   int* status) {
+    pdl_launch();
+    pdl_wait();
     const int t = blockIdx.x;
     const int seq = token_seq[t];
     if (seq < 0) return;  // padding
@@ -220,14 +223,12 @@ cudaError_t launch_rope_store(int dtype, void* qkv, const int* positions, const 
     const int work = max(heads * head_dim / 2, kv_heads * head_dim);
     const int threads = min(512, max(32, ((work + 31) / 32) * 32));
     if (dtype == kBF16)
-        rope_store_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        return launch(rope_store_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream,
             (__nv_bfloat16*)qkv, positions, cos_sin, max_pos, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, token_seq,
             block_table, table_stride, n_seqs, n_pages, heads, kv_heads, head_dim, page_size, rotate, store, status);
-    else
-        rope_store_kernel<float><<<n_tokens, threads, 0, stream>>>(
+    return launch(rope_store_kernel<float>, n_tokens, threads, 0, stream,
             (float*)qkv, positions, cos_sin, max_pos, (float*)k_cache, (float*)v_cache, token_seq, block_table,
             table_stride, n_seqs, n_pages, heads, kv_heads, head_dim, page_size, rotate, store, status);
-    return cudaGetLastError();
 }
 
 }  // namespace vtb

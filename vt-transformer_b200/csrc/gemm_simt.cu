@@ -9,6 +9,7 @@
 // plain twin of the tensor-core products.
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace vtb {
 
@@ -29,6 +30,8 @@ template <typename TA, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ a, const TA* __restrict__ w, const float* __restrict__ bias,
                  TC* __restrict__ c, int m, int n, int k) {
+    pdl_launch();
+    pdl_wait();
     __shared__ __align__(16) float as[BK][BM + PAD];
     __shared__ __align__(16) float ws[BK][BN + PAD];
     const int tid = threadIdx.x;
@@ -79,16 +82,14 @@ cudaError_t launch_gemm_simt(int in_dtype, int out_dtype, const void* a, const v
     if (m == 0 || n == 0) return cudaSuccess;
     dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
     if (in_dtype == kF32 && out_dtype == kF32)
-        gemm_simt_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)a, (const float*)w, bias, (float*)c, m, n, k);
-    else if (in_dtype == kBF16 && out_dtype == kBF16)
-        gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(
+        return launch(gemm_simt_kernel<float, float>, grid, 256, 0, stream, (const float*)a, (const float*)w, bias, (float*)c, m, n, k);
+    if (in_dtype == kBF16 && out_dtype == kBF16)
+        return launch(gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16>, grid, 256, 0, stream,
             (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, bias, (__nv_bfloat16*)c, m, n, k);
-    else if (in_dtype == kBF16 && out_dtype == kF32)
-        gemm_simt_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>(
+    if (in_dtype == kBF16 && out_dtype == kF32)
+        return launch(gemm_simt_kernel<__nv_bfloat16, float>, grid, 256, 0, stream,
             (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, bias, (float*)c, m, n, k);
-    else
-        return cudaErrorInvalidValue;
-    return cudaGetLastError();
+    return cudaErrorInvalidValue;
 }
 
 }  // namespace vtb

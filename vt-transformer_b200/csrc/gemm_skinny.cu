@@ -19,6 +19,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -51,6 +52,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                    const float* __restrict__ bias, TOut* __restrict__ out, int m, int n, int k) {
     __shared__ float red[WARPS][NT][16][8 + 1];
     __shared__ float tile[NT * 128];
+    pdl_launch();
+    pdl_wait();
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned rank = cluster.block_rank(), csize = cluster.num_blocks();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -131,19 +134,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 template <int NT, typename TOut>
 cudaError_t launch_nt(const __nv_bfloat16* x, const __nv_bfloat16* w, const float* bias, TOut* out, int m, int n, int k,
                       int ksplit, cudaStream_t stream) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(ksplit, (n + 15) / 16, 1);
-    cfg.blockDim = dim3(WARPS * 32, 1, 1);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = ksplit;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NT, TOut>, x, w, bias, out, m, n, k);
+    return launch(gemm_skinny_kernel<NT, TOut>, dim3(ksplit, (n + 15) / 16, 1), dim3(WARPS * 32, 1, 1), 0, stream,
+                  dim3(ksplit, 1, 1), x, w, bias, out, m, n, k);
 }
 
 template <typename TOut>

@@ -7,9 +7,10 @@
 // Here both x [M, K] and w [N, K] are K-major, so either can be the 128-row operand of the MMA:
 //   * many rows of x (prompt portions): a tile is 128 rows of x by BN rows of w, D[token, feature];
 //   * few rows of x (decode): "swapped": a tile is 128 rows of w by all rows of x (BN = 16..64),
-//     D[feature, token], so a weight is read once and the small batch rides along.  The k range of a
-//     matrix with few tiles is cut over a thread-block cluster and the shares are added in rank
-//     order through distributed shared memory.
+//     D[feature, token], so a weight is read once and the small batch rides along.  A matrix with
+//     fewer tiles than SMs has its k range cut over several CTAs (grid z) so that one wave of CTAs
+//     covers the machine; each CTA leaves its share in a scratch buffer and counts itself in; the
+//     CTA that arrives last adds the shares in rank order and stores (no CTA waits for another).
 //
 // One CTA computes one tile.  Warp 0 issues the TMA loads (one elected thread), warp 1 owns the
 // tensor memory and issues the MMAs (one elected thread), warps 2..5 read the accumulator back
@@ -18,13 +19,11 @@
 // TMA fills what lies outside a matrix with zeros, so any M, N and K (K % 8 == 0) is taken.
 // Every wait on a barrier is bounded by a clock limit; a wait that runs out records it in the status
 // word and the CTA winds down: tensor memory is freed and the kernel returns.
-#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "common.cuh"
 #include "kernels.h"
-
-namespace cg = cooperative_groups;
+#include "launch.cuh"
 
 namespace vtb {
 
@@ -128,7 +127,8 @@ template <> __device__ __forceinline__ void store8<float>(float* p, const float*
 template <int BN, int STAGES, bool SWAP, typename TOut>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo, int* status) {
+               const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo,
+               float* __restrict__ scratch, int* __restrict__ counters, int* status) {
     constexpr int B_STAGE = BN * BK * 2;
     constexpr int COLS = BN < 32 ? 32 : BN;          // tensor-memory columns: a power of two, at least 32
     extern __shared__ unsigned char smem_raw[];
@@ -139,9 +139,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t* empty = full + STAGES;
     uint64_t* acc_done = empty + STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+    int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
-    cg::cluster_group cluster = cg::this_cluster();
-    const int ksplit = (int)cluster.num_blocks(), krank = (int)cluster.block_rank();
+    const int ksplit = (int)gridDim.z, krank = (int)blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // consecutive CTAs take consecutive tiles of the 128-row operand and share the other operand's tile:
     // for prompt portions the weights' tile is fetched from HBM once and then found in L2
@@ -169,6 +169,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     bool timed_out = false;
+    // barriers and tensor memory are set up; from here on global memory is touched
+    pdl_launch();
+    pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -199,7 +202,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncwarp();
 
     // ---- epilogue: warps 2..5, each its quarter of the lanes --------------------------------------
-    float* share = reinterpret_cast<float*>(smem);     // [BN][128] floats, over the stages, when k is split
     if (warp >= 2) {
         const int q = warp & 3;
         const int r = q * 32 + lane;                   // lane of the accumulator = row of the 128-row operand
@@ -207,6 +209,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (nkb > 0) ok = mbar_wait(acc_done, 0);
         if (!ok) timed_out = true;
         tc_fence_after();
+        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        float* mine = scratch + ((size_t)tile * ksplit + krank) * (BN * BM);     // this CTA's share [BN][128]
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
             float v[16];
@@ -221,7 +225,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             if (ksplit > 1) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) share[(c0 + i) * BM + r] = v[i];
+                for (int i = 0; i < 16; ++i) __stcg(mine + (c0 + i) * BM + r, v[i]);
                 continue;
             }
             if (SWAP) {
@@ -254,23 +258,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
         }
-    }
-    if (ksplit > 1) {
-        // all MMAs of this CTA are done (acc_done), so the stages may be overwritten by the shares
-        cluster.sync();
-        if (warp >= 2 && SWAP) {
-            const int r = (warp & 3) * 32 + lane;
-            const int n = a_row0 + r;
-            for (int c = krank; c < BN; c += ksplit) {
-                const int m = b_row0 + c;
-                if (m >= rows_b || n >= rows_a) continue;
-                float s = 0.f;
-                for (int rk = 0; rk < ksplit; ++rk) s += cluster.map_shared_rank(share, rk)[c * BM + r];
-                if (bias) s += bias[n];
-                out[(size_t)m * ldo + n] = from_float<TOut>(s);
+        if (ksplit > 1) {
+            // count this CTA in; the one that finds all others counted adds the shares and stores
+            __threadfence();
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");
+            if (threadIdx.x == 64) *last_flag = (atomicAdd(&counters[tile], 1) == ksplit - 1) ? 1 : 0;
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");
+            if (*last_flag) {
+                __threadfence();
+                const float* all = scratch + (size_t)tile * ksplit * (BN * BM);
+                const int n = a_row0 + r;
+                if (SWAP && n < rows_a) {
+                    const float b = bias ? bias[n] : 0.f;
+                    // 16 columns at a time, all their loads in flight together; ranks added in order
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        if (b_row0 + c0 >= rows_b) break;
+                        float sum[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) sum[i] = 0.f;
+#pragma unroll 4
+                        for (int rk = 0; rk < ksplit; ++rk) {
+                            const float* src = all + ((size_t)rk * BN + c0) * BM + r;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) sum[i] += __ldcg(src + i * BM);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int m = b_row0 + c0 + i;
+                            if (m < rows_b) out[(size_t)m * ldo + n] = from_float<TOut>(sum[i] + b);
+                        }
+                    }
+                }
+                if (threadIdx.x == 64) counters[tile] = 0;      // ready for the next launch
             }
         }
-        cluster.sync();
     }
     if (timed_out && status) set_status(status, kStatusWaitTimeout, blockIdx.x + blockIdx.y * gridDim.x);
     tc_fence_before();
@@ -313,7 +335,7 @@ bool make_map(CUtensorMap* map, const void* ptr, int rows, int k, int box_rows) 
 
 template <int BN, int STAGES, bool SWAP, typename TOut>
 cudaError_t launch_cfg(const void* a, int rows_a, const void* b, int rows_b, int k, const float* bias, TOut* out, int ldo,
-                       int ksplit, int* status, cudaStream_t stream) {
+                       int ksplit, float* scratch, int* counters, int* status, cudaStream_t stream) {
     CUtensorMap map_a, map_b;
     if (!make_map(&map_a, a, rows_a, k, BM) || !make_map(&map_b, b, rows_b, k, BN)) return cudaErrorInvalidValue;
     constexpr int smem = STAGES * (A_STAGE + BN * BK * 2) + 1024 + 256;
@@ -323,45 +345,60 @@ cudaError_t launch_cfg(const void* a, int rows_a, const void* b, int rows_b, int
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((rows_a + BM - 1) / BM, (rows_b + BN - 1) / BN, ksplit);
-    cfg.blockDim = dim3(THREADS, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = ksplit;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, SWAP, TOut>, map_a, map_b, bias, out, rows_a, rows_b, k, ldo, status);
+    return launch(gemm_tc_kernel<BN, STAGES, SWAP, TOut>, dim3((rows_a + BM - 1) / BM, (rows_b + BN - 1) / BN, ksplit),
+                  dim3(THREADS, 1, 1), smem, stream, map_a, map_b, bias, out, rows_a, rows_b, k, ldo, scratch, counters, status);
 }
 
 template <typename TOut>
-cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* out, int m, int n, int k, int* status,
-                         cudaStream_t stream) {
+cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* out, int m, int n, int k, float* scratch,
+                         long long scratch_floats, int* counters, int n_counters, int* status, cudaStream_t stream) {
     if (m <= 64) {
-        // swapped: w is the 128-row operand; cut k over a cluster while the tiles are fewer than the SMs
+        // swapped: w is the 128-row operand.  One CTA fits an SM, so the CTAs run in waves of one an SM;
+        // cut k over s CTAs so that the last wave is full, counting a fixed cost a CTA (set-up, filling
+        // the ring, the merge) as a few k-blocks: least waves * (k-blocks a CTA + cost).
+        static int sms = 0;
+        if (sms == 0) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        }
+        const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
         const int tiles = (n + BM - 1) / BM, nkb = (k + BK - 1) / BK;
         int ksplit = 1;
-        while (ksplit < 8 && tiles * ksplit < 148 && nkb / (ksplit * 2) >= 4) ksplit *= 2;
-        if (m <= 16) return launch_cfg<16, 8, true, TOut>(w, n, x, m, k, bias, out, n, ksplit, status, stream);
-        if (m <= 32) return launch_cfg<32, 8, true, TOut>(w, n, x, m, k, bias, out, n, ksplit, status, stream);
-        return launch_cfg<64, 6, true, TOut>(w, n, x, m, k, bias, out, n, ksplit, status, stream);
+        long best = -1;
+        for (int s = 1; s <= 16; ++s) {
+            if (s > 1 && (nkb / s < 4 || scratch == nullptr || counters == nullptr || tiles > n_counters ||
+                          (long long)tiles * s * bn * BM > scratch_floats))
+                break;
+            const long waves = (tiles * s + sms - 1) / sms;
+            const long cost = waves * ((nkb + s - 1) / s + 6 + (s > 1 ? 2 : 0));
+            if (best < 0 || cost < best) {
+                best = cost;
+                ksplit = s;
+            }
+        }
+        if (bn == 16) return launch_cfg<16, 8, true, TOut>(w, n, x, m, k, bias, out, n, ksplit, scratch, counters, status, stream);
+        if (bn == 32) return launch_cfg<32, 8, true, TOut>(w, n, x, m, k, bias, out, n, ksplit, scratch, counters, status, stream);
+        return launch_cfg<64, 6, true, TOut>(w, n, x, m, k, bias, out, n, ksplit, scratch, counters, status, stream);
     }
-    if (n <= 128 || m <= 128) return launch_cfg<128, 4, false, TOut>(x, m, w, n, k, bias, out, n, 1, status, stream);
-    return launch_cfg<256, 4, false, TOut>(x, m, w, n, k, bias, out, n, 1, status, stream);
+    if (n <= 128 || m <= 128)
+        return launch_cfg<128, 4, false, TOut>(x, m, w, n, k, bias, out, n, 1, nullptr, nullptr, status, stream);
+    return launch_cfg<256, 4, false, TOut>(x, m, w, n, k, bias, out, n, 1, nullptr, nullptr, status, stream);
 }
 
 }  // namespace
 
 cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n, int k,
-                           int* status, cudaStream_t stream) {
+                           float* scratch, long long scratch_floats, int* counters, int n_counters, int* status,
+                           cudaStream_t stream) {
     if (m == 0 || n == 0) return cudaSuccess;
     if (k % 8 != 0 || k < 8) return cudaErrorInvalidValue;
-    if (out_dtype == kBF16) return launch_typed<__nv_bfloat16>(x, w, bias, (__nv_bfloat16*)out, m, n, k, status, stream);
-    if (out_dtype == kF32) return launch_typed<float>(x, w, bias, (float*)out, m, n, k, status, stream);
+    if (out_dtype == kBF16)
+        return launch_typed<__nv_bfloat16>(x, w, bias, (__nv_bfloat16*)out, m, n, k, scratch, scratch_floats, counters,
+                                           n_counters, status, stream);
+    if (out_dtype == kF32)
+        return launch_typed<float>(x, w, bias, (float*)out, m, n, k, scratch, scratch_floats, counters, n_counters, status,
+                                   stream);
     return cudaErrorInvalidValue;
 }
 

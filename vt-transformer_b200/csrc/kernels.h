@@ -53,9 +53,12 @@ cudaError_t launch_gemm_skinny(int out_dtype, const void* x, const void* w, cons
 
 // out[M, N] = x[M, K] w[N, K]^T (+ bias) with tcgen05.mma fed by TMA, accumulators in tensor memory.
 // bfloat16 x and w, out bfloat16 or float, any M and N, k % 8 == 0.  status receives kStatusWaitTimeout
-// if a bounded wait inside the kernel runs out.
+// if a bounded wait inside the kernel runs out.  scratch (floats) and counters (ints, zero before the
+// first launch; the kernel leaves them zero) let a small batch cut k over several CTAs; without them
+// k is not cut.  Launches that share them must not overlap on the GPU.
 cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n, int k,
-                           int* status, cudaStream_t stream);
+                           float* scratch, long long scratch_floats, int* counters, int n_counters, int* status,
+                           cudaStream_t stream);
 
 // Tensor-core attention over the paged cache (bfloat16).  A tile is 16 * warps rows, row r being
 // (token r / group, head r % group); `tiles` lists (sequence, first token) pairs, or is null when

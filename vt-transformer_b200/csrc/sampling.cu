@@ -11,6 +11,7 @@
 // with a host implementation on the same logits and the same uniform number.
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace vtb {
 
@@ -77,6 +78,8 @@ __global__ void __launch_bounds__(kThreads)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
     __shared__ float shv[32];
     __shared__ int shi[32];
+    pdl_launch();
+    pdl_wait();
     const float* l = logits + (size_t)blockIdx.x * vocab;
     float best;
     int bi;
@@ -92,6 +95,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     __shared__ int shi[32];
     __shared__ double shd[32];
     __shared__ double warp_prefix[32];
+    pdl_launch();
+    pdl_wait();
     const int row = blockIdx.x;
     const float* l = logits + (size_t)row * vocab;
     const float temp = temperature[row];
@@ -192,15 +197,13 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 
 cudaError_t launch_argmax(const float* logits, int* out, int n_rows, int vocab, cudaStream_t stream) {
     if (n_rows == 0) return cudaSuccess;
-    argmax_kernel<<<n_rows, kThreads, 0, stream>>>(logits, out, vocab);
-    return cudaGetLastError();
+    return launch(argmax_kernel, n_rows, kThreads, 0, stream, logits, out, vocab);
 }
 
 cudaError_t launch_sample(const float* logits, const float* temperature, const int* top_k, const float* top_p,
                           const float* u, int* out, int n_rows, int vocab, cudaStream_t stream) {
     if (n_rows == 0) return cudaSuccess;
-    sample_kernel<<<n_rows, kThreads, 0, stream>>>(logits, temperature, top_k, top_p, u, out, vocab);
-    return cudaGetLastError();
+    return launch(sample_kernel, n_rows, kThreads, 0, stream, logits, temperature, top_k, top_p, u, out, vocab);
 }
 
 }  // namespace vtb

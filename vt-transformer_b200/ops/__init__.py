@@ -70,8 +70,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
 
     float32 x and w: the 32-bit kernel (FFMA in a fixed order, no TF32).  A weight kept in
     32-bit beside bfloat16 activations goes the same way, with x widened.  bfloat16: the
-    weight-streaming kernel for up to 64 rows of x, the tcgen05 kernel (TMA, tensor memory)
-    beyond.
+    tcgen05 kernel (TMA, tensor memory), with w as the 128-row operand for up to 64 rows of x
+    and x beyond.
     """
     be = backend()
     if w.dtype == torch.float32:
@@ -89,15 +89,29 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
     if m <= SKINNY_MAX_ROWS and SMALL_BATCH_KERNEL == "skinny":
         be.gemm_skinny(x, w, bias, out)
     else:
-        be.gemm_tc(x, w, bias, out, status)
+        scratch, counters = _split_workspace(x.device)
+        be.gemm_tc(x, w, bias, out, status, scratch, counters)
     return out
 
 
+_workspaces = {}
+
+
+def _split_workspace(device):
+    """Scratch and arrival counters with which the tcgen05 kernel cuts k over CTAs for small batches:
+    4M floats and 4,096 counters a device, made once.  Launches that use them run in one stream."""
+    ws = _workspaces.get(device)
+    if ws is None:
+        ws = (torch.empty(4 << 20, dtype=torch.float32, device=device), torch.zeros(4096, dtype=torch.int32, device=device))
+        _workspaces[device] = ws
+    return ws
+
+
 SKINNY_MAX_ROWS = 64            # rows of x up to which the small-batch kernel may run
-# "skinny": mma.sync weight streaming; "tc": the tcgen05 kernel with w as the 128-row operand.
+# "tc": the tcgen05 kernel with w as the 128-row operand; "skinny": mma.sync weight streaming.
 # The environment variable VTB200_SMALL_BATCH_KERNEL overrides it (for measurements).
 import os as _os
-SMALL_BATCH_KERNEL = _os.environ.get("VTB200_SMALL_BATCH_KERNEL", "skinny")
+SMALL_BATCH_KERNEL = _os.environ.get("VTB200_SMALL_BATCH_KERNEL", "tc")
 ATTENTION_KERNEL = "auto"   # "auto", or "simt" to force the plain kernel (tests compare the two)
 
 
