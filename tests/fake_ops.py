@@ -30,9 +30,13 @@ def rmsnorm(x, delta, weight, eps, out, rows=None, status=None):
     out.copy_((weight * v * r).to(out.dtype))
 
 
-def silu_mul(gu, out):
+def silu_mul(gu, out, interleave=0):
     inter = out.shape[1]
-    g, u = gu[:, :inter].float(), gu[:, inter:].float()
+    if interleave:
+        pairs = gu.view(gu.shape[0], inter // 8, 2, 8).float()
+        g, u = pairs[:, :, 0].reshape(-1, inter), pairs[:, :, 1].reshape(-1, inter)
+    else:
+        g, u = gu[:, :inter].float(), gu[:, inter:].float()
     out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
 
 

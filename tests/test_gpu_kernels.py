@@ -247,6 +247,37 @@ def test_tcgen05_product(m, n, k):
     assert status.tolist() == [0, 0] and int(counters.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("m", [1, 8, 40, 64, 65, 300])
+@pytest.mark.parametrize("inter,k", [(8, 64), (136, 72), (344, 128), (18944 // 8, 3584)])
+def test_gate_up_product_with_the_activation_in_its_epilogue(m, inter, k):
+    """silu(x Wg^T) * (x Wu^T) from one product over the interleaved rows, fused (tcgen05 epilogue) and
+    in two kernels (product, then the elementwise kernel on the interleaved layout), in both dtypes of
+    the elementwise kernel."""
+    torch.manual_seed(13)
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    wg = (torch.randn(inter, k, device=DEV) / math.sqrt(k) * 2).to(torch.bfloat16)
+    wu = (torch.randn(inter, k, device=DEV) / math.sqrt(k) * 2).to(torch.bfloat16)
+    g, u = x.cpu().double() @ wg.cpu().double().t(), x.cpu().double() @ wu.cpu().double().t()
+    ref = g / (1 + torch.exp(-g)) * u
+    o = ops()
+    packed = o.interleave_gate_up(wg, wu)
+    assert torch.equal(packed[:8], wg[:8]) and torch.equal(packed[8:16], wu[:8])
+    fused = torch.full((m, inter), float("nan"), device=DEV, dtype=torch.bfloat16)
+    o.linear_silu_mul(x, packed, fused)
+    close(fused, ref, torch.bfloat16, 2)
+    o.FUSE_SILU = False
+    try:
+        two = torch.full((m, inter), float("nan"), device=DEV, dtype=torch.bfloat16)
+        o.linear_silu_mul(x, packed, two)
+    finally:
+        o.FUSE_SILU = True
+    close(two, ref, torch.bfloat16, 3)                       # gate and up are rounded to bfloat16 on the way
+    xf, pf = x.float(), packed.float()
+    out32 = torch.empty(m, inter, device=DEV)
+    o.linear_silu_mul(xf, pf, out32)
+    close(out32, ref, torch.float32, 40)
+
+
 def test_tcgen05_product_takes_each_element_once():
     """x and w of small integers: every product and sum is exact in bfloat16 and float, so a tile read
     from the wrong place, a k-block counted twice or dropped, shows as a wrong integer."""

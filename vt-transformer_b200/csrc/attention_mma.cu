@@ -325,6 +325,303 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
     }
 }
 
+// ---- single-token steps -----------------------------------------------------------------------------
+// A CTA of four warps serves one (sequence, KV head, run of keys).  The run's blocks of 32 keys go to
+// the warps in turn; each warp streams its blocks through its own two-stage cp.async ring and keeps a
+// running maximum, sum and output for the up to 16 rows (token, head of the group).  The four results
+// are merged in shared memory.  With more than one run a sequence (n_splits > 1) the CTA leaves its
+// merged result in scratch and counts itself in; the CTA that arrives last merges the runs and stores,
+// so there is no second kernel and no CTA waits for another.
+constexpr int DKB = 32;    // keys in a warp's block
+constexpr int DWARPS = 4;
+
+template <int D>
+__global__ void __launch_bounds__(DWARPS * 32)
+attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
+    constexpr int LD = D + 8;
+    constexpr int WARP_BYTES = 2 * 2 * DKB * LD * 2;          // K and V, two stages
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int last_flag;
+    pdl_launch();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+    const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int q_begin = p.cu_q[seq];
+    const int q_len = p.cu_q[seq + 1] - q_begin;
+    const int ntok = min(p.tokens_per_tile, q_len);
+    if (ntok <= 0) return;                                     // padding: a sequence without tokens
+    const int group = p.heads / p.kv_heads;
+    const int rows_valid = ntok * group;
+    const int start = p.q_start[seq];
+    const int pos_lo = start, pos_hi = start + ntok - 1;
+    int key_lo = (p.window > 0) ? max(0, pos_lo - p.window + 1) : 0;
+    key_lo = key_lo / DKB * DKB;
+    const int key_hi = pos_hi + 1;
+    const int nblk = (key_hi - key_lo + DKB - 1) / DKB;
+    const int blk0 = (int)((long long)split * nblk / p.n_splits), blk1 = (int)((long long)(split + 1) * nblk / p.n_splits);
+
+    unsigned char* wbase = smem_raw + (size_t)warp * WARP_BYTES;
+    __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(wbase);                 // [2][DKB][LD]
+    __nv_bfloat16* vs = ks + 2 * DKB * LD;
+
+    int row[2], pos[2], tok[2], head[2];
+    bool valid[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        row[i] = gq + 8 * i;
+        valid[i] = row[i] < rows_valid;
+        const int tk = valid[i] ? row[i] / group : 0;
+        tok[i] = q_begin + tk;
+        pos[i] = pos_lo + tk;
+        head[i] = kvh * group + (valid[i] ? row[i] % group : 0);
+    }
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const __nv_bfloat16* qp = p.qkv + (size_t)tok[i] * p.qkv_stride + (size_t)head[i] * D;
+#pragma unroll
+        for (int ks_ = 0; ks_ < D / 16; ++ks_) {
+            qf[ks_][i] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp + ks_ * 16 + 2 * tq) : 0u;
+            qf[ks_][i + 2] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp + ks_ * 16 + 8 + 2 * tq) : 0u;
+        }
+    }
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+
+    const int* table = p.block_table + (size_t)seq * p.table_stride;
+    auto load_block = [&](int blk, int stage) {
+        const int kb = key_lo + blk * DKB;
+        constexpr int CHUNKS = D / 8;
+        size_t base[2];
+        bool okp[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {                          // the block's two runs of 16 keys, a page each
+            const int key = kb + 16 * h;
+            okp[h] = key < key_hi;
+            base[h] = 0;
+            if (okp[h]) {
+                const int page = table[key / p.page_size];
+                if (page < 0 || page >= p.n_pages) okp[h] = false;
+                else base[h] = (((size_t)page * p.kv_heads + kvh) * p.page_size + key % p.page_size) * D;
+            }
+        }
+        for (int c = lane; c < DKB * CHUNKS; c += 32) {
+            const int r = c / CHUNKS, piece = c % CHUNKS;
+            const int h = r >> 4;
+            const bool ok = okp[h] && (kb + r) < key_hi;
+            const size_t off = base[h] + (size_t)(r & 15) * D + piece * 8;
+            cp_async16(ks + ((size_t)stage * DKB + r) * LD + piece * 8, p.k_cache + (ok ? off : 0), ok);
+            cp_async16(vs + ((size_t)stage * DKB + r) * LD + piece * 8, p.v_cache + (ok ? off : 0), ok);
+        }
+    };
+
+    const int first = blk0 + warp;
+    if (first < blk1) {
+        load_block(first, 0);
+        cp_async_commit();
+    }
+    int it = 0;
+    for (int blk = first; blk < blk1; blk += DWARPS, ++it) {
+        const int stage = it & 1;
+        if (blk + DWARPS < blk1) {
+            load_block(blk + DWARPS, stage ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncwarp();
+        const __nv_bfloat16* kst = ks + (size_t)stage * DKB * LD;
+        const __nv_bfloat16* vst = vs + (size_t)stage * DKB * LD;
+        const int kb = key_lo + blk * DKB;
+        float s[DKB / 8][4];
+#pragma unroll
+        for (int j = 0; j < DKB / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+        for (int ks_ = 0; ks_ < D / 16; ++ks_) {
+#pragma unroll
+            for (int j = 0; j < DKB / 8; ++j) {
+                const __nv_bfloat16* kp = kst + (size_t)(j * 8 + gq) * LD + ks_ * 16 + 2 * tq;
+                mma_bf16(s[j], qf[ks_], *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
+            }
+        }
+        float mnew[2] = {mrow[0], mrow[1]};
+#pragma unroll
+        for (int j = 0; j < DKB / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = e >> 1;
+                const int key = kb + j * 8 + 2 * tq + (e & 1);
+                const bool see = valid[i] && key <= pos[i] && (p.window <= 0 || key > pos[i] - p.window);
+                s[j][e] = see ? s[j][e] * p.scale_log2 : -INFINITY;
+                mnew[i] = fmaxf(mnew[i], s[j][e]);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mnew[i] = fmaxf(mnew[i], __shfl_xor_sync(0xffffffffu, mnew[i], 1));
+            mnew[i] = fmaxf(mnew[i], __shfl_xor_sync(0xffffffffu, mnew[i], 2));
+            corr[i] = (mnew[i] == -INFINITY) ? 1.f : exp2f(mrow[i] - mnew[i]);
+            mrow[i] = mnew[i];
+            lrow[i] *= corr[i];
+        }
+        const float base2[2] = {mnew[0] == -INFINITY ? 0.f : mnew[0], mnew[1] == -INFINITY ? 0.f : mnew[1]};
+#pragma unroll
+        for (int j = 0; j < DKB / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pv = exp2f(s[j][e] - base2[e >> 1]);
+                s[j][e] = pv;
+                lrow[e >> 1] += pv;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+#pragma unroll
+        for (int kk = 0; kk < DKB / 16; ++kk) {
+            uint32_t pf[4];
+            pf[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            pf[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            pf[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pf[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int dn = 0; dn < D / 16; ++dn) {
+                uint32_t vf[4];
+                const int mat = lane >> 3, r = lane & 7;
+                ldmatrix_x4_trans(vf, vst + (size_t)(kk * 16 + (mat & 1) * 8 + r) * LD + dn * 16 + (mat >> 1) * 8);
+                mma_bf16(o[2 * dn], pf, vf[0], vf[1]);
+                mma_bf16(o[2 * dn + 1], pf, vf[2], vf[3]);
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 1);
+        lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 2);
+    }
+    // each warp leaves (output [16][D], maximum [16], sum [16]) at the start of its own buffers
+    float* wo = reinterpret_cast<float*>(wbase);
+    float* wm = wo + 16 * D;
+    float* wl = wm + 16;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int dt = 0; dt < D / 8; ++dt)
+            *reinterpret_cast<float2*>(wo + row[i] * D + dt * 8 + 2 * tq) = make_float2(o[dt][2 * i], o[dt][2 * i + 1]);
+        if (tq == 0) {
+            wm[row[i]] = mrow[i];
+            wl[row[i]] = lrow[i];
+        }
+    }
+    __syncthreads();
+    // merge the four warps: every thread takes elements (row, d) of the [16][D] output
+    const int tile = seq * p.kv_heads + kvh;
+    for (int e = threadIdx.x; e < 16 * D; e += DWARPS * 32) {
+        const int r = e / D, d = e % D;
+        if (r >= rows_valid) continue;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DWARPS; ++w) {
+            const float* b = reinterpret_cast<const float*>(smem_raw + (size_t)w * WARP_BYTES);
+            if (b[16 * D + 16 + r] > 0.f) mx = fmaxf(mx, b[16 * D + r]);
+        }
+        float acc = 0.f, tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < DWARPS; ++w) {
+            const float* b = reinterpret_cast<const float*>(smem_raw + (size_t)w * WARP_BYTES);
+            const float l = b[16 * D + 16 + r];
+            if (l > 0.f) {
+                const float wgt = exp2f(b[16 * D + r] - mx);
+                acc += b[e] * wgt;
+                tot += l * wgt;
+            }
+        }
+        const int t = q_begin + r / group, h = kvh * group + r % group;
+        if (p.n_splits == 1) {
+            p.out[((size_t)t * p.heads + h) * D + d] = __float2bfloat16_rn(tot > 0.f ? acc / tot : 0.f);
+        } else {
+            const size_t idx = ((size_t)split * p.n_tokens + t) * p.heads + h;
+            __stcg(p.part_o + idx * D + d, acc);
+            if (d == 0) {
+                __stcg(p.part_ml + idx * 2, mx);
+                __stcg(p.part_ml + idx * 2 + 1, tot);
+            }
+        }
+    }
+    if (p.n_splits == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last_flag = (atomicAdd(&counters[tile], 1) == p.n_splits - 1) ? 1 : 0;
+    __syncthreads();
+    if (!last_flag) return;
+    __threadfence();
+    // The last CTA merges the runs.  First the maxima and sums of all (row, run), loaded side by side and
+    // turned into one weight a (row, run) in shared memory; then the outputs, runs added in order.
+    constexpr int MAXS = 64;
+    float* wgt = reinterpret_cast<float*>(smem_raw);            // [16][MAXS] weights, then [16] totals
+    float* tot_s = wgt + 16 * MAXS;
+    const size_t stride = (size_t)p.n_tokens * p.heads;
+    for (int e = threadIdx.x; e < 16 * p.n_splits; e += DWARPS * 32) {
+        const int r = e / p.n_splits, sp = e % p.n_splits;
+        float m = -INFINITY, l = 0.f;
+        if (r < rows_valid) {
+            const size_t idx = sp * stride + (size_t)(q_begin + r / group) * p.heads + kvh * group + r % group;
+            m = __ldcg(p.part_ml + idx * 2);
+            l = __ldcg(p.part_ml + idx * 2 + 1);
+        }
+        wgt[r * MAXS + sp] = (l > 0.f) ? m : -INFINITY;      // for now the maximum (or -inf for an empty run)
+        wgt[16 * MAXS + 16 + r * MAXS + sp] = l;               // and the sum, behind the totals
+    }
+    __syncthreads();
+    if (threadIdx.x < 16) {
+        const int r = threadIdx.x;
+        float mx = -INFINITY;
+        for (int sp = 0; sp < p.n_splits; ++sp) mx = fmaxf(mx, wgt[r * MAXS + sp]);
+        float tot = 0.f;
+        for (int sp = 0; sp < p.n_splits; ++sp) {
+            const float m = wgt[r * MAXS + sp];
+            const float w = (m == -INFINITY) ? 0.f : exp2f(m - mx);
+            wgt[r * MAXS + sp] = w;
+            tot += wgt[16 * MAXS + 16 + r * MAXS + sp] * w;
+        }
+        tot_s[r] = tot;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 16 * D; e += DWARPS * 32) {
+        const int r = e / D, d = e % D;
+        if (r >= rows_valid) continue;
+        const size_t idx0 = (size_t)(q_begin + r / group) * p.heads + kvh * group + r % group;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int sp = 0; sp < p.n_splits; ++sp) acc += __ldcg(p.part_o + (sp * stride + idx0) * D + d) * wgt[r * MAXS + sp];
+        const float tot = tot_s[r];
+        p.out[idx0 * D + d] = __float2bfloat16_rn(tot > 0.f ? acc / tot : 0.f);
+    }
+    if (threadIdx.x == 0) counters[tile] = 0;
+}
+
+template <int D>
+cudaError_t launch_decode_d(const AttnParams& p, int n_seqs, int* counters, cudaStream_t stream) {
+    constexpr int smem = DWARPS * 2 * 2 * DKB * (D + 8) * 2;
+    static_assert(2 * 2 * DKB * (D + 8) * 2 >= (16 * D + 32) * 4, "a warp's buffers must hold its merged result");
+    static_assert(DWARPS * 2 * 2 * DKB * (D + 8) * 2 >= (2 * 16 * 64 + 16) * 4, "the merge of the runs needs its weights");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    return launch(attention_decode_kernel<D>, dim3(n_seqs, p.kv_heads, p.n_splits), dim3(DWARPS * 32, 1, 1), smem, stream, p,
+                  counters);
+}
+
 template <int D, int WARPS>
 cudaError_t launch_one(const AttnParams& p, int n_tiles, cudaStream_t stream) {
     constexpr int smem = 2 * 2 * KB * (D + 8) * (int)sizeof(__nv_bfloat16);
@@ -398,6 +695,52 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
         case 96: return launch_d<96>(p, warps, n_tiles, stream);
         case 112: return launch_d<112>(p, warps, n_tiles, stream);
         case 128: return launch_d<128>(p, warps, n_tiles, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, const void* k_cache, const void* v_cache,
+                                    const int* cu_q, const int* q_start, const int* block_table, int table_stride,
+                                    int n_seqs, int n_pages, int n_tokens, int heads, int kv_heads, int head_dim,
+                                    int page_size, int window, float scale, int n_splits, float* part_o, float* part_ml,
+                                    int* counters, cudaStream_t stream) {
+    if (n_seqs == 0 || n_tokens == 0) return cudaSuccess;
+    if (!attention_mma_supports(head_dim, heads, kv_heads, 1) || page_size % 16 != 0) return cudaErrorInvalidValue;
+    if (n_splits < 1) n_splits = 1;
+    if (n_splits > 64) return cudaErrorInvalidValue;   // the merge keeps a weight a run in shared memory
+    if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return cudaErrorInvalidValue;
+    AttnParams p;
+    p.qkv = (const __nv_bfloat16*)qkv;
+    p.qkv_stride = qkv_stride;
+    p.out = (__nv_bfloat16*)out;
+    p.k_cache = (const __nv_bfloat16*)k_cache;
+    p.v_cache = (const __nv_bfloat16*)v_cache;
+    p.cu_q = cu_q;
+    p.q_start = q_start;
+    p.block_table = block_table;
+    p.table_stride = table_stride;
+    p.tiles = nullptr;
+    p.n_pages = n_pages;
+    p.heads = heads;
+    p.kv_heads = kv_heads;
+    p.page_size = page_size;
+    p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.tokens_per_tile = 16 / (heads / kv_heads);
+    p.n_splits = n_splits;
+    p.part_o = part_o;
+    p.part_ml = part_ml;
+    p.n_tokens = n_tokens;
+    p.status = nullptr;
+    switch (head_dim) {
+        case 16: return launch_decode_d<16>(p, n_seqs, counters, stream);
+        case 32: return launch_decode_d<32>(p, n_seqs, counters, stream);
+        case 48: return launch_decode_d<48>(p, n_seqs, counters, stream);
+        case 64: return launch_decode_d<64>(p, n_seqs, counters, stream);
+        case 80: return launch_decode_d<80>(p, n_seqs, counters, stream);
+        case 96: return launch_decode_d<96>(p, n_seqs, counters, stream);
+        case 112: return launch_decode_d<112>(p, n_seqs, counters, stream);
+        case 128: return launch_decode_d<128>(p, n_seqs, counters, stream);
     }
     return cudaErrorInvalidValue;
 }

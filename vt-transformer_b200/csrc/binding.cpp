@@ -85,15 +85,16 @@ void rmsnorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, doubl
                                      stream_of(x)), "rmsnorm");
 }
 
-void silu_mul(const Tensor& gu, Tensor& out) {
+void silu_mul(const Tensor& gu, Tensor& out, int64_t interleave) {
     check_cuda(gu, "gu"); check_cuda(out, "out");
     TORCH_CHECK(gu.dim() == 2 && out.dim() == 2 && gu.size(1) == 2 * out.size(1) && gu.size(0) == out.size(0),
                 "silu_mul: gu must be [tokens, 2 * inter] and out [tokens, inter]");
     TORCH_CHECK(gu.scalar_type() == out.scalar_type(), "silu_mul: one dtype");
     TORCH_CHECK(out.size(1) % 8 == 0, "silu_mul: intermediate size ", out.size(1), " must be a multiple of 8");
     c10::cuda::CUDAGuard guard(gu.device());
+    TORCH_CHECK(interleave == 0 || interleave == 8, "silu_mul: interleave must be 0 or 8");
     check_launch(vtb::launch_silu_mul(dtype_code(gu, "gu"), gu.data_ptr(), out.data_ptr(), gu.size(0), out.size(1),
-                                      stream_of(gu)), "silu_mul");
+                                      interleave, stream_of(gu)), "silu_mul");
 }
 
 void check_cache(const Tensor& k_cache, const Tensor& v_cache, const Tensor& ref, int kv_heads, int head_dim) {
@@ -175,12 +176,16 @@ void gemm_skinny(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, T
 }
 
 void gemm_tc(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tensor& out, c10::optional<Tensor> status,
-             c10::optional<Tensor> scratch, c10::optional<Tensor> counters) {
+             c10::optional<Tensor> scratch, c10::optional<Tensor> counters, int64_t epilogue) {
     check_cuda(x, "x"); check_cuda(w, "w"); check_cuda(out, "out");
     TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16, "gemm_tc: x and w must be bfloat16");
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm_tc: 2-d tensors");
     const int m = x.size(0), k = x.size(1), n = w.size(0);
-    TORCH_CHECK(w.size(1) == k && out.size(0) == m && out.size(1) == n, "gemm_tc: shapes [m,k] x [n,k] -> [m,n]");
+    TORCH_CHECK(epilogue == 0 || epilogue == 1, "gemm_tc: epilogue must be 0 (bias) or 1 (silu(gate) * up)");
+    TORCH_CHECK(w.size(1) == k && out.size(0) == m && out.size(1) == (epilogue == 1 ? n / 2 : n),
+                "gemm_tc: shapes [m,k] x [n,k] -> [m,n] (or [m,n/2] with the silu epilogue)");
+    TORCH_CHECK(epilogue == 0 || (n % 16 == 0 && !bias.has_value() && out.scalar_type() == torch::kBFloat16),
+                "gemm_tc: the silu epilogue takes n % 16 == 0, no bias and a bfloat16 out");
     TORCH_CHECK(k % 8 == 0, "gemm_tc: inner size ", k, " must be a multiple of 8 (TMA rows start on 16-byte boundaries)");
     TORCH_CHECK(((uintptr_t)x.data_ptr() & 15) == 0 && ((uintptr_t)w.data_ptr() & 15) == 0,
                 "gemm_tc: x and w must start on 16-byte boundaries");
@@ -202,8 +207,8 @@ void gemm_tc(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tenso
         cn = counters->numel();
     }
     c10::cuda::CUDAGuard guard(x.device());
-    check_launch(vtb::launch_gemm_tc(dtype_code(out, "out"), x.data_ptr(), w.data_ptr(), bp, out.data_ptr(), m, n, k, sp, sn,
-                                     cp, cn, status_ptr(status), stream_of(x)), "gemm_tc");
+    check_launch(vtb::launch_gemm_tc(dtype_code(out, "out"), x.data_ptr(), w.data_ptr(), bp, out.data_ptr(), m, n, k,
+                                     (int)epilogue, sp, sn, cp, cn, status_ptr(status), stream_of(x)), "gemm_tc");
 }
 
 bool attention_mma_supports(int64_t head_dim, int64_t heads, int64_t kv_heads, int64_t warps) {
@@ -255,6 +260,46 @@ void attention_mma(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const 
                                            k_cache.size(0), n_tokens, heads, kv_heads, head_dim, k_cache.size(2), window,
                                            (float)scale, warps, n_splits, po, pm, status_ptr(status), stream_of(qkv)),
                  "attention_mma");
+}
+
+void attention_decode(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache, const Tensor& cu_q,
+                      const Tensor& q_start, const Tensor& block_table, int64_t heads, int64_t kv_heads, int64_t head_dim,
+                      int64_t window, double scale, int64_t n_splits, c10::optional<Tensor> part_o,
+                      c10::optional<Tensor> part_ml, c10::optional<Tensor> counters) {
+    check_cuda(qkv, "qkv"); check_cuda(out, "out"); check_i32(cu_q, "cu_q"); check_i32(q_start, "q_start");
+    check_i32(block_table, "block_table");
+    TORCH_CHECK(qkv.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16,
+                "attention_decode: bfloat16 only");
+    TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) >= heads * head_dim, "attention_decode: qkv must hold the queries first");
+    TORCH_CHECK(out.dim() == 2 && out.size(0) == qkv.size(0) && out.size(1) == heads * head_dim,
+                "attention_decode: out must be [tokens, heads * head_dim]");
+    TORCH_CHECK(heads % kv_heads == 0 && vtb::attention_mma_supports(head_dim, heads, kv_heads, 1),
+                "attention_decode: head_dim ", head_dim, " with ", heads / std::max<int64_t>(kv_heads, 1),
+                " heads in a group is not supported (head_dim a multiple of 16 up to 128, group <= 16)");
+    check_cache(k_cache, v_cache, qkv, kv_heads, head_dim);
+    TORCH_CHECK(k_cache.size(2) % 16 == 0, "attention_decode: page size must be a multiple of 16");
+    const int n_seqs = cu_q.numel() - 1, n_tokens = qkv.size(0);
+    TORCH_CHECK(q_start.numel() == n_seqs && block_table.dim() == 2 && block_table.size(0) == n_seqs,
+                "attention_decode: one q_start and one block-table row for each sequence");
+    float *po = nullptr, *pm = nullptr;
+    int* pc = nullptr;
+    if (n_splits > 1) {
+        TORCH_CHECK(part_o.has_value() && part_ml.has_value() && counters.has_value(),
+                    "attention_decode: runs need scratch tensors and counters");
+        check_f32(*part_o, "part_o"); check_f32(*part_ml, "part_ml"); check_i32(*counters, "counters");
+        TORCH_CHECK(part_o->numel() >= n_splits * n_tokens * heads * head_dim &&
+                        part_ml->numel() >= n_splits * n_tokens * heads * 2 && counters->numel() >= n_seqs * kv_heads,
+                    "attention_decode: scratch too small");
+        po = part_o->data_ptr<float>();
+        pm = part_ml->data_ptr<float>();
+        pc = counters->data_ptr<int>();
+    }
+    c10::cuda::CUDAGuard guard(qkv.device());
+    check_launch(vtb::launch_attention_decode(qkv.data_ptr(), qkv.size(1), out.data_ptr(), k_cache.data_ptr(),
+                                              v_cache.data_ptr(), cu_q.data_ptr<int>(), q_start.data_ptr<int>(),
+                                              block_table.data_ptr<int>(), block_table.size(1), n_seqs, k_cache.size(0),
+                                              n_tokens, heads, kv_heads, head_dim, k_cache.size(2), window, (float)scale,
+                                              n_splits, po, pm, pc, stream_of(qkv)), "attention_decode");
 }
 
 void attention_simt(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache,
@@ -309,7 +354,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("embedding", &embedding, py::arg("table"), py::arg("ids"), py::arg("out"), py::arg("status") = py::none());
     m.def("rmsnorm", &rmsnorm, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("eps"), py::arg("out"),
           py::arg("rows") = py::none(), py::arg("status") = py::none());
-    m.def("silu_mul", &silu_mul, py::arg("gu"), py::arg("out"));
+    m.def("silu_mul", &silu_mul, py::arg("gu"), py::arg("out"), py::arg("interleave") = 0);
     m.def("rope_store", &rope_store, py::arg("qkv"), py::arg("positions"), py::arg("cos_sin"), py::arg("k_cache"),
           py::arg("v_cache"), py::arg("token_seq"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),
           py::arg("head_dim"), py::arg("store"), py::arg("status") = py::none());
@@ -319,13 +364,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("status") = py::none());
     m.def("gemm_skinny", &gemm_skinny, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"));
     m.def("gemm_tc", &gemm_tc, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"), py::arg("status") = py::none(),
-          py::arg("scratch") = py::none(), py::arg("counters") = py::none());
+          py::arg("scratch") = py::none(), py::arg("counters") = py::none(), py::arg("epilogue") = 0);
     m.def("attention_mma_supports", &attention_mma_supports);
     m.def("attention_mma", &attention_mma, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
           py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("tiles"), py::arg("heads"),
           py::arg("kv_heads"), py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("warps"),
           py::arg("n_splits"), py::arg("part_o") = py::none(), py::arg("part_ml") = py::none(),
           py::arg("status") = py::none());
+    m.def("attention_decode", &attention_decode, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
+          py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),
+          py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("n_splits"), py::arg("part_o") = py::none(),
+          py::arg("part_ml") = py::none(), py::arg("counters") = py::none());
     m.def("argmax", &argmax, py::arg("logits"), py::arg("out"));
     m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"),
           py::arg("u"), py::arg("out"));

@@ -111,7 +111,7 @@ cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const flo
 // ------------------------------------------------------------------------- silu * up
 
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tokens, int inter) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tokens, int inter, int interleave) {
     pdl_launch();
     pdl_wait();
     const int per_row = inter / 8;
@@ -120,22 +120,25 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
         const int t = (int)(e / per_row);
         const int i = (int)(e % per_row) * 8;
         float g[8], u[8], y[8];
-        Vec8<T>::load(gu + (size_t)t * 2 * inter + i, g);
-        Vec8<T>::load(gu + (size_t)t * 2 * inter + inter + i, u);
+        const T* row = gu + (size_t)t * 2 * inter;
+        Vec8<T>::load(row + (interleave ? 2 * i : i), g);
+        Vec8<T>::load(row + (interleave ? 2 * i + 8 : inter + i), u);
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[j] = g[j] / (1.f + expf(-g[j])) * u[j];
         Vec8<T>::store(out + (size_t)t * inter + i, y);
     }
 }
 
-cudaError_t launch_silu_mul(int dtype, const void* gu, void* out, int n_tokens, int inter, cudaStream_t stream) {
+cudaError_t launch_silu_mul(int dtype, const void* gu, void* out, int n_tokens, int inter, int interleave,
+                            cudaStream_t stream) {
+    if (interleave != 0 && interleave != 8) return cudaErrorInvalidValue;
     const size_t total = (size_t)n_tokens * (inter / 8);
     if (total == 0) return cudaSuccess;
     const int threads = 256;
     const int blocks = (int)min((size_t)148 * 16, (total + threads - 1) / threads);
     if (dtype == kBF16)
-        return launch(silu_mul_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter);
-    return launch(silu_mul_kernel<float>, blocks, threads, 0, stream, (const float*)gu, (float*)out, n_tokens, inter);
+        return launch(silu_mul_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, interleave);
+    return launch(silu_mul_kernel<float>, blocks, threads, 0, stream, (const float*)gu, (float*)out, n_tokens, inter, interleave);
 }
 
 // ------------------------------------------------------------------------- rotation + cache store

@@ -12,10 +12,12 @@
 //     covers the machine; each CTA leaves its share in a scratch buffer and counts itself in; the
 //     CTA that arrives last adds the shares in rank order and stores (no CTA waits for another).
 //
-// One CTA computes one tile.  Warp 0 issues the TMA loads (one elected thread), warp 1 owns the
-// tensor memory and issues the MMAs (one elected thread), warps 2..5 read the accumulator back
-// (tcgen05.ld, each warp its quarter of the 128 lanes) and store.  A ring of STAGES stages of 64 k
-// (128-byte rows, 128-byte swizzle) lies between them, with a full and an empty mbarrier a stage.
+// The kernel is persistent: one CTA an SM, each taking tiles in turn.  Warp 0 issues the TMA loads
+// (one elected thread), warp 1 owns the tensor memory and issues the MMAs (one elected thread), warps
+// 2..5 read the accumulator back (tcgen05.ld, each warp its quarter of the 128 lanes) and store.  A
+// ring of STAGES stages of 64 k (128-byte rows, 128-byte swizzle) lies between loads and MMAs, with a
+// full and an empty mbarrier a stage, and runs on across tiles.  The accumulator is double-buffered
+// in tensor memory, so the epilogue of a tile runs under the MMAs of the next one.
 // TMA fills what lies outside a matrix with zeros, so any M, N and K (K % 8 == 0) is taken.
 // Every wait on a barrier is bounded by a clock limit; a wait that runs out records it in the status
 // word and the CTA winds down: tensor memory is freed and the kernel returns.
@@ -42,6 +44,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 // Waits for the phase with the given parity; false if the clock limit ran out first.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
@@ -123,11 +128,73 @@ template <> __device__ __forceinline__ void store8<float>(float* p, const float*
     *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
 }
 
+// Writes 16 finished sums of one accumulator lane: columns c0 .. c0 + 15 of lane r of the tile.
+// EPI 0: out = sum + bias.  EPI 1 (gate and up rows of w interleaved in runs of 8: g0..g7, u0..u7,
+// g8.., ...): out[token, 8 j + i] = silu(sum of row 16 j + i) * (sum of row 16 j + 8 + i), in 32-bit,
+// silu(z) = z / (1 + exp(-z)) (v1/tensortype/cuda_kernels/silu_product.cu:15-17); out has half the
+// columns.  Every lane of a warp must call it (the swapped form trades values between lanes).
+template <bool SWAP, int EPI, typename TOut>
+__device__ __forceinline__ void emit16(float (&v)[16], int r, int a_row0, int b_row0, int c0, int rows_a, int rows_b,
+                                       const float* __restrict__ bias, TOut* __restrict__ out, int ldo) {
+    if (SWAP) {
+        const int n = a_row0 + r;                  // feature (row of w)
+        if (EPI == 1) {
+            const bool gate = (r & 8) == 0;
+            const int f = ((n >> 4) << 3) + (n & 7);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[i], 8);
+                const int m = b_row0 + c0 + i;     // token
+                if (gate && n < rows_a && m < rows_b)
+                    out[(size_t)m * ldo + f] = from_float<TOut>(v[i] / (1.f + expf(-v[i])) * other);
+            }
+        } else if (n < rows_a) {
+            const float b = bias ? bias[n] : 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int m = b_row0 + c0 + i;
+                if (m < rows_b) out[(size_t)m * ldo + n] = from_float<TOut>(v[i] + b);
+            }
+        }
+    } else {
+        const int m = a_row0 + r;                  // token
+        if (m >= rows_a) return;
+        const int n0 = b_row0 + c0;                // feature of v[0]
+        if (EPI == 1) {
+            if (n0 + 16 > rows_b) return;          // rows of w come in whole runs of 16
+            float act[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) act[j] = v[j] / (1.f + expf(-v[j])) * v[8 + j];
+            TOut* o = out + (size_t)m * ldo + (n0 >> 1);
+            if ((ldo & 7) == 0) {
+                store8<TOut>(o, act);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = from_float<TOut>(act[j]);
+            }
+            return;
+        }
+        TOut* o = out + (size_t)m * ldo + n0;
+        if (bias) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] += (n0 + i < rows_b) ? bias[n0 + i] : 0.f;
+        }
+        if ((ldo & 7) == 0 && n0 + 16 <= rows_b) {
+            store8<TOut>(o, v);
+            store8<TOut>(o + 8, v + 8);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (n0 + i < rows_b) o[i] = from_float<TOut>(v[i]);
+        }
+    }
+}
+
 // BN: rows of the other operand in a tile (columns of the accumulator).  SWAP: the 128-row operand is w.
-template <int BN, int STAGES, bool SWAP, typename TOut>
+template <int BN, int STAGES, bool SWAP, int EPI, typename TOut>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo,
+               const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo, int ksplit,
                float* __restrict__ scratch, int* __restrict__ counters, int* status) {
     constexpr int B_STAGE = BN * BK * 2;
     constexpr int COLS = BN < 32 ? 32 : BN;          // tensor-memory columns: a power of two, at least 32
@@ -137,31 +204,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     unsigned char* b_s = smem + STAGES * A_STAGE;
     uint64_t* full = reinterpret_cast<uint64_t*>(b_s + STAGES * B_STAGE);
     uint64_t* empty = full + STAGES;
-    uint64_t* acc_done = empty + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+    uint64_t* acc_full = empty + STAGES;       // [2]: the MMAs of a unit are done, its accumulator is whole
+    uint64_t* acc_empty = acc_full + 2;        // [2]: the epilogue has read the accumulator, it may be overwritten
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
-    const int ksplit = (int)gridDim.z, krank = (int)blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // consecutive CTAs take consecutive tiles of the 128-row operand and share the other operand's tile:
-    // for prompt portions the weights' tile is fetched from HBM once and then found in L2
-    const int a_row0 = blockIdx.x * BM, b_row0 = blockIdx.y * BN;
+    const int a_tiles = (rows_a + BM - 1) / BM, b_tiles = (rows_b + BN - 1) / BN;
+    const int units = a_tiles * b_tiles * ksplit;
     const int nkb_all = (k + BK - 1) / BK;
-    const int per = (nkb_all + ksplit - 1) / ksplit;
-    const int kb0 = krank * per, kb1 = min(nkb_all, kb0 + per);
-    const int nkb = max(0, kb1 - kb0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(acc_done, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);       // one arrival from each epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(COLS));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(2 * COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
     tc_fence_before();
@@ -173,30 +239,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     pdl_launch();
     pdl_wait();
 
+    // A CTA takes the units blockIdx.x, blockIdx.x + gridDim.x, ...  A unit is (tile of the 128-row operand,
+    // tile of the other operand, share of k), the first index running fastest: CTAs that run together
+    // share the other operand's tile, which is then fetched from HBM once and found in L2 after.
     if (warp == 0) {
         if (lane == 0) {
-            for (int it = 0; it < nkb; ++it) {
-                const int s = it % STAGES;
-                if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) { timed_out = true; break; }
-                mbar_expect_tx(&full[s], A_STAGE + B_STAGE);
-                tma_load_2d(a_s + s * A_STAGE, &map_a, (kb0 + it) * BK, a_row0, &full[s]);
-                tma_load_2d(b_s + s * B_STAGE, &map_b, (kb0 + it) * BK, b_row0, &full[s]);
+            int kit = 0;                               // k-blocks loaded so far, over all units: ring position
+            for (int u = blockIdx.x; u < units && !timed_out; u += gridDim.x) {
+                const int a_row0 = (u % a_tiles) * BM, b_row0 = ((u / a_tiles) % b_tiles) * BN;
+                const int krank = u / (a_tiles * b_tiles);
+                const int kb0 = (int)((long long)krank * nkb_all / ksplit), kb1 = (int)((long long)(krank + 1) * nkb_all / ksplit);
+                for (int kb = kb0; kb < kb1; ++kb, ++kit) {
+                    const int s = kit % STAGES;
+                    if (kit >= STAGES && !mbar_wait(&empty[s], ((kit / STAGES) & 1) ^ 1)) { timed_out = true; break; }
+                    mbar_expect_tx(&full[s], A_STAGE + B_STAGE);
+                    tma_load_2d(a_s + s * A_STAGE, &map_a, kb * BK, a_row0, &full[s]);
+                    tma_load_2d(b_s + s * B_STAGE, &map_b, kb * BK, b_row0, &full[s]);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(BM, BN);
-            for (int it = 0; it < nkb; ++it) {
-                const int s = it % STAGES;
-                if (!mbar_wait(&full[s], (it / STAGES) & 1)) { timed_out = true; break; }
+            int kit = 0, ui = 0;
+            for (int u = blockIdx.x; u < units && !timed_out; u += gridDim.x, ++ui) {
+                const int krank = u / (a_tiles * b_tiles);
+                const int kb0 = (int)((long long)krank * nkb_all / ksplit), kb1 = (int)((long long)(krank + 1) * nkb_all / ksplit);
+                const int buf = ui & 1;
+                // the accumulator of two units ago must have been read
+                if (ui >= 2 && !mbar_wait(&acc_empty[buf], ((ui >> 1) & 1) ^ 1)) { timed_out = true; break; }
                 tc_fence_after();
-                const uint64_t ad = smem_desc(a_s + s * A_STAGE), bd = smem_desc(b_s + s * B_STAGE);
+                const uint32_t acc = tmem + (uint32_t)(buf * COLS);
+                for (int kb = kb0; kb < kb1; ++kb, ++kit) {
+                    const int s = kit % STAGES;
+                    if (!mbar_wait(&full[s], (kit / STAGES) & 1)) { timed_out = true; break; }
+                    tc_fence_after();
+                    const uint64_t ad = smem_desc(a_s + s * A_STAGE), bd = smem_desc(b_s + s * B_STAGE);
 #pragma unroll
-                for (int kk = 0; kk < BK / 16; ++kk)   // 16 k = 32 bytes further along the swizzled row
-                    tc_mma(tmem, ad + 2 * kk, bd + 2 * kk, idesc, (it > 0 || kk > 0) ? 1u : 0u);
-                tc_commit(&empty[s]);                  // the stage is free when these MMAs have read it
+                    for (int kk = 0; kk < BK / 16; ++kk)   // 16 k = 32 bytes further along the swizzled row
+                        tc_mma(acc, ad + 2 * kk, bd + 2 * kk, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+                    tc_commit(&empty[s]);                  // the stage is free when these MMAs have read it
+                }
+                tc_commit(&acc_full[buf]);                 // the accumulator is whole when all MMAs are done
             }
-            tc_commit(acc_done);                       // the accumulator is whole when all MMAs are done
         }
     }
     __syncwarp();
@@ -205,71 +290,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp >= 2) {
         const int q = warp & 3;
         const int r = q * 32 + lane;                   // lane of the accumulator = row of the 128-row operand
-        bool ok = true;
-        if (nkb > 0) ok = mbar_wait(acc_done, 0);
-        if (!ok) timed_out = true;
-        tc_fence_after();
-        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-        float* mine = scratch + ((size_t)tile * ksplit + krank) * (BN * BM);     // this CTA's share [BN][128]
+        int ui = 0;
+        for (int u = blockIdx.x; u < units; u += gridDim.x, ++ui) {
+            const int a_tile = u % a_tiles, b_tile = (u / a_tiles) % b_tiles, krank = u / (a_tiles * b_tiles);
+            const int a_row0 = a_tile * BM, b_row0 = b_tile * BN;
+            const int buf = ui & 1;
+            bool ok = !timed_out && mbar_wait(&acc_full[buf], (ui >> 1) & 1);
+            if (!ok) timed_out = true;
+            tc_fence_after();
+            const int tile = b_tile * a_tiles + a_tile;
+            float* mine = scratch + ((size_t)tile * ksplit + krank) * (BN * BM);     // this unit's share [BN][128]
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-            float v[16];
-            if (nkb > 0 && ok) {
-                uint32_t raw[16];
-                tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, raw);
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                if (ok) {
+                    uint32_t raw[16];
+                    tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * COLS + c0), raw);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(raw[i]);
-            } else {
+                    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(raw[i]);
+                } else {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                }
+                if (c0 + 16 >= BN) {
+                    // the last columns are in registers: the MMA warp may overwrite this accumulator
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                }
+                if (ksplit > 1) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) __stcg(mine + (c0 + i) * BM + r, v[i]);
+                    continue;
+                }
+                emit16<SWAP, EPI, TOut>(v, r, a_row0, b_row0, c0, rows_a, rows_b, bias, out, ldo);
             }
             if (ksplit > 1) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) __stcg(mine + (c0 + i) * BM + r, v[i]);
-                continue;
-            }
-            if (SWAP) {
-                const int n = a_row0 + r;              // feature
-                if (n < rows_a) {
-                    const float b = bias ? bias[n] : 0.f;
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int m = b_row0 + c0 + i; // token
-                        if (m < rows_b) out[(size_t)m * ldo + n] = from_float<TOut>(v[i] + b);
-                    }
-                }
-            } else {
-                const int m = a_row0 + r;              // token
-                if (m < rows_a) {
-                    const int n0 = b_row0 + c0;        // feature of v[0]
-                    TOut* o = out + (size_t)m * ldo + n0;
-                    if (bias) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) v[i] += (n0 + i < rows_b) ? bias[n0 + i] : 0.f;
-                    }
-                    if ((ldo & 7) == 0 && n0 + 16 <= rows_b) {
-                        store8<TOut>(o, v);
-                        store8<TOut>(o + 8, v + 8);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            if (n0 + i < rows_b) o[i] = from_float<TOut>(v[i]);
-                    }
-                }
-            }
-        }
-        if (ksplit > 1) {
-            // count this CTA in; the one that finds all others counted adds the shares and stores
-            __threadfence();
-            asm volatile("bar.sync 1, 128;\n" ::: "memory");
-            if (threadIdx.x == 64) *last_flag = (atomicAdd(&counters[tile], 1) == ksplit - 1) ? 1 : 0;
-            asm volatile("bar.sync 1, 128;\n" ::: "memory");
-            if (*last_flag) {
+                // count this unit in; the one that finds all others counted adds the shares and stores
                 __threadfence();
-                const float* all = scratch + (size_t)tile * ksplit * (BN * BM);
-                const int n = a_row0 + r;
-                if (SWAP && n < rows_a) {
-                    const float b = bias ? bias[n] : 0.f;
+                asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                if (threadIdx.x == 64) *last_flag = (atomicAdd(&counters[tile], 1) == ksplit - 1) ? 1 : 0;
+                asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                const bool last = *last_flag != 0;
+                asm volatile("bar.sync 1, 128;\n" ::: "memory");   // all have read the flag before it is written again
+                if (last) {
+                    __threadfence();
+                    const float* all = scratch + (size_t)tile * ksplit * (BN * BM);
+                    const bool live = SWAP && (a_row0 + r) < rows_a;
                     // 16 columns at a time, all their loads in flight together; ranks added in order
 #pragma unroll 1
                     for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -277,28 +344,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         float sum[16];
 #pragma unroll
                         for (int i = 0; i < 16; ++i) sum[i] = 0.f;
+                        if (live) {
 #pragma unroll 4
-                        for (int rk = 0; rk < ksplit; ++rk) {
-                            const float* src = all + ((size_t)rk * BN + c0) * BM + r;
+                            for (int rk = 0; rk < ksplit; ++rk) {
+                                const float* src = all + ((size_t)rk * BN + c0) * BM + r;
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) sum[i] += __ldcg(src + i * BM);
+                                for (int i = 0; i < 16; ++i) sum[i] += __ldcg(src + i * BM);
+                            }
                         }
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const int m = b_row0 + c0 + i;
-                            if (m < rows_b) out[(size_t)m * ldo + n] = from_float<TOut>(sum[i] + b);
-                        }
+                        emit16<SWAP, EPI, TOut>(sum, r, a_row0, b_row0, c0, rows_a, rows_b, bias, out, ldo);
                     }
+                    if (threadIdx.x == 64) counters[tile] = 0;      // ready for the next launch
                 }
-                if (threadIdx.x == 64) counters[tile] = 0;      // ready for the next launch
             }
         }
     }
-    if (timed_out && status) set_status(status, kStatusWaitTimeout, blockIdx.x + blockIdx.y * gridDim.x);
+    if (timed_out && status) set_status(status, kStatusWaitTimeout, blockIdx.x);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(COLS));
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(2 * COLS));
     }
 }
 
@@ -333,7 +398,17 @@ bool make_map(CUtensorMap* map, const void* ptr, int rows, int k, int box_rows) 
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int STAGES, bool SWAP, typename TOut>
+int sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    return sms;
+}
+
+template <int BN, int STAGES, bool SWAP, int EPI, typename TOut>
 cudaError_t launch_cfg(const void* a, int rows_a, const void* b, int rows_b, int k, const float* bias, TOut* out, int ldo,
                        int ksplit, float* scratch, int* counters, int* status, cudaStream_t stream) {
     CUtensorMap map_a, map_b;
@@ -341,33 +416,30 @@ cudaError_t launch_cfg(const void* a, int rows_a, const void* b, int rows_b, int
     constexpr int smem = STAGES * (A_STAGE + BN * BK * 2) + 1024 + 256;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, EPI, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    return launch(gemm_tc_kernel<BN, STAGES, SWAP, TOut>, dim3((rows_a + BM - 1) / BM, (rows_b + BN - 1) / BN, ksplit),
-                  dim3(THREADS, 1, 1), smem, stream, map_a, map_b, bias, out, rows_a, rows_b, k, ldo, scratch, counters, status);
+    const int units = ((rows_a + BM - 1) / BM) * ((rows_b + BN - 1) / BN) * ksplit;
+    return launch(gemm_tc_kernel<BN, STAGES, SWAP, EPI, TOut>, dim3(units < sm_count() ? units : sm_count(), 1, 1),
+                  dim3(THREADS, 1, 1), smem, stream, map_a, map_b, bias, out, rows_a, rows_b, k, ldo, ksplit, scratch, counters,
+                  status);
 }
 
-template <typename TOut>
+template <int EPI, typename TOut>
 cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* out, int m, int n, int k, float* scratch,
                          long long scratch_floats, int* counters, int n_counters, int* status, cudaStream_t stream) {
     if (m <= 64) {
         // swapped: w is the 128-row operand.  One CTA fits an SM, so the CTAs run in waves of one an SM;
         // cut k over s CTAs so that the last wave is full, counting a fixed cost a CTA (set-up, filling
         // the ring, the merge) as a few k-blocks: least waves * (k-blocks a CTA + cost).
-        static int sms = 0;
-        if (sms == 0) {
-            int dev = 0;
-            cudaGetDevice(&dev);
-            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-        }
+        const int sms = sm_count();
         const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
         const int tiles = (n + BM - 1) / BM, nkb = (k + BK - 1) / BK;
         int ksplit = 1;
         long best = -1;
         for (int s = 1; s <= 16; ++s) {
-            if (s > 1 && (nkb / s < 4 || scratch == nullptr || counters == nullptr || tiles > n_counters ||
+            if (s > 1 && (nkb / s < 4 || s > nkb || scratch == nullptr || counters == nullptr || tiles > n_counters ||
                           (long long)tiles * s * bn * BM > scratch_floats))
                 break;
             const long waves = (tiles * s + sms - 1) / sms;
@@ -377,28 +449,34 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
                 ksplit = s;
             }
         }
-        if (bn == 16) return launch_cfg<16, 8, true, TOut>(w, n, x, m, k, bias, out, n, ksplit, scratch, counters, status, stream);
-        if (bn == 32) return launch_cfg<32, 8, true, TOut>(w, n, x, m, k, bias, out, n, ksplit, scratch, counters, status, stream);
-        return launch_cfg<64, 6, true, TOut>(w, n, x, m, k, bias, out, n, ksplit, scratch, counters, status, stream);
+        if (bn == 16) return launch_cfg<16, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, ksplit, scratch, counters, status, stream);
+        if (bn == 32) return launch_cfg<32, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, ksplit, scratch, counters, status, stream);
+        return launch_cfg<64, 6, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, ksplit, scratch, counters, status, stream);
     }
     if (n <= 128 || m <= 128)
-        return launch_cfg<128, 4, false, TOut>(x, m, w, n, k, bias, out, n, 1, nullptr, nullptr, status, stream);
-    return launch_cfg<256, 4, false, TOut>(x, m, w, n, k, bias, out, n, 1, nullptr, nullptr, status, stream);
+        return launch_cfg<128, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, EPI == 1 ? n / 2 : n, 1, nullptr, nullptr, status, stream);
+    return launch_cfg<256, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, EPI == 1 ? n / 2 : n, 1, nullptr, nullptr, status, stream);
 }
 
 }  // namespace
 
 cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n, int k,
-                           float* scratch, long long scratch_floats, int* counters, int n_counters, int* status,
-                           cudaStream_t stream) {
+                           int epilogue, float* scratch, long long scratch_floats, int* counters, int n_counters,
+                           int* status, cudaStream_t stream) {
     if (m == 0 || n == 0) return cudaSuccess;
     if (k % 8 != 0 || k < 8) return cudaErrorInvalidValue;
+    if (epilogue == 1) {
+        if (n % 16 != 0 || bias != nullptr || out_dtype != kBF16) return cudaErrorInvalidValue;
+        return launch_typed<1, __nv_bfloat16>(x, w, nullptr, (__nv_bfloat16*)out, m, n, k, scratch, scratch_floats,
+                                              counters, n_counters, status, stream);
+    }
+    if (epilogue != 0) return cudaErrorInvalidValue;
     if (out_dtype == kBF16)
-        return launch_typed<__nv_bfloat16>(x, w, bias, (__nv_bfloat16*)out, m, n, k, scratch, scratch_floats, counters,
-                                           n_counters, status, stream);
+        return launch_typed<0, __nv_bfloat16>(x, w, bias, (__nv_bfloat16*)out, m, n, k, scratch, scratch_floats, counters,
+                                              n_counters, status, stream);
     if (out_dtype == kF32)
-        return launch_typed<float>(x, w, bias, (float*)out, m, n, k, scratch, scratch_floats, counters, n_counters, status,
-                                   stream);
+        return launch_typed<0, float>(x, w, bias, (float*)out, m, n, k, scratch, scratch_floats, counters, n_counters,
+                                      status, stream);
     return cudaErrorInvalidValue;
 }
 

@@ -20,8 +20,11 @@ cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const flo
                            void* out, const int* rows, int n_rows, int n_tokens, int hidden, int* status,
                            cudaStream_t stream);
 
-// out[t, i] = silu(gu[t, i]) * gu[t, inter + i].  inter % 8 == 0.
-cudaError_t launch_silu_mul(int dtype, const void* gu, void* out, int n_tokens, int inter, cudaStream_t stream);
+// out[t, i] = silu(gate) * up.  interleave 0: gate = gu[t, i], up = gu[t, inter + i].  interleave 8: gate and up
+// columns alternate in runs of 8 (g0..g7, u0..u7, g8.., ...): gate = gu[t, 16 (i / 8) + i % 8], up 8 further.
+// inter % 8 == 0.
+cudaError_t launch_silu_mul(int dtype, const void* gu, void* out, int n_tokens, int inter, int interleave,
+                            cudaStream_t stream);
 
 // Rotates q (in place) and k by the token's position and stores k and v into the pages.
 // qkv [n_tokens, (heads + 2 kv_heads) * head_dim]; cos_sin [max_pos, head_dim / 2] of (cos, sin);
@@ -56,9 +59,11 @@ cudaError_t launch_gemm_skinny(int out_dtype, const void* x, const void* w, cons
 // if a bounded wait inside the kernel runs out.  scratch (floats) and counters (ints, zero before the
 // first launch; the kernel leaves them zero) let a small batch cut k over several CTAs; without them
 // k is not cut.  Launches that share them must not overlap on the GPU.
+// epilogue 0: out[M, N] = sums + bias.  epilogue 1 (bfloat16 out, no bias, N % 16 == 0): the rows of w are
+// gate and up rows interleaved in runs of 8 (g0..g7, u0..u7, g8.., ...) and out[M, N / 2] = silu(gate) * up.
 cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n, int k,
-                           float* scratch, long long scratch_floats, int* counters, int n_counters, int* status,
-                           cudaStream_t stream);
+                           int epilogue, float* scratch, long long scratch_floats, int* counters, int n_counters,
+                           int* status, cudaStream_t stream);
 
 // Tensor-core attention over the paged cache (bfloat16).  A tile is 16 * warps rows, row r being
 // (token r / group, head r % group); `tiles` lists (sequence, first token) pairs, or is null when
@@ -71,6 +76,16 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
                                  const int* tiles, int n_tiles, int n_pages, int n_tokens, int heads, int kv_heads,
                                  int head_dim, int page_size, int window, float scale, int warps, int n_splits,
                                  float* part_o, float* part_ml, int* status, cudaStream_t stream);
+
+// Attention of single-token steps: every sequence brings tokens_per_tile = 16 / group tokens at most (one in a
+// decode step).  Grid (sequences, kv_heads, n_splits), four warps a CTA.  With n_splits > 1 the runs' results
+// pass through part_o [splits, tokens, heads, head_dim] and part_ml [splits, tokens, heads, 2], and
+// counters [sequences * kv_heads] (zero before the first launch; left zero) tells the last CTA to merge.
+cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, const void* k_cache, const void* v_cache,
+                                    const int* cu_q, const int* q_start, const int* block_table, int table_stride,
+                                    int n_seqs, int n_pages, int n_tokens, int heads, int kv_heads, int head_dim,
+                                    int page_size, int window, float scale, int n_splits, float* part_o, float* part_ml,
+                                    int* counters, cudaStream_t stream);
 
 // out[r] = index of the largest logit of row r (the lowest index among equals).
 cudaError_t launch_argmax(const float* logits, int* out, int n_rows, int vocab, cudaStream_t stream);

@@ -51,9 +51,42 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     return out
 
 
-def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    backend().silu_mul(gu, out)
+def silu_mul(gu: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> torch.Tensor:
+    """out = silu(gate) * up.  ``interleave`` 0: gu = [gate | up]; 8: gate and up columns alternate in
+    runs of 8 (``interleave_gate_up``)."""
+    backend().silu_mul(gu, out, interleave)
     return out
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """Packs the rows of the gate and up matrices [I, H] into one matrix [2 I, H] in runs of 8:
+    g0..g7, u0..u7, g8..g15, u8..u15, ...  One product over it gives gate and up of the same 8
+    features side by side, so that silu(gate) * up can be formed where the product's result lies
+    (a thread's registers) and only [T, I] is written."""
+    inter, hidden = w_gate.shape
+    if inter % 8:
+        raise ValueError(f"intermediate size {inter} must be a multiple of 8")
+    return torch.stack([w_gate.view(inter // 8, 8, hidden), w_up.view(inter // 8, 8, hidden)], dim=1).reshape(
+        2 * inter, hidden).contiguous()
+
+
+def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, status=None) -> torch.Tensor:
+    """out[T, I] = silu(x Wg^T) * (x Wu^T) for ``w_gate_up = interleave_gate_up(Wg, Wu)``.  bfloat16: one
+    tcgen05 kernel whose epilogue forms the product from the 32-bit sums.  Otherwise the product
+    into [T, 2 I] and the elementwise kernel."""
+    be = backend()
+    if x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and FUSE_SILU and \
+            not (x.shape[0] <= SKINNY_MAX_ROWS and SMALL_BATCH_KERNEL == "skinny"):
+        scratch, counters = _split_workspace(x.device)
+        be.gemm_tc(x, w_gate_up, None, out, status, scratch, counters, 1)
+        return out
+    gu = torch.empty((x.shape[0], w_gate_up.shape[0]), dtype=x.dtype, device=x.device)
+    linear(x, w_gate_up, None, gu, status)
+    be.silu_mul(gu, out, 8)
+    return out
+
+
+FUSE_SILU = True    # False: always the separate elementwise kernel (tests compare the two)
 
 
 def rope_store(qkv, positions, cos_sin, k_cache, v_cache, token_seq, block_table, heads: int, kv_heads: int,
@@ -145,15 +178,15 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
     group = heads // kv_heads
     if qkv.dtype == torch.bfloat16 and ATTENTION_KERNEL == "auto":
         if ctx.max_q_len == 1 and be.attention_mma_supports(head_dim, heads, kv_heads, 1):
-            span = ctx.max_kv_len if not w else min(ctx.max_kv_len, w + 63)
-            n_blocks = max(1, -(-span // 64))
-            splits = max(1, min(n_blocks, -(-DECODE_TARGET_CTAS // (ctx.n_seqs * kv_heads)), 32))
-            part_o = part_ml = None
+            span = ctx.max_kv_len if not w else min(ctx.max_kv_len, w + 31)
+            splits = _decode_splits(ctx.n_seqs * kv_heads, max(1, -(-span // 32)), qkv.device)
+            part_o = part_ml = counters = None
             if splits > 1:
                 part_o = torch.empty((splits, ctx.n_tokens, heads, head_dim), dtype=torch.float32, device=qkv.device)
                 part_ml = torch.empty((splits, ctx.n_tokens, heads, 2), dtype=torch.float32, device=qkv.device)
-            be.attention_mma(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, None, heads, kv_heads,
-                             head_dim, w, float(scale), 1, splits, part_o, part_ml, status)
+                counters = _attention_counters(qkv.device, ctx.n_seqs * kv_heads)
+            be.attention_decode(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, heads, kv_heads,
+                                head_dim, w, float(scale), splits, part_o, part_ml, counters)
             return out
         if be.attention_mma_supports(head_dim, heads, kv_heads, 4):
             tiles = _attention_tiles(ctx, 64 // group, qkv.device)
@@ -165,7 +198,36 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
     return out
 
 
-DECODE_TARGET_CTAS = 444    # three one-warp CTAs of the split-key kernel fit an SM (shared memory), 148 SMs
+_sm_counts = {}
+_counters = {}
+
+
+def _decode_splits(pairs: int, blocks: int, device) -> int:
+    """Into how many runs the keys of a sequence are cut in a single-token step.  One CTA of the kernel
+    fits an SM, so CTAs run in waves of one an SM: least waves * (rounds of four 32-key blocks a CTA +
+    a fixed cost of a CTA, counted as three rounds)."""
+    sms = _sm_counts.get(device)
+    if sms is None:
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        _sm_counts[device] = sms
+    best, best_cost = 1, None
+    for s in range(1, 33):
+        if s > 1 and blocks // s < 2:
+            break
+        waves = -(-pairs * s // sms)
+        cost = waves * (-(-blocks // (4 * s)) + 3 + (1 if s > 1 else 0))
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
+
+
+def _attention_counters(device, n: int) -> torch.Tensor:
+    """Arrival counters of the decode attention's runs: zero, and left zero by every launch."""
+    c = _counters.get(device)
+    if c is None or c.numel() < n:
+        c = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
+        _counters[device] = c
+    return c
 
 
 # --------------------------------------------------------------------------- sampling
@@ -192,5 +254,5 @@ def _counted(fn):
     return wrapper
 
 
-for _name in ("embedding", "rmsnorm", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):
+for _name in ("embedding", "rmsnorm", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # linear_silu_mul counts through linear or below
     globals()[_name] = _counted(globals()[_name])

@@ -11,7 +11,8 @@ class GatedMLP(FeedForward):
     """down(silu(gate(h)) * up(h)) without biases, silu(z) = z / (1 + exp(-z)) in 32-bit
     (v1/models/qwen2-7b/inference_fp16.dag:333-337,
     v1/tensortype/cuda_kernels/silu_product.cu:15-17).  Gate and up are one product over
-    the packed rows of the two matrices."""
+    the rows of the two matrices interleaved in runs of 8 (``ops.interleave_gate_up``), so
+    that the activation can be formed in the product's epilogue."""
 
     graph_safe = True
 
@@ -35,7 +36,7 @@ class GatedMLP(FeedForward):
         mats = [rt.param(get(f"{p}{n}.weight")) for n in (g, u)]
         if mats[0].dtype != mats[1].dtype:
             mats = [m.float() for m in mats]
-        self.w_gate_up = torch.cat(mats, dim=0).contiguous()
+        self.w_gate_up = rt.ops.interleave_gate_up(mats[0], mats[1])
         del mats
         self.w_down = rt.param(get(f"{p}{d}.weight"))
 
@@ -46,10 +47,8 @@ class GatedMLP(FeedForward):
     def forward(self, h, ctx):
         s, ops = self.spec, self.rt.ops
         T = h.shape[0]
-        gu = torch.empty((T, 2 * s.inter), dtype=h.dtype, device=h.device)
-        ops.linear(h, self.w_gate_up, None, gu)
         act = torch.empty((T, s.inter), dtype=h.dtype, device=h.device)
-        ops.silu_mul(gu, act)
+        ops.linear_silu_mul(h, self.w_gate_up, act)
         out = torch.empty((T, s.hidden), dtype=h.dtype, device=h.device)
         ops.linear(act, self.w_down, None, out)
         return out
