@@ -235,9 +235,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     bool timed_out = false;
-    // barriers and tensor memory are set up; from here on global memory is touched
+    // Barriers and tensor memory are set up.  The kernels before this one in the stream may still be
+    // running (programmatic dependent launch): nothing they write may be read, and nothing they read may
+    // be written, before pdl_wait.  The weights are written by no kernel, so the loader starts to fetch
+    // the first stages of the weight operand at once; x, the bias and all stores wait.
     pdl_launch();
-    pdl_wait();
 
     // A CTA takes the units blockIdx.x, blockIdx.x + gridDim.x, ...  A unit is (tile of the 128-row operand,
     // tile of the other operand, share of k), the first index running fastest: CTAs that run together
@@ -245,11 +247,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         if (lane == 0) {
             int kit = 0;                               // k-blocks loaded so far, over all units: ring position
+            bool waited = false;
             for (int u = blockIdx.x; u < units && !timed_out; u += gridDim.x) {
                 const int a_row0 = (u % a_tiles) * BM, b_row0 = ((u / a_tiles) % b_tiles) * BN;
                 const int krank = u / (a_tiles * b_tiles);
                 const int kb0 = (int)((long long)krank * nkb_all / ksplit), kb1 = (int)((long long)(krank + 1) * nkb_all / ksplit);
-                for (int kb = kb0; kb < kb1; ++kb, ++kit) {
+                int kb = kb0;
+                if (!waited) {
+                    // first unit: the weight halves of the first stages go out before the wait
+                    const int early = min(STAGES, kb1 - kb0);
+                    for (int i = 0; i < early; ++i) {
+                        mbar_expect_tx(&full[i], A_STAGE + B_STAGE);
+                        if (SWAP) tma_load_2d(a_s + i * A_STAGE, &map_a, (kb0 + i) * BK, a_row0, &full[i]);
+                        else tma_load_2d(b_s + i * B_STAGE, &map_b, (kb0 + i) * BK, b_row0, &full[i]);
+                    }
+                    pdl_wait();
+                    waited = true;
+                    for (int i = 0; i < early; ++i) {
+                        if (SWAP) tma_load_2d(b_s + i * B_STAGE, &map_b, (kb0 + i) * BK, b_row0, &full[i]);
+                        else tma_load_2d(a_s + i * A_STAGE, &map_a, (kb0 + i) * BK, a_row0, &full[i]);
+                    }
+                    kb += early;
+                    kit += early;
+                }
+                for (; kb < kb1; ++kb, ++kit) {
                     const int s = kit % STAGES;
                     if (kit >= STAGES && !mbar_wait(&empty[s], ((kit / STAGES) & 1) ^ 1)) { timed_out = true; break; }
                     mbar_expect_tx(&full[s], A_STAGE + B_STAGE);
@@ -285,6 +306,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     }
     __syncwarp();
+    pdl_wait();    // every thread waits before it stores or leaves (the loader did so above already)
 
     // ---- epilogue: warps 2..5, each its quarter of the lanes --------------------------------------
     if (warp >= 2) {
