@@ -194,8 +194,8 @@ __device__ __forceinline__ void emit16(float (&v)[16], int r, int a_row0, int b_
 template <int BN, int STAGES, bool SWAP, int EPI, typename TOut>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo, int ksplit,
-               float* __restrict__ scratch, int* __restrict__ counters, int* status) {
+               const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo, int n_full,
+               int s_tail, float* __restrict__ scratch, int* __restrict__ counters, int* status) {
     constexpr int B_STAGE = BN * BK * 2;
     constexpr int COLS = BN < 32 ? 32 : BN;          // tensor-memory columns: a power of two, at least 32
     extern __shared__ unsigned char smem_raw[];
@@ -211,8 +211,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a_tiles = (rows_a + BM - 1) / BM, b_tiles = (rows_b + BN - 1) / BN;
-    const int units = a_tiles * b_tiles * ksplit;
+    // Units of work: the first n_full tiles whole, every tile after them cut into s_tail shares of k.
+    const int units = n_full + (a_tiles * b_tiles - n_full) * s_tail;
     const int nkb_all = (k + BK - 1) / BK;
+    auto unit_of = [&](int u, int& tile, int& krank, int& ks) {
+        if (u < n_full) { tile = u; krank = 0; ks = 1; }
+        else { const int t = u - n_full; tile = n_full + t / s_tail; krank = t % s_tail; ks = s_tail; }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -249,9 +254,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int kit = 0;                               // k-blocks loaded so far, over all units: ring position
             bool waited = false;
             for (int u = blockIdx.x; u < units && !timed_out; u += gridDim.x) {
-                const int a_row0 = (u % a_tiles) * BM, b_row0 = ((u / a_tiles) % b_tiles) * BN;
-                const int krank = u / (a_tiles * b_tiles);
-                const int kb0 = (int)((long long)krank * nkb_all / ksplit), kb1 = (int)((long long)(krank + 1) * nkb_all / ksplit);
+                int tile, krank, ks;
+                unit_of(u, tile, krank, ks);
+                const int a_row0 = (tile % a_tiles) * BM, b_row0 = (tile / a_tiles) * BN;
+                const int kb0 = (int)((long long)krank * nkb_all / ks), kb1 = (int)((long long)(krank + 1) * nkb_all / ks);
                 int kb = kb0;
                 if (!waited) {
                     // first unit: the weight halves of the first stages go out before the wait
@@ -284,8 +290,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t idesc = instr_desc(BM, BN);
             int kit = 0, ui = 0;
             for (int u = blockIdx.x; u < units && !timed_out; u += gridDim.x, ++ui) {
-                const int krank = u / (a_tiles * b_tiles);
-                const int kb0 = (int)((long long)krank * nkb_all / ksplit), kb1 = (int)((long long)(krank + 1) * nkb_all / ksplit);
+                int tile, krank, ks;
+                unit_of(u, tile, krank, ks);
+                const int kb0 = (int)((long long)krank * nkb_all / ks), kb1 = (int)((long long)(krank + 1) * nkb_all / ks);
                 const int buf = ui & 1;
                 // the accumulator of two units ago must have been read
                 if (ui >= 2 && !mbar_wait(&acc_empty[buf], ((ui >> 1) & 1) ^ 1)) { timed_out = true; break; }
@@ -314,14 +321,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int r = q * 32 + lane;                   // lane of the accumulator = row of the 128-row operand
         int ui = 0;
         for (int u = blockIdx.x; u < units; u += gridDim.x, ++ui) {
-            const int a_tile = u % a_tiles, b_tile = (u / a_tiles) % b_tiles, krank = u / (a_tiles * b_tiles);
-            const int a_row0 = a_tile * BM, b_row0 = b_tile * BN;
+            int tile, krank, ksplit;
+            unit_of(u, tile, krank, ksplit);
+            const int a_row0 = (tile % a_tiles) * BM, b_row0 = (tile / a_tiles) * BN;
+            const int cut = tile - n_full;              // index among the tiles that are cut
             const int buf = ui & 1;
             bool ok = !timed_out && mbar_wait(&acc_full[buf], (ui >> 1) & 1);
             if (!ok) timed_out = true;
             tc_fence_after();
-            const int tile = b_tile * a_tiles + a_tile;
-            float* mine = scratch + ((size_t)tile * ksplit + krank) * (BN * BM);     // this unit's share [BN][128]
+            float* mine = scratch + ((size_t)cut * ksplit + krank) * (BN * BM);      // this unit's share [BN][128]
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 float v[16];
@@ -351,14 +359,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 // count this unit in; the one that finds all others counted adds the shares and stores
                 __threadfence();
                 asm volatile("bar.sync 1, 128;\n" ::: "memory");
-                if (threadIdx.x == 64) *last_flag = (atomicAdd(&counters[tile], 1) == ksplit - 1) ? 1 : 0;
+                if (threadIdx.x == 64) *last_flag = (atomicAdd(&counters[cut], 1) == ksplit - 1) ? 1 : 0;
                 asm volatile("bar.sync 1, 128;\n" ::: "memory");
                 const bool last = *last_flag != 0;
                 asm volatile("bar.sync 1, 128;\n" ::: "memory");   // all have read the flag before it is written again
                 if (last) {
                     __threadfence();
-                    const float* all = scratch + (size_t)tile * ksplit * (BN * BM);
-                    const bool live = SWAP && (a_row0 + r) < rows_a;
+                    const float* all = scratch + (size_t)cut * ksplit * (BN * BM);
+                    const bool live = (a_row0 + r) < rows_a;
                     // 16 columns at a time, all their loads in flight together; ranks added in order
 #pragma unroll 1
                     for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -376,7 +384,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         }
                         emit16<SWAP, EPI, TOut>(sum, r, a_row0, b_row0, c0, rows_a, rows_b, bias, out, ldo);
                     }
-                    if (threadIdx.x == 64) counters[tile] = 0;      // ready for the next launch
+                    if (threadIdx.x == 64) counters[cut] = 0;       // ready for the next launch
                 }
             }
         }
@@ -432,7 +440,7 @@ int sm_count() {
 
 template <int BN, int STAGES, bool SWAP, int EPI, typename TOut>
 cudaError_t launch_cfg(const void* a, int rows_a, const void* b, int rows_b, int k, const float* bias, TOut* out, int ldo,
-                       int ksplit, float* scratch, int* counters, int* status, cudaStream_t stream) {
+                       int n_full, int s_tail, float* scratch, int* counters, int* status, cudaStream_t stream) {
     CUtensorMap map_a, map_b;
     if (!make_map(&map_a, a, rows_a, k, BM) || !make_map(&map_b, b, rows_b, k, BN)) return cudaErrorInvalidValue;
     constexpr int smem = STAGES * (A_STAGE + BN * BK * 2) + 1024 + 256;
@@ -442,10 +450,11 @@ cudaError_t launch_cfg(const void* a, int rows_a, const void* b, int rows_b, int
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    const int units = ((rows_a + BM - 1) / BM) * ((rows_b + BN - 1) / BN) * ksplit;
+    const int tiles = ((rows_a + BM - 1) / BM) * ((rows_b + BN - 1) / BN);
+    const int units = n_full + (tiles - n_full) * s_tail;
     return launch(gemm_tc_kernel<BN, STAGES, SWAP, EPI, TOut>, dim3(units < sm_count() ? units : sm_count(), 1, 1),
-                  dim3(THREADS, 1, 1), smem, stream, map_a, map_b, bias, out, rows_a, rows_b, k, ldo, ksplit, scratch, counters,
-                  status);
+                  dim3(THREADS, 1, 1), smem, stream, map_a, map_b, bias, out, rows_a, rows_b, k, ldo, n_full, s_tail, scratch,
+                  counters, status);
 }
 
 template <int EPI, typename TOut>
@@ -471,13 +480,37 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
                 ksplit = s;
             }
         }
-        if (bn == 16) return launch_cfg<16, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, ksplit, scratch, counters, status, stream);
-        if (bn == 32) return launch_cfg<32, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, ksplit, scratch, counters, status, stream);
-        return launch_cfg<64, 6, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, ksplit, scratch, counters, status, stream);
+        if (bn == 16) return launch_cfg<16, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
+        if (bn == 32) return launch_cfg<32, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
+        return launch_cfg<64, 6, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
     }
-    if (n <= 128 || m <= 128)
-        return launch_cfg<128, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, EPI == 1 ? n / 2 : n, 1, nullptr, nullptr, status, stream);
-    return launch_cfg<256, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, EPI == 1 ? n / 2 : n, 1, nullptr, nullptr, status, stream);
+    // x is the 128-row operand: tiles of 128 tokens by 256 (or 128) features, one an SM at a time.  With fewer
+    // tiles than SMs and a long k, every tile is cut into shares of k so that more SMs work.  (Cutting the
+    // tiles of the last, partial round of a larger product was tried and lost: merging the shares of a
+    // 128x256 tile costs the CTA that does it more than the shorter round saves.)
+    const int sms = sm_count();
+    const bool wide = !(n <= 128 || m <= 128);
+    const int bn = wide ? 256 : 128;
+    const int tiles = ((m + BM - 1) / BM) * ((n + bn - 1) / bn), nkb = (k + BK - 1) / BK;
+    int rem = tiles % sms, n_full = tiles - rem, s_tail = 1;
+    if (tiles < sms && scratch != nullptr && counters != nullptr && rem <= n_counters) {
+        double best = 1.0;
+        for (int s = 2; s <= 4; ++s) {
+            // a share must be long enough to pay for the merge of the shares
+            if (nkb / s < 48 || (long long)rem * s * bn * BM > scratch_floats) break;
+            const double cost = (double)((rem * s + sms - 1) / sms) / s + 0.04;
+            if (cost < best) {
+                best = cost;
+                s_tail = s;
+            }
+        }
+    }
+    if (s_tail == 1) n_full = tiles;
+    if (wide)
+        return launch_cfg<256, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, EPI == 1 ? n / 2 : n, n_full, s_tail, scratch,
+                                                     counters, status, stream);
+    return launch_cfg<128, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, EPI == 1 ? n / 2 : n, n_full, s_tail, scratch, counters,
+                                                 status, stream);
 }
 
 }  // namespace

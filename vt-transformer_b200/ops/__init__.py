@@ -132,10 +132,10 @@ _workspaces = {}
 
 def _split_workspace(device):
     """Scratch and arrival counters with which the tcgen05 kernel cuts k over CTAs for small batches:
-    4M floats and 4,096 counters a device, made once.  Launches that use them run in one stream."""
+    8M floats and 4,096 counters a device, made once.  Launches that use them run in one stream."""
     ws = _workspaces.get(device)
     if ws is None:
-        ws = (torch.empty(4 << 20, dtype=torch.float32, device=device), torch.zeros(4096, dtype=torch.int32, device=device))
+        ws = (torch.empty(8 << 20, dtype=torch.float32, device=device), torch.zeros(4096, dtype=torch.int32, device=device))
         _workspaces[device] = ws
     return ws
 
