@@ -45,6 +45,20 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
                  : "r"(s));
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(s));
+}
+
+// 2^x, the hardware approximation (2 ulp); exp2(-inf) = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -142,20 +156,29 @@ attention_mma_kernel(const AttnParams p) {
     auto load_block = [&](int blk, int stage) {
         const int kb = key_lo + blk * KB;
         constexpr int CHUNKS = D / 8;          // 16-byte pieces in a row
+        // the block's four runs of 16 keys lie in one page each: their bases once, then plain offsets
+        static_assert(KB == 64, "four runs of 16 keys");
+        size_t base[4];
+        bool okp[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            const int key = kb + 16 * h;
+            okp[h] = key < key_hi;
+            base[h] = 0;
+            if (okp[h]) {
+                const int page = table[key / p.page_size];
+                // a page behind a window may be gone already; its keys are masked below
+                if (page < 0 || page >= p.n_pages) okp[h] = false;
+                else base[h] = (((size_t)page * p.kv_heads + kvh) * p.page_size + key % p.page_size) * D;
+            }
+        }
         for (int c = threadIdx.x; c < KB * CHUNKS; c += THREADS) {
             const int r = c / CHUNKS, piece = c % CHUNKS;
-            const int key = kb + r;
-            bool ok = key < key_hi;
-            size_t off = 0;
-            if (ok) {
-                const int page = table[key / p.page_size];
-                if (page < 0 || page >= p.n_pages) {
-                    // a page behind a window may be gone already; its keys are masked below
-                    ok = false;
-                } else {
-                    off = (((size_t)page * p.kv_heads + kvh) * p.page_size + key % p.page_size) * D + piece * 8;
-                }
-            }
+            const int h = r >> 4;                  // selected without indexing, so the bases stay in registers
+            const size_t bh = h == 0 ? base[0] : h == 1 ? base[1] : h == 2 ? base[2] : base[3];
+            const bool oh = h == 0 ? okp[0] : h == 1 ? okp[1] : h == 2 ? okp[2] : okp[3];
+            const bool ok = oh && (kb + r) < key_hi;
+            const size_t off = ok ? bh + (size_t)(r & 15) * D + piece * 8 : 0;
             cp_async16(ks + ((size_t)stage * KB + r) * LD + piece * 8, p.k_cache + off, ok);
             cp_async16(vs + ((size_t)stage * KB + r) * LD + piece * 8, p.v_cache + off, ok);
         }
@@ -186,24 +209,39 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
         for (int ks_ = 0; ks_ < D / 16; ++ks_) {
 #pragma unroll
-            for (int j = 0; j < KB / 8; ++j) {
-                const __nv_bfloat16* kp = kst + (size_t)(j * 8 + gq) * LD + ks_ * 16 + 2 * tq;
-                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kp);
-                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kp + 8);
-                mma_bf16(s[j], qf[ks_], b0, b1);
+            for (int j = 0; j < KB / 8; j += 2) {
+                // four 8x8 pieces of K: (keys of tile j, d 0..7), (tile j, d 8..15), (tile j+1, d 0..7), (tile j+1, d 8..15)
+                uint32_t kf[4];
+                const int mat = lane >> 3, r = lane & 7;
+                ldmatrix_x4(kf, kst + (size_t)((j + (mat >> 1)) * 8 + r) * LD + ks_ * 16 + (mat & 1) * 8);
+                mma_bf16(s[j], qf[ks_], kf[0], kf[1]);
+                mma_bf16(s[j + 1], qf[ks_], kf[2], kf[3]);
             }
         }
         // mask, running maximum and sum (log2 domain)
         float mnew[2] = {mrow[0], mrow[1]};
+        // a block all of whose keys every row of the tile sees needs no mask
+        const bool open = (kb + KB - 1 <= pos_lo) && (p.window <= 0 || kb > pos_hi - p.window);
+        if (open) {
 #pragma unroll
-        for (int j = 0; j < KB / 8; ++j) {
+            for (int j = 0; j < KB / 8; ++j) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int i = e >> 1;
-                const int key = kb + j * 8 + 2 * tq + (e & 1);
-                const bool see = valid[i] && key <= pos[i] && (p.window <= 0 || key > pos[i] - p.window);
-                s[j][e] = see ? s[j][e] * p.scale_log2 : -INFINITY;
-                mnew[i] = fmaxf(mnew[i], s[j][e]);
+                for (int e = 0; e < 4; ++e) {
+                    s[j][e] *= p.scale_log2;
+                    mnew[e >> 1] = fmaxf(mnew[e >> 1], s[j][e]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < KB / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = e >> 1;
+                    const int key = kb + j * 8 + 2 * tq + (e & 1);
+                    const bool see = valid[i] && key <= pos[i] && (p.window <= 0 || key > pos[i] - p.window);
+                    s[j][e] = see ? s[j][e] * p.scale_log2 : -INFINITY;
+                    mnew[i] = fmaxf(mnew[i], s[j][e]);
+                }
             }
         }
         float corr[2];
@@ -211,7 +249,7 @@ attention_mma_kernel(const AttnParams p) {
         for (int i = 0; i < 2; ++i) {
             mnew[i] = fmaxf(mnew[i], __shfl_xor_sync(0xffffffffu, mnew[i], 1));
             mnew[i] = fmaxf(mnew[i], __shfl_xor_sync(0xffffffffu, mnew[i], 2));
-            corr[i] = (mnew[i] == -INFINITY) ? 1.f : exp2f(mrow[i] - mnew[i]);
+            corr[i] = (mnew[i] == -INFINITY) ? 1.f : fast_exp2(mrow[i] - mnew[i]);
             mrow[i] = mnew[i];
             lrow[i] *= corr[i];
         }
@@ -220,7 +258,7 @@ attention_mma_kernel(const AttnParams p) {
         for (int j = 0; j < KB / 8; ++j) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float pv = exp2f(s[j][e] - base[e >> 1]);   // exp2(-inf) = 0 for masked keys
+                const float pv = fast_exp2(s[j][e] - base[e >> 1]);   // 2^(-inf) = 0 for masked keys
                 s[j][e] = pv;
                 lrow[e >> 1] += pv;
             }
@@ -410,8 +448,8 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
         for (int c = lane; c < DKB * CHUNKS; c += 32) {
             const int r = c / CHUNKS, piece = c % CHUNKS;
             const int h = r >> 4;
-            const bool ok = okp[h] && (kb + r) < key_hi;
-            const size_t off = base[h] + (size_t)(r & 15) * D + piece * 8;
+            const bool ok = (h == 0 ? okp[0] : okp[1]) && (kb + r) < key_hi;
+            const size_t off = (h == 0 ? base[0] : base[1]) + (size_t)(r & 15) * D + piece * 8;
             cp_async16(ks + ((size_t)stage * DKB + r) * LD + piece * 8, p.k_cache + (ok ? off : 0), ok);
             cp_async16(vs + ((size_t)stage * DKB + r) * LD + piece * 8, p.v_cache + (ok ? off : 0), ok);
         }
@@ -644,14 +682,16 @@ cudaError_t launch_one(const AttnParams& p, int n_tiles, cudaStream_t stream) {
 
 template <int D>
 cudaError_t launch_d(const AttnParams& p, int warps, int n_tiles, cudaStream_t stream) {
-    return warps == 1 ? launch_one<D, 1>(p, n_tiles, stream) : launch_one<D, 4>(p, n_tiles, stream);
+    if (warps == 1) return launch_one<D, 1>(p, n_tiles, stream);
+    if (warps == 8) return launch_one<D, 8>(p, n_tiles, stream);
+    return launch_one<D, 4>(p, n_tiles, stream);
 }
 
 }  // namespace
 
 bool attention_mma_supports(int head_dim, int heads, int kv_heads, int warps) {
     if (head_dim % 16 != 0 || head_dim > 128 || head_dim < 16) return false;
-    if (warps != 1 && warps != 4) return false;
+    if (warps != 1 && warps != 4 && warps != 8) return false;
     return heads / kv_heads <= 16 * warps;
 }
 

@@ -171,8 +171,8 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
     """Attention of the step's tokens over the paged keys and values of their sequences.
     ``ctx`` is the step's ``StepContext``.  bfloat16 runs on the tensor cores where the kernel
     takes the sizes (head_dim a multiple of 16 up to 128): single-token steps with the keys of a
-    sequence split over several CTAs, other steps in tiles of 64 rows of (token, head of the
-    group).  Everything else, and all of float32, runs the plain kernel."""
+    sequence split over several CTAs, other steps in tiles of 64 or 128 rows of (token, head of
+    the group).  Everything else, and all of float32, runs the plain kernel."""
     be = backend()
     w = int(window) if window else 0
     group = heads // kv_heads
@@ -188,10 +188,12 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
             be.attention_decode(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, heads, kv_heads,
                                 head_dim, w, float(scale), splits, part_o, part_ml, counters)
             return out
-        if be.attention_mma_supports(head_dim, heads, kv_heads, 4):
-            tiles = _attention_tiles(ctx, 64 // group, qkv.device)
+        # tiles of 128 rows (8 warps) where the portions are long enough to fill them, else of 64
+        warps = 8 if ctx.max_q_len * group >= 128 and be.attention_mma_supports(head_dim, heads, kv_heads, 8) else 4
+        if be.attention_mma_supports(head_dim, heads, kv_heads, warps):
+            tiles = _attention_tiles(ctx, (16 * warps) // group, qkv.device)
             be.attention_mma(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, tiles, heads, kv_heads,
-                             head_dim, w, float(scale), 4, 1, None, None, status)
+                             head_dim, w, float(scale), warps, 1, None, None, status)
             return out
     be.attention_simt(qkv, out, k_cache, v_cache, ctx.positions, ctx.token_seq, block_table, heads, kv_heads,
                       head_dim, w, float(scale), status)
