@@ -263,10 +263,12 @@ attention_mma_kernel(const AttnParams p) {
                 lrow[e >> 1] += pv;
             }
         }
+        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // no maximum moved: nothing to rescale
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
-            o[i][0] *= corr[0]; o[i][1] *= corr[0];
-            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            for (int i = 0; i < D / 8; ++i) {
+                o[i][0] *= corr[0]; o[i][1] *= corr[0];
+                o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            }
         }
         // O += P V
 #pragma unroll
@@ -516,10 +518,12 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
                 lrow[e >> 1] += pv;
             }
         }
+        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // no maximum moved: nothing to rescale
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
-            o[i][0] *= corr[0]; o[i][1] *= corr[0];
-            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            for (int i = 0; i < D / 8; ++i) {
+                o[i][0] *= corr[0]; o[i][1] *= corr[0];
+                o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            }
         }
 #pragma unroll
         for (int kk = 0; kk < DKB / 16; ++kk) {

@@ -153,11 +153,13 @@ ATTENTION_KERNEL = "auto"   # "auto", or "simt" to force the plain kernel (tests
 
 def _attention_tiles(ctx, tokens_per_tile: int, device):
     """(sequence, first token) for every tile of the step: each sequence's new tokens in runs of
-    ``tokens_per_tile``.  Built once a step and kept in ``ctx.extras``."""
+    ``tokens_per_tile``, ordered by falling number of keys.  Built once a step and kept in ``ctx.extras``."""
     key = ("attention_tiles", tokens_per_tile)
     tiles = ctx.extras.get(key)
     if tiles is None:
         pairs = [(i, a) for i, s in enumerate(ctx.seqs) for a in range(0, s.length, tokens_per_tile)]
+        # the tiles with the most keys first: the CTAs that start last are then the short ones
+        pairs.sort(key=lambda p: -(ctx.seqs[p[0]].start + p[1]))
         host = torch.tensor(pairs, dtype=torch.int32).view(-1, 2)
         if torch.device(device).type == "cuda":
             host = host.pin_memory()
