@@ -13,9 +13,13 @@
 // A tile is 16 * WARPS rows; row r is (token r / group, head r % group) of its tile.  Keys come in
 // blocks of 64 through a two-stage cp.async pipeline; a run of 16 keys never crosses a page
 // (page_size % 16 == 0).  S = Q K^T and O += P V are mma.sync m16n8k16 (P rounded to bfloat16).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "launch.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace vtb {
 
@@ -83,6 +87,7 @@ struct AttnParams {
     float* part_ml;         // [splits, tokens, heads, 2] running maximum (log2 domain) and sum
     int n_tokens;
     int* status;
+    int cluster_merge;      // 1: the runs of a sequence are the CTAs of a cluster and merge through their shared memory
 };
 
 template <int D, int WARPS>
@@ -565,6 +570,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
     __syncthreads();
     // merge the four warps: every thread takes elements (row, d) of the [16][D] output
     const int tile = seq * p.kv_heads + kvh;
+    float* res = reinterpret_cast<float*>(smem_raw + (size_t)DWARPS * WARP_BYTES);   // [16][D], then maxima [16], sums [16]
     for (int e = threadIdx.x; e < 16 * D; e += DWARPS * 32) {
         const int r = e / D, d = e % D;
         if (r >= rows_valid) continue;
@@ -588,6 +594,12 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
         const int t = q_begin + r / group, h = kvh * group + r % group;
         if (p.n_splits == 1) {
             p.out[((size_t)t * p.heads + h) * D + d] = __float2bfloat16_rn(tot > 0.f ? acc / tot : 0.f);
+        } else if (p.cluster_merge) {
+            res[e] = acc;
+            if (d == 0) {
+                res[16 * D + r] = mx;
+                res[16 * D + 16 + r] = tot;
+            }
         } else {
             const size_t idx = ((size_t)split * p.n_tokens + t) * p.heads + h;
             __stcg(p.part_o + idx * D + d, acc);
@@ -596,6 +608,37 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
                 __stcg(p.part_ml + idx * 2 + 1, tot);
             }
         }
+    }
+    if (p.n_splits == 1) return;
+    if (p.cluster_merge) {
+        // the runs are the CTAs of one cluster: each takes a share of the elements and reads every
+        // CTA's result through distributed shared memory, runs added in rank order
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        const int ranks = (int)cluster.num_blocks(), me = (int)cluster.block_rank();
+        for (int e = me * DWARPS * 32 + threadIdx.x; e < 16 * D; e += ranks * DWARPS * 32) {
+            const int r = e / D, d = e % D;
+            if (r >= rows_valid) continue;
+            float mx = -INFINITY;
+            for (int rk = 0; rk < ranks; ++rk) {
+                const float* o_r = cluster.map_shared_rank(res, rk);
+                if (o_r[16 * D + 16 + r] > 0.f) mx = fmaxf(mx, o_r[16 * D + r]);
+            }
+            float acc = 0.f, tot = 0.f;
+            for (int rk = 0; rk < ranks; ++rk) {
+                const float* o_r = cluster.map_shared_rank(res, rk);
+                const float l = o_r[16 * D + 16 + r];
+                if (l > 0.f) {
+                    const float wgt = exp2f(o_r[16 * D + r] - mx);
+                    acc += o_r[e] * wgt;
+                    tot += l * wgt;
+                }
+            }
+            const int t = q_begin + r / group, h = kvh * group + r % group;
+            p.out[((size_t)t * p.heads + h) * D + d] = __float2bfloat16_rn(tot > 0.f ? acc / tot : 0.f);
+        }
+        cluster.sync();    // nobody leaves while its shared memory is still being read
+        return;
     }
     if (p.n_splits == 1) return;
     __threadfence();
@@ -651,7 +694,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
 
 template <int D>
 cudaError_t launch_decode_d(const AttnParams& p, int n_seqs, int* counters, cudaStream_t stream) {
-    constexpr int smem = DWARPS * 2 * 2 * DKB * (D + 8) * 2;
+    constexpr int smem = DWARPS * 2 * 2 * DKB * (D + 8) * 2 + (16 * D + 32) * 4;
     static_assert(2 * 2 * DKB * (D + 8) * 2 >= (16 * D + 32) * 4, "a warp's buffers must hold its merged result");
     static_assert(DWARPS * 2 * 2 * DKB * (D + 8) * 2 >= (2 * 16 * 64 + 16) * 4, "the merge of the runs needs its weights");
     static bool configured = false;
@@ -660,8 +703,8 @@ cudaError_t launch_decode_d(const AttnParams& p, int n_seqs, int* counters, cuda
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    return launch(attention_decode_kernel<D>, dim3(n_seqs, p.kv_heads, p.n_splits), dim3(DWARPS * 32, 1, 1), smem, stream, p,
-                  counters);
+    return launch(attention_decode_kernel<D>, dim3(n_seqs, p.kv_heads, p.n_splits), dim3(DWARPS * 32, 1, 1), smem, stream,
+                  dim3(1, 1, p.cluster_merge ? p.n_splits : 1), p, counters);
 }
 
 template <int D, int WARPS>
@@ -708,6 +751,7 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
     if (!attention_mma_supports(head_dim, heads, kv_heads, warps) || page_size % 16 != 0) return cudaErrorInvalidValue;
     if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return cudaErrorInvalidValue;
     AttnParams p;
+    p.cluster_merge = 0;
     p.qkv = (const __nv_bfloat16*)qkv;
     p.qkv_stride = qkv_stride;
     p.out = (__nv_bfloat16*)out;
@@ -752,8 +796,11 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
     if (!attention_mma_supports(head_dim, heads, kv_heads, 1) || page_size % 16 != 0) return cudaErrorInvalidValue;
     if (n_splits < 1) n_splits = 1;
     if (n_splits > 64) return cudaErrorInvalidValue;   // the merge keeps a weight a run in shared memory
-    if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return cudaErrorInvalidValue;
+    // up to 8 runs are the CTAs of a cluster and need no scratch; more go through scratch and a counter
+    const bool cluster = n_splits > 1 && n_splits <= 8;
+    if (n_splits > 8 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return cudaErrorInvalidValue;
     AttnParams p;
+    p.cluster_merge = cluster ? 1 : 0;
     p.qkv = (const __nv_bfloat16*)qkv;
     p.qkv_stride = qkv_stride;
     p.out = (__nv_bfloat16*)out;

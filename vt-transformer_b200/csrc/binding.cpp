@@ -283,9 +283,9 @@ void attention_decode(const Tensor& qkv, Tensor& out, const Tensor& k_cache, con
                 "attention_decode: one q_start and one block-table row for each sequence");
     float *po = nullptr, *pm = nullptr;
     int* pc = nullptr;
-    if (n_splits > 1) {
+    if (n_splits > 8) {
         TORCH_CHECK(part_o.has_value() && part_ml.has_value() && counters.has_value(),
-                    "attention_decode: runs need scratch tensors and counters");
+                    "attention_decode: more than 8 runs need scratch tensors and counters");
         check_f32(*part_o, "part_o"); check_f32(*part_ml, "part_ml"); check_i32(*counters, "counters");
         TORCH_CHECK(part_o->numel() >= n_splits * n_tokens * heads * head_dim &&
                         part_ml->numel() >= n_splits * n_tokens * heads * 2 && counters->numel() >= n_seqs * kv_heads,

@@ -183,7 +183,7 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
             span = ctx.max_kv_len if not w else min(ctx.max_kv_len, w + 31)
             splits = _decode_splits(ctx.n_seqs * kv_heads, max(1, -(-span // 32)), qkv.device)
             part_o = part_ml = counters = None
-            if splits > 1:
+            if splits > 8:
                 part_o = torch.empty((splits, ctx.n_tokens, heads, head_dim), dtype=torch.float32, device=qkv.device)
                 part_ml = torch.empty((splits, ctx.n_tokens, heads, 2), dtype=torch.float32, device=qkv.device)
                 counters = _attention_counters(qkv.device, ctx.n_seqs * kv_heads)
@@ -218,8 +218,11 @@ def _decode_splits(pairs: int, blocks: int, device) -> int:
     for s in range(1, 33):
         if s > 1 and blocks // s < 2:
             break
-        waves = -(-pairs * s // sms)
-        cost = waves * (-(-blocks // (4 * s)) + 3 + (1 if s > 1 else 0))
+        # up to 8 runs are the CTAs of a thread-block cluster (merged through shared memory; clusters
+        # pack into the GPCs with some loss); more runs meet in scratch, which costs more
+        slots = sms if s == 1 else (int(sms * 0.86) // s * s if s <= 8 else sms)
+        waves = -(-pairs * s // max(slots, 1))
+        cost = waves * (-(-blocks // (4 * s)) + 3 + (0 if s == 1 else 0.5 if s <= 8 else 2))
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
     return best
