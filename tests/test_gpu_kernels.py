@@ -204,6 +204,47 @@ def test_single_token_steps_split_the_keys(heads, kv_heads, d, page_size, window
         at += n
 
 
+@pytest.mark.parametrize("heads,kv_heads,d,page_size,window,rotate", [(28, 4, 128, 16, None, True), (6, 2, 48, 32, 40, True),
+                                                                      (4, 4, 16, 16, None, True), (8, 1, 64, 16, None, False)])
+def test_single_token_step_rotates_and_stores_inside_the_attention_kernel(heads, kv_heads, d, page_size, window, rotate):
+    """A decode step's rotation, cache store and attention as one kernel against the same as two kernels:
+    the same output, the same page contents, for a run that writes the cache and for one that only reads."""
+    import helpers
+    from vt_transformer_b200 import ops as o
+    from vt_transformer_b200.parts.rope import rotation_table
+    dtype = torch.bfloat16
+    torch.manual_seed(14)
+    seq_lens = [1, 300, 64, 65, 33, 17]                   # the new token is the last of each
+    total = sum(seq_lens)
+    k = torch.randn(total, kv_heads, d, device=DEV).to(dtype)
+    v = torch.randn(total, kv_heads, d, device=DEV).to(dtype)
+    kc0, vc0, table = paged_cache(k, v, seq_lens, page_size, 700 // page_size + 8, dtype, seed=4)
+    kc0, vc0 = torch.nan_to_num(kc0), torch.nan_to_num(vc0)
+    T = len(seq_lens)
+    qkv0 = torch.randn(T, (heads + 2 * kv_heads) * d, device=DEV).to(dtype)
+    cs = rotation_table(400, d, 10000.0).to(DEV) if rotate else None
+    ctx = helpers.step_context([1] * T, [n - 1 for n in seq_lens], DEV)
+    results = {}
+    for store in (True, False):
+        for fused in (True, False):
+            o.FUSE_ROPE = fused
+            try:
+                qkv, kc, vc = qkv0.clone(), kc0.clone(), vc0.clone()
+                out = torch.empty(T, heads * d, device=DEV, dtype=dtype)
+                status = torch.zeros(2, dtype=torch.int32, device=DEV)
+                o.rope_attention(qkv, out, cs, kc, vc, ctx, table, heads, kv_heads, d, window, 1 / math.sqrt(d), store=store,
+                                 status=status)
+                assert status.tolist() == [0, 0]
+                results[(store, fused)] = (out, kc, vc)
+            finally:
+                o.FUSE_ROPE = True
+        a, b = results[(store, True)], results[(store, False)]
+        close(a[0], b[0].double().cpu(), dtype, 2)
+        assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])          # the pages hold the same bits
+        assert torch.equal(a[1], kc0) != store                               # and were written iff the run stores
+    assert float((results[(True, True)][0].float() - results[(False, True)][0].float()).abs().max()) > 0.01
+
+
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 33, 64])
 @pytest.mark.parametrize("n,k", [(40, 64), (301, 72), (1000, 344), (4608, 3584), (100, 18944)])
 def test_weight_streaming_product(m, n, k):

@@ -88,6 +88,13 @@ struct AttnParams {
     int n_tokens;
     int* status;
     int cluster_merge;      // 1: the runs of a sequence are the CTAs of a cluster and merge through their shared memory
+    // single-token steps may rotate q and k and store k and v themselves (no separate kernel before them)
+    int fuse_rope;          // 1: q and k in qkv are not rotated yet and the token's k and v are not in the cache yet
+    const float2* cos_sin;  // [max_pos, D / 2] (cos, sin), or null: no rotation
+    int max_pos;
+    int store_kv;           // 1: write the token's k and v into their page
+    __nv_bfloat16* k_out;   // the cache again, writable
+    __nv_bfloat16* v_out;
 };
 
 template <int D, int WARPS>
@@ -430,6 +437,31 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
             qf[ks_][i + 2] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp + ks_ * 16 + 8 + 2 * tq) : 0u;
         }
     }
+    if (p.fuse_rope && p.cos_sin != nullptr) {
+        // rotate q in registers: the 8-wide chunk u of the first half pairs with chunk u + D / 16 (pairs (i, i + D/2),
+        // v1/tensortype/cuda_kernels/rotary_embed.cu:19-29); 32-bit arithmetic, one rounding, as the separate kernel does
+        constexpr int HC = D / 16;             // 8-wide chunks in half a head
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if (!valid[i]) continue;
+            if (pos[i] >= p.max_pos) {
+                if (tq == 0) set_status(p.status, kStatusBadPosition, pos[i]);
+                continue;
+            }
+            const float2* cs = p.cos_sin + (size_t)pos[i] * (D / 2);
+#pragma unroll
+            for (int u = 0; u < HC; ++u) {
+                const int v = u + HC;
+                uint32_t& xa = qf[u / 2][(u % 2) * 2 + i];
+                uint32_t& ya = qf[v / 2][(v % 2) * 2 + i];
+                const float2 x = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xa));
+                const float2 y = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&ya));
+                const float2 c0 = cs[u * 8 + 2 * tq], c1 = cs[u * 8 + 2 * tq + 1];
+                xa = pack_bf16(x.x * c0.x - y.x * c0.y, x.y * c1.x - y.y * c1.y);
+                ya = pack_bf16(y.x * c0.x + x.x * c0.y, y.y * c1.x + x.y * c1.y);
+            }
+        }
+    }
     float o[D / 8][4];
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -481,6 +513,47 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
         const __nv_bfloat16* kst = ks + (size_t)stage * DKB * LD;
         const __nv_bfloat16* vst = vs + (size_t)stage * DKB * LD;
         const int kb = key_lo + blk * DKB;
+        if (p.fuse_rope && p.store_kv && pos_lo >= kb && pos_lo < kb + DKB) {
+            // the step's own token lies in this block: its k (rotated) and v come from qkv and go into the
+            // block in shared memory and into their page.  (A run of a layer that only reads another run's
+            // cache finds the token's k and v there already.)
+            const int r = pos_lo - kb;
+            const __nv_bfloat16* krow = p.qkv + (size_t)q_begin * p.qkv_stride + (size_t)(p.heads + kvh) * D;
+            const __nv_bfloat16* vrow = krow + (size_t)p.kv_heads * D;
+            __nv_bfloat16* ksm = ks + ((size_t)stage * DKB + r) * LD;
+            __nv_bfloat16* vsm = vs + ((size_t)stage * DKB + r) * LD;
+            __nv_bfloat16 *kg = nullptr, *vg = nullptr;
+            {
+                const int page = table[pos_lo / p.page_size];
+                if (page >= 0 && page < p.n_pages) {
+                    const size_t off = (((size_t)page * p.kv_heads + kvh) * p.page_size + pos_lo % p.page_size) * D;
+                    kg = p.k_out + off;
+                    vg = p.v_out + off;
+                } else if (lane == 0) {
+                    set_status(p.status, kStatusBadPage, page);
+                }
+            }
+            const bool rot = p.cos_sin != nullptr && pos_lo < p.max_pos;
+            const float2* cs = p.cos_sin + (size_t)(rot ? pos_lo : 0) * (D / 2);
+            for (int i = lane; i < D / 2; i += 32) {
+                const float a = __bfloat162float(krow[i]), b = __bfloat162float(krow[i + D / 2]);
+                __nv_bfloat16 ka = krow[i], kb2 = krow[i + D / 2];
+                if (rot) {
+                    const float2 c = cs[i];
+                    ka = __float2bfloat16_rn(a * c.x - b * c.y);
+                    kb2 = __float2bfloat16_rn(b * c.x + a * c.y);
+                }
+                ksm[i] = ka;
+                ksm[i + D / 2] = kb2;
+                if (kg) { kg[i] = ka; kg[i + D / 2] = kb2; }
+            }
+            for (int i = lane; i < D; i += 32) {
+                const __nv_bfloat16 vv = vrow[i];
+                vsm[i] = vv;
+                if (vg) vg[i] = vv;
+            }
+            __syncwarp();
+        }
         float s[DKB / 8][4];
 #pragma unroll
         for (int j = 0; j < DKB / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -752,6 +825,12 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
     if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return cudaErrorInvalidValue;
     AttnParams p;
     p.cluster_merge = 0;
+    p.fuse_rope = 0;
+    p.cos_sin = nullptr;
+    p.max_pos = 0;
+    p.store_kv = 0;
+    p.k_out = nullptr;
+    p.v_out = nullptr;
     p.qkv = (const __nv_bfloat16*)qkv;
     p.qkv_stride = qkv_stride;
     p.out = (__nv_bfloat16*)out;
@@ -791,7 +870,8 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
                                     const int* cu_q, const int* q_start, const int* block_table, int table_stride,
                                     int n_seqs, int n_pages, int n_tokens, int heads, int kv_heads, int head_dim,
                                     int page_size, int window, float scale, int n_splits, float* part_o, float* part_ml,
-                                    int* counters, cudaStream_t stream) {
+                                    int* counters, int fuse_rope, const float2* cos_sin, int max_pos, int store_kv,
+                                    int* status, cudaStream_t stream) {
     if (n_seqs == 0 || n_tokens == 0) return cudaSuccess;
     if (!attention_mma_supports(head_dim, heads, kv_heads, 1) || page_size % 16 != 0) return cudaErrorInvalidValue;
     if (n_splits < 1) n_splits = 1;
@@ -817,12 +897,18 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
     p.page_size = page_size;
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
-    p.tokens_per_tile = 16 / (heads / kv_heads);
+    p.tokens_per_tile = fuse_rope ? 1 : 16 / (heads / kv_heads);
     p.n_splits = n_splits;
     p.part_o = part_o;
     p.part_ml = part_ml;
     p.n_tokens = n_tokens;
-    p.status = nullptr;
+    p.status = status;
+    p.fuse_rope = fuse_rope;
+    p.cos_sin = cos_sin;
+    p.max_pos = max_pos;
+    p.store_kv = store_kv;
+    p.k_out = (__nv_bfloat16*)const_cast<void*>(k_cache);
+    p.v_out = (__nv_bfloat16*)const_cast<void*>(v_cache);
     switch (head_dim) {
         case 16: return launch_decode_d<16>(p, n_seqs, counters, stream);
         case 32: return launch_decode_d<32>(p, n_seqs, counters, stream);

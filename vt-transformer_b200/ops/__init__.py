@@ -168,6 +168,38 @@ def _attention_tiles(ctx, tokens_per_tile: int, device):
     return tiles
 
 
+def rope_attention(qkv, out, cos_sin, k_cache, v_cache, ctx, block_table, heads: int, kv_heads: int, head_dim: int,
+                   window: Optional[int], scale: float, store: bool = True, status=None) -> torch.Tensor:
+    """Rotation of q and k by the tokens' positions, store of k and v into their pages (if ``store``),
+    and attention over the pages: the three steps of the attention mixer between its two products.
+    In a bfloat16 step of single tokens they are one kernel (the attention kernel rotates q in its
+    registers and puts the token's own k and v into its key block and into the page); otherwise the
+    rotation kernel runs first."""
+    global launches
+    be = backend()
+    if (qkv.dtype == torch.bfloat16 and ATTENTION_KERNEL == "auto" and FUSE_ROPE and ctx.max_q_len == 1
+            and ctx.n_tokens == ctx.n_seqs and be.attention_mma_supports(head_dim, heads, kv_heads, 1)):
+        launches += 1
+        w = int(window) if window else 0
+        span = ctx.max_kv_len if not w else min(ctx.max_kv_len, w + 31)
+        splits = _decode_splits(ctx.n_seqs * kv_heads, max(1, -(-span // 32)), qkv.device)
+        part_o = part_ml = counters = None
+        if splits > 8:
+            part_o = torch.empty((splits, ctx.n_tokens, heads, head_dim), dtype=torch.float32, device=qkv.device)
+            part_ml = torch.empty((splits, ctx.n_tokens, heads, 2), dtype=torch.float32, device=qkv.device)
+            counters = _attention_counters(qkv.device, ctx.n_seqs * kv_heads)
+        be.attention_decode(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, heads, kv_heads, head_dim, w,
+                            float(scale), splits, part_o, part_ml, counters, True, cos_sin, bool(store), status)
+        return out
+    rope_store(qkv, ctx.positions, cos_sin, k_cache, v_cache, ctx.token_seq, block_table, heads, kv_heads, head_dim,
+               store=store, status=status)
+    return paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads, kv_heads, head_dim, window, scale,
+                           status=status)
+
+
+FUSE_ROPE = True    # False: always the separate rotation kernel (tests compare the two)
+
+
 def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv_heads: int, head_dim: int,
                     window: Optional[int], scale: float, status=None) -> torch.Tensor:
     """Attention of the step's tokens over the paged keys and values of their sequences.

@@ -72,11 +72,9 @@ class PagedAttention(Mixer):
         T = h.shape[0]
         qkv = torch.empty((T, self.q_dim + 2 * self.kv_dim), dtype=h.dtype, device=h.device)
         ops.linear(h, self.w_qkv, self.b_qkv, qkv)
-        ops.rope_store(qkv, ctx.positions, self.position.table, cache.k, cache.v, ctx.token_seq, cache.block_table,
-                       s.heads, s.kv_heads, s.head_dim, store=cache.writes, status=ctx.status)
         o = torch.empty((T, self.q_dim), dtype=h.dtype, device=h.device)
-        ops.paged_attention(qkv, o, cache.k, cache.v, ctx, cache.block_table, s.heads, s.kv_heads, s.head_dim,
-                            s.window, self.scale, status=ctx.status)
+        ops.rope_attention(qkv, o, self.position.table, cache.k, cache.v, ctx, cache.block_table, s.heads, s.kv_heads,
+                           s.head_dim, s.window, self.scale, store=cache.writes, status=ctx.status)
         out = torch.empty((T, s.hidden), dtype=h.dtype, device=h.device)
         ops.linear(o, self.w_o, self.b_o, out)
         return out
