@@ -480,9 +480,9 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
                 ksplit = s;
             }
         }
-        if (bn == 16) return launch_cfg<16, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
-        if (bn == 32) return launch_cfg<32, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
-        return launch_cfg<64, 6, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
+        if (bn == 16) return launch_cfg<16, 11, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
+        if (bn == 32) return launch_cfg<32, 10, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
+        return launch_cfg<64, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
     }
     // x is the 128-row operand: tiles of 128 tokens by 256 (or 128) features, one an SM at a time.  With fewer
     // tiles than SMs and a long k, every tile is cut into shares of k so that more SMs work.  (Cutting the
