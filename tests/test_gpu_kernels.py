@@ -167,6 +167,48 @@ def test_attention_over_pages(dtype, heads, kv_heads, d, page_size, window):
         at_q, at_k = at_q + ql, at_k + n
 
 
+@pytest.mark.parametrize("heads,kv_heads,d,page_size,window", [(28, 4, 128, 16, None), (8, 1, 128, 64, 200), (3, 3, 128, 16, None),
+                                                               (12, 2, 128, 32, 129), (32, 1, 128, 16, None)])
+def test_prompt_portions_on_tcgen05(heads, kv_heads, d, page_size, window):
+    """Portions long enough for tiles of 128 rows run the tcgen05 kernel: many blocks of 128 keys, a portion
+    that starts in the middle of a sequence and of a page, ends that are no multiple of 16, a window's edge
+    inside a block.  The pages' unused rows hold NaN.  Compared with the plain implementation and with the
+    mma.sync kernel."""
+    import helpers
+    from vt_transformer_b200 import ops as o
+    dtype = torch.bfloat16
+    torch.manual_seed(21)
+    seq_lens = [700, 333, 1501, 130]
+    q_lens = [700, 45, 261, 129]
+    total = sum(seq_lens)
+    k = torch.randn(total, kv_heads, d, device=DEV).to(dtype)
+    v = torch.randn(total, kv_heads, d, device=DEV).to(dtype)
+    kc, vc, table = paged_cache(k, v, seq_lens, page_size, 2800 // page_size + 8, dtype, seed=4)
+    T = sum(q_lens)
+    q = (torch.randn(T, heads, d, device=DEV) * 2).to(dtype)
+    qkv = torch.cat([q.view(T, -1), torch.zeros(T, 2 * kv_heads * d, device=DEV, dtype=dtype)], dim=1).contiguous()
+    ctx = helpers.step_context(q_lens, [n - ql for n, ql in zip(seq_lens, q_lens)], DEV)
+    assert o.backend().attention_tc_supports(d, heads, kv_heads)
+    out = torch.full((T, heads * d), float("nan"), device=DEV, dtype=dtype)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    o.paged_attention(qkv, out, kc, vc, ctx, table, heads, kv_heads, d, window, 1 / math.sqrt(d), status=status)
+    assert status.tolist() == [0, 0]
+    other = torch.empty_like(out)
+    o.ATTENTION_KERNEL = "mma"
+    try:
+        o.paged_attention(qkv, other, kc, vc, ctx, table, heads, kv_heads, d, window, 1 / math.sqrt(d), status=status)
+    finally:
+        o.ATTENTION_KERNEL = "auto"
+    at_q = at_k = 0
+    for n, ql in zip(seq_lens, q_lens):
+        qq = torch.zeros(n, heads, d, dtype=torch.float64)
+        qq[n - ql:] = q[at_q:at_q + ql].cpu().double()
+        ref = plain.attention(qq, k[at_k:at_k + n].cpu().double(), v[at_k:at_k + n].cpu().double(), window)[n - ql:]
+        close(out[at_q:at_q + ql].view(ql, heads, d), ref, dtype, 4)
+        close(other[at_q:at_q + ql].view(ql, heads, d), ref, dtype, 4)
+        at_q, at_k = at_q + ql, at_k + n
+
+
 @pytest.mark.parametrize("heads,kv_heads,d,page_size,window", [(28, 4, 128, 16, None), (6, 2, 80, 32, None), (4, 4, 16, 16, 40),
                                                                (16, 1, 64, 64, 100), (14, 2, 64, 16, None), (40, 2, 32, 16, None)])
 def test_single_token_steps_split_the_keys(heads, kv_heads, d, page_size, window):

@@ -262,6 +262,43 @@ void attention_mma(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const 
                  "attention_mma");
 }
 
+bool attention_tc_supports(int64_t head_dim, int64_t heads, int64_t kv_heads) {
+    return vtb::attention_tc_supports(head_dim, heads, kv_heads);
+}
+
+void attention_tc(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache, const Tensor& cu_q,
+                  const Tensor& q_start, const Tensor& block_table, const Tensor& tiles, int64_t heads, int64_t kv_heads,
+                  int64_t head_dim, int64_t window, double scale, c10::optional<Tensor> status) {
+    check_cuda(qkv, "qkv"); check_cuda(out, "out"); check_i32(cu_q, "cu_q"); check_i32(q_start, "q_start");
+    check_i32(block_table, "block_table"); check_i32(tiles, "tiles");
+    TORCH_CHECK(qkv.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16,
+                "attention_tc: bfloat16 only");
+    TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) >= heads * head_dim && qkv.size(1) % 8 == 0 && qkv.is_contiguous(),
+                "attention_tc: qkv must hold the queries first, rows a multiple of 16 bytes");
+    TORCH_CHECK(out.dim() == 2 && out.size(0) == qkv.size(0) && out.size(1) == heads * head_dim && out.is_contiguous(),
+                "attention_tc: out must be [tokens, heads * head_dim]");
+    TORCH_CHECK(heads % kv_heads == 0 && vtb::attention_tc_supports(head_dim, heads, kv_heads),
+                "attention_tc: head_dim ", head_dim, " with ", heads / std::max<int64_t>(kv_heads, 1),
+                " heads in a group is not supported (head_dim 128, group <= 128)");
+    check_cache(k_cache, v_cache, qkv, kv_heads, head_dim);
+    TORCH_CHECK(k_cache.size(2) % 16 == 0, "attention_tc: page size must be a multiple of 16");
+    TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous() &&
+                    reinterpret_cast<uintptr_t>(k_cache.data_ptr()) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(v_cache.data_ptr()) % 16 == 0,
+                "attention_tc: the caches must be dense and 16-byte aligned");
+    const int n_seqs = cu_q.numel() - 1;
+    TORCH_CHECK(q_start.numel() == n_seqs && block_table.dim() == 2 && block_table.size(0) == n_seqs,
+                "attention_tc: one q_start and one block-table row for each sequence");
+    TORCH_CHECK(tiles.dim() == 2 && tiles.size(1) == 2, "attention_tc: tiles must be [n, 2]");
+    c10::cuda::CUDAGuard guard(qkv.device());
+    check_launch(vtb::launch_attention_tc(qkv.data_ptr(), qkv.size(1), out.data_ptr(), k_cache.data_ptr(),
+                                          v_cache.data_ptr(), cu_q.data_ptr<int>(), q_start.data_ptr<int>(),
+                                          block_table.data_ptr<int>(), block_table.size(1), tiles.data_ptr<int>(),
+                                          tiles.size(0), k_cache.size(0), heads, kv_heads, head_dim, k_cache.size(2),
+                                          window, (float)scale, status_ptr(status), stream_of(qkv)),
+                 "attention_tc");
+}
+
 void attention_decode(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache, const Tensor& cu_q,
                       const Tensor& q_start, const Tensor& block_table, int64_t heads, int64_t kv_heads, int64_t head_dim,
                       int64_t window, double scale, int64_t n_splits, c10::optional<Tensor> part_o,
@@ -386,6 +423,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("kv_heads"), py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("warps"),
           py::arg("n_splits"), py::arg("part_o") = py::none(), py::arg("part_ml") = py::none(),
           py::arg("status") = py::none());
+    m.def("attention_tc_supports", &attention_tc_supports);
+    m.def("attention_tc", &attention_tc, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
+          py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("tiles"), py::arg("heads"),
+          py::arg("kv_heads"), py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("status") = py::none());
     m.def("attention_decode", &attention_decode, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
           py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),
           py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("n_splits"), py::arg("part_o") = py::none(),

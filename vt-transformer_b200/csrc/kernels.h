@@ -77,6 +77,14 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
                                  int head_dim, int page_size, int window, float scale, int warps, int n_splits,
                                  float* part_o, float* part_ml, int* status, cudaStream_t stream);
 
+// Attention of prompt portions on tcgen05 tensor cores with the scores in tensor memory (head size 128):
+// tiles of 128 rows of (token, head of the group) as in launch_attention_mma with 8 warps.
+bool attention_tc_supports(int head_dim, int heads, int kv_heads);
+cudaError_t launch_attention_tc(const void* qkv, int qkv_stride, void* out, const void* k_cache, const void* v_cache,
+                                const int* cu_q, const int* q_start, const int* block_table, int table_stride,
+                                const int* tiles, int n_tiles, int n_pages, int heads, int kv_heads, int head_dim,
+                                int page_size, int window, float scale, int* status, cudaStream_t stream);
+
 // Attention of single-token steps: every sequence brings tokens_per_tile = 16 / group tokens at most (one in a
 // decode step).  Grid (sequences, kv_heads, n_splits), four warps a CTA.  With n_splits > 1 the runs' results
 // pass through part_o [splits, tokens, heads, head_dim] and part_ml [splits, tokens, heads, 2], and

@@ -145,7 +145,8 @@ SKINNY_MAX_ROWS = 64            # rows of x up to which the small-batch kernel m
 # The environment variable VTB200_SMALL_BATCH_KERNEL overrides it (for measurements).
 import os as _os
 SMALL_BATCH_KERNEL = _os.environ.get("VTB200_SMALL_BATCH_KERNEL", "tc")
-ATTENTION_KERNEL = "auto"   # "auto", or "simt" to force the plain kernel (tests compare the two)
+# "auto"; "mma": no tcgen05 attention (the mma.sync kernels only); "simt": the plain kernel (tests compare them)
+ATTENTION_KERNEL = "auto"
 
 
 # --------------------------------------------------------------------------- attention
@@ -177,7 +178,7 @@ def rope_attention(qkv, out, cos_sin, k_cache, v_cache, ctx, block_table, heads:
     rotation kernel runs first."""
     global launches
     be = backend()
-    if (qkv.dtype == torch.bfloat16 and ATTENTION_KERNEL == "auto" and FUSE_ROPE and ctx.max_q_len == 1
+    if (qkv.dtype == torch.bfloat16 and ATTENTION_KERNEL in ("auto", "mma") and FUSE_ROPE and ctx.max_q_len == 1
             and ctx.n_tokens == ctx.n_seqs and be.attention_mma_supports(head_dim, heads, kv_heads, 1)):
         launches += 1
         w = int(window) if window else 0
@@ -210,7 +211,7 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
     be = backend()
     w = int(window) if window else 0
     group = heads // kv_heads
-    if qkv.dtype == torch.bfloat16 and ATTENTION_KERNEL == "auto":
+    if qkv.dtype == torch.bfloat16 and ATTENTION_KERNEL in ("auto", "mma"):
         if ctx.max_q_len == 1 and be.attention_mma_supports(head_dim, heads, kv_heads, 1):
             span = ctx.max_kv_len if not w else min(ctx.max_kv_len, w + 31)
             splits = _decode_splits(ctx.n_seqs * kv_heads, max(1, -(-span // 32)), qkv.device)
@@ -222,7 +223,14 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
             be.attention_decode(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, heads, kv_heads,
                                 head_dim, w, float(scale), splits, part_o, part_ml, counters)
             return out
-        # tiles of 128 rows (8 warps) where the portions are long enough to fill them, else of 64
+        # portions long enough to fill tiles of 128 rows: the tcgen05 kernel where it takes the sizes
+        if (ATTENTION_KERNEL == "auto" and ctx.max_q_len * group >= 128
+                and be.attention_tc_supports(head_dim, heads, kv_heads) and k_cache.shape[2] % 16 == 0):
+            tiles = _attention_tiles(ctx, 128 // group, qkv.device)
+            be.attention_tc(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, tiles, heads, kv_heads,
+                            head_dim, w, float(scale), status)
+            return out
+        # mma.sync tiles of 128 rows (8 warps) where the portions are long enough to fill them, else of 64
         warps = 8 if ctx.max_q_len * group >= 128 and be.attention_mma_supports(head_dim, heads, kv_heads, 8) else 4
         if be.attention_mma_supports(head_dim, heads, kv_heads, warps):
             tiles = _attention_tiles(ctx, (16 * warps) // group, qkv.device)
