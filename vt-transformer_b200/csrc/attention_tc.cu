@@ -55,6 +55,66 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// Largest raw score of a row of S (128 columns of tensor memory at s_addr).  MASKED: keys this row does not
+// see (beyond its position, or before its window) count as -infinity.
+template <bool MASKED>
+__device__ __forceinline__ float row_max(uint32_t s_addr, int kb, int pos, int window, bool valid) {
+    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+    for (int c0 = 0; c0 < TK; c0 += 32) {
+        uint32_t raw[32];
+        tc_ld32(s_addr + c0, raw);
+        if (MASKED) {
+            // keys [lo, hi) of this chunk are seen
+            const int hi = valid ? min(32, pos - (kb + c0) + 1) : 0;
+            const int lo = (window > 0) ? max(0, pos - window + 1 - (kb + c0)) : 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                mx[i & 3] = fmaxf(mx[i & 3], (i >= lo && i < hi) ? __uint_as_float(raw[i]) : -INFINITY);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(raw[i]));
+        }
+    }
+    return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+}
+
+// P = 2^(raw * scale - base) of a row, rounded to bfloat16 and written into the row's 16-byte pieces of the
+// swizzled K-major P tile; returns the sum of the row (of the unrounded values).
+template <bool MASKED>
+__device__ __forceinline__ float write_p(uint32_t s_addr, unsigned char* p_s, int r, int kb, int pos, int window,
+                                         bool valid, float scale_log2, float base) {
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+    for (int c0 = 0; c0 < TK; c0 += 32) {
+        uint32_t raw[32];
+        tc_ld32(s_addr + c0, raw);
+        const int hi = valid ? min(32, pos - (kb + c0) + 1) : 0;
+        const int lo = (window > 0) ? max(0, pos - window + 1 - (kb + c0)) : 0;
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            float pv[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                pv[e] = ex2(fmaf(__uint_as_float(raw[i + e]), scale_log2, -base));
+                if (MASKED) pv[e] = (i + e >= lo && i + e < hi) ? pv[e] : 0.f;
+            }
+            sum[(i >> 1) & 3] += pv[0] + pv[1];
+            __nv_bfloat162 b = __floats2bfloat162_rn(pv[0], pv[1]);
+            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        // 32 keys = four 16-byte pieces of this row of P
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+            const int c = (c0 >> 3) + q4;              // piece index among the 16 of the row
+            *reinterpret_cast<uint4*>(p_s + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) =
+                make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+        }
+    }
+    return (sum[0] + sum[1]) + (sum[2] + sum[3]);
+}
+
 template <int D>
 __global__ void __launch_bounds__(ATC_THREADS)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -218,18 +278,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             // a block all of whose keys every row of the tile sees needs no mask
             const bool open = (kb + TK - 1 <= pos_lo) && (p.window <= 0 || kb > pos_hi - p.window);
             const uint32_t s_addr = tmem + lane_base + (uint32_t)(st * TK);
-            float mx = m;
-#pragma unroll 1
-            for (int c0 = 0; c0 < TK; c0 += 32) {
-                uint32_t raw[32];
-                tc_ld32(s_addr + c0, raw);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = kb + c0 + i;
-                    const bool see = open || (valid && key <= pos && (p.window <= 0 || key > pos - p.window));
-                    mx = fmaxf(mx, see ? __uint_as_float(raw[i]) * p.scale_log2 : -INFINITY);
-                }
-            }
+            const float raw_max = open ? row_max<false>(s_addr, kb, pos, p.window, valid)
+                                       : row_max<true>(s_addr, kb, pos, p.window, valid);
+            const float mx = fmaxf(m, raw_max * p.scale_log2);          // the scale is positive
             const float corr = (mx == -INFINITY) ? 1.f : ex2(m - mx);
             const float base = (mx == -INFINITY) ? 0.f : mx;
             m = mx;
@@ -237,41 +288,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 // the product of the block before: O = (O + P V) * correction.  Its MMAs have read P, too.
                 if (!mbar_wait(pv_full, (j - 1) & 1)) { timed_out = true; break; }
                 tc_fence_after();
+                const bool rescale = __any_sync(0xffffffffu, corr != 1.f);
 #pragma unroll
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t raw[32];
                     tc_ld32(tmem + lane_base + 2 * TK + c0, raw);
+                    if (rescale) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c0 + i] = (o[c0 + i] + __uint_as_float(raw[i])) * corr;
-                }
-            }
-            float lsum = 0.f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < TK; c0 += 32) {
-                uint32_t raw[32];
-                tc_ld32(s_addr + c0, raw);
-                uint32_t pk[16];
+                        for (int i = 0; i < 32; ++i) o[c0 + i] = (o[c0 + i] + __uint_as_float(raw[i])) * corr;
+                    } else {
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float pv[2];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int key = kb + c0 + i + e;
-                        const bool see = open || (valid && key <= pos && (p.window <= 0 || key > pos - p.window));
-                        pv[e] = see ? ex2(__uint_as_float(raw[i + e]) * p.scale_log2 - base) : 0.f;
-                        lsum += pv[e];
+                        for (int i = 0; i < 32; ++i) o[c0 + i] += __uint_as_float(raw[i]);
                     }
-                    __nv_bfloat162 b = __floats2bfloat162_rn(pv[0], pv[1]);
-                    pk[i >> 1] = *reinterpret_cast<uint32_t*>(&b);
-                }
-                // 32 keys = four 16-byte pieces of this row of P (K-major over keys, swizzled)
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int c = (c0 >> 3) + q4;              // piece index among the 16 of the row
-                    *reinterpret_cast<uint4*>(p_s + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) =
-                        make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
                 }
             }
+            const float lsum = open ? write_p<false>(s_addr, p_s, r, kb, pos, p.window, valid, p.scale_log2, base)
+                                    : write_p<true>(s_addr, p_s, r, kb, pos, p.window, valid, p.scale_log2, base);
             l = l * corr + lsum;
             if (j == nb - 1) {
                 // The last run of 16 keys may reach beyond the last key, into rows of the page that hold
