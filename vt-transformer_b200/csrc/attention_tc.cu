@@ -8,13 +8,19 @@
 //   block  128 keys = 8 runs of 16 keys, each run inside one page; TMA brings a run of K and of V as two
 //          boxes of 64 dims (128-byte rows, 128-byte swizzle); runs beyond the last key are zero-filled
 //   S      = Q K^T: A = Q (K-major), B = K block (K-major, N = 128 keys), accumulator [128 x 128] floats in
-//          tensor memory, double-buffered so that S of the next block is computed under the softmax
-//   P      four warps, one row a thread: tcgen05.ld of the row of S, scale, mask, running maximum, 2^x,
-//          sum; P rounded to bfloat16 and written into shared memory in the swizzled K-major layout
-//   PV     = P V: A = P (K-major over keys), B = V block as it lies ([key][dim]: MN-major), [128 x 128]
-//          floats in tensor memory; the softmax warps add it to their registers: O = (O + PV) * correction
+//          tensor memory; two buffers, one for the even and one for the odd blocks
+//   P      two groups of four warps, one for the even and one for the odd blocks, a thread a row:
+//          tcgen05.ld of the row of S, scale, mask, maximum, 2^x, sum; P rounded to bfloat16 and stored
+//          (tcgen05.st) over the columns of S that have been read: it is the A operand of the next product
+//   PV     O += P V: A = P in tensor memory, B = V block as it lies ([key][dim]: MN-major); each group has
+//          its own accumulator O [128 x 128] and its own running maximum and sum, which meet at the end
 //
-// Warp 0 loads (one thread), warp 1 issues the MMAs (one thread), warps 2..5 do the softmax and keep O.
+// While one group works on the scores of its block, the tensor cores compute the other group's products.
+// The maximum a group scales by is raised only when the true maximum has moved by more than 2^8 (P stays
+// below 2^8, exact in the 32-bit sum and with the same relative rounding in bfloat16); raising it means
+// multiplying O in tensor memory by the correction, which then happens in few blocks only.
+//
+// Warp 0 loads (one thread), warp 1 issues the MMAs (one thread), warps 2..5 and 6..9 are the two groups.
 // Every wait on a barrier is bounded; a wait that runs out sets the status word and the CTA winds down.
 #include <cuda.h>
 
@@ -31,7 +37,8 @@ constexpr int TQ = 128;              // rows of a tile
 constexpr int TK = 128;              // keys of a block
 constexpr int HALF_BYTES = 128 * 128;   // 128 rows of 128 bytes (64 bfloat16): 16 KB
 constexpr int RUN_BYTES = 16 * 128;     // 16 keys of a run in one half
-constexpr int ATC_THREADS = 192;
+constexpr int ATC_THREADS = 320;        // loader, MMA issuer, two groups of four softmax warps
+constexpr float RAISE = 8.f;            // the scaling maximum follows the true one when it is this far behind (log2)
 
 struct AttnTcParams {
     const __nv_bfloat16* qkv;
@@ -55,8 +62,8 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// Largest raw score of a row of S (128 columns of tensor memory at s_addr).  MASKED: keys this row does not
-// see (beyond its position, or before its window) count as -infinity.
+// Largest raw score of a row of S (128 columns of tensor memory at s_addr; kb: their first key).  MASKED:
+// keys this row does not see (beyond its position, or before its window) count as -infinity.
 template <bool MASKED>
 __device__ __forceinline__ float row_max(uint32_t s_addr, int kb, int pos, int window, bool valid) {
     float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -79,11 +86,11 @@ __device__ __forceinline__ float row_max(uint32_t s_addr, int kb, int pos, int w
     return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 }
 
-// P = 2^(raw * scale - base) of a row, rounded to bfloat16 and written into the row's 16-byte pieces of the
-// swizzled K-major P tile; returns the sum of the row (of the unrounded values).
+// P = 2^(raw * scale - base) of a row, rounded to bfloat16 and stored over the first 64 columns of the row of S
+// (two keys a column; 32 keys are read before their 16 columns are written); returns the sum of the unrounded values.
 template <bool MASKED>
-__device__ __forceinline__ float write_p(uint32_t s_addr, unsigned char* p_s, int r, int kb, int pos, int window,
-                                         bool valid, float scale_log2, float base) {
+__device__ __forceinline__ float write_p(uint32_t s_addr, int kb, int pos, int window, bool valid, float scale_log2,
+                                         float base) {
     float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
     for (int c0 = 0; c0 < TK; c0 += 32) {
@@ -104,13 +111,7 @@ __device__ __forceinline__ float write_p(uint32_t s_addr, unsigned char* p_s, in
             __nv_bfloat162 b = __floats2bfloat162_rn(pv[0], pv[1]);
             pk[i >> 1] = *reinterpret_cast<uint32_t*>(&b);
         }
-        // 32 keys = four 16-byte pieces of this row of P
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-            const int c = (c0 >> 3) + q4;              // piece index among the 16 of the row
-            *reinterpret_cast<uint4*>(p_s + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) =
-                make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-        }
+        tc_st16(s_addr + (c0 >> 1), pk);
     }
     return (sum[0] + sum[1]) + (sum[2] + sum[3]);
 }
@@ -127,11 +128,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     unsigned char* q_s = smem;
     unsigned char* k_s = q_s + TILE_BYTES;               // [2][TILE_BYTES]
     unsigned char* v_s = k_s + 2 * TILE_BYTES;           // [2][TILE_BYTES]
-    unsigned char* p_s = v_s + 2 * TILE_BYTES;           // [2 halves of 64 keys][16 KB]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * HALF_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * TILE_BYTES);
     uint64_t *k_full = bars, *k_empty = bars + 2, *v_full = bars + 4, *v_empty = bars + 6, *s_full = bars + 8,
-             *s_empty = bars + 10, *p_full = bars + 12, *pv_full = bars + 13, *q_full = bars + 14;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+             *p_full = bars + 10, *o_done = bars + 12, *q_full = bars + 14, *pair = bars + 15;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+    float* xch = reinterpret_cast<float*>(bars + 20);     // [2 groups][128 rows][maximum, sum]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -141,11 +142,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             mbar_init(&v_full[i], 1);
             mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1);
-            mbar_init(&s_empty[i], 4);
+            mbar_init(&p_full[i], 4);
+            mbar_init(&o_done[i], 1);
         }
-        mbar_init(p_full, 4);
-        mbar_init(pv_full, 1);
-        mbar_init(q_full, 4);
+        mbar_init(q_full, 8);
+        for (int i = 0; i < 4; ++i) mbar_init(&pair[i], 2);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
@@ -156,7 +157,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = *tmem_slot;          // columns 0..127 and 128..255: S (two buffers); 256..383: P V
+    // columns 0..127 and 128..255: S of the even and of the odd blocks (P over their first 64);
+    // 256..383 and 384..511: O of the even and of the odd blocks
+    const uint32_t tmem = *tmem_slot;
     pdl_launch();
     pdl_wait();                                 // q, and the keys and values of this step, come from kernels before
 
@@ -177,36 +180,46 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     bool timed_out = false;
 
     if (warp == 0) {
-        if (lane == 0 && nb > 0) {
+        if (nb > 0) {
+            // Lane `run` (0..7) looks up the page of its run of 16 keys and issues the run's boxes; lane 0 waits
+            // for the stage and announces the bytes.  The block table is read one block ahead of its use.
             const int* table = p.block_table + (size_t)seq * p.table_stride;
-            for (int j = 0; j < nb && !timed_out; ++j) {
-                const int st = j & 1;
-                if (j >= 2 && !mbar_wait(&k_empty[st], ((j >> 1) & 1) ^ 1)) { timed_out = true; break; }
-                int rows[TK / 16];
-#pragma unroll
-                for (int run = 0; run < TK / 16; ++run) {
-                    const int key = key_lo + j * TK + run * 16;
-                    int row = p.cache_rows;                      // outside the cache: the box is filled with zeros
-                    if (key < key_hi) {
-                        const int page = table[key / p.page_size];
-                        // a page behind a window may be gone already; its keys are masked
-                        if (page >= 0 && page < p.n_pages) row = (page * p.kv_heads + kvh) * p.page_size + key % p.page_size;
-                    }
-                    rows[run] = row;
+            auto row_of = [&](int j) -> int {
+                const int key = key_lo + j * TK + (lane & 7) * 16;
+                int row = p.cache_rows;                      // outside the cache: the box is filled with zeros
+                if (j < nb && key < key_hi) {
+                    const int page = table[key / p.page_size];
+                    // a page behind a window may be gone already; its keys are masked
+                    if (page >= 0 && page < p.n_pages) row = (page * p.kv_heads + kvh) * p.page_size + key % p.page_size;
                 }
-                mbar_expect_tx(&k_full[st], TILE_BYTES);
-#pragma unroll
-                for (int run = 0; run < TK / 16; ++run)
+                return row;
+            };
+            // K or V of block j into its stage (j % 2), once the product that read the stage before is done
+            auto load = [&](int j, int row, const CUtensorMap* map, unsigned char* base, uint64_t* full, uint64_t* empty) -> bool {
+                const int st = j & 1;
+                int ok = 1;
+                if (lane == 0) {
+                    if (j >= 2 && !mbar_wait(&empty[st], ((j >> 1) & 1) ^ 1)) ok = 0;
+                    if (ok) mbar_expect_tx(&full[st], TILE_BYTES);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) return false;
+                if (lane < TK / 16) {
 #pragma unroll
                     for (int h = 0; h < HALVES; ++h)
-                        tma_load_2d(k_s + st * TILE_BYTES + h * HALF_BYTES + run * RUN_BYTES, &map_k, h * 64, rows[run], &k_full[st]);
-                if (j >= 2 && !mbar_wait(&v_empty[st], ((j >> 1) & 1) ^ 1)) { timed_out = true; break; }
-                mbar_expect_tx(&v_full[st], TILE_BYTES);
-#pragma unroll
-                for (int run = 0; run < TK / 16; ++run)
-#pragma unroll
-                    for (int h = 0; h < HALVES; ++h)
-                        tma_load_2d(v_s + st * TILE_BYTES + h * HALF_BYTES + run * RUN_BYTES, &map_v, h * 64, rows[run], &v_full[st]);
+                        tma_load_2d(base + st * TILE_BYTES + h * HALF_BYTES + lane * RUN_BYTES, map, h * 64, row, &full[st]);
+                }
+                return true;
+            };
+            // in the order in which the products want them: K0, K1, V0, K2, V1, ...
+            int row_cur = row_of(0), row_next = row_of(1);
+            if (!load(0, row_cur, &map_k, k_s, k_full, k_empty)) timed_out = true;
+            for (int j = 0; j < nb && !timed_out; ++j) {
+                const int row_after = row_of(j + 2);
+                if (j + 1 < nb && !load(j + 1, row_next, &map_k, k_s, k_full, k_empty)) { timed_out = true; break; }
+                if (!load(j, row_cur, &map_v, v_s, v_full, v_empty)) timed_out = true;
+                row_cur = row_next;
+                row_next = row_after;
             }
         }
     } else if (warp == 1) {
@@ -215,7 +228,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             auto issue_s = [&](int j) -> bool {
                 const int st = j & 1;
                 if (!mbar_wait(&k_full[st], (j >> 1) & 1)) return false;
-                if (j >= 2 && !mbar_wait(&s_empty[st], ((j >> 1) & 1) ^ 1)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h)
@@ -230,22 +242,26 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             if (!mbar_wait(q_full, 0)) timed_out = true;
             tc_fence_after();
             if (!timed_out && !issue_s(0)) timed_out = true;
+            if (!timed_out && nb > 1 && !issue_s(1)) timed_out = true;
             for (int j = 0; j < nb && !timed_out; ++j) {
-                if (j + 1 < nb && !issue_s(j + 1)) { timed_out = true; break; }
                 const int st = j & 1;
-                if (!mbar_wait(p_full, j & 1) || !mbar_wait(&v_full[st], (j >> 1) & 1)) { timed_out = true; break; }
+                if (!mbar_wait(&p_full[st], (j >> 1) & 1) || !mbar_wait(&v_full[st], (j >> 1) & 1)) { timed_out = true; break; }
                 tc_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < TK / 16; ++ks)   // 16 keys: A 32 bytes along P's rows, B 16 rows of V further
-                    tc_mma(tmem + 2 * TK, smem_desc(p_s + (ks >> 2) * HALF_BYTES) + 2 * (ks & 3),
-                           smem_desc_lbo(v_s + st * TILE_BYTES + ks * RUN_BYTES, HALF_BYTES), idesc_pv, ks ? 1u : 0u);
+                for (int ks = 0; ks < TK / 16; ++ks)   // 16 keys: 8 columns of P, 16 rows of V further
+                    tc_mma_ta(tmem + 2 * TK + st * D, tmem + (uint32_t)(st * TK + ks * 8),
+                              smem_desc_lbo(v_s + st * TILE_BYTES + ks * RUN_BYTES, HALF_BYTES), idesc_pv, (j >= 2 || ks) ? 1u : 0u);
                 tc_commit(&v_empty[st]);
-                tc_commit(pv_full);
+                tc_commit(&o_done[st]);
+                // the scores of the group's next block go where this P lies: the tensor cores run the
+                // products in the order in which they were issued
+                if (j + 2 < nb && !issue_s(j + 2)) { timed_out = true; break; }
             }
         }
     } else {
-        // ---- softmax warps: thread = row of the tile ---------------------------------------------------
+        // ---- softmax warps: group g has the blocks g, g + 2, ...; a thread a row ---------------------------
         const int qd = warp & 3;
+        const int g = (warp - 2) >> 2;
         const int r = qd * 32 + lane;
         const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
         const bool valid = r < rows_valid;
@@ -254,100 +270,116 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         const int pos = pos_lo + tk;
         const int head = kvh * group + (valid ? r % group : 0);
         if (nb > 0) {
-            // Q row into shared memory, K-major with the 128-byte swizzle: 16-byte piece c of a 128-byte row
-            // goes to piece c ^ (row % 8)
-            const uint4* src = reinterpret_cast<const uint4*>(p.qkv + (size_t)tok * p.qkv_stride + (size_t)head * D);
+            // half a Q row into shared memory, K-major with the 128-byte swizzle: 16-byte piece c of a 128-byte
+            // row goes to piece c ^ (row % 8)
+            const uint4* src = reinterpret_cast<const uint4*>(p.qkv + (size_t)tok * p.qkv_stride + (size_t)head * D + g * 64);
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) {
+            for (int c = 0; c < 8; ++c) {
                 const uint4 v = valid ? src[c] : make_uint4(0u, 0u, 0u, 0u);
-                *reinterpret_cast<uint4*>(q_s + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+                *reinterpret_cast<uint4*>(q_s + g * HALF_BYTES + r * 128 + ((c ^ (r & 7)) << 4)) = v;
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(q_full);
         }
-        float o[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.f;
-        float m = -INFINITY, l = 0.f;
-        for (int j = 0; j < nb && !timed_out; ++j) {
-            const int st = j & 1;
-            if (!mbar_wait(&s_full[st], (j >> 1) & 1)) { timed_out = true; break; }
+        const uint32_t s_addr = tmem + lane_base + (uint32_t)(g * TK);
+        const uint32_t o_addr = tmem + lane_base + (uint32_t)(2 * TK + g * D);
+        float m = -INFINITY, l = 0.f;       // the maximum P is scaled by (in log2 units), and the sum at that scale
+        for (int j = g; j < nb && !timed_out; j += 2) {
+            const int u = j >> 1;           // the group's u-th block
+            if (!mbar_wait(&s_full[g], u & 1)) { timed_out = true; break; }
             tc_fence_after();
             const int kb = key_lo + j * TK;
             // a block all of whose keys every row of the tile sees needs no mask
             const bool open = (kb + TK - 1 <= pos_lo) && (p.window <= 0 || kb > pos_hi - p.window);
-            const uint32_t s_addr = tmem + lane_base + (uint32_t)(st * TK);
             const float raw_max = open ? row_max<false>(s_addr, kb, pos, p.window, valid)
                                        : row_max<true>(s_addr, kb, pos, p.window, valid);
             const float mx = fmaxf(m, raw_max * p.scale_log2);          // the scale is positive
-            const float corr = (mx == -INFINITY) ? 1.f : ex2(m - mx);
-            const float base = (mx == -INFINITY) ? 0.f : mx;
-            m = mx;
-            if (j > 0) {
-                // the product of the block before: O = (O + P V) * correction.  Its MMAs have read P, too.
-                if (!mbar_wait(pv_full, (j - 1) & 1)) { timed_out = true; break; }
+            // a row that has seen no key yet takes the maximum as it is: its O is still zero
+            const bool raise = (m != -INFINITY) && (mx > m + RAISE);
+            if (__any_sync(0xffffffffu, raise)) {
+                // O of this group, as the product of its block before left it, times 2^(old - new maximum)
+                if (!mbar_wait(&o_done[g], (u - 1) & 1)) { timed_out = true; break; }
                 tc_fence_after();
-                const bool rescale = __any_sync(0xffffffffu, corr != 1.f);
-#pragma unroll
+                const float corr = raise ? ex2(m - mx) : 1.f;
+#pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t raw[32];
-                    tc_ld32(tmem + lane_base + 2 * TK + c0, raw);
-                    if (rescale) {
+                    tc_ld32(o_addr + c0, raw);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[c0 + i] = (o[c0 + i] + __uint_as_float(raw[i])) * corr;
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[c0 + i] += __uint_as_float(raw[i]);
-                    }
+                    for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * corr);
+                    tc_st32(o_addr + c0, raw);
                 }
+                l *= corr;
+                if (raise) m = mx;
             }
-            const float lsum = open ? write_p<false>(s_addr, p_s, r, kb, pos, p.window, valid, p.scale_log2, base)
-                                    : write_p<true>(s_addr, p_s, r, kb, pos, p.window, valid, p.scale_log2, base);
-            l = l * corr + lsum;
+            if (m == -INFINITY) m = mx;
+            const float base = (m == -INFINITY) ? 0.f : m;
+            const float lsum = open ? write_p<false>(s_addr, kb, pos, p.window, valid, p.scale_log2, base)
+                                    : write_p<true>(s_addr, kb, pos, p.window, valid, p.scale_log2, base);
+            l += lsum;
+            tc_wait_st();
             if (j == nb - 1) {
                 // The last run of 16 keys may reach beyond the last key, into rows of the page that hold
                 // whatever was there before.  Their P is 0, but 0 times a stale NaN or infinity is not:
                 // those rows of V are cleared before the product reads them.
                 const int first = key_hi - kb, last = min(TK, (first + 15) / 16 * 16);
                 if (first < last) {
-                    if (!mbar_wait(&v_full[st], (j >> 1) & 1)) { timed_out = true; break; }
-                    for (int idx = threadIdx.x - 64; idx < (last - first) * HALVES * 8; idx += 128) {
+                    if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1)) { timed_out = true; break; }
+                    for (int idx = r; idx < (last - first) * HALVES * 8; idx += 128) {
                         const int row = first + idx / (HALVES * 8), piece = idx % (HALVES * 8);
-                        *reinterpret_cast<uint4*>(v_s + st * TILE_BYTES + (piece >> 3) * HALF_BYTES + row * 128 + ((piece & 7) << 4)) =
+                        *reinterpret_cast<uint4*>(v_s + (j & 1) * TILE_BYTES + (piece >> 3) * HALF_BYTES + row * 128 + ((piece & 7) << 4)) =
                             make_uint4(0u, 0u, 0u, 0u);
                     }
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 }
             }
-            // S has been read and P is written: tell the MMA warp
+            // P is in tensor memory: tell the MMA warp
             tc_fence_before();
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&s_empty[st]);
-                mbar_arrive(p_full);
-            }
+            if (lane == 0) mbar_arrive(&p_full[g]);
         }
         if (nb > 0 && !timed_out) {
-            if (!mbar_wait(pv_full, (nb - 1) & 1)) timed_out = true;
+            // the two groups' maxima and sums of the row meet; each thread then writes 64 dims of it
+            xch[(g * 128 + r) * 2] = m;
+            xch[(g * 128 + r) * 2 + 1] = l;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pair[qd]);
+            if (!mbar_wait(&pair[qd], 0)) timed_out = true;
+            const int n_even = (nb + 1) >> 1, n_odd = nb >> 1;
+            if (!timed_out && !mbar_wait(&o_done[0], (n_even - 1) & 1)) timed_out = true;
+            if (!timed_out && n_odd > 0 && !mbar_wait(&o_done[1], (n_odd - 1) & 1)) timed_out = true;
             tc_fence_after();
             if (!timed_out) {
+                const float m_other = xch[((g ^ 1) * 128 + r) * 2], l_other = xch[((g ^ 1) * 128 + r) * 2 + 1];
+                const float m_all = fmaxf(m, m_other);
+                const float w_mine = (m == -INFINITY) ? 0.f : ex2(m - m_all);
+                const float w_other = (m_other == -INFINITY) ? 0.f : ex2(m_other - m_all);
+                const float sum = l * w_mine + l_other * w_other;
+                const float inv = sum > 0.f ? 1.f / sum : 0.f;
+                const float w_even = (g == 0 ? w_mine : w_other) * inv, w_odd = (g == 0 ? w_other : w_mine) * inv;
+                __nv_bfloat16* dst = p.out + ((size_t)tok * p.heads + head) * D + g * 64;
                 // the loads of tensor memory are warp-wide: rows without a query take part and store nothing
-                const float inv = l > 0.f ? 1.f / l : 0.f;
-                __nv_bfloat16* dst = p.out + ((size_t)tok * p.heads + head) * D;
+#pragma unroll 1
+                for (int c0 = 0; c0 < 64; c0 += 32) {
+                    uint32_t even[32], odd[32];
+                    tc_ld32(tmem + lane_base + 2 * TK + g * 64 + c0, even);
+                    if (n_odd > 0) {
+                        tc_ld32(tmem + lane_base + 2 * TK + D + g * 64 + c0, odd);
+                    } else {
 #pragma unroll
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                    uint32_t raw[32];
-                    tc_ld32(tmem + lane_base + 2 * TK + c0, raw);
+                        for (int i = 0; i < 32; ++i) odd[i] = 0u;
+                    }
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
-                        uint4 u;
-                        __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&u);
+                        uint4 u4;
+                        __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&u4);
 #pragma unroll
                         for (int e = 0; e < 4; ++e)
-                            hp[e] = __floats2bfloat162_rn((o[c0 + i + 2 * e] + __uint_as_float(raw[i + 2 * e])) * inv,
-                                                          (o[c0 + i + 2 * e + 1] + __uint_as_float(raw[i + 2 * e + 1])) * inv);
-                        if (valid) *reinterpret_cast<uint4*>(dst + c0 + i) = u;
+                            hp[e] = __floats2bfloat162_rn(
+                                __uint_as_float(even[i + 2 * e]) * w_even + __uint_as_float(odd[i + 2 * e]) * w_odd,
+                                __uint_as_float(even[i + 2 * e + 1]) * w_even + __uint_as_float(odd[i + 2 * e + 1]) * w_odd);
+                        if (valid) *reinterpret_cast<uint4*>(dst + c0 + i) = u4;
                     }
                 }
             }
@@ -397,7 +429,7 @@ cudaError_t launch_attention_tc(const void* qkv, int qkv_stride, void* out, cons
     p.tokens_per_tile = TQ / (heads / kv_heads);
     p.cache_rows = (int)cache_rows;
     p.status = status;
-    constexpr int smem = (2 + 2 * 2 * 2 + 2) * HALF_BYTES + 1024 + 256;     // Q, K x2, V x2 (two halves each), P
+    constexpr int smem = (2 + 2 * 2 * 2) * HALF_BYTES + 1024 + 256 + 2 * 128 * 2 * 4;     // Q, K x2, V x2 (two halves each); barriers; the exchange
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
