@@ -5,8 +5,10 @@
 // as in attention_mma.cu; here both products run as tcgen05.mma with their results in tensor memory:
 //
 //   tile   128 rows, a row being (token, head of the KV group): a key is fetched once for the whole group
-//   block  128 keys = 8 runs of 16 keys, each run inside one page; TMA brings a run of K and of V as two
-//          boxes of 64 dims (128-byte rows, 128-byte swizzle); runs beyond the last key are zero-filled
+//   block  128 keys in runs of 16, 32, 64 or 128 keys (the largest that divides the page size), each run
+//          inside one page; TMA brings a run of K and of V as two boxes of 64 dims (128-byte rows, 128-byte
+//          swizzle); runs beyond the last key are zero-filled.  The TMA unit takes a box in some tens of
+//          cycles whatever its size: pages of 16 keys hold this kernel to about half of what pages of 64 allow
 //   S      = Q K^T: A = Q (K-major), B = K block (K-major, N = 128 keys), accumulator [128 x 128] floats in
 //          tensor memory; two buffers, one for the even and one for the odd blocks
 //   P      two groups of four warps, one for the even and one for the odd blocks, a thread a row:
@@ -36,7 +38,7 @@ namespace {
 constexpr int TQ = 128;              // rows of a tile
 constexpr int TK = 128;              // keys of a block
 constexpr int HALF_BYTES = 128 * 128;   // 128 rows of 128 bytes (64 bfloat16): 16 KB
-constexpr int RUN_BYTES = 16 * 128;     // 16 keys of a run in one half
+constexpr int STEP_BYTES = 16 * 128;    // the 16 keys of one MMA in one half
 constexpr int ATC_THREADS = 320;        // loader, MMA issuer, two groups of four softmax warps
 constexpr float RAISE = 8.f;            // the scaling maximum follows the true one when it is this far behind (log2)
 
@@ -52,6 +54,7 @@ struct AttnTcParams {
     int n_pages, heads, kv_heads, page_size, window;
     float scale_log2;
     int tokens_per_tile;
+    int run_keys;            // keys of a run: 16, 32, 64 or 128, a divisor of the page size
     int cache_rows;          // pages * kv_heads * page_size: a row index beyond it makes TMA fill zeros
     int* status;
 };
@@ -181,13 +184,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 
     if (warp == 0) {
         if (nb > 0) {
-            // Lane `run` (0..7) looks up the page of its run of 16 keys and issues the run's boxes; lane 0 waits
+            // Lane `run` looks up the page of its run of keys and issues the run's boxes; lane 0 waits
             // for the stage and announces the bytes.  The block table is read one block ahead of its use.
             const int* table = p.block_table + (size_t)seq * p.table_stride;
             auto row_of = [&](int j) -> int {
-                const int key = key_lo + j * TK + (lane & 7) * 16;
+                const int key = key_lo + j * TK + (lane & 7) * p.run_keys;
                 int row = p.cache_rows;                      // outside the cache: the box is filled with zeros
-                if (j < nb && key < key_hi) {
+                if (j < nb && key < key_hi && (lane & 7) * p.run_keys < TK) {
                     const int page = table[key / p.page_size];
                     // a page behind a window may be gone already; its keys are masked
                     if (page >= 0 && page < p.n_pages) row = (page * p.kv_heads + kvh) * p.page_size + key % p.page_size;
@@ -204,10 +207,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) return false;
-                if (lane < TK / 16) {
+                if (lane * p.run_keys < TK) {
 #pragma unroll
                     for (int h = 0; h < HALVES; ++h)
-                        tma_load_2d(base + st * TILE_BYTES + h * HALF_BYTES + lane * RUN_BYTES, map, h * 64, row, &full[st]);
+                        tma_load_2d(base + st * TILE_BYTES + h * HALF_BYTES + lane * p.run_keys * 128, map, h * 64, row, &full[st]);
                 }
                 return true;
             };
@@ -250,7 +253,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 #pragma unroll
                 for (int ks = 0; ks < TK / 16; ++ks)   // 16 keys: 8 columns of P, 16 rows of V further
                     tc_mma_ta(tmem + 2 * TK + st * D, tmem + (uint32_t)(st * TK + ks * 8),
-                              smem_desc_lbo(v_s + st * TILE_BYTES + ks * RUN_BYTES, HALF_BYTES), idesc_pv, (j >= 2 || ks) ? 1u : 0u);
+                              smem_desc_lbo(v_s + st * TILE_BYTES + ks * STEP_BYTES, HALF_BYTES), idesc_pv, (j >= 2 || ks) ? 1u : 0u);
                 tc_commit(&v_empty[st]);
                 tc_commit(&o_done[st]);
                 // the scores of the group's next block go where this P lies: the tensor cores run the
@@ -320,10 +323,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             l += lsum;
             tc_wait_st();
             if (j == nb - 1) {
-                // The last run of 16 keys may reach beyond the last key, into rows of the page that hold
+                // The last run of keys may reach beyond the last key, into rows of the page that hold
                 // whatever was there before.  Their P is 0, but 0 times a stale NaN or infinity is not:
                 // those rows of V are cleared before the product reads them.
-                const int first = key_hi - kb, last = min(TK, (first + 15) / 16 * 16);
+                const int first = key_hi - kb, last = min(TK, (first + p.run_keys - 1) / p.run_keys * p.run_keys);
                 if (first < last) {
                     if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1)) { timed_out = true; break; }
                     for (int idx = r; idx < (last - first) * HALVES * 8; idx += 128) {
@@ -407,9 +410,10 @@ cudaError_t launch_attention_tc(const void* qkv, int qkv_stride, void* out, cons
     if (n_tiles == 0) return cudaSuccess;
     if (!attention_tc_supports(head_dim, heads, kv_heads) || page_size % 16 != 0 || tiles == nullptr) return cudaErrorInvalidValue;
     const long long cache_rows = (long long)n_pages * kv_heads * page_size;
-    if (cache_rows >= (1LL << 31) - 16) return cudaErrorInvalidValue;
+    if (cache_rows >= (1LL << 31) - 256) return cudaErrorInvalidValue;
     CUtensorMap map_k, map_v;
-    if (!make_map(&map_k, k_cache, cache_rows, head_dim, 16) || !make_map(&map_v, v_cache, cache_rows, head_dim, 16))
+    const int run_keys = page_size % 128 == 0 ? 128 : page_size % 64 == 0 ? 64 : page_size % 32 == 0 ? 32 : 16;
+    if (!make_map(&map_k, k_cache, cache_rows, head_dim, run_keys) || !make_map(&map_v, v_cache, cache_rows, head_dim, run_keys))
         return cudaErrorInvalidValue;
     AttnTcParams p;
     p.qkv = (const __nv_bfloat16*)qkv;
@@ -428,6 +432,7 @@ cudaError_t launch_attention_tc(const void* qkv, int qkv_stride, void* out, cons
     p.scale_log2 = scale * 1.4426950408889634f;
     p.tokens_per_tile = TQ / (heads / kv_heads);
     p.cache_rows = (int)cache_rows;
+    p.run_keys = run_keys;
     p.status = status;
     constexpr int smem = (2 + 2 * 2 * 2) * HALF_BYTES + 1024 + 256 + 2 * 128 * 2 * 4;     // Q, K x2, V x2 (two halves each); barriers; the exchange
     static bool configured = false;
