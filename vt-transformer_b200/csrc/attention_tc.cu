@@ -228,6 +228,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     } else if (warp == 1) {
         if (lane == 0 && nb > 0) {
             const uint32_t idesc_s = instr_desc(TQ, TK), idesc_pv = instr_desc(TQ, D, true);
+            // descriptors of the tiles' first bytes; a tile further on adds its distance / 16 to the address field
+            const uint64_t desc_q = smem_desc(q_s), desc_k = smem_desc(k_s), desc_v = smem_desc_lbo(v_s, HALF_BYTES);
             auto issue_s = [&](int j) -> bool {
                 const int st = j & 1;
                 if (!mbar_wait(&k_full[st], (j >> 1) & 1)) return false;
@@ -236,8 +238,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 for (int h = 0; h < HALVES; ++h)
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)     // 16 dims = 32 bytes further along the swizzled rows
-                        tc_mma(tmem + (uint32_t)(st * TK), smem_desc(q_s + h * HALF_BYTES) + 2 * kk,
-                               smem_desc(k_s + st * TILE_BYTES + h * HALF_BYTES) + 2 * kk, idesc_s, (h | kk) ? 1u : 0u);
+                        tc_mma(tmem + (uint32_t)(st * TK), desc_q + (uint64_t)((h * HALF_BYTES >> 4) + 2 * kk),
+                               desc_k + (uint64_t)(((st * TILE_BYTES + h * HALF_BYTES) >> 4) + 2 * kk), idesc_s, (h | kk) ? 1u : 0u);
                 tc_commit(&k_empty[st]);
                 tc_commit(&s_full[st]);
                 return true;
@@ -253,7 +255,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 #pragma unroll
                 for (int ks = 0; ks < TK / 16; ++ks)   // 16 keys: 8 columns of P, 16 rows of V further
                     tc_mma_ta(tmem + 2 * TK + st * D, tmem + (uint32_t)(st * TK + ks * 8),
-                              smem_desc_lbo(v_s + st * TILE_BYTES + ks * STEP_BYTES, HALF_BYTES), idesc_pv, (j >= 2 || ks) ? 1u : 0u);
+                              desc_v + (uint64_t)((st * TILE_BYTES + ks * STEP_BYTES) >> 4), idesc_pv, (j >= 2 || ks) ? 1u : 0u);
                 tc_commit(&v_empty[st]);
                 tc_commit(&o_done[st]);
                 // the scores of the group's next block go where this P lies: the tensor cores run the
