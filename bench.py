@@ -27,7 +27,7 @@ MODEL = dict(architectures=["Qwen2ForCausalLM"], vocab_size=152064, hidden_size=
              num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, head_dim=128, rms_norm_eps=1e-6,
              rope_theta=1000000.0, max_position_embeddings=32768, tie_word_embeddings=False,
              sliding_window=131072, use_sliding_window=False, max_window_layers=28, torch_dtype="bfloat16")
-PROMPT_LEN, CONTEXT, PREFILL_TOKENS, PAGE = 1024, 4096, 2048, 16
+PROMPT_LEN, CONTEXT, PREFILL_TOKENS, PAGE = 1024, 4096, 2048, 64
 
 
 def peaks():

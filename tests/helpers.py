@@ -27,12 +27,18 @@ CONFIGS: Dict[str, dict] = {
               num_hidden_layers=4, num_attention_heads=6, num_key_value_heads=3, head_dim=48, rms_norm_eps=3e-5,
               rope_theta=500000.0, max_position_embeddings=192, tie_word_embeddings=False,
               use_sliding_window=True, sliding_window=20, max_window_layers=2),
+    # the head size of the tcgen05 attention kernel, prompts long enough for its tiles of 128 rows and
+    # blocks of 128 keys, a window on the second layer that cuts through them
+    "D": dict(architectures=["Qwen2ForCausalLM"], vocab_size=400, hidden_size=96, intermediate_size=200,
+              num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6,
+              rope_theta=10000.0, max_position_embeddings=512, tie_word_embeddings=False,
+              use_sliding_window=True, sliding_window=150, max_window_layers=1),
 }
-SIGMA = {"A": 0.02, "B": 0.05, "C": 0.08}
-SEED = {"A": 11, "B": 22, "C": 33}
+SIGMA = {"A": 0.02, "B": 0.05, "C": 0.08, "D": 0.06}
+SEED = {"A": 11, "B": 22, "C": 33, "D": 44}
 # request lengths of the replay tests: a single token, page edges (16, 32), beyond 32 for the
 # one-by-one tail, several pages
-LENGTHS = {"A": [5, 17, 33, 70, 100], "B": [1, 8, 31, 70, 129], "C": [3, 16, 48, 81, 120]}
+LENGTHS = {"A": [5, 17, 33, 70, 100], "B": [1, 8, 31, 70, 129], "C": [3, 16, 48, 81, 120], "D": [44, 150, 333, 64]}
 
 # logits of the tiny models are of order 1; the 32-bit path differs from the plain
 # implementation by the order of its sums only, the bfloat16 path by the rounding of weights'

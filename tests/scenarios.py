@@ -225,7 +225,7 @@ def greedy_generation_case(folder, name, device, dtype, n_new=16):
     logit lies within the tolerance of the largest."""
     from vt_transformer_b200 import LLM, SamplingParams
     prompts = helpers.prompts_for(name)[:3]
-    llm = LLM(folder, dtype=dtype, device=device, max_running_reqs=3, num_pages=24, max_seq_len=160,
+    llm = LLM(folder, dtype=dtype, device=device, max_running_reqs=3, num_pages=24, max_seq_len=160, page_size=16,
               max_extend_tokens=48, chunk_size=24)
     outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True))
     for p, o in zip(prompts, outs):
@@ -257,7 +257,7 @@ def temperature_generation_case(folder, name, device, dtype, n_new=24):
                dict(max_running_reqs=4, num_pages=40, max_extend_tokens=28, chunk_size=24),
                dict(max_running_reqs=4, num_pages=11, max_extend_tokens=40, chunk_size=24),
                dict(max_running_reqs=2, num_pages=9, max_extend_tokens=16, chunk_size=5)):
-        llm = LLM(folder, dtype=dtype, device=device, max_seq_len=160, **kw)
+        llm = LLM(folder, dtype=dtype, device=device, max_seq_len=160, page_size=16, **kw)
         results.append(llm.generate(prompts, params))
         preemptions.append(llm.stats["preemptions"])
         llm.runner.cache.check()

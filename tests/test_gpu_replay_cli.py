@@ -9,7 +9,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_trace_run_replays_every_family(folders, tmp_path, name, dtype):
     folder = folders(name)
     prompts = helpers.prompts_for(name)
@@ -17,7 +17,12 @@ def test_trace_run_replays_every_family(folders, tmp_path, name, dtype):
     for t in (helpers.trace_whole(prompts), helpers.trace_tail(prompts), helpers.trace_portions(prompts),
               helpers.trace_mixed(prompts, max_live=4, seed=9), helpers.trace_mixed(prompts, max_live=2, seed=10, tag="n")):
         trace.extend(t)
-    got = helpers.run_trace_cli(folder, trace, dtype, str(tmp_path / "out"), helpers.tokens_needed(trace, 64))
+    if name == "D":
+        # portions long enough for the tcgen05 attention kernel that start in the middle of a sequence
+        trace.extend(helpers.trace_portions(prompts, sizes=(60, 2, 45, 100, 3, 70), tag="q"))
+    # the engine's own page size (64) for A and D, smaller pages for B and C
+    extra = {"B": ("--page-size", "16"), "C": ("--page-size", "32")}.get(name, ())
+    got = helpers.run_trace_cli(folder, trace, dtype, str(tmp_path / "out"), helpers.tokens_needed(trace, 64), extra)
     helpers.compare_trace(folder, prompts, trace, got, helpers.TOL[dtype])
 
 

@@ -39,6 +39,12 @@ class OutOfRows(RuntimeError):
     """All request rows are taken."""
 
 
+# Tokens in a page where the caller names none.  The kernels read keys in runs of 16, so any multiple of 16
+# works; the tcgen05 attention kernel brings a page's keys with one TMA box of up to 128 rows, and a box costs
+# the TMA unit about the same whatever its size, so pages of 64 serve long prompts better than pages of 16.
+DEFAULT_PAGE_SIZE = 64
+
+
 class PagePool:
     """Pages 0..n-1 with a LIFO free list.  ``give`` refuses a page that is free already
     or that the pool does not have."""

@@ -54,7 +54,7 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--max-running-reqs", type=int, default=128)
     g.add_argument("--num-pages", type=int, default=None)
     g.add_argument("--max-seq-len", type=int, default=4096)
-    g.add_argument("--page-size", type=int, default=16)
+    g.add_argument("--page-size", type=int, default=None, help="tokens in a page (default: the engine's, 64)")
     g.add_argument("--max-extend-tokens", type=int, default=8192, help="token budget of a step")
     g.add_argument("--chunk-size", type=int, default=None, help="longest portion of one prompt in a step")
     g.add_argument("--stats", action="store_true", help="print the scheduler's counters at the end")
@@ -76,9 +76,10 @@ def _generate(args) -> int:
     if not prompts and not args.shell_mode:
         print("no prompt: give --prompt-ids, --prompt-file or --shell-mode", file=sys.stderr)
         return 2
+    sizes = {} if args.page_size is None else {"page_size": args.page_size}
     llm = LLM(args.model, dtype=args.dtype, device=args.device, max_running_reqs=args.max_running_reqs,
-              num_pages=args.num_pages, max_seq_len=args.max_seq_len, page_size=args.page_size,
-              max_extend_tokens=args.max_extend_tokens, chunk_size=args.chunk_size)
+              num_pages=args.num_pages, max_seq_len=args.max_seq_len,
+              max_extend_tokens=args.max_extend_tokens, chunk_size=args.chunk_size, **sizes)
     params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                             ignore_eos=args.ignore_eos, max_tokens=args.max_tokens, seed=args.seed)
 

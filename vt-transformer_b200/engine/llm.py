@@ -14,6 +14,7 @@ from typing import Dict, List, Optional, Sequence, Union
 
 import torch
 
+from ..cache.manager import DEFAULT_PAGE_SIZE
 from ..config.registry import load_config
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
@@ -24,7 +25,7 @@ from .scheduler import ReqResult, Scheduler, SchedulerConfig, StepResult
 class LLM:
     def __init__(self, model: str, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_running_reqs: int = 128, num_pages: Optional[int] = None, max_seq_len: int = 4096,
-                 page_size: int = 16, max_extend_tokens: int = 8192, default_max_output: int = 1024,
+                 page_size: int = DEFAULT_PAGE_SIZE, max_extend_tokens: int = 8192, default_max_output: int = 1024,
                  chunk_size: Optional[int] = None, runner: Optional[ModelRunner] = None):
         """``model``: a folder with config.json and model.safetensors.  ``num_pages`` None
         sizes the pool for ``max_running_reqs`` requests of ``max_seq_len`` tokens, capped at

@@ -16,7 +16,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from .. import ops as _ops
-from ..cache.manager import CacheManager
+from ..cache.manager import DEFAULT_PAGE_SIZE, CacheManager
 from ..config.registry import get_architecture, load_config
 from ..models.base import DecoderModel
 from ..parts.base import Runtime
@@ -60,7 +60,7 @@ class ModelRunner:
 
     # ---- construction --------------------------------------------------------------------
     @classmethod
-    def build(cls, config, source_factory, *, dtype="bfloat16", device="cuda:0", page_size: int = 16,
+    def build(cls, config, source_factory, *, dtype="bfloat16", device="cuda:0", page_size: int = DEFAULT_PAGE_SIZE,
               num_pages: Optional[int] = None, max_tokens: Optional[int] = None, max_requests: int = 8,
               max_seq_len: Optional[int] = None, ops=None) -> "ModelRunner":
         """``source_factory(param_table)`` returns the ``WeightSource``.  The pool holds

@@ -24,7 +24,7 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, List, Optional, Sequence, Tuple
 
-from ..cache.manager import OutOfPages
+from ..cache.manager import DEFAULT_PAGE_SIZE, OutOfPages
 from ..sampling.params import SamplingParams
 from .batch import StepEntry
 
@@ -32,12 +32,12 @@ from .batch import StepEntry
 @dataclass
 class SchedulerConfig:
     """Names and defaults of vt-transformer/core/vt_scheduler.hpp:33-38, except
-    ``page_size`` (16 here: the attention kernels read keys in runs of 16) and
+    ``page_size`` (64 here: the attention kernels read keys in runs of 16 and bring a page with one TMA box) and
     ``chunk_size`` (the longest portion of one prompt in a step; the reference has none)."""
     max_running_reqs: int = 128
     num_pages: int = 1024
     max_seq_len: int = 4096
-    page_size: int = 16
+    page_size: int = DEFAULT_PAGE_SIZE
     max_extend_tokens: int = 8192
     default_max_output: int = 1024
     chunk_size: Optional[int] = None
