@@ -95,6 +95,10 @@ struct AttnParams {
     int store_kv;           // 1: write the token's k and v into their page
     __nv_bfloat16* k_out;   // the cache again, writable
     __nv_bfloat16* v_out;
+    // weights that the next kernel of the stream streams (or null): single-token steps ask for them to be
+    // brought into L2 meanwhile; the keys and values of such a step leave most of the memory bandwidth idle
+    const unsigned char* next_w;
+    unsigned long long next_bytes;
 };
 
 template <int D, int WARPS>
@@ -394,14 +398,20 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
     constexpr int WARP_BYTES = 2 * 2 * DKB * LD * 2;          // K and V, two stages
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int last_flag;
+    // The kernels before this one in the stream may still be running (programmatic dependent launch).  What
+    // the step's description says (lengths, block tables: copied from the host before the step's first kernel)
+    // and the keys and values of earlier steps may be read at once; q, and a key or value written in this
+    // step, only after pdl_wait.
     pdl_launch();
-    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
     const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int q_begin = p.cu_q[seq];
     const int q_len = p.cu_q[seq + 1] - q_begin;
     const int ntok = min(p.tokens_per_tile, q_len);
-    if (ntok <= 0) return;                                     // padding: a sequence without tokens
+    if (ntok <= 0) {                                           // padding: a sequence without tokens
+        pdl_wait();
+        return;
+    }
     const int group = p.heads / p.kv_heads;
     const int rows_valid = ntok * group;
     const int start = p.q_start[seq];
@@ -426,6 +436,59 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
         tok[i] = q_begin + tk;
         pos[i] = pos_lo + tk;
         head[i] = kvh * group + (valid[i] ? row[i] % group : 0);
+    }
+    const int* table = p.block_table + (size_t)seq * p.table_stride;
+    auto load_block = [&](int blk, int stage) {
+        const int kb = key_lo + blk * DKB;
+        constexpr int CHUNKS = D / 8;
+        size_t base[2];
+        bool okp[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {                          // the block's two runs of 16 keys, a page each
+            const int key = kb + 16 * h;
+            okp[h] = key < key_hi;
+            base[h] = 0;
+            if (okp[h]) {
+                const int page = table[key / p.page_size];
+                if (page < 0 || page >= p.n_pages) okp[h] = false;
+                else base[h] = (((size_t)page * p.kv_heads + kvh) * p.page_size + key % p.page_size) * D;
+            }
+        }
+        for (int c = lane; c < DKB * CHUNKS; c += 32) {
+            const int r = c / CHUNKS, piece = c % CHUNKS;
+            const int h = r >> 4;
+            const bool ok = (h == 0 ? okp[0] : okp[1]) && (kb + r) < key_hi;
+            const size_t off = (h == 0 ? base[0] : base[1]) + (size_t)(r & 15) * D + piece * 8;
+            cp_async16(ks + ((size_t)stage * DKB + r) * LD + piece * 8, p.k_cache + (ok ? off : 0), ok);
+            cp_async16(vs + ((size_t)stage * DKB + r) * LD + piece * 8, p.v_cache + (ok ? off : 0), ok);
+        }
+    };
+
+    const int first = blk0 + warp;
+    // the warp's first block: its keys are of earlier steps, unless the step's own token lies in it and
+    // another kernel of this step has put it there
+    const bool own_in_first = pos_lo >= key_lo + first * DKB && pos_lo < key_lo + (first + 1) * DKB;
+    const bool early = first < blk1 && (!own_in_first || (p.fuse_rope && p.store_kv));
+    if (early) {
+        load_block(first, 0);
+        cp_async_commit();
+    }
+    if (p.next_w != nullptr) {
+        // this thread's share of the next kernel's weights, towards L2
+        const unsigned long long ctas = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
+        const unsigned long long me = ((unsigned long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        const unsigned long long piece = ((p.next_bytes + ctas * DWARPS * 32 - 1) / (ctas * DWARPS * 32) + 15) / 16 * 16;
+        const unsigned long long at = (me * DWARPS * 32 + threadIdx.x) * piece;
+        if (at < p.next_bytes) {
+            const unsigned long long n = min(piece, p.next_bytes - at) / 16 * 16;
+            if (n > 0)
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(p.next_w + at), "r"((uint32_t)n) : "memory");
+        }
+    }
+    pdl_wait();
+    if (first < blk1 && !early) {
+        load_block(first, 0);
+        cp_async_commit();
     }
     uint32_t qf[D / 16][4];
 #pragma unroll
@@ -467,38 +530,6 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
 
-    const int* table = p.block_table + (size_t)seq * p.table_stride;
-    auto load_block = [&](int blk, int stage) {
-        const int kb = key_lo + blk * DKB;
-        constexpr int CHUNKS = D / 8;
-        size_t base[2];
-        bool okp[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {                          // the block's two runs of 16 keys, a page each
-            const int key = kb + 16 * h;
-            okp[h] = key < key_hi;
-            base[h] = 0;
-            if (okp[h]) {
-                const int page = table[key / p.page_size];
-                if (page < 0 || page >= p.n_pages) okp[h] = false;
-                else base[h] = (((size_t)page * p.kv_heads + kvh) * p.page_size + key % p.page_size) * D;
-            }
-        }
-        for (int c = lane; c < DKB * CHUNKS; c += 32) {
-            const int r = c / CHUNKS, piece = c % CHUNKS;
-            const int h = r >> 4;
-            const bool ok = (h == 0 ? okp[0] : okp[1]) && (kb + r) < key_hi;
-            const size_t off = (h == 0 ? base[0] : base[1]) + (size_t)(r & 15) * D + piece * 8;
-            cp_async16(ks + ((size_t)stage * DKB + r) * LD + piece * 8, p.k_cache + (ok ? off : 0), ok);
-            cp_async16(vs + ((size_t)stage * DKB + r) * LD + piece * 8, p.v_cache + (ok ? off : 0), ok);
-        }
-    };
-
-    const int first = blk0 + warp;
-    if (first < blk1) {
-        load_block(first, 0);
-        cp_async_commit();
-    }
     int it = 0;
     for (int blk = first; blk < blk1; blk += DWARPS, ++it) {
         const int stage = it & 1;
@@ -831,6 +862,8 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
     p.store_kv = 0;
     p.k_out = nullptr;
     p.v_out = nullptr;
+    p.next_w = nullptr;
+    p.next_bytes = 0;
     p.qkv = (const __nv_bfloat16*)qkv;
     p.qkv_stride = qkv_stride;
     p.out = (__nv_bfloat16*)out;
@@ -871,7 +904,7 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
                                     int n_seqs, int n_pages, int n_tokens, int heads, int kv_heads, int head_dim,
                                     int page_size, int window, float scale, int n_splits, float* part_o, float* part_ml,
                                     int* counters, int fuse_rope, const float2* cos_sin, int max_pos, int store_kv,
-                                    int* status, cudaStream_t stream) {
+                                    const void* next_w, long long next_bytes, int* status, cudaStream_t stream) {
     if (n_seqs == 0 || n_tokens == 0) return cudaSuccess;
     if (!attention_mma_supports(head_dim, heads, kv_heads, 1) || page_size % 16 != 0) return cudaErrorInvalidValue;
     if (n_splits < 1) n_splits = 1;
@@ -909,6 +942,10 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
     p.store_kv = store_kv;
     p.k_out = (__nv_bfloat16*)const_cast<void*>(k_cache);
     p.v_out = (__nv_bfloat16*)const_cast<void*>(v_cache);
+    // at most 48 MB: what is brought must still be in L2 when the next kernel asks for it
+    p.next_w = (next_w != nullptr && next_bytes >= 16 && reinterpret_cast<uintptr_t>(next_w) % 16 == 0)
+                   ? static_cast<const unsigned char*>(next_w) : nullptr;
+    p.next_bytes = (unsigned long long)(next_bytes < (48LL << 20) ? next_bytes : (48LL << 20));
     switch (head_dim) {
         case 16: return launch_decode_d<16>(p, n_seqs, counters, stream);
         case 32: return launch_decode_d<32>(p, n_seqs, counters, stream);
