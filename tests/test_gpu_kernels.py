@@ -246,6 +246,38 @@ def test_single_token_steps_split_the_keys(heads, kv_heads, d, page_size, window
         at += n
 
 
+@pytest.mark.parametrize("heads,kv_heads,d,page_size,n_seqs,longest", [(28, 4, 128, 16, 50, 300), (8, 2, 64, 32, 90, 200),
+                                                                        (14, 2, 128, 64, 40, 1500), (6, 2, 80, 16, 80, 100)])
+def test_single_token_steps_with_more_ctas_than_sms(heads, kv_heads, d, page_size, n_seqs, longest):
+    """Many sequences: more CTAs than SMs, so the kernel runs with three warps a CTA and two CTAs an SM
+    (head sizes 64 and 128), alone or with the keys of a sequence cut into runs."""
+    import helpers
+    from vt_transformer_b200 import ops as o
+    dtype = torch.bfloat16
+    torch.manual_seed(13)
+    rng = random.Random(5)
+    seq_lens = [rng.randrange(1, longest) for _ in range(n_seqs - 1)] + [longest]
+    total = sum(seq_lens)
+    k = torch.randn(total, kv_heads, d, device=DEV).to(dtype)
+    v = torch.randn(total, kv_heads, d, device=DEV).to(dtype)
+    kc, vc, table = paged_cache(k, v, seq_lens, page_size, sum(-(-n // page_size) for n in seq_lens) + 3, dtype, seed=6)
+    T = len(seq_lens)
+    q = (torch.randn(T, heads, d, device=DEV) * 2).to(dtype)
+    qkv = torch.cat([q.view(T, -1), torch.zeros(T, 2 * kv_heads * d, device=DEV, dtype=dtype)], dim=1).contiguous()
+    ctx = helpers.step_context([1] * T, [n - 1 for n in seq_lens], DEV)
+    out = torch.full((T, heads * d), float("nan"), device=DEV, dtype=dtype)
+    o.paged_attention(qkv, out, kc, vc, ctx, table, heads, kv_heads, d, None, 1 / math.sqrt(d))
+    at = 0
+    for i, n in enumerate(seq_lens):
+        if i % 7 == 0 or n == longest:            # the plain implementation is slow: a sample of the sequences
+            qq = torch.zeros(n, heads, d, dtype=torch.float64)
+            qq[n - 1] = q[i].cpu().double()
+            ref = plain.attention(qq, k[at:at + n].cpu().double(), v[at:at + n].cpu().double(), None)[n - 1]
+            close(out[i].view(heads, d), ref, dtype, 4)
+        at += n
+    assert not bool(torch.isnan(out.float()).any())
+
+
 @pytest.mark.parametrize("heads,kv_heads,d,page_size,window,rotate", [(28, 4, 128, 16, None, True), (6, 2, 48, 32, 40, True),
                                                                       (4, 4, 16, 16, None, True), (8, 1, 64, 16, None, False)])
 def test_single_token_step_rotates_and_stores_inside_the_attention_kernel(heads, kv_heads, d, page_size, window, rotate):

@@ -389,10 +389,10 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
 // merged result in scratch and counts itself in; the CTA that arrives last merges the runs and stores,
 // so there is no second kernel and no CTA waits for another.
 constexpr int DKB = 32;    // keys in a warp's block
-constexpr int DWARPS = 4;
+constexpr int DWARPS = 4;   // warps of a CTA; 3 where two CTAs are to fit an SM (more CTAs than SMs)
 
-template <int D>
-__global__ void __launch_bounds__(DWARPS * 32)
+template <int D, int W>
+__global__ void __launch_bounds__(W * 32)
 attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
     constexpr int LD = D + 8;
     constexpr int WARP_BYTES = 2 * 2 * DKB * LD * 2;          // K and V, two stages
@@ -477,8 +477,8 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
         // this thread's share of the next kernel's weights, towards L2
         const unsigned long long ctas = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
         const unsigned long long me = ((unsigned long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-        const unsigned long long piece = ((p.next_bytes + ctas * DWARPS * 32 - 1) / (ctas * DWARPS * 32) + 15) / 16 * 16;
-        const unsigned long long at = (me * DWARPS * 32 + threadIdx.x) * piece;
+        const unsigned long long piece = ((p.next_bytes + ctas * W * 32 - 1) / (ctas * W * 32) + 15) / 16 * 16;
+        const unsigned long long at = (me * W * 32 + threadIdx.x) * piece;
         if (at < p.next_bytes) {
             const unsigned long long n = min(piece, p.next_bytes - at) / 16 * 16;
             if (n > 0)
@@ -531,10 +531,10 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
     float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
 
     int it = 0;
-    for (int blk = first; blk < blk1; blk += DWARPS, ++it) {
+    for (int blk = first; blk < blk1; blk += W, ++it) {
         const int stage = it & 1;
-        if (blk + DWARPS < blk1) {
-            load_block(blk + DWARPS, stage ^ 1);
+        if (blk + W < blk1) {
+            load_block(blk + W, stage ^ 1);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -674,19 +674,19 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
     __syncthreads();
     // merge the four warps: every thread takes elements (row, d) of the [16][D] output
     const int tile = seq * p.kv_heads + kvh;
-    float* res = reinterpret_cast<float*>(smem_raw + (size_t)DWARPS * WARP_BYTES);   // [16][D], then maxima [16], sums [16]
-    for (int e = threadIdx.x; e < 16 * D; e += DWARPS * 32) {
+    float* res = reinterpret_cast<float*>(smem_raw + (size_t)W * WARP_BYTES);   // [16][D], then maxima [16], sums [16]
+    for (int e = threadIdx.x; e < 16 * D; e += W * 32) {
         const int r = e / D, d = e % D;
         if (r >= rows_valid) continue;
         float mx = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < DWARPS; ++w) {
+        for (int w = 0; w < W; ++w) {
             const float* b = reinterpret_cast<const float*>(smem_raw + (size_t)w * WARP_BYTES);
             if (b[16 * D + 16 + r] > 0.f) mx = fmaxf(mx, b[16 * D + r]);
         }
         float acc = 0.f, tot = 0.f;
 #pragma unroll
-        for (int w = 0; w < DWARPS; ++w) {
+        for (int w = 0; w < W; ++w) {
             const float* b = reinterpret_cast<const float*>(smem_raw + (size_t)w * WARP_BYTES);
             const float l = b[16 * D + 16 + r];
             if (l > 0.f) {
@@ -720,7 +720,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
         cg::cluster_group cluster = cg::this_cluster();
         cluster.sync();
         const int ranks = (int)cluster.num_blocks(), me = (int)cluster.block_rank();
-        for (int e = me * DWARPS * 32 + threadIdx.x; e < 16 * D; e += ranks * DWARPS * 32) {
+        for (int e = me * W * 32 + threadIdx.x; e < 16 * D; e += ranks * W * 32) {
             const int r = e / D, d = e % D;
             if (r >= rows_valid) continue;
             float mx = -INFINITY;
@@ -757,7 +757,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
     float* wgt = reinterpret_cast<float*>(smem_raw);            // [16][MAXS] weights, then [16] totals
     float* tot_s = wgt + 16 * MAXS;
     const size_t stride = (size_t)p.n_tokens * p.heads;
-    for (int e = threadIdx.x; e < 16 * p.n_splits; e += DWARPS * 32) {
+    for (int e = threadIdx.x; e < 16 * p.n_splits; e += W * 32) {
         const int r = e / p.n_splits, sp = e % p.n_splits;
         float m = -INFINITY, l = 0.f;
         if (r < rows_valid) {
@@ -783,7 +783,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
         tot_s[r] = tot;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < 16 * D; e += DWARPS * 32) {
+    for (int e = threadIdx.x; e < 16 * D; e += W * 32) {
         const int r = e / D, d = e % D;
         if (r >= rows_valid) continue;
         const size_t idx0 = (size_t)(q_begin + r / group) * p.heads + kvh * group + r % group;
@@ -796,19 +796,32 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
     if (threadIdx.x == 0) counters[tile] = 0;
 }
 
-template <int D>
-cudaError_t launch_decode_d(const AttnParams& p, int n_seqs, int* counters, cudaStream_t stream) {
-    constexpr int smem = DWARPS * 2 * 2 * DKB * (D + 8) * 2 + (16 * D + 32) * 4;
+template <int D, int W>
+cudaError_t launch_decode_w(const AttnParams& p, int n_seqs, int* counters, cudaStream_t stream) {
+    constexpr int smem = W * 2 * 2 * DKB * (D + 8) * 2 + (16 * D + 32) * 4;
     static_assert(2 * 2 * DKB * (D + 8) * 2 >= (16 * D + 32) * 4, "a warp's buffers must hold its merged result");
-    static_assert(DWARPS * 2 * 2 * DKB * (D + 8) * 2 >= (2 * 16 * 64 + 16) * 4, "the merge of the runs needs its weights");
+    static_assert(W * 2 * 2 * DKB * (D + 8) * 2 >= (2 * 16 * 64 + 16) * 4, "the merge of the runs needs its weights");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    return launch(attention_decode_kernel<D>, dim3(n_seqs, p.kv_heads, p.n_splits), dim3(DWARPS * 32, 1, 1), smem, stream,
+    return launch(attention_decode_kernel<D, W>, dim3(n_seqs, p.kv_heads, p.n_splits), dim3(W * 32, 1, 1), smem, stream,
                   dim3(1, 1, p.cluster_merge ? p.n_splits : 1), p, counters);
+}
+
+// With more CTAs than SMs the kernel runs with three warps a CTA where that lets two CTAs share an SM (head
+// sizes 64 and 128): the CTAs then need not run in rounds of one an SM, whose last round is partly empty.
+template <int D>
+cudaError_t launch_decode_d(const AttnParams& p, int n_seqs, int* counters, cudaStream_t stream) {
+    if constexpr (D == 128 || D == 64) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 0;
+        if (sms > 0 && (long long)n_seqs * p.kv_heads * p.n_splits > sms) return launch_decode_w<D, 3>(p, n_seqs, counters, stream);
+    }
+    return launch_decode_w<D, DWARPS>(p, n_seqs, counters, stream);
 }
 
 template <int D, int WARPS>

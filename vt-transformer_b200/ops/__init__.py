@@ -279,9 +279,10 @@ _counters = {}
 
 
 def _decode_splits(pairs: int, blocks: int, device) -> int:
-    """Into how many runs the keys of a sequence are cut in a single-token step.  One CTA of the kernel
-    fits an SM, so CTAs run in waves of one an SM: least waves * (rounds of four 32-key blocks a CTA +
-    a fixed cost of a CTA, counted as three rounds)."""
+    """Into how many runs the keys of a sequence are cut in a single-token step.  With up to one CTA an SM
+    the CTAs have four warps and run in waves of one an SM; with more, three warps, two CTAs an SM, each
+    slower for the company.  Least waves * (rounds of one 32-key block a warp + a fixed cost of a CTA,
+    counted as three rounds)."""
     sms = _sm_counts.get(device)
     if sms is None:
         sms = torch.cuda.get_device_properties(device).multi_processor_count
@@ -290,11 +291,16 @@ def _decode_splits(pairs: int, blocks: int, device) -> int:
     for s in range(1, 33):
         if s > 1 and blocks // s < 2:
             break
+        two = pairs * s > sms
+        warps = 3 if two else 4
         # up to 8 runs are the CTAs of a thread-block cluster (merged through shared memory; clusters
         # pack into the GPCs with some loss); more runs meet in scratch, which costs more
         slots = sms if s == 1 else (int(sms * 0.86) // s * s if s <= 8 else sms)
+        if two:
+            slots *= 2
         waves = -(-pairs * s // max(slots, 1))
-        cost = waves * (-(-blocks // (4 * s)) + 3 + (0 if s == 1 else 0.5 if s <= 8 else 2))
+        rounds = -(-blocks // (warps * s)) * (1.5 if two else 1.0)
+        cost = waves * (rounds + 3 + (0 if s == 1 else 0.5 if s <= 8 else 2))
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
     return best
