@@ -393,6 +393,41 @@ def test_gate_up_product_with_the_activation_in_its_epilogue(m, inter, k):
     close(out32, ref, torch.float32, 40)
 
 
+@pytest.mark.parametrize("m", [1, 8, 17, 64])
+@pytest.mark.parametrize("n,k", [(40, 64), (301, 72), (3584, 3584), (520, 18944)])
+def test_tcgen05_product_leaves_its_shares_unadded_and_the_norm_adds_them(m, n, k):
+    """Small batches on the way into the residual stream: the product's kernel writes the sums of each share
+    of k as 32-bit [shares, m, n] (the bias with share 0) and the norm adds them, in order, to the stream."""
+    o = ops()
+    torch.manual_seed(15)
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    bias = torch.randn(n, device=DEV)
+    ref = plain.linear(x.cpu().double(), w.cpu().double(), bias.cpu().double())
+    got = o.linear_to_stream(x, w, bias)
+    assert isinstance(got, o.SplitSum) and got.shares.dtype == torch.float32
+    assert got.shares.shape == (o.backend().gemm_tc_shares(m, n, k), m, n) and tuple(got.shape) == (m, n)
+    close(o.dense(got), ref, torch.float32, 40)
+    if k >= 3584:
+        assert got.shares.shape[0] > 1, "a long inner dimension on few tiles should have been cut"
+    if n % 8 == 0:
+        stream = torch.randn(m, n, device=DEV)
+        g = 1 + 0.1 * torch.randn(n, device=DEV)
+        total = stream.cpu().double() + o.dense(got).cpu().double()
+        rows = torch.tensor([m - 1, 0], dtype=torch.int32, device=DEV)
+        for r in (None, rows):
+            s1 = stream.clone()
+            out = torch.empty(m if r is None else 2, n, device=DEV, dtype=torch.bfloat16)
+            o.rmsnorm(s1, g, 1e-6, out, delta=got, rows=r)
+            idx = torch.arange(m) if r is None else r.cpu().long()
+            assert float((s1.cpu().double()[idx] - total[idx]).abs().max()) <= 1e-5
+            close(out, plain.rms_norm(total[idx], g.cpu().double(), 1e-6), torch.bfloat16, 2)
+    # the same numbers as the kernel that adds the shares itself, to the last bit of its bfloat16 result's rounding
+    merged = torch.empty(m, n, device=DEV, dtype=torch.float32)
+    o.backend().gemm_tc(x, w, bias, merged, None, *o._split_workspace(torch.device(DEV)))
+    close(o.dense(got), merged.cpu().double(), torch.float32, 2)
+
+
 def test_tcgen05_product_takes_each_element_once():
     """x and w of small integers: every product and sum is exact in bfloat16 and float, so a tile read
     from the wrong place, a k-block counted twice or dropped, shows as a wrong integer."""

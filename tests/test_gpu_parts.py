@@ -18,6 +18,11 @@ def runtime(dtype):
     return Runtime(torch.device(DEV), dtype, ops)
 
 
+def ops_module():
+    from vt_transformer_b200 import ops
+    return ops
+
+
 def tensors_for(part, sigma=0.1, seed=0):
     from vt_transformer_b200.weights.loader import random_tensor
     return {name: random_tensor(name, spec, seed, sigma) for name, spec in part.param_specs().items()}
@@ -57,7 +62,7 @@ def test_feed_forward_part(dtype):
     assert set(w) == {"mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight"}
     part.load(w.__getitem__)
     h = torch.randn(21, 136, device=DEV).to(dtype)
-    out = part.forward(h, None)
+    out = ops_module().dense(part.forward(h, None))     # a small bfloat16 batch leaves unadded shares
     ref = plain.swiglu(h.cpu().double(), *(w[f"mlp.{n}_proj.weight"].double() for n in ("gate", "up", "down")))
     close(out, ref, dtype)
     with pytest.raises(ValueError, match="gelu"):
@@ -84,7 +89,7 @@ def test_attention_part_in_two_portions(dtype, window):
     for a, b in ((0, 27), (27, 40)):
         import helpers
         ctx = helpers.step_context([b - a], [a], DEV, status=torch.zeros(2, dtype=torch.int32, device=DEV))
-        outs.append(part.forward(h[a:b].contiguous(), ctx, view))
+        outs.append(ops_module().dense(part.forward(h[a:b].contiguous(), ctx, view), dtype))
         assert ctx.status.tolist() == [0, 0]
     hd = h.cpu().double()
     cos, sin = plain.rotation_table(64, 32, 7777.0)
@@ -116,7 +121,7 @@ def test_block_part_and_the_residual_stream(dtype):
     import helpers
     part.forward(stream, helpers.step_context([T], [0], DEV), view)
     assert stream.x.dtype == torch.float32 and stream.pending is not None
-    got = stream.x.cpu().double() + stream.pending.cpu().double()
+    got = stream.x.cpu().double() + ops_module().dense(stream.pending).cpu().double()
     x = x0.cpu().double()
     wd = {k: v.double() for k, v in w.items()}
     h = plain.rms_norm(x, wd["b.input_layernorm.weight"], 1e-6)
@@ -136,6 +141,6 @@ def test_a_matrix_stored_in_32_bit_stays_32_bit_on_the_bfloat16_path():
     part.load(w.__getitem__)
     assert part.w_down.dtype == torch.float32 and part.w_gate_up.dtype == torch.float32
     h = torch.randn(5, 64, device=DEV).to(torch.bfloat16)
-    out = part.forward(h, None)
+    out = ops_module().dense(part.forward(h, None))
     ref = plain.swiglu(h.cpu().double(), *(w[f"m.{n}_proj.weight"].double() for n in ("gate", "up", "down")))
     assert float((out.cpu().double() - ref).abs().max()) <= 3e-2

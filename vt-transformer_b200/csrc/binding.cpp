@@ -65,7 +65,16 @@ void rmsnorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, doubl
     TORCH_CHECK(weight.numel() == hidden && out.size(1) == hidden, "rmsnorm: weight and out must match hidden size");
     const int code = dtype_code(out, "out");
     const void* dp = nullptr;
-    if (delta.has_value()) {
+    const float* pp = nullptr;
+    int n_parts = 0;
+    if (delta.has_value() && delta->dim() == 3) {
+        // the unadded shares of a matrix product: [shares, tokens, hidden] in 32-bit
+        check_f32(*delta, "delta");
+        TORCH_CHECK(delta->size(1) == x.size(0) && delta->size(2) == hidden && delta->size(0) >= 1,
+                    "rmsnorm: shares of a delta must be [shares, tokens, hidden]");
+        pp = delta->data_ptr<float>();
+        n_parts = delta->size(0);
+    } else if (delta.has_value()) {
         check_cuda(*delta, "delta");
         TORCH_CHECK(delta->scalar_type() == out.scalar_type(), "rmsnorm: delta and out must have one dtype");
         TORCH_CHECK(delta->sizes() == x.sizes(), "rmsnorm: delta must have the shape of x");
@@ -80,7 +89,7 @@ void rmsnorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, doubl
     }
     TORCH_CHECK(out.size(0) == n_rows, "rmsnorm: out must have one row for each normed row");
     c10::cuda::CUDAGuard guard(x.device());
-    check_launch(vtb::launch_rmsnorm(code, x.data_ptr<float>(), dp, weight.data_ptr<float>(), (float)eps,
+    check_launch(vtb::launch_rmsnorm(code, x.data_ptr<float>(), dp, pp, n_parts, weight.data_ptr<float>(), (float)eps,
                                      out.data_ptr(), rp, n_rows, x.size(0), hidden, status_ptr(status),
                                      stream_of(x)), "rmsnorm");
 }
@@ -180,12 +189,18 @@ void gemm_tc(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tenso
              c10::optional<Tensor> next_w) {
     check_cuda(x, "x"); check_cuda(w, "w"); check_cuda(out, "out");
     TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16, "gemm_tc: x and w must be bfloat16");
-    TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm_tc: 2-d tensors");
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 2, "gemm_tc: x and w must be 2-d");
     const int m = x.size(0), k = x.size(1), n = w.size(0);
-    TORCH_CHECK(epilogue == 0 || epilogue == 1, "gemm_tc: epilogue must be 0 (bias) or 1 (silu(gate) * up)");
-    TORCH_CHECK(w.size(1) == k && out.size(0) == m && out.size(1) == (epilogue == 1 ? n / 2 : n),
-                "gemm_tc: shapes [m,k] x [n,k] -> [m,n] (or [m,n/2] with the silu epilogue)");
-    TORCH_CHECK(epilogue == 0 || (n % 16 == 0 && !bias.has_value() && out.scalar_type() == torch::kBFloat16),
+    TORCH_CHECK(epilogue >= 0 && epilogue <= 2, "gemm_tc: epilogue must be 0 (bias), 1 (silu(gate) * up) or 2 (unadded shares)");
+    if (epilogue == 2) {
+        TORCH_CHECK(w.size(1) == k && out.dim() == 3 && out.scalar_type() == torch::kFloat32 && out.is_contiguous() &&
+                        out.size(0) == vtb::gemm_tc_shares(m, n, k) && out.size(1) == m && out.size(2) == n,
+                    "gemm_tc: the shares of k go to a float32 out [gemm_tc_shares(m, n, k), m, n]");
+    } else {
+        TORCH_CHECK(w.size(1) == k && out.dim() == 2 && out.size(0) == m && out.size(1) == (epilogue == 1 ? n / 2 : n),
+                    "gemm_tc: shapes [m,k] x [n,k] -> [m,n] (or [m,n/2] with the silu epilogue)");
+    }
+    TORCH_CHECK(epilogue != 1 || (n % 16 == 0 && !bias.has_value() && out.scalar_type() == torch::kBFloat16),
                 "gemm_tc: the silu epilogue takes n % 16 == 0, no bias and a bfloat16 out");
     TORCH_CHECK(k % 8 == 0, "gemm_tc: inner size ", k, " must be a multiple of 8 (TMA rows start on 16-byte boundaries)");
     TORCH_CHECK(((uintptr_t)x.data_ptr() & 15) == 0 && ((uintptr_t)w.data_ptr() & 15) == 0,
@@ -437,6 +452,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_tc", &gemm_tc, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"), py::arg("status") = py::none(),
           py::arg("scratch") = py::none(), py::arg("counters") = py::none(), py::arg("epilogue") = 0,
           py::arg("next_w") = py::none());
+    m.def("gemm_tc_shares", [](int64_t m, int64_t n, int64_t k) { return (int64_t)vtb::gemm_tc_shares(m, n, k); });
     m.def("attention_mma_supports", &attention_mma_supports);
     m.def("attention_mma", &attention_mma, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
           py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("tiles"), py::arg("heads"),

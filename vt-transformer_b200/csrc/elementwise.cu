@@ -53,11 +53,13 @@ cudaError_t launch_embedding(int table_dtype, const void* table, const int* ids,
 
 // One block a row.  Pass 1 forms v = x (+ delta) in 32-bit, writes it back when there is a
 // delta, and sums v^2; pass 2 reads v again (its own writes) and scales it.  The sum's order
-// depends on hidden and the block size only, never on the batch.
+// depends on hidden and the block size only, never on the batch.  The delta may also come as `n_parts` 32-bit
+// shares [n_parts, n_tokens, hidden] (a matrix product whose inner dimension was cut over CTAs leaves its shares
+// unadded): they are added here in the order of their index.
 template <typename T>
-__global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ weight,
-                               float eps, T* __restrict__ out, const int* __restrict__ rows, int n_tokens, int hidden,
-                               int* status) {
+__global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ parts,
+                               int n_parts, const float* __restrict__ weight, float eps, T* __restrict__ out,
+                               const int* __restrict__ rows, int n_tokens, int hidden, int* status) {
     __shared__ float scratch[32];
     pdl_launch();
     pdl_wait();
@@ -80,6 +82,17 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] += d[j];
             Vec8<float>::store(xr + i, v);
+        } else if (parts) {
+            const float* pr = parts + (size_t)t * hidden + i;
+            const size_t stride = (size_t)n_tokens * hidden;
+#pragma unroll 4
+            for (int q = 0; q < n_parts; ++q) {
+                float d[8];
+                Vec8<float>::load(pr + q * stride, d);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += d[j];
+            }
+            Vec8<float>::store(xr + i, v);
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
@@ -96,15 +109,16 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
     }
 }
 
-cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const float* weight, float eps,
-                           void* out, const int* rows, int n_rows, int n_tokens, int hidden, int* status,
-                           cudaStream_t stream) {
+cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
+                           const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
+                           int hidden, int* status, cudaStream_t stream) {
+    if (delta != nullptr && parts != nullptr) return cudaErrorInvalidValue;
     if (n_rows == 0) return cudaSuccess;
     int threads = min(512, max(32, ((hidden / 8 + 31) / 32) * 32));
     if (out_dtype == kBF16)
-        return launch(rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, (const __nv_bfloat16*)delta, weight, eps,
+        return launch(rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, (const __nv_bfloat16*)delta, parts, n_parts, weight, eps,
                       (__nv_bfloat16*)out, rows, n_tokens, hidden, status);
-    return launch(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, (const float*)delta, weight, eps, (float*)out, rows, n_tokens,
+    return launch(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, (const float*)delta, parts, n_parts, weight, eps, (float*)out, rows, n_tokens,
                   hidden, status);
 }
 

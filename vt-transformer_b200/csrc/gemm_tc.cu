@@ -282,7 +282,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             bool ok = !timed_out && mbar_wait(&acc_full[buf], (ui >> 1) & 1);
             if (!ok) timed_out = true;
             tc_fence_after();
-            float* mine = scratch + ((size_t)cut * ksplit + krank) * (BN * BM);      // this unit's share [BN][128]
+            float* mine = (EPI == 2) ? nullptr : scratch + ((size_t)cut * ksplit + krank) * (BN * BM);   // this unit's share [BN][128]
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 float v[16];
@@ -301,6 +301,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[buf]);
                 }
+                if (EPI == 2) {
+                    // this share of k as it is, into out[share]: the kernel that reads the result adds the shares
+                    if (ok)
+                        emit16<SWAP, 0, TOut>(v, r, a_row0, b_row0, c0, rows_a, rows_b, krank == 0 ? bias : nullptr,
+                                              out + (size_t)krank * rows_b * ldo, ldo);
+                    continue;
+                }
                 if (ksplit > 1) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) __stcg(mine + (c0 + i) * BM + r, v[i]);
@@ -308,7 +315,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 emit16<SWAP, EPI, TOut>(v, r, a_row0, b_row0, c0, rows_a, rows_b, bias, out, ldo);
             }
-            if (ksplit > 1) {
+            if (EPI != 2 && ksplit > 1) {
                 // count this unit in; the one that finds all others counted adds the shares and stores
                 __threadfence();
                 asm volatile("bar.sync 1, 128;\n" ::: "memory");
@@ -413,7 +420,8 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
         // swapped: w is the 128-row operand
         const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
         const bool have_scratch = scratch != nullptr && counters != nullptr;
-        const int ksplit = small_batch_ksplit(n, k, bn, have_scratch, scratch_floats, n_counters);
+        const int ksplit = (EPI == 2) ? gemm_tc_shares(m, n, k)
+                                      : small_batch_ksplit(n, k, bn, have_scratch, scratch_floats, n_counters);
         if (next_w != nullptr && next_n > 0 && next_k >= 8 && next_k % 8 == 0) {
             // the product after this one is taken to have as many rows of x as this one
             nx.w = static_cast<const unsigned char*>(next_w);
@@ -428,36 +436,45 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
         if (bn == 32) return launch_cfg<32, 10, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, nx, stream);
         return launch_cfg<64, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, nx, stream);
     }
-    // x is the 128-row operand: tiles of 128 tokens by 256 (or 128) features, one an SM at a time.  With fewer
-    // tiles than SMs and a long k, every tile is cut into shares of k so that more SMs work.  (Cutting the
-    // tiles of the last, partial round of a larger product was tried and lost: merging the shares of a
-    // 128x256 tile costs the CTA that does it more than the shorter round saves.)
-    const int sms = sm_count();
-    const bool wide = !(n <= 128 || m <= 128);
-    const int bn = wide ? 256 : 128;
-    const int tiles = ((m + BM - 1) / BM) * ((n + bn - 1) / bn), nkb = (k + BK - 1) / BK;
-    int rem = tiles % sms, n_full = tiles - rem, s_tail = 1;
-    if (tiles < sms && scratch != nullptr && counters != nullptr && rem <= n_counters) {
-        double best = 1.0;
-        for (int s = 2; s <= 4; ++s) {
-            // a share must be long enough to pay for the merge of the shares
-            if (nkb / s < 48 || (long long)rem * s * bn * BM > scratch_floats) break;
-            const double cost = (double)((rem * s + sms - 1) / sms) / s + 0.04;
-            if (cost < best) {
-                best = cost;
-                s_tail = s;
+    if constexpr (EPI == 2) {
+        return cudaErrorInvalidValue;     // shares are left unadded for small batches only
+    } else {
+        // x is the 128-row operand: tiles of 128 tokens by 256 (or 128) features, one an SM at a time.  With fewer
+        // tiles than SMs and a long k, every tile is cut into shares of k so that more SMs work.  (Cutting the
+        // tiles of the last, partial round of a larger product was tried and lost: merging the shares of a
+        // 128x256 tile costs the CTA that does it more than the shorter round saves.)
+        const int sms = sm_count();
+        const bool wide = !(n <= 128 || m <= 128);
+        const int bn = wide ? 256 : 128;
+        const int tiles = ((m + BM - 1) / BM) * ((n + bn - 1) / bn), nkb = (k + BK - 1) / BK;
+        int rem = tiles % sms, n_full = tiles - rem, s_tail = 1;
+        if (tiles < sms && scratch != nullptr && counters != nullptr && rem <= n_counters) {
+            double best = 1.0;
+            for (int s = 2; s <= 4; ++s) {
+                // a share must be long enough to pay for the merge of the shares
+                if (nkb / s < 48 || (long long)rem * s * bn * BM > scratch_floats) break;
+                const double cost = (double)((rem * s + sms - 1) / sms) / s + 0.04;
+                if (cost < best) {
+                    best = cost;
+                    s_tail = s;
+                }
             }
         }
+        if (s_tail == 1) n_full = tiles;
+        if (wide)
+            return launch_cfg<256, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, EPI == 1 ? n / 2 : n, n_full, s_tail, scratch,
+                                                         counters, status, nx, stream);
+        return launch_cfg<128, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, EPI == 1 ? n / 2 : n, n_full, s_tail, scratch, counters,
+                                                     status, nx, stream);
     }
-    if (s_tail == 1) n_full = tiles;
-    if (wide)
-        return launch_cfg<256, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, EPI == 1 ? n / 2 : n, n_full, s_tail, scratch,
-                                                     counters, status, nx, stream);
-    return launch_cfg<128, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, EPI == 1 ? n / 2 : n, n_full, s_tail, scratch, counters,
-                                                 status, nx, stream);
 }
 
 }  // namespace
+
+int gemm_tc_shares(int m, int n, int k) {
+    const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+    return small_batch_ksplit(n, k, bn, true, 1LL << 60, 1 << 30);
+}
 
 cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n, int k,
                            int epilogue, float* scratch, long long scratch_floats, int* counters, int n_counters,
@@ -468,6 +485,11 @@ cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const fl
         if (n % 16 != 0 || bias != nullptr || out_dtype != kBF16) return cudaErrorInvalidValue;
         return launch_typed<1, __nv_bfloat16>(x, w, nullptr, (__nv_bfloat16*)out, m, n, k, scratch, scratch_floats,
                                               counters, n_counters, status, next_w, next_n, next_k, stream);
+    }
+    if (epilogue == 2) {
+        if (out_dtype != kF32 || m > 64) return cudaErrorInvalidValue;
+        return launch_typed<2, float>(x, w, bias, (float*)out, m, n, k, nullptr, 0, nullptr, 0, status, next_w, next_n, next_k,
+                                      stream);
     }
     if (epilogue != 0) return cudaErrorInvalidValue;
     if (out_dtype == kBF16)

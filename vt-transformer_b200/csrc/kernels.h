@@ -15,10 +15,11 @@ cudaError_t launch_embedding(int table_dtype, const void* table, const int* ids,
                              int hidden, int vocab, int* status, cudaStream_t stream);
 
 // For r in 0..n_rows: t = rows ? rows[r] : r; v = x[t] (+ delta[t], written back to x[t]);
-// out[r] = weight * v * rsqrt(mean(v^2) + eps).  x float, weight float, delta/out of out_dtype.
-cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const float* weight, float eps,
-                           void* out, const int* rows, int n_rows, int n_tokens, int hidden, int* status,
-                           cudaStream_t stream);
+// out[r] = weight * v * rsqrt(mean(v^2) + eps).  x float, weight float, delta/out of out_dtype.  Instead of
+// delta: parts [n_parts, n_tokens, hidden] float, the unadded shares of a delta, added in the order of their index.
+cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
+                           const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
+                           int hidden, int* status, cudaStream_t stream);
 
 // out[t, i] = silu(gate) * up.  interleave 0: gate = gu[t, i], up = gu[t, inter + i].  interleave 8: gate and up
 // columns alternate in runs of 8 (g0..g7, u0..u7, g8.., ...): gate = gu[t, 16 (i / 8) + i % 8], up 8 further.
@@ -61,8 +62,11 @@ cudaError_t launch_gemm_skinny(int out_dtype, const void* x, const void* w, cons
 // k is not cut.  Launches that share them must not overlap on the GPU.
 // epilogue 0: out[M, N] = sums + bias.  epilogue 1 (bfloat16 out, no bias, N % 16 == 0): the rows of w are
 // gate and up rows interleaved in runs of 8 (g0..g7, u0..u7, g8.., ...) and out[M, N / 2] = silu(gate) * up.
+// epilogue 2 (float out, M <= 64): k is cut into gemm_tc_shares(M, N, K) shares and out[share, M, N] takes each
+// share's sums as they are (the bias with share 0); the kernel that reads them adds them (launch_rmsnorm).
 // next_w (or null): the [next_n, next_k] bfloat16 weights of the small-batch product that follows in the stream;
 // the kernel asks for the part of them that product reads first to be brought into L2 (a hint, for M <= 64).
+int gemm_tc_shares(int m, int n, int k);
 cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n, int k,
                            int epilogue, float* scratch, long long scratch_floats, int* counters, int n_counters,
                            int* status, const void* next_w, int next_n, int next_k, cudaStream_t stream);

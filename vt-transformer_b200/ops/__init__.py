@@ -74,8 +74,44 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status=
     return out
 
 
-def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None, status=None) -> torch.Tensor:
+class SplitSum:
+    """The result [T, N] of a matrix product as the unadded 32-bit shares [shares, T, N] that the CTAs working
+    on different parts of the inner dimension have left (``linear_to_stream``).  ``rmsnorm`` takes it as its
+    delta and adds the shares, in the order of their index, while it reads them: the product's kernel is spared
+    the merge of the shares at its end, and the delta reaches the 32-bit residual stream unrounded."""
+
+    def __init__(self, shares: torch.Tensor):
+        self.shares = shares
+
+    @property
+    def shape(self):
+        return self.shares.shape[1:]
+
+    @property
+    def device(self):
+        return self.shares.device
+
+    def dense(self, dtype=None) -> torch.Tensor:
+        """The sum as an ordinary tensor (tests, and parts that need one)."""
+        total = self.shares[0].clone()
+        for i in range(1, self.shares.shape[0]):
+            total += self.shares[i]
+        return total if dtype is None else total.to(dtype)
+
+
+def dense(t, dtype=None) -> torch.Tensor:
+    """``t`` as an ordinary tensor, whether it is one or a ``SplitSum``."""
+    if isinstance(t, SplitSum):
+        return t.dense(dtype)
+    return t if dtype is None else t.to(dtype)
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta=None,
+            rows: Optional[torch.Tensor] = None, status=None) -> torch.Tensor:
+    """out = weight * v * rsqrt(mean(v^2) + eps) over the rows ``rows`` (all) of v = x + delta, which is
+    written back to x.  ``delta``: None, a tensor of out's dtype, or a ``SplitSum``."""
+    if isinstance(delta, SplitSum):
+        delta = delta.shares
     backend().rmsnorm(x, delta, weight, float(eps), out, rows, status)
     return out
 
@@ -154,6 +190,27 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
         scratch, counters = _split_workspace(x.device)
         be.gemm_tc(x, w, bias, out, status, scratch, counters, 0, _next_weights(("w", w.data_ptr()), w))
     return out
+
+
+STREAM_SHARES = os.environ.get("VTB200_STREAM_SHARES", "1") != "0"   # False: linear_to_stream always adds the shares itself
+
+
+def linear_to_stream(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], status=None):
+    """x w^T (+ bias) for a result that goes straight into the residual stream (``ResidualStream.add``): a
+    tensor [T, N] of x's dtype, or, for bfloat16 batches small enough that the kernel cuts the inner dimension
+    over CTAs, a ``SplitSum`` of the unadded 32-bit shares, which the next norm adds."""
+    m = x.shape[0]
+    if (STREAM_SHARES and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < m <= SKINNY_MAX_ROWS
+            and SMALL_BATCH_KERNEL != "skinny"):
+        be = backend()
+        n, k = w.shape
+        shares = torch.empty((be.gemm_tc_shares(m, n, k), m, n), dtype=torch.float32, device=x.device)
+        global launches
+        launches += 1
+        be.gemm_tc(x, w, bias, shares, status, None, None, 2, _next_weights(("w", w.data_ptr()), w))
+        return SplitSum(shares)
+    out = torch.empty((m, w.shape[0]), dtype=x.dtype, device=x.device)
+    return linear(x, w, bias, out, status)
 
 
 _workspaces = {}

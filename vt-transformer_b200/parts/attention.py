@@ -75,6 +75,4 @@ class PagedAttention(Mixer):
         o = torch.empty((T, self.q_dim), dtype=h.dtype, device=h.device)
         ops.rope_attention(qkv, o, self.position.table, cache.k, cache.v, ctx, cache.block_table, s.heads, s.kv_heads,
                            s.head_dim, s.window, self.scale, store=cache.writes, status=ctx.status)
-        out = torch.empty((T, s.hidden), dtype=h.dtype, device=h.device)
-        ops.linear(o, self.w_o, self.b_o, out)
-        return out
+        return ops.linear_to_stream(o, self.w_o, self.b_o)

@@ -145,7 +145,8 @@ class PositionEncoding(Part):
 class Mixer(Part):
     """``forward(h, ctx, cache)``: h [T, hidden] normed input in the compute dtype, ctx the
     ``StepContext`` of the step, cache the ``CacheView`` of this run (None if
-    ``cache_spec`` is None).  Returns [T, hidden] in the compute dtype."""
+    ``cache_spec`` is None).  Returns [T, hidden] in the compute dtype (or, for a last product
+    done with ``ops.linear_to_stream``, what that returned): the block adds it to the stream."""
     category = "mixer"
 
     def cache_spec(self):
@@ -179,7 +180,9 @@ class ResidualStream:
 
     A block leaves the output of its last part in ``pending``; the next norm adds it
     while it reads the stream (one pass over memory instead of two), so the sum is
-    formed in 32-bit whatever the compute dtype is."""
+    formed in 32-bit whatever the compute dtype is.  The delta is a tensor [T, H] of the
+    compute dtype or what ``ops.linear_to_stream`` returned (for small batches the unadded
+    32-bit shares of the product, which the norm adds as well)."""
 
     def __init__(self, x: torch.Tensor, status: Optional[torch.Tensor] = None):
         self.x = x
@@ -190,7 +193,7 @@ class ResidualStream:
         delta, self.pending = self.pending, None
         return norm(self.x, delta=delta, rows=rows, status=self.status)
 
-    def add(self, delta: torch.Tensor) -> None:
+    def add(self, delta) -> None:
         if self.pending is not None:
             raise RuntimeError("the residual stream holds a delta that no norm has added yet")
         self.pending = delta

@@ -49,6 +49,4 @@ class GatedMLP(FeedForward):
         T = h.shape[0]
         act = torch.empty((T, s.inter), dtype=h.dtype, device=h.device)
         ops.linear_silu_mul(h, self.w_gate_up, act)
-        out = torch.empty((T, s.hidden), dtype=h.dtype, device=h.device)
-        ops.linear(act, self.w_down, None, out)
-        return out
+        return ops.linear_to_stream(act, self.w_down, None)
