@@ -1,8 +1,8 @@
 """The kernels as Python functions over torch tensors.
 
-Every function runs a hand-written sm_100a kernel of ``csrc`` (or, for the bfloat16
-matrix products of large batches, the library product that vt-transformer's engine also
-uses: cuBLASLt, v1/tensortype/cuda_kernels/lt_sgemm.cu:55-126).  There is no CPU path and
+Every function runs a hand-written sm_100a kernel of ``csrc``; the matrix products too (the
+reference's engine calls cuBLASLt for them, v1/tensortype/cuda_kernels/lt_sgemm.cu:55-126; here
+they are tcgen05 kernels of the package, and an FFMA kernel in 32-bit).  There is no CPU path and
 no fallback: if the extension cannot be loaded or built, the first call raises.
 
 ``backend()`` returns the extension module.  Tests of the host-side logic may put an
