@@ -438,21 +438,24 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
         head[i] = kvh * group + (valid[i] ? row[i] % group : 0);
     }
     const int* table = p.block_table + (size_t)seq * p.table_stride;
-    auto load_block = [&](int blk, int stage) {
+    // the pages of a block's two runs of 16 keys (-1: none); looked up a block ahead of the block's loads
+    auto pages_of = [&](int blk, int (&pg)[2]) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int key = key_lo + blk * DKB + 16 * h;
+            pg[h] = (blk < blk1 && key < key_hi) ? table[key / p.page_size] : -1;
+        }
+    };
+    auto load_block = [&](int blk, int stage, const int (&pg)[2]) {
         const int kb = key_lo + blk * DKB;
         constexpr int CHUNKS = D / 8;
         size_t base[2];
         bool okp[2];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {                          // the block's two runs of 16 keys, a page each
+        for (int h = 0; h < 2; ++h) {
             const int key = kb + 16 * h;
-            okp[h] = key < key_hi;
-            base[h] = 0;
-            if (okp[h]) {
-                const int page = table[key / p.page_size];
-                if (page < 0 || page >= p.n_pages) okp[h] = false;
-                else base[h] = (((size_t)page * p.kv_heads + kvh) * p.page_size + key % p.page_size) * D;
-            }
+            okp[h] = key < key_hi && pg[h] >= 0 && pg[h] < p.n_pages;
+            base[h] = okp[h] ? (((size_t)pg[h] * p.kv_heads + kvh) * p.page_size + key % p.page_size) * D : 0;
         }
         for (int c = lane; c < DKB * CHUNKS; c += 32) {
             const int r = c / CHUNKS, piece = c % CHUNKS;
@@ -469,8 +472,11 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
     // another kernel of this step has put it there
     const bool own_in_first = pos_lo >= key_lo + first * DKB && pos_lo < key_lo + (first + 1) * DKB;
     const bool early = first < blk1 && (!own_in_first || (p.fuse_rope && p.store_kv));
+    int pg_cur[2], pg_next[2];
+    pages_of(first, pg_cur);
+    pages_of(first + W, pg_next);
     if (early) {
-        load_block(first, 0);
+        load_block(first, 0, pg_cur);
         cp_async_commit();
     }
     if (p.next_w != nullptr) {
@@ -487,7 +493,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
     }
     pdl_wait();
     if (first < blk1 && !early) {
-        load_block(first, 0);
+        load_block(first, 0, pg_cur);
         cp_async_commit();
     }
     uint32_t qf[D / 16][4];
@@ -534,8 +540,9 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
     for (int blk = first; blk < blk1; blk += W, ++it) {
         const int stage = it & 1;
         if (blk + W < blk1) {
-            load_block(blk + W, stage ^ 1);
+            load_block(blk + W, stage ^ 1, pg_next);
             cp_async_commit();
+            pages_of(blk + 2 * W, pg_next);        // for the next turn; the answer comes under this block's work
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
@@ -672,38 +679,45 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
         }
     }
     __syncthreads();
-    // merge the four warps: every thread takes elements (row, d) of the [16][D] output
+    // merge the warps: first one weight a (row, warp), the row's maximum and its sum; then every thread takes
+    // elements (row, d) of the [16][D] output
     const int tile = seq * p.kv_heads + kvh;
     float* res = reinterpret_cast<float*>(smem_raw + (size_t)W * WARP_BYTES);   // [16][D], then maxima [16], sums [16]
-    for (int e = threadIdx.x; e < 16 * D; e += W * 32) {
-        const int r = e / D, d = e % D;
-        if (r >= rows_valid) continue;
+    float* wwgt = res + 16 * D + 32;                                            // [16][W] weights, then [16][8] for the runs
+    if (threadIdx.x < 16) {
+        const int r = threadIdx.x;
         float mx = -INFINITY;
 #pragma unroll
         for (int w = 0; w < W; ++w) {
             const float* b = reinterpret_cast<const float*>(smem_raw + (size_t)w * WARP_BYTES);
             if (b[16 * D + 16 + r] > 0.f) mx = fmaxf(mx, b[16 * D + r]);
         }
-        float acc = 0.f, tot = 0.f;
+        float tot = 0.f;
 #pragma unroll
         for (int w = 0; w < W; ++w) {
             const float* b = reinterpret_cast<const float*>(smem_raw + (size_t)w * WARP_BYTES);
             const float l = b[16 * D + 16 + r];
-            if (l > 0.f) {
-                const float wgt = exp2f(b[16 * D + r] - mx);
-                acc += b[e] * wgt;
-                tot += l * wgt;
-            }
+            const float wg = (l > 0.f) ? exp2f(b[16 * D + r] - mx) : 0.f;
+            wwgt[r * W + w] = wg;
+            tot += l * wg;
         }
+        res[16 * D + r] = mx;
+        res[16 * D + 16 + r] = tot;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 16 * D; e += W * 32) {
+        const int r = e / D, d = e % D;
+        if (r >= rows_valid) continue;
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < W; ++w)
+            acc += reinterpret_cast<const float*>(smem_raw + (size_t)w * WARP_BYTES)[e] * wwgt[r * W + w];
+        const float mx = res[16 * D + r], tot = res[16 * D + 16 + r];
         const int t = q_begin + r / group, h = kvh * group + r % group;
         if (p.n_splits == 1) {
             p.out[((size_t)t * p.heads + h) * D + d] = __float2bfloat16_rn(tot > 0.f ? acc / tot : 0.f);
         } else if (p.cluster_merge) {
             res[e] = acc;
-            if (d == 0) {
-                res[16 * D + r] = mx;
-                res[16 * D + 16 + r] = tot;
-            }
         } else {
             const size_t idx = ((size_t)split * p.n_tokens + t) * p.heads + h;
             __stcg(p.part_o + idx * D + d, acc);
@@ -720,24 +734,43 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
         cg::cluster_group cluster = cg::this_cluster();
         cluster.sync();
         const int ranks = (int)cluster.num_blocks(), me = (int)cluster.block_rank();
+        // one weight a (row, run) and the row's sum, from the runs' maxima and sums (all read at once) ...
+        float* rwgt = wwgt + 16 * W;             // [16][8]
+        float* rtot = rwgt + 16 * 8;             // [16]
+        if (threadIdx.x < 16) {
+            const int r = threadIdx.x;
+            float m[8], l[8];
+#pragma unroll
+            for (int rk = 0; rk < 8; ++rk) {
+                const float* o_r = cluster.map_shared_rank(res, rk < ranks ? rk : me);
+                m[rk] = o_r[16 * D + r];
+                l[rk] = rk < ranks ? o_r[16 * D + 16 + r] : 0.f;
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int rk = 0; rk < 8; ++rk)
+                if (l[rk] > 0.f) mx = fmaxf(mx, m[rk]);
+            float tot = 0.f;
+#pragma unroll
+            for (int rk = 0; rk < 8; ++rk) {
+                const float wg = (l[rk] > 0.f) ? exp2f(m[rk] - mx) : 0.f;
+                rwgt[r * 8 + rk] = wg;
+                tot += l[rk] * wg;
+            }
+            rtot[r] = tot;
+        }
+        __syncthreads();
+        // ... then this CTA's share of the elements, the runs added in rank order
         for (int e = me * W * 32 + threadIdx.x; e < 16 * D; e += ranks * W * 32) {
             const int r = e / D, d = e % D;
             if (r >= rows_valid) continue;
-            float mx = -INFINITY;
-            for (int rk = 0; rk < ranks; ++rk) {
-                const float* o_r = cluster.map_shared_rank(res, rk);
-                if (o_r[16 * D + 16 + r] > 0.f) mx = fmaxf(mx, o_r[16 * D + r]);
-            }
-            float acc = 0.f, tot = 0.f;
-            for (int rk = 0; rk < ranks; ++rk) {
-                const float* o_r = cluster.map_shared_rank(res, rk);
-                const float l = o_r[16 * D + 16 + r];
-                if (l > 0.f) {
-                    const float wgt = exp2f(o_r[16 * D + r] - mx);
-                    acc += o_r[e] * wgt;
-                    tot += l * wgt;
-                }
-            }
+            float v[8];
+#pragma unroll
+            for (int rk = 0; rk < 8; ++rk) v[rk] = rk < ranks ? cluster.map_shared_rank(res, rk)[e] : 0.f;
+            float acc = 0.f;
+#pragma unroll
+            for (int rk = 0; rk < 8; ++rk) acc += v[rk] * rwgt[r * 8 + rk];
+            const float tot = rtot[r];
             const int t = q_begin + r / group, h = kvh * group + r % group;
             p.out[((size_t)t * p.heads + h) * D + d] = __float2bfloat16_rn(tot > 0.f ? acc / tot : 0.f);
         }
@@ -798,7 +831,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
 
 template <int D, int W>
 cudaError_t launch_decode_w(const AttnParams& p, int n_seqs, int* counters, cudaStream_t stream) {
-    constexpr int smem = W * 2 * 2 * DKB * (D + 8) * 2 + (16 * D + 32) * 4;
+    constexpr int smem = W * 2 * 2 * DKB * (D + 8) * 2 + (16 * D + 32 + 16 * W + 16 * 8 + 16) * 4;
     static_assert(2 * 2 * DKB * (D + 8) * 2 >= (16 * D + 32) * 4, "a warp's buffers must hold its merged result");
     static_assert(W * 2 * 2 * DKB * (D + 8) * 2 >= (2 * 16 * 64 + 16) * 4, "the merge of the runs needs its weights");
     static bool configured = false;
