@@ -95,10 +95,6 @@ struct AttnParams {
     int store_kv;           // 1: write the token's k and v into their page
     __nv_bfloat16* k_out;   // the cache again, writable
     __nv_bfloat16* v_out;
-    // weights that the next kernel of the stream streams (or null): single-token steps ask for them to be
-    // brought into L2 meanwhile; the keys and values of such a step leave most of the memory bandwidth idle
-    const unsigned char* next_w;
-    unsigned long long next_bytes;
 };
 
 template <int D, int WARPS>
@@ -478,18 +474,6 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
     if (early) {
         load_block(first, 0, pg_cur);
         cp_async_commit();
-    }
-    if (p.next_w != nullptr) {
-        // this thread's share of the next kernel's weights, towards L2
-        const unsigned long long ctas = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
-        const unsigned long long me = ((unsigned long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-        const unsigned long long piece = ((p.next_bytes + ctas * W * 32 - 1) / (ctas * W * 32) + 15) / 16 * 16;
-        const unsigned long long at = (me * W * 32 + threadIdx.x) * piece;
-        if (at < p.next_bytes) {
-            const unsigned long long n = min(piece, p.next_bytes - at) / 16 * 16;
-            if (n > 0)
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(p.next_w + at), "r"((uint32_t)n) : "memory");
-        }
     }
     pdl_wait();
     if (first < blk1 && !early) {
@@ -908,8 +892,6 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
     p.store_kv = 0;
     p.k_out = nullptr;
     p.v_out = nullptr;
-    p.next_w = nullptr;
-    p.next_bytes = 0;
     p.qkv = (const __nv_bfloat16*)qkv;
     p.qkv_stride = qkv_stride;
     p.out = (__nv_bfloat16*)out;
@@ -950,7 +932,7 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
                                     int n_seqs, int n_pages, int n_tokens, int heads, int kv_heads, int head_dim,
                                     int page_size, int window, float scale, int n_splits, float* part_o, float* part_ml,
                                     int* counters, int fuse_rope, const float2* cos_sin, int max_pos, int store_kv,
-                                    const void* next_w, long long next_bytes, int* status, cudaStream_t stream) {
+                                    int* status, cudaStream_t stream) {
     if (n_seqs == 0 || n_tokens == 0) return cudaSuccess;
     if (!attention_mma_supports(head_dim, heads, kv_heads, 1) || page_size % 16 != 0) return cudaErrorInvalidValue;
     if (n_splits < 1) n_splits = 1;
@@ -988,10 +970,6 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
     p.store_kv = store_kv;
     p.k_out = (__nv_bfloat16*)const_cast<void*>(k_cache);
     p.v_out = (__nv_bfloat16*)const_cast<void*>(v_cache);
-    // at most 48 MB: what is brought must still be in L2 when the next kernel asks for it
-    p.next_w = (next_w != nullptr && next_bytes >= 16 && reinterpret_cast<uintptr_t>(next_w) % 16 == 0)
-                   ? static_cast<const unsigned char*>(next_w) : nullptr;
-    p.next_bytes = (unsigned long long)(next_bytes < (48LL << 20) ? next_bytes : (48LL << 20));
     switch (head_dim) {
         case 16: return launch_decode_d<16>(p, n_seqs, counters, stream);
         case 32: return launch_decode_d<32>(p, n_seqs, counters, stream);

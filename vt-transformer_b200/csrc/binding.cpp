@@ -185,8 +185,7 @@ void gemm_skinny(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, T
 }
 
 void gemm_tc(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tensor& out, c10::optional<Tensor> status,
-             c10::optional<Tensor> scratch, c10::optional<Tensor> counters, int64_t epilogue,
-             c10::optional<Tensor> next_w) {
+             c10::optional<Tensor> scratch, c10::optional<Tensor> counters, int64_t epilogue) {
     check_cuda(x, "x"); check_cuda(w, "w"); check_cuda(out, "out");
     TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16, "gemm_tc: x and w must be bfloat16");
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2, "gemm_tc: x and w must be 2-d");
@@ -222,20 +221,9 @@ void gemm_tc(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tenso
         cp = counters->data_ptr<int>();
         cn = counters->numel();
     }
-    // the weights of the product that follows, if the caller knows them: a hint, taken only in the form
-    // this kernel streams (bfloat16, dense, 16-byte aligned, on this device)
-    const void* np = nullptr;
-    int nn = 0, nk = 0;
-    if (next_w.has_value() && next_w->is_cuda() && next_w->device() == x.device() && next_w->dim() == 2 &&
-        next_w->scalar_type() == torch::kBFloat16 && next_w->is_contiguous() &&
-        ((uintptr_t)next_w->data_ptr() & 15) == 0 && next_w->size(1) % 8 == 0) {
-        np = next_w->data_ptr();
-        nn = next_w->size(0);
-        nk = next_w->size(1);
-    }
     c10::cuda::CUDAGuard guard(x.device());
     check_launch(vtb::launch_gemm_tc(dtype_code(out, "out"), x.data_ptr(), w.data_ptr(), bp, out.data_ptr(), m, n, k,
-                                     (int)epilogue, sp, sn, cp, cn, status_ptr(status), np, nn, nk, stream_of(x)), "gemm_tc");
+                                     (int)epilogue, sp, sn, cp, cn, status_ptr(status), stream_of(x)), "gemm_tc");
 }
 
 bool attention_mma_supports(int64_t head_dim, int64_t heads, int64_t kv_heads, int64_t warps) {
@@ -330,8 +318,7 @@ void attention_decode(const Tensor& qkv, Tensor& out, const Tensor& k_cache, con
                       const Tensor& q_start, const Tensor& block_table, int64_t heads, int64_t kv_heads, int64_t head_dim,
                       int64_t window, double scale, int64_t n_splits, c10::optional<Tensor> part_o,
                       c10::optional<Tensor> part_ml, c10::optional<Tensor> counters, bool fuse_rope,
-                      c10::optional<Tensor> cos_sin, bool store_kv, c10::optional<Tensor> status,
-                      c10::optional<Tensor> next_w) {
+                      c10::optional<Tensor> cos_sin, bool store_kv, c10::optional<Tensor> status) {
     check_cuda(qkv, "qkv"); check_cuda(out, "out"); check_i32(cu_q, "cu_q"); check_i32(q_start, "q_start");
     check_i32(block_table, "block_table");
     TORCH_CHECK(qkv.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16,
@@ -373,19 +360,13 @@ void attention_decode(const Tensor& qkv, Tensor& out, const Tensor& k_cache, con
         TORCH_CHECK(n_tokens == n_seqs, "attention_decode: the fused rotation takes one token a sequence");
         TORCH_CHECK(qkv.size(1) == (heads + 2 * kv_heads) * head_dim, "attention_decode: qkv must hold q, k and v");
     }
-    const void* np = nullptr;
-    long long nbytes = 0;
-    if (next_w.has_value() && next_w->is_cuda() && next_w->device() == qkv.device() && next_w->is_contiguous()) {
-        np = next_w->data_ptr();
-        nbytes = (long long)next_w->numel() * next_w->element_size();
-    }
     c10::cuda::CUDAGuard guard(qkv.device());
     check_launch(vtb::launch_attention_decode(qkv.data_ptr(), qkv.size(1), out.data_ptr(), k_cache.data_ptr(),
                                               v_cache.data_ptr(), cu_q.data_ptr<int>(), q_start.data_ptr<int>(),
                                               block_table.data_ptr<int>(), block_table.size(1), n_seqs, k_cache.size(0),
                                               n_tokens, heads, kv_heads, head_dim, k_cache.size(2), window, (float)scale,
                                               n_splits, po, pm, pc, fuse_rope ? 1 : 0, cs, max_pos, store_kv ? 1 : 0,
-                                              np, nbytes, status_ptr(status), stream_of(qkv)), "attention_decode");
+                                              status_ptr(status), stream_of(qkv)), "attention_decode");
 }
 
 void attention_simt(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache,
@@ -450,8 +431,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("status") = py::none());
     m.def("gemm_skinny", &gemm_skinny, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"));
     m.def("gemm_tc", &gemm_tc, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"), py::arg("status") = py::none(),
-          py::arg("scratch") = py::none(), py::arg("counters") = py::none(), py::arg("epilogue") = 0,
-          py::arg("next_w") = py::none());
+          py::arg("scratch") = py::none(), py::arg("counters") = py::none(), py::arg("epilogue") = 0);
     m.def("gemm_tc_shares", [](int64_t m, int64_t n, int64_t k) { return (int64_t)vtb::gemm_tc_shares(m, n, k); });
     m.def("attention_mma_supports", &attention_mma_supports);
     m.def("attention_mma", &attention_mma, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
@@ -467,8 +447,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),
           py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("n_splits"), py::arg("part_o") = py::none(),
           py::arg("part_ml") = py::none(), py::arg("counters") = py::none(), py::arg("fuse_rope") = false,
-          py::arg("cos_sin") = py::none(), py::arg("store_kv") = false, py::arg("status") = py::none(),
-          py::arg("next_w") = py::none());
+          py::arg("cos_sin") = py::none(), py::arg("store_kv") = false, py::arg("status") = py::none());
     m.def("argmax", &argmax, py::arg("logits"), py::arg("out"));
     m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"),
           py::arg("u"), py::arg("out"));

@@ -111,42 +111,12 @@ __device__ __forceinline__ void emit16(float (&v)[16], int r, int a_row0, int b_
     }
 }
 
-// The weights the next small-batch product of the stream will read first: CTA c of that launch starts with
-// `depth` k-blocks of 128 rows of `w` (its first unit).  A kernel that is given this asks for those bytes to be
-// brought into L2 once its own loads are all on their way, so that the memory system has work while this
-// kernel merges and stores and the next one sets itself up.  Only a hint: nothing waits for it.
-struct NextWeights {
-    const unsigned char* w;      // nullptr: nothing to prefetch
-    int rows, k;                 // [rows, k] bfloat16, row-major
-    int ksplit, grid, depth;     // shares of k a tile, CTAs of the next launch, k-blocks to bring for each
-};
-
-__device__ __forceinline__ void prefetch_next_weights(const NextWeights& nx, int lane) {
-    if (nx.w == nullptr) return;
-    const int nkb = (nx.k + BK - 1) / BK;
-    const size_t row_bytes = (size_t)nx.k * 2;
-    for (int c = blockIdx.x; c < nx.grid; c += gridDim.x) {
-        const int tile = c / nx.ksplit, krank = c % nx.ksplit;
-        const int kb0 = (int)((long long)krank * nkb / nx.ksplit), kb1 = (int)((long long)(krank + 1) * nkb / nx.ksplit);
-        const int col0 = kb0 * BK, col1 = min(nx.k, min(kb1, kb0 + nx.depth) * BK);
-        const uint32_t bytes = (uint32_t)(col1 - col0) * 2;        // a multiple of 16: k is a multiple of 8
-        if (col1 <= col0) continue;
-        for (int r = lane; r < BM; r += 32) {
-            const int row = tile * BM + r;
-            if (row >= nx.rows) break;
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(nx.w + (size_t)row * row_bytes + (size_t)col0 * 2),
-                         "r"(bytes)
-                         : "memory");
-        }
-    }
-}
-
 // BN: rows of the other operand in a tile (columns of the accumulator).  SWAP: the 128-row operand is w.
 template <int BN, int STAGES, bool SWAP, int EPI, typename TOut>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo, int n_full,
-               int s_tail, float* __restrict__ scratch, int* __restrict__ counters, int* status, const NextWeights nx) {
+               int s_tail, float* __restrict__ scratch, int* __restrict__ counters, int* status) {
     constexpr int B_STAGE = BN * BK * 2;
     constexpr int COLS = BN < 32 ? 32 : BN;          // tensor-memory columns: a power of two, at least 32
     extern __shared__ unsigned char smem_raw[];
@@ -236,8 +206,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
         }
-        __syncwarp();
-        prefetch_next_weights(nx, lane);       // this CTA's loads are all on their way
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(BM, BN);
@@ -371,8 +339,7 @@ int sm_count() {
 
 template <int BN, int STAGES, bool SWAP, int EPI, typename TOut>
 cudaError_t launch_cfg(const void* a, int rows_a, const void* b, int rows_b, int k, const float* bias, TOut* out, int ldo,
-                       int n_full, int s_tail, float* scratch, int* counters, int* status, const NextWeights& nx,
-                       cudaStream_t stream) {
+                       int n_full, int s_tail, float* scratch, int* counters, int* status, cudaStream_t stream) {
     CUtensorMap map_a, map_b;
     if (!make_map(&map_a, a, rows_a, k, BM) || !make_map(&map_b, b, rows_b, k, BN)) return cudaErrorInvalidValue;
     constexpr int smem = STAGES * (A_STAGE + BN * BK * 2) + 1024 + 256;
@@ -386,7 +353,7 @@ cudaError_t launch_cfg(const void* a, int rows_a, const void* b, int rows_b, int
     const int units = n_full + (tiles - n_full) * s_tail;
     return launch(gemm_tc_kernel<BN, STAGES, SWAP, EPI, TOut>, dim3(units < sm_count() ? units : sm_count(), 1, 1),
                   dim3(THREADS, 1, 1), smem, stream, map_a, map_b, bias, out, rows_a, rows_b, k, ldo, n_full, s_tail, scratch,
-                  counters, status, nx);
+                  counters, status);
 }
 
 // Into how many shares k is cut when w is the 128-row operand (small batches).  One CTA fits an SM, so the
@@ -413,28 +380,16 @@ int small_batch_ksplit(int n, int k, int bn, bool have_scratch, long long scratc
 
 template <int EPI, typename TOut>
 cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* out, int m, int n, int k, float* scratch,
-                         long long scratch_floats, int* counters, int n_counters, int* status, const void* next_w,
-                         int next_n, int next_k, cudaStream_t stream) {
-    NextWeights nx{nullptr, 0, 0, 1, 0, 0};
+                         long long scratch_floats, int* counters, int n_counters, int* status, cudaStream_t stream) {
     if (m <= 64) {
         // swapped: w is the 128-row operand
         const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
         const bool have_scratch = scratch != nullptr && counters != nullptr;
         const int ksplit = (EPI == 2) ? gemm_tc_shares(m, n, k)
                                       : small_batch_ksplit(n, k, bn, have_scratch, scratch_floats, n_counters);
-        if (next_w != nullptr && next_n > 0 && next_k >= 8 && next_k % 8 == 0) {
-            // the product after this one is taken to have as many rows of x as this one
-            nx.w = static_cast<const unsigned char*>(next_w);
-            nx.rows = next_n;
-            nx.k = next_k;
-            nx.ksplit = small_batch_ksplit(next_n, next_k, bn, have_scratch, scratch_floats, n_counters);
-            const int units = ((next_n + BM - 1) / BM) * nx.ksplit;
-            nx.grid = units < sm_count() ? units : sm_count();
-            nx.depth = 16;
-        }
-        if (bn == 16) return launch_cfg<16, 11, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, nx, stream);
-        if (bn == 32) return launch_cfg<32, 10, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, nx, stream);
-        return launch_cfg<64, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, nx, stream);
+        if (bn == 16) return launch_cfg<16, 11, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
+        if (bn == 32) return launch_cfg<32, 10, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
+        return launch_cfg<64, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
     }
     if constexpr (EPI == 2) {
         return cudaErrorInvalidValue;     // shares are left unadded for small batches only
@@ -463,9 +418,9 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
         if (s_tail == 1) n_full = tiles;
         if (wide)
             return launch_cfg<256, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, EPI == 1 ? n / 2 : n, n_full, s_tail, scratch,
-                                                         counters, status, nx, stream);
+                                                         counters, status, stream);
         return launch_cfg<128, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, EPI == 1 ? n / 2 : n, n_full, s_tail, scratch, counters,
-                                                     status, nx, stream);
+                                                     status, stream);
     }
 }
 
@@ -478,26 +433,25 @@ int gemm_tc_shares(int m, int n, int k) {
 
 cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n, int k,
                            int epilogue, float* scratch, long long scratch_floats, int* counters, int n_counters,
-                           int* status, const void* next_w, int next_n, int next_k, cudaStream_t stream) {
+                           int* status, cudaStream_t stream) {
     if (m == 0 || n == 0) return cudaSuccess;
     if (k % 8 != 0 || k < 8) return cudaErrorInvalidValue;
     if (epilogue == 1) {
         if (n % 16 != 0 || bias != nullptr || out_dtype != kBF16) return cudaErrorInvalidValue;
         return launch_typed<1, __nv_bfloat16>(x, w, nullptr, (__nv_bfloat16*)out, m, n, k, scratch, scratch_floats,
-                                              counters, n_counters, status, next_w, next_n, next_k, stream);
+                                              counters, n_counters, status, stream);
     }
     if (epilogue == 2) {
         if (out_dtype != kF32 || m > 64) return cudaErrorInvalidValue;
-        return launch_typed<2, float>(x, w, bias, (float*)out, m, n, k, nullptr, 0, nullptr, 0, status, next_w, next_n, next_k,
-                                      stream);
+        return launch_typed<2, float>(x, w, bias, (float*)out, m, n, k, nullptr, 0, nullptr, 0, status, stream);
     }
     if (epilogue != 0) return cudaErrorInvalidValue;
     if (out_dtype == kBF16)
         return launch_typed<0, __nv_bfloat16>(x, w, bias, (__nv_bfloat16*)out, m, n, k, scratch, scratch_floats, counters,
-                                              n_counters, status, next_w, next_n, next_k, stream);
+                                              n_counters, status, stream);
     if (out_dtype == kF32)
         return launch_typed<0, float>(x, w, bias, (float*)out, m, n, k, scratch, scratch_floats, counters, n_counters,
-                                      status, next_w, next_n, next_k, stream);
+                                      status, stream);
     return cudaErrorInvalidValue;
 }
 

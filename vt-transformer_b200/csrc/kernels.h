@@ -64,12 +64,10 @@ cudaError_t launch_gemm_skinny(int out_dtype, const void* x, const void* w, cons
 // gate and up rows interleaved in runs of 8 (g0..g7, u0..u7, g8.., ...) and out[M, N / 2] = silu(gate) * up.
 // epilogue 2 (float out, M <= 64): k is cut into gemm_tc_shares(M, N, K) shares and out[share, M, N] takes each
 // share's sums as they are (the bias with share 0); the kernel that reads them adds them (launch_rmsnorm).
-// next_w (or null): the [next_n, next_k] bfloat16 weights of the small-batch product that follows in the stream;
-// the kernel asks for the part of them that product reads first to be brought into L2 (a hint, for M <= 64).
 int gemm_tc_shares(int m, int n, int k);
 cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n, int k,
                            int epilogue, float* scratch, long long scratch_floats, int* counters, int n_counters,
-                           int* status, const void* next_w, int next_n, int next_k, cudaStream_t stream);
+                           int* status, cudaStream_t stream);
 
 // Tensor-core attention over the paged cache (bfloat16).  A tile is 16 * warps rows, row r being
 // (token r / group, head r % group); `tiles` lists (sequence, first token) pairs, or is null when
@@ -103,7 +101,7 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
                                     int n_seqs, int n_pages, int n_tokens, int heads, int kv_heads, int head_dim,
                                     int page_size, int window, float scale, int n_splits, float* part_o, float* part_ml,
                                     int* counters, int fuse_rope, const float2* cos_sin, int max_pos, int store_kv,
-                                    const void* next_w, long long next_bytes, int* status, cudaStream_t stream);
+                                    int* status, cudaStream_t stream);
 
 // out[r] = index of the largest logit of row r (the lowest index among equals).
 cudaError_t launch_argmax(const float* logits, int* out, int n_rows, int vocab, cudaStream_t stream);

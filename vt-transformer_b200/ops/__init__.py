@@ -12,7 +12,6 @@ does.
 from __future__ import annotations
 
 import os
-import weakref
 from typing import Optional
 
 import torch
@@ -37,33 +36,6 @@ def use_backend(obj) -> None:
     the real one at the next call."""
     global _backend
     _backend = obj
-
-
-# --------------------------------------------------------------------------- what follows what
-#
-# A decode step streams every weight once and its kernels are short: where one kernel merges and stores and
-# the next sets itself up, the memory system would idle.  So a kernel of a small batch is told which weights
-# the kernel after it will stream, and asks for their first bytes to be brought into L2 when its own loads are
-# on their way.  Which weights follow is not said by any part: it is what followed the last time the same
-# kernel ran (steps repeat), kept here by the address of the kernel's own weights or cache.  A hint only:
-# a wrong or missing one costs a little bandwidth or nothing.
-
-PREFETCH_NEXT = os.environ.get("VTB200_PREFETCH_NEXT", "1") != "0"
-_follow = {}        # key of a kernel -> weak reference to the weights streamed by the kernel after it
-_prev_key = None
-
-
-def _next_weights(key, w=None):
-    """Notes that ``w`` (the weights of the calling kernel, or None if it streams none) follows the kernel
-    that called before, and returns what followed ``key`` the last time (or None)."""
-    global _prev_key
-    if not PREFETCH_NEXT:
-        return None
-    if _prev_key is not None:
-        _follow[_prev_key] = None if w is None else weakref.ref(w)
-    _prev_key = key
-    ref = _follow.get(key)
-    return None if ref is None else ref()
 
 
 # --------------------------------------------------------------------------- elementwise
@@ -143,7 +115,7 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
     if x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and FUSE_SILU and \
             not (x.shape[0] <= SKINNY_MAX_ROWS and SMALL_BATCH_KERNEL == "skinny"):
         scratch, counters = _split_workspace(x.device)
-        be.gemm_tc(x, w_gate_up, None, out, status, scratch, counters, 1, _next_weights(("w", w_gate_up.data_ptr()), w_gate_up))
+        be.gemm_tc(x, w_gate_up, None, out, status, scratch, counters, 1)
         return out
     gu = torch.empty((x.shape[0], w_gate_up.shape[0]), dtype=x.dtype, device=x.device)
     linear(x, w_gate_up, None, gu, status)
@@ -188,7 +160,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
         be.gemm_skinny(x, w, bias, out)
     else:
         scratch, counters = _split_workspace(x.device)
-        be.gemm_tc(x, w, bias, out, status, scratch, counters, 0, _next_weights(("w", w.data_ptr()), w))
+        be.gemm_tc(x, w, bias, out, status, scratch, counters)
     return out
 
 
@@ -207,7 +179,7 @@ def linear_to_stream(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
         shares = torch.empty((be.gemm_tc_shares(m, n, k), m, n), dtype=torch.float32, device=x.device)
         global launches
         launches += 1
-        be.gemm_tc(x, w, bias, shares, status, None, None, 2, _next_weights(("w", w.data_ptr()), w))
+        be.gemm_tc(x, w, bias, shares, status, None, None, 2)
         return SplitSum(shares)
     out = torch.empty((m, w.shape[0]), dtype=x.dtype, device=x.device)
     return linear(x, w, bias, out, status)
@@ -276,8 +248,7 @@ def rope_attention(qkv, out, cos_sin, k_cache, v_cache, ctx, block_table, heads:
             part_ml = torch.empty((splits, ctx.n_tokens, heads, 2), dtype=torch.float32, device=qkv.device)
             counters = _attention_counters(qkv.device, ctx.n_seqs * kv_heads)
         be.attention_decode(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, heads, kv_heads, head_dim, w,
-                            float(scale), splits, part_o, part_ml, counters, True, cos_sin, bool(store), status,
-                            _next_weights(("a", k_cache.data_ptr())))
+                            float(scale), splits, part_o, part_ml, counters, True, cos_sin, bool(store), status)
         return out
     rope_store(qkv, ctx.positions, cos_sin, k_cache, v_cache, ctx.token_seq, block_table, heads, kv_heads, head_dim,
                store=store, status=status)
@@ -298,7 +269,6 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
     be = backend()
     w = int(window) if window else 0
     group = heads // kv_heads
-    next_w = _next_weights(("a", k_cache.data_ptr()))
     if qkv.dtype == torch.bfloat16 and ATTENTION_KERNEL in ("auto", "mma"):
         if ctx.max_q_len == 1 and be.attention_mma_supports(head_dim, heads, kv_heads, 1):
             span = ctx.max_kv_len if not w else min(ctx.max_kv_len, w + 31)
@@ -309,8 +279,7 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
                 part_ml = torch.empty((splits, ctx.n_tokens, heads, 2), dtype=torch.float32, device=qkv.device)
                 counters = _attention_counters(qkv.device, ctx.n_seqs * kv_heads)
             be.attention_decode(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, heads, kv_heads,
-                                head_dim, w, float(scale), splits, part_o, part_ml, counters, False, None, False, None,
-                                next_w)
+                                head_dim, w, float(scale), splits, part_o, part_ml, counters)
             return out
         # portions long enough to fill tiles of 128 rows: the tcgen05 kernel where it takes the sizes
         if (ATTENTION_KERNEL == "auto" and ctx.max_q_len * group >= 128
