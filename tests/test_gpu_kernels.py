@@ -317,6 +317,16 @@ def test_single_token_step_rotates_and_stores_inside_the_attention_kernel(heads,
         assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])          # the pages hold the same bits
         assert torch.equal(a[1], kc0) != store                               # and were written iff the run stores
     assert float((results[(True, True)][0].float() - results[(False, True)][0].float()).abs().max()) > 0.01
+    # q, k and v as three unadded 32-bit shares that sum (in bfloat16) to the same values: the same output and pages
+    parts = torch.randn(3, *qkv0.shape, device=DEV)
+    parts[0] = qkv0.float() - parts[1] - parts[2]
+    parts[0] += qkv0.float() - (parts[0] + parts[1] + parts[2])          # what rounding took
+    assert torch.equal((parts[0] + parts[1] + parts[2]).to(dtype), qkv0)
+    kc, vc = kc0.clone(), vc0.clone()
+    out = torch.empty(T, heads * d, device=DEV, dtype=dtype)
+    o.rope_attention(o.SplitSum(parts), out, cs, kc, vc, ctx, table, heads, kv_heads, d, window, 1 / math.sqrt(d), store=True)
+    ref = results[(True, True)]
+    assert torch.equal(out, ref[0]) and torch.equal(kc, ref[1]) and torch.equal(vc, ref[2])
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 33, 64])

@@ -95,6 +95,10 @@ struct AttnParams {
     int store_kv;           // 1: write the token's k and v into their page
     __nv_bfloat16* k_out;   // the cache again, writable
     __nv_bfloat16* v_out;
+    // single-token steps may also take q, k and v as the unadded 32-bit shares [n_shares, tokens, qkv_stride] that
+    // the product before them left (its inner dimension cut over CTAs): they are added, in order, where they are read
+    const float* qkv_shares;
+    int n_shares;
 };
 
 template <int D, int WARPS>
@@ -481,13 +485,41 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
         cp_async_commit();
     }
     uint32_t qf[D / 16][4];
+    // With q, k and v as unadded shares (one token a sequence): this CTA's part of the token's row, that is its
+    // group's heads of q, then its head of k and of v, is added once, share by share, and kept as bfloat16 in the
+    // shared memory that later takes the merged result.
+    __nv_bfloat16* own = reinterpret_cast<__nv_bfloat16*>(smem_raw + (size_t)W * WARP_BYTES);     // [group + 2][D]
+    if (p.qkv_shares != nullptr) {
+        const size_t share_stride = (size_t)p.n_tokens * p.qkv_stride;
+        const float* row0 = p.qkv_shares + (size_t)q_begin * p.qkv_stride;
+        for (int e = threadIdx.x; e < (group + 2) * (D / 2); e += W * 32) {
+            const int j = e / (D / 2), d2 = (e % (D / 2)) * 2;
+            const int col = (j < group ? (kvh * group + j) : (j == group ? p.heads + kvh : p.heads + p.kv_heads + kvh)) * D + d2;
+            float2 v[8];                       // all shares' loads in flight together; added in order
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                v[q] = (q < p.n_shares) ? __ldcg(reinterpret_cast<const float2*>(row0 + q * share_stride + col)) : make_float2(0.f, 0.f);
+            float2 acc = v[0];
+#pragma unroll
+            for (int q = 1; q < 8; ++q) {
+                acc.x += v[q].x;
+                acc.y += v[q].y;
+            }
+            *reinterpret_cast<uint32_t*>(own + j * D + d2) = pack_bf16(acc.x, acc.y);
+        }
+        __syncthreads();
+    }
+    // two neighbouring values of q: row `t` of qkv, head `h`, at `d`
+    auto pair_at = [&](int t, int h, int d) -> uint32_t {
+        if (p.qkv_shares != nullptr) return *reinterpret_cast<const uint32_t*>(own + (h - kvh * group) * D + d);
+        return *reinterpret_cast<const uint32_t*>(p.qkv + (size_t)t * p.qkv_stride + (size_t)h * D + d);
+    };
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        const __nv_bfloat16* qp = p.qkv + (size_t)tok[i] * p.qkv_stride + (size_t)head[i] * D;
 #pragma unroll
         for (int ks_ = 0; ks_ < D / 16; ++ks_) {
-            qf[ks_][i] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp + ks_ * 16 + 2 * tq) : 0u;
-            qf[ks_][i + 2] = valid[i] ? *reinterpret_cast<const uint32_t*>(qp + ks_ * 16 + 8 + 2 * tq) : 0u;
+            qf[ks_][i] = valid[i] ? pair_at(tok[i], head[i], ks_ * 16 + 2 * tq) : 0u;
+            qf[ks_][i + 2] = valid[i] ? pair_at(tok[i], head[i], ks_ * 16 + 8 + 2 * tq) : 0u;
         }
     }
     if (p.fuse_rope && p.cos_sin != nullptr) {
@@ -540,8 +572,11 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
             // block in shared memory and into their page.  (A run of a layer that only reads another run's
             // cache finds the token's k and v there already.)
             const int r = pos_lo - kb;
-            const __nv_bfloat16* krow = p.qkv + (size_t)q_begin * p.qkv_stride + (size_t)(p.heads + kvh) * D;
-            const __nv_bfloat16* vrow = krow + (size_t)p.kv_heads * D;
+            const int kcol = (p.heads + kvh) * D, vcol = kcol + p.kv_heads * D;
+            auto value_at = [&](int col) -> __nv_bfloat16 {       // col: from the start of the token's k
+                if (p.qkv_shares != nullptr) return own[group * D + (col < kcol + D ? col - kcol : D + col - vcol)];
+                return p.qkv[(size_t)q_begin * p.qkv_stride + col];
+            };
             __nv_bfloat16* ksm = ks + ((size_t)stage * DKB + r) * LD;
             __nv_bfloat16* vsm = vs + ((size_t)stage * DKB + r) * LD;
             __nv_bfloat16 *kg = nullptr, *vg = nullptr;
@@ -558,8 +593,8 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
             const bool rot = p.cos_sin != nullptr && pos_lo < p.max_pos;
             const float2* cs = p.cos_sin + (size_t)(rot ? pos_lo : 0) * (D / 2);
             for (int i = lane; i < D / 2; i += 32) {
-                const float a = __bfloat162float(krow[i]), b = __bfloat162float(krow[i + D / 2]);
-                __nv_bfloat16 ka = krow[i], kb2 = krow[i + D / 2];
+                __nv_bfloat16 ka = value_at(kcol + i), kb2 = value_at(kcol + i + D / 2);
+                const float a = __bfloat162float(ka), b = __bfloat162float(kb2);
                 if (rot) {
                     const float2 c = cs[i];
                     ka = __float2bfloat16_rn(a * c.x - b * c.y);
@@ -570,7 +605,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
                 if (kg) { kg[i] = ka; kg[i + D / 2] = kb2; }
             }
             for (int i = lane; i < D; i += 32) {
-                const __nv_bfloat16 vv = vrow[i];
+                const __nv_bfloat16 vv = value_at(vcol + i);
                 vsm[i] = vv;
                 if (vg) vg[i] = vv;
             }
@@ -892,6 +927,8 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
     p.store_kv = 0;
     p.k_out = nullptr;
     p.v_out = nullptr;
+    p.qkv_shares = nullptr;
+    p.n_shares = 0;
     p.qkv = (const __nv_bfloat16*)qkv;
     p.qkv_stride = qkv_stride;
     p.out = (__nv_bfloat16*)out;
@@ -932,7 +969,7 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
                                     int n_seqs, int n_pages, int n_tokens, int heads, int kv_heads, int head_dim,
                                     int page_size, int window, float scale, int n_splits, float* part_o, float* part_ml,
                                     int* counters, int fuse_rope, const float2* cos_sin, int max_pos, int store_kv,
-                                    int* status, cudaStream_t stream) {
+                                    const float* qkv_shares, int n_shares, int* status, cudaStream_t stream) {
     if (n_seqs == 0 || n_tokens == 0) return cudaSuccess;
     if (!attention_mma_supports(head_dim, heads, kv_heads, 1) || page_size % 16 != 0) return cudaErrorInvalidValue;
     if (n_splits < 1) n_splits = 1;
@@ -970,6 +1007,9 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
     p.store_kv = store_kv;
     p.k_out = (__nv_bfloat16*)const_cast<void*>(k_cache);
     p.v_out = (__nv_bfloat16*)const_cast<void*>(v_cache);
+    if (qkv_shares != nullptr && (!fuse_rope || n_shares < 1 || n_shares > 8)) return cudaErrorInvalidValue;
+    p.qkv_shares = qkv_shares;
+    p.n_shares = n_shares;
     switch (head_dim) {
         case 16: return launch_decode_d<16>(p, n_seqs, counters, stream);
         case 32: return launch_decode_d<32>(p, n_seqs, counters, stream);

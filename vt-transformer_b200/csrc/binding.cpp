@@ -318,7 +318,8 @@ void attention_decode(const Tensor& qkv, Tensor& out, const Tensor& k_cache, con
                       const Tensor& q_start, const Tensor& block_table, int64_t heads, int64_t kv_heads, int64_t head_dim,
                       int64_t window, double scale, int64_t n_splits, c10::optional<Tensor> part_o,
                       c10::optional<Tensor> part_ml, c10::optional<Tensor> counters, bool fuse_rope,
-                      c10::optional<Tensor> cos_sin, bool store_kv, c10::optional<Tensor> status) {
+                      c10::optional<Tensor> cos_sin, bool store_kv, c10::optional<Tensor> status,
+                      c10::optional<Tensor> qkv_shares) {
     check_cuda(qkv, "qkv"); check_cuda(out, "out"); check_i32(cu_q, "cu_q"); check_i32(q_start, "q_start");
     check_i32(block_table, "block_table");
     TORCH_CHECK(qkv.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16,
@@ -360,13 +361,23 @@ void attention_decode(const Tensor& qkv, Tensor& out, const Tensor& k_cache, con
         TORCH_CHECK(n_tokens == n_seqs, "attention_decode: the fused rotation takes one token a sequence");
         TORCH_CHECK(qkv.size(1) == (heads + 2 * kv_heads) * head_dim, "attention_decode: qkv must hold q, k and v");
     }
+    const float* shp = nullptr;
+    int n_shares = 0;
+    if (qkv_shares.has_value()) {
+        check_f32(*qkv_shares, "qkv_shares");
+        TORCH_CHECK(fuse_rope && qkv_shares->dim() == 3 && qkv_shares->size(1) == n_tokens && qkv_shares->size(2) == qkv.size(1) &&
+                        qkv_shares->is_contiguous() && qkv_shares->size(0) >= 1 && qkv.size(1) % 2 == 0,
+                    "attention_decode: shares of qkv must be [shares, tokens, width of qkv] float, with the fused rotation");
+        shp = qkv_shares->data_ptr<float>();
+        n_shares = qkv_shares->size(0);
+    }
     c10::cuda::CUDAGuard guard(qkv.device());
     check_launch(vtb::launch_attention_decode(qkv.data_ptr(), qkv.size(1), out.data_ptr(), k_cache.data_ptr(),
                                               v_cache.data_ptr(), cu_q.data_ptr<int>(), q_start.data_ptr<int>(),
                                               block_table.data_ptr<int>(), block_table.size(1), n_seqs, k_cache.size(0),
                                               n_tokens, heads, kv_heads, head_dim, k_cache.size(2), window, (float)scale,
                                               n_splits, po, pm, pc, fuse_rope ? 1 : 0, cs, max_pos, store_kv ? 1 : 0,
-                                              status_ptr(status), stream_of(qkv)), "attention_decode");
+                                              shp, n_shares, status_ptr(status), stream_of(qkv)), "attention_decode");
 }
 
 void attention_simt(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache,
@@ -447,7 +458,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),
           py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("n_splits"), py::arg("part_o") = py::none(),
           py::arg("part_ml") = py::none(), py::arg("counters") = py::none(), py::arg("fuse_rope") = false,
-          py::arg("cos_sin") = py::none(), py::arg("store_kv") = false, py::arg("status") = py::none());
+          py::arg("cos_sin") = py::none(), py::arg("store_kv") = false, py::arg("status") = py::none(),
+          py::arg("qkv_shares") = py::none());
     m.def("argmax", &argmax, py::arg("logits"), py::arg("out"));
     m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"),
           py::arg("u"), py::arg("out"));

@@ -9,6 +9,8 @@ by the kernels from there.  Padding tokens belong to no sequence; kernels skip t
 """
 from __future__ import annotations
 
+import gc
+
 from typing import Dict, List, Sequence, Tuple
 
 import numpy as np
@@ -65,9 +67,18 @@ class DecodeGraph:
         torch.cuda.synchronize(dev)
         self.graph = torch.cuda.CUDAGraph()
         launches_before = runner.rt.ops.launches
-        with torch.cuda.graph(self.graph):
-            self.ctx.extras.clear()
-            self.logits = runner.model.forward(self.ctx, views)
+        # No garbage collection while the stream is capturing: collecting an older graph there (a runner that
+        # is no longer used) destroys it, which CUDA does not allow inside a capture and which would spoil this one.
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.ctx.extras.clear()
+                self.logits = runner.model.forward(self.ctx, views)
+        finally:
+            if was_enabled:
+                gc.enable()
         self.launches = runner.rt.ops.launches - launches_before
 
     def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:

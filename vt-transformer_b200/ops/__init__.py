@@ -227,17 +227,31 @@ def _attention_tiles(ctx, tokens_per_tile: int, device):
     return tiles
 
 
+def single_token_step_is_one_kernel(ctx, dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
+    """Whether ``rope_attention`` will run rotation, cache store and attention of this step as one kernel: a
+    bfloat16 step of single tokens at sizes the tensor-core kernel takes.  That kernel also takes q, k and v as
+    the unadded shares of the product before it (``linear_to_stream``)."""
+    return (dtype == torch.bfloat16 and ATTENTION_KERNEL in ("auto", "mma") and FUSE_ROPE and ctx.max_q_len == 1
+            and ctx.n_tokens == ctx.n_seqs and backend().attention_mma_supports(head_dim, heads, kv_heads, 1))
+
+
 def rope_attention(qkv, out, cos_sin, k_cache, v_cache, ctx, block_table, heads: int, kv_heads: int, head_dim: int,
                    window: Optional[int], scale: float, store: bool = True, status=None) -> torch.Tensor:
     """Rotation of q and k by the tokens' positions, store of k and v into their pages (if ``store``),
     and attention over the pages: the three steps of the attention mixer between its two products.
     In a bfloat16 step of single tokens they are one kernel (the attention kernel rotates q in its
     registers and puts the token's own k and v into its key block and into the page); otherwise the
-    rotation kernel runs first."""
+    rotation kernel runs first.  ``qkv`` may be a ``SplitSum`` where ``single_token_step_is_one_kernel``."""
     global launches
     be = backend()
-    if (qkv.dtype == torch.bfloat16 and ATTENTION_KERNEL in ("auto", "mma") and FUSE_ROPE and ctx.max_q_len == 1
-            and ctx.n_tokens == ctx.n_seqs and be.attention_mma_supports(head_dim, heads, kv_heads, 1)):
+    shares = None
+    if isinstance(qkv, SplitSum):
+        if qkv.shares.shape[0] <= 8 and single_token_step_is_one_kernel(ctx, out.dtype, heads, kv_heads, head_dim):
+            shares = qkv.shares
+            qkv = torch.empty(tuple(qkv.shape), dtype=out.dtype, device=out.device)     # for its shape only
+        else:
+            qkv = qkv.dense(out.dtype)
+    if single_token_step_is_one_kernel(ctx, qkv.dtype, heads, kv_heads, head_dim):
         launches += 1
         w = int(window) if window else 0
         span = ctx.max_kv_len if not w else min(ctx.max_kv_len, w + 31)
@@ -248,7 +262,7 @@ def rope_attention(qkv, out, cos_sin, k_cache, v_cache, ctx, block_table, heads:
             part_ml = torch.empty((splits, ctx.n_tokens, heads, 2), dtype=torch.float32, device=qkv.device)
             counters = _attention_counters(qkv.device, ctx.n_seqs * kv_heads)
         be.attention_decode(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, heads, kv_heads, head_dim, w,
-                            float(scale), splits, part_o, part_ml, counters, True, cos_sin, bool(store), status)
+                            float(scale), splits, part_o, part_ml, counters, True, cos_sin, bool(store), status, shares)
         return out
     rope_store(qkv, ctx.positions, cos_sin, k_cache, v_cache, ctx.token_seq, block_table, heads, kv_heads, head_dim,
                store=store, status=status)

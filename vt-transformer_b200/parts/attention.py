@@ -70,8 +70,11 @@ class PagedAttention(Mixer):
     def forward(self, h, ctx, cache):
         s, ops = self.spec, self.rt.ops
         T = h.shape[0]
-        qkv = torch.empty((T, self.q_dim + 2 * self.kv_dim), dtype=h.dtype, device=h.device)
-        ops.linear(h, self.w_qkv, self.b_qkv, qkv)
+        if ops.single_token_step_is_one_kernel(ctx, h.dtype, s.heads, s.kv_heads, s.head_dim):
+            qkv = ops.linear_to_stream(h, self.w_qkv, self.b_qkv)      # that kernel adds the shares of k itself
+        else:
+            qkv = torch.empty((T, self.q_dim + 2 * self.kv_dim), dtype=h.dtype, device=h.device)
+            ops.linear(h, self.w_qkv, self.b_qkv, qkv)
         o = torch.empty((T, self.q_dim), dtype=h.dtype, device=h.device)
         ops.rope_attention(qkv, o, self.position.table, cache.k, cache.v, ctx, cache.block_table, s.heads, s.kv_heads,
                            s.head_dim, s.window, self.scale, store=cache.writes, status=ctx.status)
