@@ -152,3 +152,48 @@ def test_random_orders_lose_no_page(seed):
         m.release(r)
     m.check()
     assert m.free_pages() == [g.pool.num_pages for g in m.groups] and m.free_rows == 4
+
+
+def test_the_native_packing_of_a_step_equals_the_python_one():
+    """The description of a step (ids, positions, offsets, rows, wanted rows, block-table rows, padding) packed by
+    csrc/host_runtime.cpp and by the Python code beside it, for random mixed steps in layouts with room to spare."""
+    import random
+
+    import numpy as np
+
+    from vt_transformer_b200.engine.batch import Layout, StepEntry, fill_host, slices_of
+
+    rng = random.Random(4)
+    m = manager(num_pages=40, max_requests=6, max_seq_len=320, window=40, window_pages=30)
+    rows = [m.admit() for _ in range(5)]
+    for _ in range(30):
+        live = rng.sample(rows, rng.randrange(1, 6))
+        entries = [StepEntry(r, [rng.randrange(1000) for _ in range(rng.choice([1, 1, 2, 7, 30]))], []) for r in live]
+        entries = [e for e in entries if m.length(e.row) + len(e.tokens) <= 320]
+        if not entries:
+            continue
+        for e in entries:
+            e.want = sorted(rng.sample(range(len(e.tokens)), rng.randrange(0, min(3, len(e.tokens)) + 1)))
+        m.extend([(e.row, m.length(e.row) + len(e.tokens)) for e in entries])
+        seqs = slices_of(entries, m)
+        want_flat = [sl.offset + w for e, sl in zip(entries, seqs) for w in e.want]
+        T = sum(len(e.tokens) for e in entries)
+        lay = Layout.make(T + rng.randrange(0, 5), len(entries) + rng.randrange(0, 3), len(want_flat) + rng.randrange(0, 3),
+                          m.max_pages, len(m.groups))
+        native = np.full(lay.total, 12345, dtype=np.int32)
+        fill_host(native, lay, entries, seqs, want_flat, m)
+
+        class NoBook:                      # the same manager without its C++ side: the Python packing
+            page_size, groups = m.page_size, m.groups
+            table_rows = staticmethod(m.table_rows)
+        plain = np.full(lay.total, 12345, dtype=np.int32)
+        fill_host(plain, lay, entries, seqs, want_flat, NoBook)
+        for i in range(len(lay.sizes)):
+            assert (lay.seg(native, i) == lay.seg(plain, i)).all(), i
+        for e in entries:
+            m.commit(e.row, m.length(e.row) + len(e.tokens))
+        if rng.random() < 0.2:
+            r = rng.choice(rows)
+            m.release(r)
+            rows[rows.index(r)] = m.admit()
+    m.check()

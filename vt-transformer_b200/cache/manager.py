@@ -45,35 +45,49 @@ class OutOfRows(RuntimeError):
 DEFAULT_PAGE_SIZE = 64
 
 
+def _host():
+    from ..csrc import build
+    return build.load_host()
+
+
 class PagePool:
-    """Pages 0..n-1 with a LIFO free list.  ``give`` refuses a page that is free already
-    or that the pool does not have."""
+    """Pages 0..n-1 with a LIFO free list (the pool of ``csrc/host_runtime.cpp``).  ``give`` refuses a
+    page that is free already or that the pool does not have."""
 
     def __init__(self, num_pages: int):
-        self.num_pages = num_pages
-        self._free = list(range(num_pages - 1, -1, -1))   # pop() hands out 0, 1, 2, ...
-        self._is_free = [True] * num_pages
+        self._pool = _host().Pool(num_pages)
+
+    @property
+    def num_pages(self) -> int:
+        return self._pool.num_pages
 
     @property
     def free(self) -> int:
-        return len(self._free)
+        return self._pool.free
 
     def take(self, n: int) -> List[int]:
-        if n > len(self._free):
-            raise OutOfPages(-1, n, len(self._free))
-        out = [self._free.pop() for _ in range(n)]
-        for p in out:
-            self._is_free[p] = False
+        out = self._pool.take(n)
+        if out is None:
+            raise OutOfPages(-1, n, self._pool.free)
         return out
 
     def give(self, pages: Iterable[int]) -> None:
-        for p in pages:
-            if not 0 <= p < self.num_pages:
-                raise ValueError(f"page {p} does not belong to a pool of {self.num_pages} pages")
-            if self._is_free[p]:
-                raise ValueError(f"page {p} is freed twice")
-            self._is_free[p] = True
-            self._free.append(p)
+        self._pool.give([int(p) for p in pages])
+
+
+class _GroupPool:
+    """What is read of a group's pool from outside: its size and how many pages are free."""
+
+    def __init__(self, book, index: int):
+        self._book, self._index = book, index
+
+    @property
+    def num_pages(self) -> int:
+        return self._book.pool_pages(self._index)
+
+    @property
+    def free(self) -> int:
+        return self._book.free_pages()[self._index]
 
 
 @dataclass
@@ -81,10 +95,9 @@ class _Group:
     index: int
     spec: KVCacheSpec
     slots: List[int]
-    pool: PagePool
+    pool: _GroupPool
     kv: Optional[torch.Tensor]          # [slots, 2, pages, kv_heads, page_size, head_dim]
-    table: np.ndarray                   # [rows, max_pages] int32, -1 where no page is held
-    first_live: np.ndarray              # [rows] first logical page that may still be held
+    table: np.ndarray                   # [rows, max_pages] int32, -1 where no page is held: a view of the book's table
 
 
 class CacheManager:
@@ -122,34 +135,36 @@ class CacheManager:
                                     if allocate else None)
             else:
                 raise TypeError(f"cache slot {slot}: unknown kind of cache spec {spec!r}")
+        plan = []
         for key, slots in by_key.items():
             kv_heads, head_dim, window = key
             n = num_pages if (window is None or window_pages is None) else window_pages
+            plan.append((key, slots, n))
+        # the bookkeeping (rows, lengths, free lists, block tables) is the C++ object; the tensors stay here
+        self.book = _host().CacheBook(page_size, max_requests, max_seq_len,
+                                      [(-1 if key[2] is None else int(key[2]), n) for key, _, n in plan])
+        for (kv_heads, head_dim, window), slots, n in plan:
             kv = None
             if allocate:
                 kv = torch.zeros((len(slots), 2, n, kv_heads, page_size, head_dim), dtype=dtype, device=device)
-            g = _Group(len(self.groups), KVCacheSpec(kv_heads, head_dim, window), slots, PagePool(n), kv,
-                       np.full((max_requests, self.max_pages), -1, dtype=np.int32),
-                       np.zeros(max_requests, dtype=np.int64))
+            index = len(self.groups)
+            g = _Group(index, KVCacheSpec(kv_heads, head_dim, window), slots, _GroupPool(self.book, index), kv,
+                       self.book.table(index))
             for i, s in enumerate(slots):
                 self.slot_group[s] = (g.index, i)
             self.groups.append(g)
-        self._free_rows = list(range(max_requests - 1, -1, -1))
-        self._live = [False] * max_requests
-        self.lengths = np.zeros(max_requests, dtype=np.int64)
+        self.lengths = self.book.lengths()        # [rows] int64: a view of the book's lengths
 
     # ---- rows ------------------------------------------------------------------------
     @property
     def free_rows(self) -> int:
-        return len(self._free_rows)
+        return self.book.free_rows
 
     def admit(self) -> int:
         """Takes a row for a new request: length 0, no pages, state slots zero."""
-        if not self._free_rows:
+        row = self.book.admit()
+        if row < 0:
             raise OutOfRows(f"all {self.max_requests} request rows are taken")
-        row = self._free_rows.pop()
-        self._live[row] = True
-        self.lengths[row] = 0
         for t in self.state.values():
             if t is not None:
                 t[row].zero_()
@@ -158,93 +173,35 @@ class CacheManager:
     def release(self, row: int) -> None:
         """Ends a request: every page it holds goes back to its pool, its tables are
         cleared, its row is free."""
-        self._check_row(row)
-        for g in self.groups:
-            held = g.table[row]
-            idx = np.nonzero(held >= 0)[0]
-            g.pool.give(int(p) for p in held[idx])
-            held[idx] = -1
-            g.first_live[row] = 0
-        self.lengths[row] = 0
-        self._live[row] = False
-        self._free_rows.append(row)
-
-    def _check_row(self, row: int) -> None:
-        if not (0 <= row < self.max_requests and self._live[row]):
-            raise ValueError(f"row {row} holds no request")
+        self.book.release(row)
 
     def length(self, row: int) -> int:
-        return int(self.lengths[row])
+        return self.book.length(row)
 
     # ---- pages -----------------------------------------------------------------------
-    def _first_needed_page(self, g: _Group, length: int) -> int:
-        """First logical page that a token at position >= length may still read."""
-        if g.spec.window is None:
-            return 0
-        return max(0, length - g.spec.window + 1) // self.page_size
-
-    def _missing(self, g: _Group, row: int, new_len: int) -> List[int]:
-        lo = self._first_needed_page(g, int(self.lengths[row]))
-        hi = -(-new_len // self.page_size)
-        seg = g.table[row, lo:hi]
-        return [lo + int(i) for i in np.nonzero(seg < 0)[0]]
-
     def pages_needed(self, items: Sequence[Tuple[int, int]]) -> List[int]:
         """Pages each group would have to hand out to cover ``(row, new_len)`` for all items."""
-        need = [0] * len(self.groups)
-        for row, new_len in items:
-            for g in self.groups:
-                need[g.index] += len(self._missing(g, row, new_len))
-        return need
+        return self.book.pages_needed([(int(r), int(n)) for r, n in items])
 
     def pages_for_new(self, n_tokens: int) -> List[int]:
         """Pages each group needs for the first ``n_tokens`` of a request not yet admitted."""
         return [-(-n_tokens // self.page_size) for _ in self.groups]
 
     def free_pages(self) -> List[int]:
-        return [g.pool.free for g in self.groups]
+        return self.book.free_pages()
 
     def extend(self, items: Sequence[Tuple[int, int]]) -> None:
         """Makes sure pages cover positions < new_len of every (row, new_len).  Either all
         pages of all items and groups are found, or ``OutOfPages`` is raised and nothing
         has changed."""
-        plans = []
-        for row, new_len in items:
-            self._check_row(row)
-            if new_len > self.max_seq_len:
-                raise ValueError(f"row {row}: length {new_len} is above max_seq_len {self.max_seq_len}")
-            if new_len < self.lengths[row]:
-                raise ValueError(f"row {row}: length {new_len} is below the cached length {self.lengths[row]}")
-        for g in self.groups:
-            want = [(row, self._missing(g, row, new_len)) for row, new_len in items]
-            total = sum(len(m) for _, m in want)
-            if total > g.pool.free:
-                raise OutOfPages(g.index, total, g.pool.free)
-            plans.append((g, want, total))
-        for g, want, total in plans:
-            pages = g.pool.take(total)
-            at = 0
-            for row, missing in want:
-                for logical in missing:
-                    g.table[row, logical] = pages[at]
-                    at += 1
+        group, needed, free = self.book.extend([(int(r), int(n)) for r, n in items])
+        if group >= 0:
+            raise OutOfPages(group, needed, free)
 
     def commit(self, row: int, new_len: int) -> None:
         """Records that positions < new_len are cached, and gives back the pages of window
         groups that no later token can read."""
-        self._check_row(row)
-        self.lengths[row] = new_len
-        for g in self.groups:
-            if g.spec.window is None:
-                continue
-            lo = self._first_needed_page(g, new_len)
-            first = int(g.first_live[row])
-            if lo > first:
-                seg = g.table[row, first:lo]
-                idx = np.nonzero(seg >= 0)[0]
-                g.pool.give(int(p) for p in seg[idx])
-                seg[idx] = -1
-                g.first_live[row] = lo
+        self.book.commit(row, int(new_len))
 
     # ---- what a step sees --------------------------------------------------------------
     def table_rows(self, group: int, rows: Sequence[int], n_pages: int) -> np.ndarray:
@@ -270,20 +227,6 @@ class CacheManager:
     # ---- invariants (tests) --------------------------------------------------------------
     def check(self) -> None:
         """No page lost, none held twice, none both held and free; rows consistent."""
-        for g in self.groups:
-            held = g.table[g.table >= 0]
-            if len(np.unique(held)) != len(held):
-                raise AssertionError(f"group {g.index}: a page is held twice")
-            if any(g.pool._is_free[int(p)] for p in held):
-                raise AssertionError(f"group {g.index}: a held page is on the free list")
-            if len(held) + g.pool.free != g.pool.num_pages:
-                raise AssertionError(f"group {g.index}: {g.pool.num_pages - len(held) - g.pool.free} pages are lost")
-            if len(set(g.pool._free)) != len(g.pool._free):
-                raise AssertionError(f"group {g.index}: a page is on the free list twice")
-            for row in range(self.max_requests):
-                if not self._live[row] and (g.table[row] >= 0).any():
-                    raise AssertionError(f"group {g.index}: free row {row} still holds pages")
-        if len(set(self._free_rows)) != len(self._free_rows):
-            raise AssertionError("a row is on the free list twice")
-        if sum(self._live) + len(self._free_rows) != self.max_requests:
-            raise AssertionError("a row is lost")
+        problem = self.book.check()
+        if problem:
+            raise AssertionError(problem)

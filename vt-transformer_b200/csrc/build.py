@@ -148,9 +148,79 @@ def _compile(name: str, verbose: bool) -> str:
     return path
 
 
-def _remove_stale(root: str, keep: str) -> None:
+def _remove_stale(root: str, keep: str, prefix: str = "vtb200_ext_") -> None:
     """Deletes the builds of earlier sources beside the one just made."""
     import shutil
     for entry in os.listdir(root):
-        if entry.startswith("vtb200_ext_") and entry != keep:
+        if entry.startswith(prefix) and entry != keep:
             shutil.rmtree(os.path.join(root, entry), ignore_errors=True)
+
+
+# ---- the host-side module: C++ without CUDA, compiled with the host compiler alone -------------------------
+
+HOST_SOURCE = "host_runtime.cpp"
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+_host = None
+
+
+def _host_name() -> str:
+    h = hashlib.sha256()
+    with open(os.path.join(_HERE, HOST_SOURCE), "rb") as f:
+        h.update(f.read())
+    h.update(" ".join(HOST_FLAGS).encode())
+    h.update(sys.version.encode())
+    return f"vtb200_host_{h.hexdigest()[:12]}"
+
+
+def load_host():
+    """The module of ``host_runtime.cpp`` (the cache manager's bookkeeping and the packing of a step's
+    description); compiled with the host compiler at the first call, into the same build folder."""
+    global _host
+    if _host is not None:
+        return _host
+    name = _host_name()
+    path = None
+    for root in (os.path.join(_HERE, "_build"),
+                 os.path.join(tempfile.gettempdir(), f"vt_transformer_b200_build_{os.getuid()}")):
+        cand = os.path.join(root, name, name + ".so")
+        if os.path.isfile(cand):
+            path = cand
+            break
+    if path is None:
+        path = _compile_host(name)
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    _host = mod
+    return mod
+
+
+def _compile_host(name: str) -> str:
+    import shutil
+    import subprocess
+    import sysconfig
+    try:
+        import pybind11
+        pybind_include = pybind11.get_include()
+    except ImportError:                       # the headers that come with torch
+        import torch
+        pybind_include = os.path.join(os.path.dirname(torch.__file__), "include")
+    compiler = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+    if compiler is None:
+        raise RuntimeError("the host-side module has to be compiled but no C++ compiler (g++) was found")
+    build_dir = os.path.join(_build_root(), name)
+    os.makedirs(build_dir, exist_ok=True)
+    out = os.path.join(build_dir, name + ".so")
+    tmp = out + f".tmp{os.getpid()}"
+    cmd = [compiler, *HOST_FLAGS, f"-DVTB_HOST_MODULE_NAME={name}", "-I", pybind_include,
+           "-I", sysconfig.get_paths()["include"], os.path.join(_HERE, HOST_SOURCE), "-o", tmp]
+    print(f"[vt_transformer_b200] compiling the host-side module into {build_dir} (first call only)",
+          file=sys.stderr, flush=True)
+    t0 = time.time()
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("compiling host_runtime.cpp failed:\n" + " ".join(cmd) + "\n" + res.stderr[-4000:])
+    os.replace(tmp, out)
+    print(f"[vt_transformer_b200] compiled in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+    _remove_stale(os.path.dirname(build_dir), name, prefix="vtb200_host_")
+    return out

@@ -93,6 +93,12 @@ def fill_host(host: np.ndarray, lay: Layout, entries: Sequence[StepEntry], seqs:
     """Writes the step's arrays into ``host``.  The layout may be larger than the step (a fixed
     layout of a captured graph): the rest is padding -- tokens of no sequence (id and sequence -1),
     sequences without tokens, block-table entries -1, wanted rows that point at themselves."""
+    book = getattr(cache, "book", None)
+    if book is not None and host.dtype == np.int32 and host.flags.c_contiguous and host.flags.writeable:
+        # the C++ side of the cache manager packs the step (csrc/host_runtime.cpp)
+        book.fill_step(host, lay.T, lay.n, lay.W, lay.n_pages, lay.offs, lay.sizes,
+                       [(e.row, e.tokens) for e in entries], [int(w) for w in want_flat])
+        return
     T, n = sum(s.length for s in seqs), len(seqs)
     tok, pos, tseq = lay.seg(host, 0), lay.seg(host, 1), lay.seg(host, 2)
     tok[T:], pos[T:], tseq[T:] = -1, 0, -1
