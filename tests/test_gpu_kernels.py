@@ -442,12 +442,26 @@ def test_tcgen05_product_takes_each_element_once():
     """x and w of small integers: every product and sum is exact in bfloat16 and float, so a tile read
     from the wrong place, a k-block counted twice or dropped, shows as a wrong integer."""
     torch.manual_seed(12)
-    for m, n, k in ((200, 300, 1096), (40, 700, 2056)):
+    # the sizes of 2,048 (and 1,990) rows make the kernel choose tiles of 208, 224, 240, 192 and again 208 features
+    # (the width whose rounds of one tile an SM come out best), the last with tiles that hang over both edges
+    for m, n, k in ((200, 300, 1096), (40, 700, 2056), (2048, 3584, 520), (2048, 2016, 264), (2048, 2160, 264),
+                    (2048, 1728, 264), (1990, 3500, 264)):
         x = torch.randint(-3, 4, (m, k), device=DEV).to(torch.bfloat16)
         w = torch.randint(-3, 4, (n, k), device=DEV).to(torch.bfloat16)
-        out = torch.empty(m, n, device=DEV, dtype=torch.float32)
-        ops().backend().gemm_tc(x, w, None, out, None, *ops()._split_workspace(torch.device(DEV)))
-        assert torch.equal(out.cpu().double(), x.cpu().double() @ w.cpu().double().t())
+        ref = x.cpu().float() @ w.cpu().float().t()          # exact: the sums stay far below 2^24
+        for out_dtype in (torch.float32, torch.bfloat16):
+            out = torch.full((m, n), float("nan"), device=DEV, dtype=out_dtype)
+            ops().backend().gemm_tc(x, w, None, out, None, *ops()._split_workspace(torch.device(DEV)))
+            assert torch.equal(out.cpu().float(), ref.to(out_dtype).float())
+    # and with the activation in the epilogue at a width of 208 (gate and up interleaved in runs of 8)
+    m, inter, k = 2048, 1792, 264
+    x = torch.randint(-2, 3, (m, k), device=DEV).to(torch.bfloat16)
+    wg = torch.randint(-2, 3, (inter, k), device=DEV).to(torch.bfloat16)
+    wu = torch.randint(-2, 3, (inter, k), device=DEV).to(torch.bfloat16)
+    act = torch.full((m, inter), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops().backend().gemm_tc(x, ops().interleave_gate_up(wg, wu), None, act, None, *ops()._split_workspace(torch.device(DEV)), 1)
+    g, u = x.cpu().double() @ wg.cpu().double().t(), x.cpu().double() @ wu.cpu().double().t()
+    close(act, g / (1 + torch.exp(-g)) * u, torch.bfloat16, 2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -118,7 +118,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo, int n_full,
                int s_tail, float* __restrict__ scratch, int* __restrict__ counters, int* status) {
     constexpr int B_STAGE = BN * BK * 2;
-    constexpr int COLS = BN < 32 ? 32 : BN;          // tensor-memory columns: a power of two, at least 32
+    constexpr int COLS = BN < 32 ? 32 : BN;          // tensor-memory columns of an accumulator
+    constexpr int ALLOC = 2 * COLS <= 64 ? 64 : 2 * COLS <= 128 ? 128 : 2 * COLS <= 256 ? 256 : 512;   // a power of two
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* a_s = smem;
@@ -153,7 +154,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(2 * COLS));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(ALLOC));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
     tc_fence_before();
@@ -321,7 +322,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(2 * COLS));
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(ALLOC));
     }
 }
 
@@ -400,7 +401,22 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
         // 128x256 tile costs the CTA that does it more than the shorter round saves.)
         const int sms = sm_count();
         const bool wide = !(n <= 128 || m <= 128);
-        const int bn = wide ? 256 : 128;
+        // The width of a tile: 256 features, or fewer where that makes the rounds of one tile an SM come out
+        // better (n = 3584 and 2,048 tokens: 224 tiles of 256 features are 1.5 rounds and take the time of 2;
+        // 288 tiles of 208 are 1.95 rounds of narrower tiles).  Cost of a width: rounds * (width + a fixed part
+        // for the 128-row operand of every k-block).
+        int bn = wide ? 256 : 128;
+        if (wide) {
+            long best = -1;
+            for (int cand : {256, 240, 224, 208, 192}) {
+                const long t = (long)((m + BM - 1) / BM) * ((n + cand - 1) / cand);
+                const long cost = ((t + sms - 1) / sms) * (cand + 24);
+                if (best < 0 || cost < best) {
+                    best = cost;
+                    bn = cand;
+                }
+            }
+        }
         const int tiles = ((m + BM - 1) / BM) * ((n + bn - 1) / bn), nkb = (k + BK - 1) / BK;
         int rem = tiles % sms, n_full = tiles - rem, s_tail = 1;
         if (tiles < sms && scratch != nullptr && counters != nullptr && rem <= n_counters) {
@@ -416,11 +432,15 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
             }
         }
         if (s_tail == 1) n_full = tiles;
-        if (wide)
-            return launch_cfg<256, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, EPI == 1 ? n / 2 : n, n_full, s_tail, scratch,
-                                                         counters, status, stream);
-        return launch_cfg<128, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, EPI == 1 ? n / 2 : n, n_full, s_tail, scratch, counters,
-                                                     status, stream);
+        const int ldo = EPI == 1 ? n / 2 : n;
+        switch (bn) {
+            case 256: return launch_cfg<256, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
+            case 240: return launch_cfg<240, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
+            case 224: return launch_cfg<224, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
+            case 208: return launch_cfg<208, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
+            case 192: return launch_cfg<192, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
+        }
+        return launch_cfg<128, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
     }
 }
 
