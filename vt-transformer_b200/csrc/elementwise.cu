@@ -62,9 +62,12 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
                                const int* __restrict__ rows, int n_tokens, int hidden, int* status) {
     __shared__ float scratch[32];
     pdl_launch();
-    pdl_wait();
+    // the norm's weight and the list of rows are written by no kernel of the step: they are read before the wait
     const int r = blockIdx.x;
     const int t = rows ? rows[r] : r;
+    float w_first[8];
+    if ((int)threadIdx.x * 8 < hidden) Vec8<float>::load(weight + threadIdx.x * 8, w_first);
+    pdl_wait();
     T* o = out + (size_t)r * hidden;
     if (t < 0 || t >= n_tokens) {
         if (threadIdx.x == 0) set_status(status, kStatusBadRow, t);
@@ -72,37 +75,56 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
     }
     float* xr = x + (size_t)t * hidden;
     const T* dr = delta ? delta + (size_t)t * hidden : nullptr;
-    float ss = 0.f;
-    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
-        float v[8];
+    const float* pr = parts ? parts + (size_t)t * hidden : nullptr;
+    const size_t stride = (size_t)n_tokens * hidden;
+    // v = x (+ delta, or + the shares in the order of their index) for the eight values at i
+    auto row_values = [&](int i, float (&v)[8]) {
         Vec8<float>::load(xr + i, v);
         if (dr) {
             float d[8];
             Vec8<T>::load(dr + i, d);
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] += d[j];
-            Vec8<float>::store(xr + i, v);
-        } else if (parts) {
-            const float* pr = parts + (size_t)t * hidden + i;
-            const size_t stride = (size_t)n_tokens * hidden;
+        } else if (pr) {
 #pragma unroll 4
             for (int q = 0; q < n_parts; ++q) {
                 float d[8];
-                Vec8<float>::load(pr + q * stride, d);
+                Vec8<float>::load(pr + i + q * stride, d);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] += d[j];
             }
-            Vec8<float>::store(xr + i, v);
         }
+    };
+    const int first = threadIdx.x * 8;
+    const bool once = hidden <= (int)blockDim.x * 8;      // a thread has all its values at once: they stay in registers
+    float keep[8];
+    float ss = 0.f;
+    for (int i = first; i < hidden; i += blockDim.x * 8) {
+        float v[8];
+        row_values(i, v);
+        if (dr || pr) Vec8<float>::store(xr + i, v);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+        for (int j = 0; j < 8; ++j) {
+            ss += v[j] * v[j];
+            keep[j] = v[j];
+        }
     }
     const float total = block_sum(ss, scratch);
     const float rs = rsqrtf(total / (float)hidden + eps);
-    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+    for (int i = first; i < hidden; i += blockDim.x * 8) {
         float v[8], w[8], y[8];
-        Vec8<float>::load(xr + i, v);
-        Vec8<float>::load(weight + i, w);
+        if (once) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = keep[j];
+        } else {
+            Vec8<float>::load(xr + i, v);       // its own writes, or x as it was
+        }
+        if (i == first) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) w[j] = w_first[j];
+        } else {
+            Vec8<float>::load(weight + i, w);
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[j] = w[j] * v[j] * rs;
         Vec8<T>::store(o + i, y);
