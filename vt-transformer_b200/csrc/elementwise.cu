@@ -220,37 +220,48 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
         slot = pos % page_size;
     }
 
+    // eight pairs (i, i + half) at a time: 16- or 32-byte loads and stores (head_dim is a multiple of 16)
+    auto rotate8 = [&](const T* src, T* dst, int i) {
+        float a[8], b[8];
+        Vec8<T>::load(src + i, a);
+        Vec8<T>::load(src + i + half, b);
+        if (rotate) {
+            float c[16];
+            Vec8<float>::load(reinterpret_cast<const float*>(cs + i), *reinterpret_cast<float(*)[8]>(c));
+            Vec8<float>::load(reinterpret_cast<const float*>(cs + i) + 8, *reinterpret_cast<float(*)[8]>(c + 8));
+            float ra[8], rb[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                ra[j] = a[j] * c[2 * j] - b[j] * c[2 * j + 1];
+                rb[j] = b[j] * c[2 * j] + a[j] * c[2 * j + 1];
+            }
+            Vec8<T>::store(dst + i, ra);
+            Vec8<T>::store(dst + i + half, rb);
+        } else {
+            Vec8<T>::store(dst + i, a);
+            Vec8<T>::store(dst + i + half, b);
+        }
+    };
+    const int half8 = half / 8;
     // queries: rotate in place
     if (rotate) {
-        for (int e = threadIdx.x; e < heads * half; e += blockDim.x) {
-            const int h = e / half, i = e % half;
-            const float2 c = cs[i];
-            T* p = row + h * head_dim;
-            const float a = to_float(p[i]), b = to_float(p[i + half]);
-            p[i] = from_float<T>(a * c.x - b * c.y);
-            p[i + half] = from_float<T>(b * c.x + a * c.y);
+        for (int e = threadIdx.x; e < heads * half8; e += blockDim.x) {
+            T* p = row + (e / half8) * head_dim;
+            rotate8(p, p, (e % half8) * 8);
         }
     }
     if (!store) return;
     // keys: rotate into the page
-    for (int e = threadIdx.x; e < kv_heads * half; e += blockDim.x) {
-        const int h = e / half, i = e % half;
-        const T* p = row + q_dim + h * head_dim;
-        T* dst = k_cache + page_base + ((size_t)h * page_size + slot) * head_dim;
-        const float a = to_float(p[i]), b = to_float(p[i + half]);
-        if (rotate) {
-            const float2 c = cs[i];
-            dst[i] = from_float<T>(a * c.x - b * c.y);
-            dst[i + half] = from_float<T>(b * c.x + a * c.y);
-        } else {
-            dst[i] = p[i];
-            dst[i + half] = p[i + half];
-        }
+    for (int e = threadIdx.x; e < kv_heads * half8; e += blockDim.x) {
+        const int h = e / half8;
+        rotate8(row + q_dim + h * head_dim, k_cache + page_base + ((size_t)h * page_size + slot) * head_dim, (e % half8) * 8);
     }
     // values: copy into the page
-    for (int e = threadIdx.x; e < kv_dim; e += blockDim.x) {
-        const int h = e / head_dim, i = e % head_dim;
-        v_cache[page_base + ((size_t)h * page_size + slot) * head_dim + i] = row[q_dim + kv_dim + e];
+    for (int e = threadIdx.x; e < kv_dim / 8; e += blockDim.x) {
+        const int h = (e * 8) / head_dim, i = (e * 8) % head_dim;
+        float v[8];
+        Vec8<T>::load(row + q_dim + kv_dim + e * 8, v);
+        Vec8<T>::store(v_cache + page_base + ((size_t)h * page_size + slot) * head_dim + i, v);
     }
 }
 
@@ -259,7 +270,8 @@ cudaError_t launch_rope_store(int dtype, void* qkv, const int* positions, const 
                               int table_stride, int n_seqs, int n_pages, int n_tokens, int heads, int kv_heads,
                               int head_dim, int page_size, int rotate, int store, int* status, cudaStream_t stream) {
     if (n_tokens == 0) return cudaSuccess;
-    const int work = max(heads * head_dim / 2, kv_heads * head_dim);
+    if (head_dim % 16 != 0) return cudaErrorInvalidValue;       // eight pairs (i, i + head_dim / 2) a thread
+    const int work = max(heads * head_dim / 16, kv_heads * head_dim / 8);
     const int threads = min(512, max(32, ((work + 31) / 32) * 32));
     if (dtype == kBF16)
         return launch(rope_store_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream,
