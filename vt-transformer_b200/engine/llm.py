@@ -67,8 +67,9 @@ class LLM:
         tokens = self.sampler.sample(logits, params, [len(r.output) for r in wanting])
         if not all(p.is_greedy for p in params):
             self.h2d_bytes_last_step += 16 * len(wanting)
-        host = tokens.tolist()          # waits for the step
-        self.runner.check_status()
+        self.runner.stage_status()
+        host = tokens.tolist()          # waits for the step, and for the copy of the status word before it
+        self.runner.check_status(staged=True)
         self.d2h_bytes_last_step = 4 * len(host) + 8
         return host
 

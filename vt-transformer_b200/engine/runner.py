@@ -51,6 +51,7 @@ class ModelRunner:
     def __init__(self, model: DecoderModel, cache: CacheManager, rt: Runtime):
         self.model, self.cache, self.rt = model, cache, rt
         self.status = torch.zeros(2, dtype=torch.int32, device=rt.device)
+        self._status_host = None
         self.steps = 0
         self.last_h2d_bytes = 0
         # single-token steps are replayed as CUDA graphs where every part allows it
@@ -156,10 +157,19 @@ class ModelRunner:
             logits = logits[torch.as_tensor(wanted, dtype=torch.long, device=logits.device)]
         return logits
 
-    def check_status(self) -> None:
-        """Reads the kernels' status word (this waits for the device) and raises if a kernel
-        reported a bad index."""
-        code, detail = (int(v) for v in self.status.tolist())
+    def stage_status(self) -> None:
+        """Enqueues a copy of the kernels' status word to pinned host memory.  A caller that then waits for a
+        later operation of the stream (the read of the sampled tokens) finds it there and ``check_status(staged=
+        True)`` costs no wait of its own."""
+        if self._status_host is None:
+            self._status_host = torch.zeros(2, dtype=torch.int32, pin_memory=self.status.is_cuda)
+        self._status_host.copy_(self.status, non_blocking=True)
+
+    def check_status(self, staged: bool = False) -> None:
+        """Raises if a kernel reported a bad index.  Reads the kernels' status word (this waits for the
+        device), or, with ``staged``, the copy that ``stage_status`` enqueued and that the caller has waited
+        for since."""
+        code, detail = (int(v) for v in (self._status_host if staged and self._status_host is not None else self.status).tolist())
         if code:
             self.status.zero_()
             raise DeviceStatusError(f"{_STATUS_TEXT.get(code, 'unknown status')} (code {code}, value {detail})")
