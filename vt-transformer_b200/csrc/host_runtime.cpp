@@ -135,6 +135,28 @@ class CacheBook {
         return py::make_tuple(-1, 0, 0);
     }
 
+    // A step of `add` tokens for each of `rows`: extend, all or nothing.  Returns (group, needed, free, longest
+    // length after the step); group -1: done.
+    py::tuple extend_each(const std::vector<int>& rows, int add) {
+        std::vector<std::pair<int, long long>> items;
+        items.reserve(rows.size());
+        long long longest = 0;
+        for (size_t i = 0; i < rows.size(); ++i) {
+            check_row(rows[i]);
+            for (size_t j = 0; j < i; ++j)
+                if (rows[j] == rows[i]) throw std::invalid_argument("row " + std::to_string(rows[i]) + " appears twice in one step");
+            const long long len = lengths_[rows[i]] + add;
+            items.emplace_back(rows[i], len);
+            if (len > longest) longest = len;
+        }
+        py::tuple r = extend(items);
+        return py::make_tuple(r[0], r[1], r[2], longest);
+    }
+
+    void commit_each(const std::vector<int>& rows, int add) {
+        for (int row : rows) commit(row, lengths_[row] + add);
+    }
+
     void commit(int row, long long new_len) {
         check_row(row);
         lengths_[row] = new_len;
@@ -329,6 +351,8 @@ PYBIND11_MODULE(VTB_HOST_MODULE_NAME, m) {
         .def("pages_needed", &CacheBook::pages_needed)
         .def("extend", &CacheBook::extend)
         .def("commit", &CacheBook::commit)
+        .def("extend_each", &CacheBook::extend_each)
+        .def("commit_each", &CacheBook::commit_each)
         .def("table", [](py::object self, int group) { return self.cast<CacheBook&>().table(group, self); })
         .def("lengths", [](py::object self) { return self.cast<CacheBook&>().lengths(self); })
         .def("check", &CacheBook::check)

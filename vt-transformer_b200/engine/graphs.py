@@ -83,7 +83,7 @@ class DecodeGraph:
 
     def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         cache = self.runner.cache
-        seqs = slices_of(entries, cache)
+        seqs = [] if hasattr(cache, "book") else slices_of(entries, cache)     # the C++ side packs from its own lengths
         slot = self.turn
         self.turn = (self.turn + 1) % len(self.ring)
         if self.events[slot] is not None:

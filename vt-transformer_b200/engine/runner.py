@@ -118,6 +118,9 @@ class ModelRunner:
         vocab = self.model.spec.vocab
         if not entries:
             return torch.empty((0, vocab), dtype=torch.float32, device=self.rt.device)
+        if (self.use_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries)
+                and all(len(e.want) == 0 or (len(e.want) == 1 and e.want[0] == 0) for e in entries)):
+            return self._graph_step(entries)
         seen = set()
         for e in entries:
             if e.row in seen:
@@ -127,14 +130,11 @@ class ModelRunner:
                 if not 0 <= w < len(e.tokens):
                     raise ValueError(f"row {e.row}: wanted place {w} is outside its {len(e.tokens)} tokens")
         self.cache.extend([(e.row, self.cache.length(e.row) + len(e.tokens)) for e in entries])
-        if self.use_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries):
-            logits = self._graph_step(entries)
-        else:
-            ctx = build_context(entries, self.cache, self.rt.device, status=self.status)
-            self.last_h2d_bytes = ctx.h2d_bytes
-            logits = self.model.forward(ctx, self.cache.views(ctx.block_tables))
-            if ctx.want_inverse is not None:
-                logits = logits[torch.as_tensor(ctx.want_inverse, device=logits.device)]
+        ctx = build_context(entries, self.cache, self.rt.device, status=self.status)
+        self.last_h2d_bytes = ctx.h2d_bytes
+        logits = self.model.forward(ctx, self.cache.views(ctx.block_tables))
+        if ctx.want_inverse is not None:
+            logits = logits[torch.as_tensor(ctx.want_inverse, device=logits.device)]
         for e in entries:
             self.cache.commit(e.row, self.cache.length(e.row) + len(e.tokens))
         self.steps += 1
@@ -144,13 +144,19 @@ class ModelRunner:
         """A step of single tokens through a captured graph.  The logits lie in the graph's own
         buffer: they are valid until the next step."""
         from .graphs import DecodeGraph, batch_bucket, context_bucket
-        max_kv = max(self.cache.length(e.row) for e in entries) + 1
+        rows = [e.row for e in entries]
+        group, needed, free, max_kv = self.cache.book.extend_each(rows, 1)      # pages for the tokens, all or none
+        if group >= 0:
+            from ..cache.manager import OutOfPages
+            raise OutOfPages(group, needed, free)
         key = (batch_bucket(len(entries)), context_bucket(max_kv))
         graph = self._graphs.get(key)
         if graph is None:
             graph = DecodeGraph(self, *key)
             self._graphs[key] = graph
         logits = graph.run(entries)
+        self.cache.book.commit_each(rows, 1)
+        self.steps += 1
         self.last_h2d_bytes = graph.layout.total * 4
         wanted = [i for i, e in enumerate(entries) if len(e.want) > 0]
         if len(wanted) != len(entries):
