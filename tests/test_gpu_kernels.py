@@ -168,7 +168,8 @@ def test_attention_over_pages(dtype, heads, kv_heads, d, page_size, window):
 
 
 @pytest.mark.parametrize("heads,kv_heads,d,page_size,window", [(28, 4, 128, 16, None), (8, 1, 128, 64, 200), (3, 3, 128, 16, None),
-                                                               (12, 2, 128, 32, 129), (32, 1, 128, 16, None), (4, 2, 128, 128, None)])
+                                                               (12, 2, 128, 32, 129), (32, 1, 128, 16, None), (4, 2, 128, 128, None),
+                                                               (14, 2, 64, 16, None), (8, 8, 64, 64, 100), (6, 1, 64, 32, None)])
 def test_prompt_portions_on_tcgen05(heads, kv_heads, d, page_size, window):
     """Portions long enough for tiles of 128 rows run the tcgen05 kernel: many blocks of 128 keys, a portion
     that starts in the middle of a sequence and of a page, ends that are no multiple of 16, a window's edge

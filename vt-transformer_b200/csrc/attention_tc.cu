@@ -1,4 +1,4 @@
-// Attention of prompt portions over the paged cache on the 5th-generation tensor cores (head size 128).
+// Attention of prompt portions over the paged cache on the 5th-generation tensor cores (head sizes 64 and 128).
 //
 // The computation is the chain of vt-transformer's graph (scores = q k^T / sqrt(d), causal mask, softmax,
 // P V: v1/models/qwen2-7b/inference_fp16.dag:307-318) done block by block with a running maximum and sum,
@@ -123,7 +123,7 @@ template <int D>
 __global__ void __launch_bounds__(ATC_THREADS)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                     const AttnTcParams p) {
-    static_assert(D == 128, "built for head size 128");
+    static_assert(D == 64 || D == 128, "built for head sizes 64 and 128");
     constexpr int HALVES = D / 64;
     constexpr int TILE_BYTES = HALVES * HALF_BYTES;      // Q, a stage of K, a stage of V
     extern __shared__ unsigned char smem_raw[];
@@ -277,11 +277,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         if (nb > 0) {
             // half a Q row into shared memory, K-major with the 128-byte swizzle: 16-byte piece c of a 128-byte
             // row goes to piece c ^ (row % 8)
-            const uint4* src = reinterpret_cast<const uint4*>(p.qkv + (size_t)tok * p.qkv_stride + (size_t)head * D + g * 64);
+            const uint4* src = reinterpret_cast<const uint4*>(p.qkv + (size_t)tok * p.qkv_stride + (size_t)head * D + g * (D / 2));
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
+            for (int c = 0; c < D / 16; ++c) {
                 const uint4 v = valid ? src[c] : make_uint4(0u, 0u, 0u, 0u);
-                *reinterpret_cast<uint4*>(q_s + g * HALF_BYTES + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+                const int piece = g * (D / 16) + c;          // the row's 16-byte piece: 8 pieces a half of 64 dims
+                *reinterpret_cast<uint4*>(q_s + (piece >> 3) * HALF_BYTES + r * 128 + (((piece & 7) ^ (r & 7)) << 4)) = v;
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             __syncwarp();
@@ -363,14 +364,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 const float sum = l * w_mine + l_other * w_other;
                 const float inv = sum > 0.f ? 1.f / sum : 0.f;
                 const float w_even = (g == 0 ? w_mine : w_other) * inv, w_odd = (g == 0 ? w_other : w_mine) * inv;
-                __nv_bfloat16* dst = p.out + ((size_t)tok * p.heads + head) * D + g * 64;
+                __nv_bfloat16* dst = p.out + ((size_t)tok * p.heads + head) * D + g * (D / 2);
                 // the loads of tensor memory are warp-wide: rows without a query take part and store nothing
 #pragma unroll 1
-                for (int c0 = 0; c0 < 64; c0 += 32) {
+                for (int c0 = 0; c0 < D / 2; c0 += 32) {
                     uint32_t even[32], odd[32];
-                    tc_ld32(tmem + lane_base + 2 * TK + g * 64 + c0, even);
+                    tc_ld32(tmem + lane_base + 2 * TK + g * (D / 2) + c0, even);
                     if (n_odd > 0) {
-                        tc_ld32(tmem + lane_base + 2 * TK + D + g * 64 + c0, odd);
+                        tc_ld32(tmem + lane_base + 2 * TK + D + g * (D / 2) + c0, odd);
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) odd[i] = 0u;
@@ -402,7 +403,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 }  // namespace
 
 bool attention_tc_supports(int head_dim, int heads, int kv_heads) {
-    return head_dim == 128 && kv_heads > 0 && heads % kv_heads == 0 && heads / kv_heads <= TQ;
+    return (head_dim == 128 || head_dim == 64) && kv_heads > 0 && heads % kv_heads == 0 && heads / kv_heads <= TQ;
 }
 
 cudaError_t launch_attention_tc(const void* qkv, int qkv_stride, void* out, const void* k_cache, const void* v_cache,
@@ -436,14 +437,18 @@ cudaError_t launch_attention_tc(const void* qkv, int qkv_stride, void* out, cons
     p.cache_rows = (int)cache_rows;
     p.run_keys = run_keys;
     p.status = status;
-    constexpr int smem = (2 + 2 * 2 * 2) * HALF_BYTES + 1024 + 256 + 2 * 128 * 2 * 4;     // Q, K x2, V x2 (two halves each); barriers; the exchange
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    // Q, two stages of K and of V (HALVES halves of 16 KB each), barriers, the exchange; never so little that two CTAs
+    // would fit an SM: each takes all of its tensor memory
+    const int halves = head_dim / 64;
+    const int smem = max((1 + 2 * 2) * halves * HALF_BYTES + 1024 + 256 + 2 * 128 * 2 * 4, 120 * 1024);
+    auto kernel = head_dim == 128 ? attention_tc_kernel<128> : attention_tc_kernel<64>;
+    static bool configured[2] = {false, false};
+    if (!configured[halves - 1]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured[halves - 1] = true;
     }
-    return launch(attention_tc_kernel<128>, dim3(n_tiles, kv_heads, 1), dim3(ATC_THREADS, 1, 1), smem, stream, map_k, map_v, p);
+    return launch(kernel, dim3(n_tiles, kv_heads, 1), dim3(ATC_THREADS, 1, 1), smem, stream, map_k, map_v, p);
 }
 
 }  // namespace vtb

@@ -279,7 +279,7 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
                     window: Optional[int], scale: float, status=None) -> torch.Tensor:
     """Attention of the step's tokens over the paged keys and values of their sequences.
     ``ctx`` is the step's ``StepContext``.  bfloat16 runs on the tensor cores where the kernel
-    takes the sizes (head_dim a multiple of 16 up to 128): single-token steps with the keys of a
+    takes the sizes (head_dim a multiple of 16 up to 128; tcgen05 for prompt portions at 64 and 128): single-token steps with the keys of a
     sequence split over several CTAs, other steps in tiles of 64 or 128 rows of (token, head of
     the group).  Everything else, and all of float32, runs the plain kernel."""
     be = backend()
