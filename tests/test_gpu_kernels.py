@@ -404,7 +404,7 @@ def test_gate_up_product_with_the_activation_in_its_epilogue(m, inter, k):
     close(out32, ref, torch.float32, 40)
 
 
-@pytest.mark.parametrize("m", [1, 8, 17, 64])
+@pytest.mark.parametrize("m", [1, 8, 17, 64, 100, 256])
 @pytest.mark.parametrize("n,k", [(40, 64), (301, 72), (3584, 3584), (520, 18944)])
 def test_tcgen05_product_leaves_its_shares_unadded_and_the_norm_adds_them(m, n, k):
     """Small batches on the way into the residual stream: the product's kernel writes the sums of each share

@@ -382,15 +382,18 @@ int small_batch_ksplit(int n, int k, int bn, bool have_scratch, long long scratc
 template <int EPI, typename TOut>
 cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* out, int m, int n, int k, float* scratch,
                          long long scratch_floats, int* counters, int n_counters, int* status, cudaStream_t stream) {
-    if (m <= 64) {
-        // swapped: w is the 128-row operand
-        const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+    if (m <= 256) {
+        // swapped: w is the 128-row operand and every weight is streamed once; the batch rides along as 16 to 256
+        // columns.  (At 256 columns a k-block's MMAs take about as long as its 16 KB of weights take to arrive.)
+        const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)));
         const bool have_scratch = scratch != nullptr && counters != nullptr;
         const int ksplit = (EPI == 2) ? gemm_tc_shares(m, n, k)
                                       : small_batch_ksplit(n, k, bn, have_scratch, scratch_floats, n_counters);
         if (bn == 16) return launch_cfg<16, 11, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
         if (bn == 32) return launch_cfg<32, 10, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
-        return launch_cfg<64, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
+        if (bn == 64) return launch_cfg<64, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
+        if (bn == 128) return launch_cfg<128, 6, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
+        return launch_cfg<256, 4, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
     }
     if constexpr (EPI == 2) {
         return cudaErrorInvalidValue;     // shares are left unadded for small batches only
@@ -447,7 +450,7 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
 }  // namespace
 
 int gemm_tc_shares(int m, int n, int k) {
-    const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+    const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)));
     return small_batch_ksplit(n, k, bn, true, 1LL << 60, 1 << 30);
 }
 
@@ -462,7 +465,7 @@ cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const fl
                                               counters, n_counters, status, stream);
     }
     if (epilogue == 2) {
-        if (out_dtype != kF32 || m > 64) return cudaErrorInvalidValue;
+        if (out_dtype != kF32 || m > 256) return cudaErrorInvalidValue;
         return launch_typed<2, float>(x, w, bias, (float*)out, m, n, k, nullptr, 0, nullptr, 0, status, stream);
     }
     if (epilogue != 0) return cudaErrorInvalidValue;

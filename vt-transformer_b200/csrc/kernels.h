@@ -62,7 +62,7 @@ cudaError_t launch_gemm_skinny(int out_dtype, const void* x, const void* w, cons
 // k is not cut.  Launches that share them must not overlap on the GPU.
 // epilogue 0: out[M, N] = sums + bias.  epilogue 1 (bfloat16 out, no bias, N % 16 == 0): the rows of w are
 // gate and up rows interleaved in runs of 8 (g0..g7, u0..u7, g8.., ...) and out[M, N / 2] = silu(gate) * up.
-// epilogue 2 (float out, M <= 64): k is cut into gemm_tc_shares(M, N, K) shares and out[share, M, N] takes each
+// epilogue 2 (float out, M <= 256): k is cut into gemm_tc_shares(M, N, K) shares and out[share, M, N] takes each
 // share's sums as they are (the bias with share 0); the kernel that reads them adds them (launch_rmsnorm).
 int gemm_tc_shares(int m, int n, int k);
 cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n, int k,

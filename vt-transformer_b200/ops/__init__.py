@@ -142,7 +142,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
 
     float32 x and w: the 32-bit kernel (FFMA in a fixed order, no TF32).  A weight kept in
     32-bit beside bfloat16 activations goes the same way, with x widened.  bfloat16: the
-    tcgen05 kernel (TMA, tensor memory), with w as the 128-row operand for up to 64 rows of x
+    tcgen05 kernel (TMA, tensor memory), with w as the 128-row operand for up to 256 rows of x
     and x beyond.
     """
     be = backend()
@@ -174,8 +174,8 @@ def linear_to_stream(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
     tensor [T, N] of x's dtype, or, for bfloat16 batches small enough that the kernel cuts the inner dimension
     over CTAs, a ``SplitSum`` of the unadded 32-bit shares, which the next norm adds."""
     m = x.shape[0]
-    if (STREAM_SHARES and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < m <= SKINNY_MAX_ROWS
-            and SMALL_BATCH_KERNEL != "skinny"):
+    if (STREAM_SHARES and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < m <= STREAM_MAX_ROWS
+            and not (SMALL_BATCH_KERNEL == "skinny" and m <= SKINNY_MAX_ROWS)):
         be = backend()
         n, k = w.shape
         shares = torch.empty((be.gemm_tc_shares(m, n, k), m, n), dtype=torch.float32, device=x.device)
@@ -201,6 +201,7 @@ def _split_workspace(device):
 
 
 SKINNY_MAX_ROWS = 64            # rows of x up to which the small-batch kernel may run
+STREAM_MAX_ROWS = 256           # rows up to which w is the 128-row operand and products may leave their shares of k unadded
 # "tc": the tcgen05 kernel with w as the 128-row operand; "skinny": mma.sync weight streaming.
 # The environment variable VTB200_SMALL_BATCH_KERNEL overrides it (for measurements).
 import os as _os
