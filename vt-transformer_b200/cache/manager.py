@@ -165,10 +165,14 @@ class CacheManager:
         row = self.book.admit()
         if row < 0:
             raise OutOfRows(f"all {self.max_requests} request rows are taken")
+        self.zero_state(row)
+        return row
+
+    def zero_state(self, row: int) -> None:
+        """Clears the row's slot in every state tensor (for a row that the book has just admitted)."""
         for t in self.state.values():
             if t is not None:
                 t[row].zero_()
-        return row
 
     def release(self, row: int) -> None:
         """Ends a request: every page it holds goes back to its pool, its tables are

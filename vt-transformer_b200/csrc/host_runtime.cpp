@@ -13,9 +13,11 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <tuple>
 #include <utility>
 #include <vector>
 
@@ -67,6 +69,8 @@ class CacheBook {
     }
 
     int max_pages() const { return max_pages_; }
+    int page_size() const { return page_size_; }
+    int n_groups() const { return (int)groups_.size(); }
     int free_rows() const { return (int)free_rows_.size(); }
 
     // -1: every row is taken
@@ -320,6 +324,117 @@ class CacheBook {
     std::vector<int> free_rows_;
 };
 
+
+// The scheduler's decision for one step, after vt-transformer's scheduler (vt-transformer/core/vt_scheduler.cpp:
+// running requests first, then admission in arrival order under max_running_reqs and max_extend_tokens) with what
+// this engine adds: portions of prompts (chunk_size), and pre-emption of the youngest running request when the
+// running requests' next tokens need more pages than are free.
+//
+// running: (row, pending tokens, cached tokens, arrival) of the running requests; waiting: pending tokens of the
+// waiting requests in queue order.  The function releases the rows of the requests it pre-empts or gives up on and
+// admits rows for the requests it lets in, in `book`; the caller moves its request objects accordingly.
+// Returns (plan, preempted, gone_running, gone_waiting, admitted):
+//   plan          (index, tokens): index >= 0 a running request, -1 - k the k-th waiting request (now admitted)
+//   preempted     indices of running requests sent back to the head of the queue, in the order of pre-emption
+//   gone_running  indices of running requests that can never go on (alone and too large for the pool)
+//   gone_waiting  indices of waiting requests for which the same holds
+//   admitted      (k, row) of the waiting requests let in, in order
+py::tuple plan_step(CacheBook& book, const std::vector<std::tuple<int, long long, long long, long long>>& running,
+                    const std::vector<long long>& waiting, int max_running, long long max_extend_tokens, long long chunk_size) {
+    const int n_groups = book.n_groups(), page_size = book.page_size();
+    std::vector<char> alive(running.size(), 1);
+    std::vector<int> preempted, gone_running, gone_waiting;
+    std::vector<std::pair<int, long long>> plan;
+    std::vector<std::pair<int, int>> admitted;
+    auto portion = [&](long long pending, long long budget) {
+        long long n = pending < budget ? pending : budget;
+        if (chunk_size > 0 && pending > 1 && n > chunk_size) n = chunk_size;
+        return n;
+    };
+    long long budget = 0;
+    std::vector<int> need, free_now;
+    for (;;) {
+        // single tokens before prompt portions, each kind in arrival order
+        std::vector<int> order;
+        for (size_t i = 0; i < running.size(); ++i)
+            if (alive[i]) order.push_back((int)i);
+        std::stable_sort(order.begin(), order.end(), [&](int a, int b) {
+            const bool pa = std::get<1>(running[a]) > 1, pb = std::get<1>(running[b]) > 1;
+            if (pa != pb) return !pa;
+            return std::get<3>(running[a]) < std::get<3>(running[b]);
+        });
+        plan.clear();
+        budget = max_extend_tokens;
+        std::vector<std::pair<int, long long>> items;
+        for (int i : order) {
+            const long long n = portion(std::get<1>(running[i]), budget);
+            if (n > 0) {
+                plan.emplace_back(i, n);
+                budget -= n;
+                items.emplace_back(std::get<0>(running[i]), std::get<2>(running[i]) + n);
+            }
+        }
+        need = book.pages_needed(items);
+        free_now = book.free_pages();
+        bool fits = true;
+        for (int g = 0; g < n_groups; ++g) fits = fits && need[g] <= free_now[g];
+        if (fits) break;
+        if (order.size() <= 1) {
+            for (int i : order) {             // alone and still too large for the pool: it can never go on
+                book.release(std::get<0>(running[i]));
+                alive[i] = 0;
+                gone_running.push_back(i);
+            }
+            continue;
+        }
+        int youngest = order[0];
+        for (int i : order)
+            if (std::get<3>(running[i]) > std::get<3>(running[youngest])) youngest = i;
+        book.release(std::get<0>(running[youngest]));
+        alive[youngest] = 0;
+        preempted.push_back(youngest);
+    }
+    std::vector<long long> left(n_groups);
+    for (int g = 0; g < n_groups; ++g) left[g] = free_now[g] - need[g];
+    int n_running = 0;
+    for (char a : alive) n_running += a;
+    // admission, first come first served; nobody overtakes the head of the queue
+    for (size_t k = 0; k < waiting.size() && budget > 0 && preempted.empty(); ++k) {
+        if (n_running >= max_running || book.free_rows() == 0) break;
+        long long n = portion(waiting[k], budget);
+        long long want = (n + page_size - 1) / page_size;
+        const long long reserve = n_running > 0 ? n_running : 0;      // a page of head-room for each running request
+        bool short_of = false;
+        for (int g = 0; g < n_groups; ++g) short_of = short_of || want + reserve > left[g];
+        if (short_of) {
+            if (n_running == 0 && plan.empty()) {
+                // nothing else holds pages: shrink the portion to what fits, or give up
+                long long fit = n;
+                if (n_groups > 0) {
+                    fit = left[0];
+                    for (int g = 1; g < n_groups; ++g) fit = left[g] < fit ? left[g] : fit;
+                    fit *= page_size;
+                }
+                if (fit <= 0) {
+                    gone_waiting.push_back((int)k);
+                    continue;
+                }
+                n = n < fit ? n : fit;
+                want = (n + page_size - 1) / page_size;
+            } else {
+                break;
+            }
+        }
+        const int row = book.admit();
+        admitted.emplace_back((int)k, row);
+        plan.emplace_back(-1 - (int)k, n);
+        budget -= n;
+        ++n_running;
+        for (int g = 0; g < n_groups; ++g) left[g] -= want;
+    }
+    return py::make_tuple(plan, preempted, gone_running, gone_waiting, admitted);
+}
+
 }  // namespace
 
 PYBIND11_MODULE(VTB_HOST_MODULE_NAME, m) {
@@ -338,6 +453,8 @@ PYBIND11_MODULE(VTB_HOST_MODULE_NAME, m) {
         .def("give", [](Pool& p, const std::vector<int>& pages) {
             for (int page : pages) p.give(page);
         });
+    m.def("plan_step", &plan_step, py::arg("book"), py::arg("running"), py::arg("waiting"), py::arg("max_running"),
+          py::arg("max_extend_tokens"), py::arg("chunk_size"));
     py::class_<CacheBook>(m, "CacheBook")
         .def(py::init<int, int, long long, const std::vector<std::pair<long long, int>>&>(), py::arg("page_size"),
              py::arg("max_requests"), py::arg("max_seq_len"), py::arg("groups"))

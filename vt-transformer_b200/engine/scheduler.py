@@ -162,68 +162,45 @@ class Scheduler:
         self.stats["preemptions"] += 1
 
     # ---- planning ------------------------------------------------------------------------------
-    def _portion(self, req: Request, budget: int) -> int:
-        n = min(req.pending, budget)
-        if self.config.chunk_size is not None and req.pending > 1:
-            n = min(n, self.config.chunk_size)
-        return n
-
-    def _plan_running(self) -> Tuple[List[Tuple[Request, int]], int]:
-        budget = self.config.max_extend_tokens
-        plan = []
-        for req in sorted(self.running, key=lambda r: (r.pending > 1, r.arrival)):
-            n = self._portion(req, budget)
-            if n > 0:
-                plan.append((req, n))
-                budget -= n
-        return plan, budget
-
     def plan(self) -> Tuple[List[Tuple[Request, int]], int]:
         """Decides the step: which requests run how many tokens.  Pre-empts and admits as
-        needed.  Returns the plan and the number of requests pre-empted."""
-        n_preempted = 0
-        while True:
-            plan, budget = self._plan_running()
-            need = self.cache.pages_needed([(r.row, r.cached + n) for r, n in plan])
-            free = self.cache.free_pages()
-            if all(n <= f for n, f in zip(need, free)):
-                break
-            if len(self.running) <= 1:
-                # alone and still too large for the pool: it can never go on
-                for req in list(self.running):
-                    self.running.remove(req)
-                    self._finish(req, "out_of_pages")
-                continue
-            self._preempt(max(self.running, key=lambda r: r.arrival))
-            n_preempted += 1
-        left = [f - n for f, n in zip(free, need)]
-        # admission, first come first served; nobody overtakes the head of the queue
-        while self.waiting and budget > 0 and n_preempted == 0:
-            if len(self.running) >= self.config.max_running_reqs or self.cache.free_rows == 0:
-                break
-            req = self.waiting[0]
-            n = self._portion(req, budget)
-            want = self.cache.pages_for_new(n)
-            reserve = len(self.running)          # a page of head-room for each running request
-            if any(w + (reserve if self.running else 0) > l for w, l in zip(want, left)):
-                if not self.running and not plan:
-                    # nothing else holds pages: shrink the portion to what fits, or give up
-                    fit = min(left) * self.cache.page_size if left else n
-                    if fit <= 0:
-                        self.waiting.popleft()
-                        self._finish(req, "out_of_pages")
-                        continue
-                    n = min(n, fit)
-                    want = self.cache.pages_for_new(n)
-                else:
-                    break
-            self.waiting.popleft()
-            req.row, req.state, req.cached = self.cache.admit(), RUNNING, 0
+        needed.  Returns the plan and the number of requests pre-empted.
+
+        The decision itself is ``plan_step`` of ``csrc/host_runtime.cpp`` (decodes first, then prompt portions
+        under ``max_extend_tokens`` and ``chunk_size``; the youngest running request is pre-empted while the
+        running requests' next tokens need more pages than are free; admission in arrival order with a page
+        of head-room for each running request); it releases and admits rows in the cache manager's book, and
+        this method moves the request objects accordingly."""
+        from ..csrc import build
+        running, waiting = list(self.running), list(self.waiting)
+        chunk = -1 if self.config.chunk_size is None else int(self.config.chunk_size)
+        plan_idx, preempted, gone_running, gone_waiting, admitted = build.load_host().plan_step(
+            self.cache.book, [(r.row, r.pending, r.cached, r.arrival) for r in running], [r.pending for r in waiting],
+            int(self.config.max_running_reqs), int(self.config.max_extend_tokens), chunk)
+        for i in gone_running:                      # alone and still too large for the pool (its row is released already)
+            req = running[i]
+            self.running.remove(req)
+            req.row = None
+            self._finish(req, "out_of_pages")
+        for i in preempted:                         # back to the head of the queue, the one pre-empted last in front
+            req = running[i]
+            self.running.remove(req)
+            req.row, req.cached, req.state = None, 0, WAITING
+            req.preemptions += 1
+            self.waiting.appendleft(req)
+            self.stats["preemptions"] += 1
+        for k in gone_waiting:
+            req = waiting[k]
+            self.waiting.remove(req)
+            self._finish(req, "out_of_pages")
+        for k, row in admitted:
+            req = waiting[k]
+            self.waiting.remove(req)
+            self.cache.zero_state(row)
+            req.row, req.state, req.cached = row, RUNNING, 0
             self.running.append(req)
-            plan.append((req, n))
-            budget -= n
-            left = [l - w for l, w in zip(left, want)]
-        return plan, n_preempted
+        plan = [((running[i] if i >= 0 else waiting[-1 - i]), int(n)) for i, n in plan_idx]
+        return plan, len(preempted)
 
     # ---- the step ----------------------------------------------------------------------------------
     def step(self) -> StepResult:
