@@ -205,6 +205,147 @@ def toy_state_case(tmp, device, dtype):
         unregister_part("mixer", "toy_running_mean")
 
 
+def define_toy_routed_parts():
+    """A feed-forward with routing (a router picks one of the experts for every token and weighs it by the
+    router's softmax) and another position encoding (rotation by angles that grow linearly with the index of the
+    pair, not geometrically).  Defined here, in the tests, registered through the public registry."""
+    from vt_transformer_b200.parts import FeedForward, FeedForwardSpec, ParamSpec, PositionEncoding, PositionSpec, register_part
+
+    @dataclass(frozen=True)
+    class RoutedSpec(FeedForwardSpec):
+        hidden: int = 0
+        inter: int = 0
+        experts: int = 2
+        kind: str = "toy_routed"
+
+    class Routed(FeedForward):
+        def param_specs(self):
+            s, out = self.spec, {self.prefix + "router.weight": ParamSpec((self.spec.experts, self.spec.hidden))}
+            for e in range(s.experts):
+                out[self.prefix + f"experts.{e}.w1.weight"] = ParamSpec((s.inter, s.hidden))
+                out[self.prefix + f"experts.{e}.w2.weight"] = ParamSpec((s.hidden, s.inter))
+            return out
+
+        def load(self, get):
+            s = self.spec
+            self.router = self.rt.param(get(self.prefix + "router.weight")).float()          # router logits in 32-bit
+            self.w1 = [self.rt.param(get(self.prefix + f"experts.{e}.w1.weight")) for e in range(s.experts)]
+            self.w2 = [self.rt.param(get(self.prefix + f"experts.{e}.w2.weight")) for e in range(s.experts)]
+
+        def forward(self, h, ctx):
+            ops = self.rt.ops
+            prob = torch.softmax(h.float() @ self.router.t(), dim=-1)
+            weight, choice = prob.max(dim=-1)
+            out = torch.zeros_like(h)
+            for e in range(self.spec.experts):
+                idx = torch.nonzero(choice == e).flatten()
+                if idx.numel() == 0:
+                    continue
+                x = h[idx].contiguous()
+                mid = torch.empty((x.shape[0], self.spec.inter), dtype=h.dtype, device=h.device)
+                ops.linear(x, self.w1[e], None, mid)
+                mid = (mid.float() * torch.sigmoid(mid.float())).to(h.dtype)
+                y = torch.empty((x.shape[0], self.spec.hidden), dtype=h.dtype, device=h.device)
+                ops.linear(mid, self.w2[e], None, y)
+                out[idx] = (y.float() * weight[idx, None]).to(h.dtype)
+            return out
+
+    @dataclass(frozen=True)
+    class LinearAnglesSpec(PositionSpec):
+        step: float = 0.0
+        kind: str = "toy_linear_angles"
+
+    class LinearAngles(PositionEncoding):
+        def load(self, get):
+            s = self.spec
+            angle = torch.arange(s.max_positions, dtype=torch.float64)[:, None] * (
+                s.step * torch.arange(1, s.dim // 2 + 1, dtype=torch.float64))[None, :]
+            self.table = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1).float().contiguous().to(self.rt.device)
+
+    register_part("feed_forward", "toy_routed", Routed, replace=True)
+    register_part("position", "toy_linear_angles", LinearAngles, replace=True)
+    return RoutedSpec, LinearAnglesSpec
+
+
+def toy_routed_case(tmp, device, dtype):
+    """A model whose first layer has the routed feed-forward and whose second layer's attention has the other
+    position encoding: registered from here, built from a folder, stepped whole, in portions and token by token."""
+    from vt_transformer_b200.config import Qwen2Config, config_from_dict, register_architecture, unregister_architecture
+    from vt_transformer_b200.models.qwen2 import qwen2_model_spec
+    from vt_transformer_b200.parts import unregister_part
+    from vt_transformer_b200.weights import write_random_model
+    Routed, Angles = define_toy_routed_parts()
+    step = 0.013
+
+    def spec(cfg):
+        base = qwen2_model_spec(cfg)
+        blocks = list(base.blocks)
+        blocks[0] = replace(blocks[0], ffn=Routed(hidden=cfg.hidden_size, inter=40, experts=3), ffn_prefix="moe.")
+        att = blocks[1].mixer
+        blocks[1] = replace(blocks[1], mixer=replace(att, position=Angles(dim=att.head_dim, max_positions=cfg.max_position_embeddings,
+                                                                          step=step)))
+        return replace(base, blocks=tuple(blocks))
+
+    register_architecture("ToyRoutedLM", Qwen2Config, spec, replace=True)
+    try:
+        d = copy.deepcopy(helpers.CONFIGS["A"])
+        d["architectures"] = ["ToyRoutedLM"]
+        folder = write_random_model(config_from_dict(d), os.path.join(tmp, "routed"), seed=5, sigma=0.3)
+        cfg, w = plain.read_config(folder), plain.read_weights(folder)
+        assert "model.layers.0.moe.experts.2.w2.weight" in w and "model.layers.0.mlp.gate_proj.weight" not in w
+
+        def reference(ids):
+            T = len(ids)
+            cos, sin = plain.rotation_table(cfg.max_pos, cfg.head_dim, cfg.theta)
+            x = plain.embed(w["model.embed_tokens.weight"], ids)
+            # layer 0: attention as it is, then the routed feed-forward
+            p = "model.layers.0."
+            h = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg.eps)
+            q = plain.rotate(plain.linear(h, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.q_proj.bias"]).view(T, cfg.heads, cfg.head_dim), range(T), cos, sin)
+            k, v = plain.layer_keys_values(cfg, w, 0, x, cos, sin)
+            x = x + plain.linear(plain.attention(q, k, v, None).reshape(T, -1), w[p + "self_attn.o_proj.weight"])
+            h = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg.eps)
+            prob = torch.softmax(h @ w[p + "moe.router.weight"].t(), dim=-1)
+            weight, choice = prob.max(dim=-1)
+            margin = float((prob.topk(2, dim=-1).values[:, 0] - prob.topk(2, dim=-1).values[:, 1]).min())
+            f = torch.zeros_like(x)
+            for t in range(T):
+                e = int(choice[t])
+                mid = plain.linear(h[t:t + 1], w[p + f"moe.experts.{e}.w1.weight"])
+                f[t] = (plain.linear(mid * torch.sigmoid(mid), w[p + f"moe.experts.{e}.w2.weight"]) * weight[t])[0]
+            x = x + f
+            # layer 1: rotation by the other angles
+            half = cfg.head_dim // 2
+            angle = torch.arange(cfg.max_pos, dtype=torch.float64)[:, None] * (step * torch.arange(1, half + 1, dtype=torch.float64))[None, :]
+            x = plain.layer(cfg, w, 1, x, torch.cos(angle), torch.sin(angle))
+            x = plain.rms_norm(x, w["model.norm.weight"], cfg.eps)
+            head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
+            return plain.linear(x, head), margin
+
+        runner = runner_for(folder, device, dtype, num_pages=12, max_requests=2)
+        assert not runner.model.graph_safe()              # the routed part loops on the host: no graphs for this model
+        ids = helpers.prompts_for("A")[3][:60]
+        ref, margin = reference(ids)
+        assert margin > (1e-4 if dtype == "float32" else 2e-2), f"a router decision is too close to call ({margin})"
+        worst = 0.0
+        for sizes in ([60], [7, 2, 30, 1, 1, 19], [40] + [1] * 20):
+            row = runner.admit()
+            got, at = [], 0
+            for k in sizes:
+                got.append(runner.step([helpers_entry(row, ids[at:at + k])]).float().cpu())
+                at += k
+            runner.check_status()
+            runner.release(row)
+            err = float((torch.cat(got).double() - ref).abs().max())
+            assert err <= 3 * helpers.TOL[dtype] * max(1.0, float(ref.abs().max())), (sizes, err)
+            worst = max(worst, err)
+        return worst
+    finally:
+        unregister_architecture("ToyRoutedLM")
+        unregister_part("feed_forward", "toy_routed")
+        unregister_part("position", "toy_linear_angles")
+
+
 # ----------------------------------------------------------------------------- generation
 
 

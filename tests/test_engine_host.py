@@ -40,6 +40,10 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(fake_backend, tmp_
     scenarios.toy_state_case(str(tmp_path), DEV, DT)
 
 
+def test_toy_feed_forward_with_routing_and_another_position_encoding(fake_backend, tmp_path):
+    scenarios.toy_routed_case(str(tmp_path), DEV, DT)
+
+
 def test_step_refuses_bad_entries_and_leaves_the_cache_alone(fake_backend, folders):
     from vt_transformer_b200.cache import OutOfPages
     from vt_transformer_b200.engine import StepEntry

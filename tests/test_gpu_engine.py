@@ -29,6 +29,11 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_feed_forward_with_routing_and_another_position_encoding(tmp_path, dtype):
+    scenarios.toy_routed_case(str(tmp_path), DEV, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "C"])
 def test_greedy_generation_through_the_entry_point(folders, name, dtype):
     scenarios.greedy_generation_case(folders(name), name, DEV, dtype)
