@@ -176,6 +176,39 @@ def main() -> int:
         return dict(tok_s=batch * steps / (ms / 1e3), ms_per_step=ms / steps, launches=launched, ctx_mean=ctx_mean,
                     clocks=info)
 
+    def prefill_ms(warm, timed):
+        """One request of 2,048 tokens, one step, logits of the last token: median of `timed` steps in ms."""
+        times = []
+        for i in range(warm + timed):
+            row = runner.admit()
+            toks = random_tokens(PREFILL_TOKENS)
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            runner.step([StepEntry(row, toks, [PREFILL_TOKENS - 1])])
+            e.record()
+            torch.cuda.synchronize()
+            if i >= warm:
+                times.append(s.elapsed_time(e))
+            runner.release(row)
+        runner.check_status()
+        return statistics.median(times)
+
+    points, prefill = {}, None
+    if not args.skip_points:
+        # The prefill is timed first and once more after the decode runs.  Eight steps back to back are a load of
+        # 0.2 s: the GPU reaches its power cap within them, so the median is nearer to a sustained figure than to a
+        # burst (a single step after one warm-up takes about a tenth less).  `frac` is against the burst peak,
+        # `frac_sustained` against the peak of a seconds-long loop.
+        ms = prefill_ms(1, 1) if args.only_prefill else prefill_ms(3, 5)
+        T, H, I, L = PREFILL_TOKENS, cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers
+        per_layer = 2 * T * H * (cfg.q_dim + 2 * cfg.kv_dim) + 2 * T * cfg.q_dim * H + 2 * T * H * 2 * I + 2 * T * I * H
+        attn = 2 * 2 * (T * (T + 1) // 2) * cfg.head_dim * cfg.num_attention_heads
+        flops = L * (per_layer + attn) + 2 * H * vocab
+        prefill = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
+                   "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(flops / ms / 1e9, 1),
+                   "frac_sustained": round(flops / (ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4)}
+
     if args.only_prefill:
         main_run = dict(tok_s=0.0, ms_per_step=1.0, launches=0, ctx_mean=0.0, clocks=None)
         args.skip_e2e = True
@@ -185,33 +218,11 @@ def main() -> int:
     step_bytes = runner.weight_bytes(args.batch) + kv_bytes
     achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
 
-    points, prefill = {}, None
     if not args.skip_points:
         for b in (() if args.only_prefill else (1, 64)):
             points[f"decode_b{b}"] = round(decode_run(b, min(args.steps, 64), 5)["tok_s"], 1)
-        # prefill of 2,048 tokens: one request, one step, logits of the last token
-        times = []
-        for i in range((1 + 1) if args.only_prefill else (3 + 5)):
-            row = runner.admit()
-            toks = random_tokens(PREFILL_TOKENS)
-            torch.cuda.synchronize()
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record()
-            runner.step([StepEntry(row, toks, [PREFILL_TOKENS - 1])])
-            e.record()
-            torch.cuda.synchronize()
-            if i >= (1 if args.only_prefill else 3):
-                times.append(s.elapsed_time(e))
-            runner.release(row)
-        runner.check_status()
-        ms = statistics.median(times)
-        T, H, I, L = PREFILL_TOKENS, cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers
-        per_layer = 2 * T * H * (cfg.q_dim + 2 * cfg.kv_dim) + 2 * T * cfg.q_dim * H + 2 * T * H * 2 * I + 2 * T * I * H
-        attn = 2 * 2 * (T * (T + 1) // 2) * cfg.head_dim * cfg.num_attention_heads
-        flops = L * (per_layer + attn) + 2 * H * vocab
-        prefill = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
-                   "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(flops / ms / 1e9, 1)}
-
+        if not args.only_prefill:
+            prefill["ms_after_decode_runs"] = round(prefill_ms(1, 3), 3)
     if args.skip_e2e:
         print(json.dumps({"value": round(main_run["tok_s"], 1), "ms_per_step": round(main_run["ms_per_step"], 4),
                           "points": points, "prefill": prefill, "note": "partial run (--skip-e2e): not a bench line"}))
