@@ -457,6 +457,28 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
             okp[h] = key < key_hi && pg[h] >= 0 && pg[h] < p.n_pages;
             base[h] = okp[h] ? (((size_t)pg[h] * p.kv_heads + kvh) * p.page_size + key % p.page_size) * D : 0;
         }
+        if constexpr (32 % CHUNKS == 0) {
+            // A whole block of a head size whose rows are a power of two long: the lane's first row and its piece
+            // of it are found once; every further copy lies a constant number of bytes from them.
+            if (okp[0] && okp[1] && kb + DKB <= key_hi) {
+                constexpr int RPI = 32 / CHUNKS;         // rows that the warp's lanes cover in one turn
+                const int r0 = lane / CHUNKS, piece = lane % CHUNKS;
+                const unsigned ks0 = (unsigned)__cvta_generic_to_shared(ks + ((size_t)stage * DKB + r0) * LD + piece * 8);
+                const unsigned vs0 = (unsigned)__cvta_generic_to_shared(vs + ((size_t)stage * DKB + r0) * LD + piece * 8);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const __nv_bfloat16* kg0 = p.k_cache + base[h] + (size_t)r0 * D + piece * 8;
+                    const __nv_bfloat16* vg0 = p.v_cache + base[h] + (size_t)r0 * D + piece * 8;
+#pragma unroll
+                    for (int i = 0; i < 16 / RPI; ++i) {
+                        const int r = 16 * h + i * RPI;  // rows below the lane's first
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(ks0 + r * LD * 2), "l"(kg0 + i * RPI * D));
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(vs0 + r * LD * 2), "l"(vg0 + i * RPI * D));
+                    }
+                }
+                return;
+            }
+        }
         for (int c = lane; c < DKB * CHUNKS; c += 32) {
             const int r = c / CHUNKS, piece = c % CHUNKS;
             const int h = r >> 4;
@@ -617,21 +639,38 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters) {
 #pragma unroll
         for (int ks_ = 0; ks_ < D / 16; ++ks_) {
 #pragma unroll
-            for (int j = 0; j < DKB / 8; ++j) {
-                const __nv_bfloat16* kp = kst + (size_t)(j * 8 + gq) * LD + ks_ * 16 + 2 * tq;
-                mma_bf16(s[j], qf[ks_], *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
+            for (int j = 0; j < DKB / 8; j += 2) {
+                // four 8x8 pieces of K: (keys of tile j, d 0..7), (tile j, d 8..15), (tile j+1, d 0..7), (tile j+1, d 8..15)
+                uint32_t kf[4];
+                const int mat = lane >> 3, r = lane & 7;
+                ldmatrix_x4(kf, kst + (size_t)((j + (mat >> 1)) * 8 + r) * LD + ks_ * 16 + (mat & 1) * 8);
+                mma_bf16(s[j], qf[ks_], kf[0], kf[1]);
+                mma_bf16(s[j + 1], qf[ks_], kf[2], kf[3]);
             }
         }
         float mnew[2] = {mrow[0], mrow[1]};
+        // a block all of whose keys every token of the tile sees needs no comparison of positions
+        const bool open = (kb + DKB - 1 <= pos_lo) && (p.window <= 0 || kb > pos_hi - p.window);
+        if (open) {
 #pragma unroll
-        for (int j = 0; j < DKB / 8; ++j) {
+            for (int j = 0; j < DKB / 8; ++j) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int i = e >> 1;
-                const int key = kb + j * 8 + 2 * tq + (e & 1);
-                const bool see = valid[i] && key <= pos[i] && (p.window <= 0 || key > pos[i] - p.window);
-                s[j][e] = see ? s[j][e] * p.scale_log2 : -INFINITY;
-                mnew[i] = fmaxf(mnew[i], s[j][e]);
+                for (int e = 0; e < 4; ++e) {
+                    s[j][e] = valid[e >> 1] ? s[j][e] * p.scale_log2 : -INFINITY;
+                    mnew[e >> 1] = fmaxf(mnew[e >> 1], s[j][e]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < DKB / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = e >> 1;
+                    const int key = kb + j * 8 + 2 * tq + (e & 1);
+                    const bool see = valid[i] && key <= pos[i] && (p.window <= 0 || key > pos[i] - p.window);
+                    s[j][e] = see ? s[j][e] * p.scale_log2 : -INFINITY;
+                    mnew[i] = fmaxf(mnew[i], s[j][e]);
+                }
             }
         }
         float corr[2];
