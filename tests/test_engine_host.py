@@ -77,3 +77,25 @@ def test_missing_extension_fails_loudly():
     if not torch.cuda.is_available():
         with pytest.raises(RuntimeError, match="no CPU path"):
             ops.backend()
+
+
+def test_single_token_steps_fetch_by_boxes_only_where_a_warp_streams_many_blocks():
+    """The choice between cp.async copies and tensor-map boxes for a decode step's keys is made on the host."""
+    import torch
+    from vt_transformer_b200 import ops as o
+    dev = torch.device("cpu")
+    # batch 8 at 1,024 keys, 3 runs: 32 blocks for 12 warps: copies
+    assert not o._decode_long_runs(32, 32, 3, 128, dev)
+    # batch 64 at 4,096 keys: 128 blocks for the three warps of a CTA: boxes
+    assert o._decode_long_runs(256, 128, 1, 128, dev)
+    assert o._decode_long_runs(256, 128, 1, 64, dev)
+    # other head sizes have no boxes
+    assert not o._decode_long_runs(256, 128, 1, 80, dev)
+    old = o.DECODE_BOXES
+    try:
+        o.DECODE_BOXES = "never"
+        assert not o._decode_long_runs(256, 128, 1, 128, dev)
+        o.DECODE_BOXES = "always"
+        assert o._decode_long_runs(32, 32, 3, 128, dev) and not o._decode_long_runs(32, 32, 3, 96, dev)
+    finally:
+        o.DECODE_BOXES = old

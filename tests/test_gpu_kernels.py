@@ -26,6 +26,17 @@ def close(got, ref, dtype, roundings=1.0):
     assert err <= bound, f"error {err:.3e} above {bound:.3e}"
 
 
+@pytest.fixture(params=["never", "always"])
+def key_fetch(request):
+    """Single-token steps fetch keys and values by cp.async or, at head sizes 64 and 128, as boxes of a tensor
+    map; the engine chooses by the length of the contexts, the tests run both."""
+    from vt_transformer_b200 import ops as o
+    old = o.DECODE_BOXES
+    o.DECODE_BOXES = request.param
+    yield request.param
+    o.DECODE_BOXES = old
+
+
 def ops():
     from vt_transformer_b200 import ops as o
     return o
@@ -211,8 +222,9 @@ def test_prompt_portions_on_tcgen05(heads, kv_heads, d, page_size, window):
 
 
 @pytest.mark.parametrize("heads,kv_heads,d,page_size,window", [(28, 4, 128, 16, None), (6, 2, 80, 32, None), (4, 4, 16, 16, 40),
-                                                               (16, 1, 64, 64, 100), (14, 2, 64, 16, None), (40, 2, 32, 16, None)])
-def test_single_token_steps_split_the_keys(heads, kv_heads, d, page_size, window):
+                                                               (16, 1, 64, 64, 100), (14, 2, 64, 16, None), (40, 2, 32, 16, None),
+                                                               (8, 2, 128, 48, None), (14, 2, 128, 32, 90)])
+def test_single_token_steps_split_the_keys(heads, kv_heads, d, page_size, window, key_fetch):
     """Every sequence brings one token (a decode step): the tensor-core kernel splits the keys of a
     sequence over several CTAs and merges the parts.  Sequences of very different lengths, one of a
     single token."""
@@ -249,7 +261,7 @@ def test_single_token_steps_split_the_keys(heads, kv_heads, d, page_size, window
 
 @pytest.mark.parametrize("heads,kv_heads,d,page_size,n_seqs,longest", [(28, 4, 128, 16, 50, 300), (8, 2, 64, 32, 90, 200),
                                                                         (14, 2, 128, 64, 40, 1500), (6, 2, 80, 16, 80, 100)])
-def test_single_token_steps_with_more_ctas_than_sms(heads, kv_heads, d, page_size, n_seqs, longest):
+def test_single_token_steps_with_more_ctas_than_sms(heads, kv_heads, d, page_size, n_seqs, longest, key_fetch):
     """Many sequences: more CTAs than SMs, so the kernel runs with three warps a CTA and two CTAs an SM
     (head sizes 64 and 128), alone or with the keys of a sequence cut into runs."""
     import helpers
@@ -280,8 +292,11 @@ def test_single_token_steps_with_more_ctas_than_sms(heads, kv_heads, d, page_siz
 
 
 @pytest.mark.parametrize("heads,kv_heads,d,page_size,window,rotate", [(28, 4, 128, 16, None, True), (6, 2, 48, 32, 40, True),
-                                                                      (4, 4, 16, 16, None, True), (8, 1, 64, 16, None, False)])
-def test_single_token_step_rotates_and_stores_inside_the_attention_kernel(heads, kv_heads, d, page_size, window, rotate):
+                                                                      (4, 4, 16, 16, None, True), (8, 1, 64, 16, None, False),
+                                                                      (24, 2, 64, 16, None, True), (9, 1, 128, 64, 70, True),
+                                                                      (14, 2, 128, 64, 200, True)])
+def test_single_token_step_rotates_and_stores_inside_the_attention_kernel(heads, kv_heads, d, page_size, window, rotate,
+                                                                          key_fetch):
     """A decode step's rotation, cache store and attention as one kernel against the same as two kernels:
     the same output, the same page contents, for a run that writes the cache and for one that only reads."""
     import helpers

@@ -98,12 +98,14 @@ cudaError_t launch_attention_tc(const void* qkv, int qkv_stride, void* out, cons
 // store_kv, writes the token's k and v into their page: no rotation kernel has to run before it.  With fuse_rope,
 // q, k and v may come as qkv_shares [n_shares, tokens, qkv_stride] float, the unadded shares of the product that
 // made them (launch_gemm_tc, epilogue 2), instead of qkv: they are added where they are read.
+// long_runs 1: the caller expects a warp to stream many blocks of keys (long contexts); head sizes 64 and 128 then
+// fetch them as boxes of a tensor map, which arrive later than cp.async copies but cost far fewer instructions.
 cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, const void* k_cache, const void* v_cache,
                                     const int* cu_q, const int* q_start, const int* block_table, int table_stride,
                                     int n_seqs, int n_pages, int n_tokens, int heads, int kv_heads, int head_dim,
                                     int page_size, int window, float scale, int n_splits, float* part_o, float* part_ml,
                                     int* counters, int fuse_rope, const float2* cos_sin, int max_pos, int store_kv,
-                                    const float* qkv_shares, int n_shares, int* status, cudaStream_t stream);
+                                    const float* qkv_shares, int n_shares, int long_runs, int* status, cudaStream_t stream);
 
 // out[r] = index of the largest logit of row r (the lowest index among equals).
 cudaError_t launch_argmax(const float* logits, int* out, int n_rows, int vocab, cudaStream_t stream);

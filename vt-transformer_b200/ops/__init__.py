@@ -264,8 +264,10 @@ def rope_attention(qkv, out, cos_sin, k_cache, v_cache, ctx, block_table, heads:
             part_o = torch.empty((splits, ctx.n_tokens, heads, head_dim), dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty((splits, ctx.n_tokens, heads, 2), dtype=torch.float32, device=qkv.device)
             counters = _attention_counters(qkv.device, ctx.n_seqs * kv_heads)
+        long_runs = _decode_long_runs(ctx.n_seqs * kv_heads, max(1, -(-span // 32)), splits, head_dim, qkv.device)
         be.attention_decode(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, heads, kv_heads, head_dim, w,
-                            float(scale), splits, part_o, part_ml, counters, True, cos_sin, bool(store), status, shares)
+                            float(scale), splits, part_o, part_ml, counters, True, cos_sin, bool(store), status, shares,
+                            long_runs)
         return out
     rope_store(qkv, ctx.positions, cos_sin, k_cache, v_cache, ctx.token_seq, block_table, heads, kv_heads, head_dim,
                store=store, status=status)
@@ -295,8 +297,9 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
                 part_o = torch.empty((splits, ctx.n_tokens, heads, head_dim), dtype=torch.float32, device=qkv.device)
                 part_ml = torch.empty((splits, ctx.n_tokens, heads, 2), dtype=torch.float32, device=qkv.device)
                 counters = _attention_counters(qkv.device, ctx.n_seqs * kv_heads)
+            long_runs = _decode_long_runs(ctx.n_seqs * kv_heads, max(1, -(-span // 32)), splits, head_dim, qkv.device)
             be.attention_decode(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, heads, kv_heads,
-                                head_dim, w, float(scale), splits, part_o, part_ml, counters)
+                                head_dim, w, float(scale), splits, part_o, part_ml, counters, long_runs=long_runs)
             return out
         # portions long enough to fill tiles of 128 rows: the tcgen05 kernel where it takes the sizes
         if (ATTENTION_KERNEL == "auto" and ctx.max_q_len * group >= 128
@@ -347,6 +350,22 @@ def _decode_splits(pairs: int, blocks: int, device) -> int:
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
     return best
+
+
+DECODE_BOXES = "auto"    # "auto" | "always" | "never": tensor-map boxes for the keys and values of single-token steps
+LONG_RUN_BLOCKS = 16     # blocks of 32 keys a warp from which the boxes pay
+
+
+def _decode_long_runs(pairs: int, blocks: int, splits: int, head_dim: int, device) -> bool:
+    """Whether a single-token step's keys and values come as boxes of a tensor map (head sizes 64 and 128):
+    a box arrives later than a cp.async copy but costs the warp one instruction, not 64, so it pays where a
+    warp streams many blocks and loses where it has a few."""
+    if head_dim not in (64, 128) or DECODE_BOXES == "never":
+        return False
+    if DECODE_BOXES == "always":
+        return True
+    warps = 3 if pairs * splits > _sm_counts.get(device, 148) else 4
+    return blocks >= LONG_RUN_BLOCKS * warps * splits
 
 
 def _attention_counters(device, n: int) -> torch.Tensor:
