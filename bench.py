@@ -100,6 +100,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has (recorded in config)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="tokens of every request's prompt (recorded in config)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the prefill")
     ap.add_argument("--skip-e2e", action="store_true", help="leave out the run through the Python entry point")
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prefill only (for profiling)")
@@ -125,11 +126,13 @@ def main() -> int:
     dev = "cuda:0"
     max_batch = max(64, args.batch)
     new_tokens = warmup + args.steps + 8
-    per_req = PROMPT_LEN + max(new_tokens, 256) + PAGE
+    prompt_len = args.prompt_len
+    context = max(CONTEXT, prompt_len + max(new_tokens, 256) + PAGE)
+    per_req = prompt_len + max(new_tokens, 256) + PAGE
     pool_tokens = max_batch * per_req + PREFILL_TOKENS
     t0 = time.time()
     runner = ModelRunner.from_random(cfg, seed=0, sigma=0.02, dtype="bfloat16", device=dev, page_size=PAGE,
-                                     num_pages=-(-pool_tokens // PAGE), max_requests=max_batch, max_seq_len=CONTEXT)
+                                     num_pages=-(-pool_tokens // PAGE), max_requests=max_batch, max_seq_len=context)
     torch.cuda.synchronize()
     build_s = time.time() - t0
     gen = torch.Generator().manual_seed(1)
@@ -139,10 +142,13 @@ def main() -> int:
         return torch.randint(0, vocab, (n,), generator=gen).tolist()
 
     def fill(batch):
-        """Admits `batch` requests and runs their 1,024-token prompts, two prompts a step."""
+        """Admits `batch` requests and runs their prompts, 2,048 tokens a step."""
         rows = [runner.admit() for _ in range(batch)]
-        for i in range(0, batch, 2):
-            runner.step([StepEntry(r, random_tokens(PROMPT_LEN), []) for r in rows[i:i + 2]])
+        chunk = max(1, 2048 // prompt_len)
+        for i in range(0, batch, chunk):
+            toks = [random_tokens(prompt_len) for _ in rows[i:i + chunk]]
+            for at in range(0, prompt_len, 2048):
+                runner.step([StepEntry(r, t[at:at + 2048], []) for r, t in zip(rows[i:i + chunk], toks)])
         return rows
 
     def decode_run(batch, steps, warm, clocks=None):
@@ -169,7 +175,7 @@ def main() -> int:
         ms = start.elapsed_time(end)
         info = clocks.stop() if clocks else None
         launched = ops.launches - launches0
-        ctx_mean = PROMPT_LEN + warm + (steps - 1) / 2.0 + 1
+        ctx_mean = prompt_len + warm + (steps - 1) / 2.0 + 1
         runner.check_status()
         for r in rows:
             runner.release(r)
@@ -231,7 +237,7 @@ def main() -> int:
     llm = LLM(None, runner=runner, max_extend_tokens=2048)
     params = SamplingParams(temperature=0.0, max_tokens=new_tokens, ignore_eos=True)
     for _ in range(args.batch):
-        llm.add_request(random_tokens(PROMPT_LEN), params)
+        llm.add_request(random_tokens(prompt_len), params)
     while any(len(r.output) == 0 for r in llm.scheduler.running) or llm.scheduler.waiting:
         llm.step()
     for _ in range(warmup):
@@ -250,14 +256,14 @@ def main() -> int:
 
     clocks = main_run["clocks"] or {}
     line = {
-        "metric": "decode tok/s at batch 8 (Qwen2-7B layer sizes, random weights, 1,024-token prompts)",
+        "metric": f"decode tok/s at batch {args.batch} (Qwen2-7B layer sizes, random weights, {prompt_len:,}-token prompts)",
         "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "config": {"model": "Qwen2-7B sizes, random N(0,0.02)", "layers": cfg.num_hidden_layers, "layers_full": layers_full,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-                   "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
+                   "global_batch": args.batch, "seq_len": context, "prompt_len": prompt_len,
                    "mean_context": round(main_run["ctx_mean"], 1), "page_size": PAGE, "parallelism": "1 GPU",
                    "l2": "inputs larger than L2 (every step reads all weights)", "peaks": pk["source"]},
         "e2e": {"value": round(produced / e2e_s, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
