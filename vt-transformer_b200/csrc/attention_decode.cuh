@@ -1,0 +1,789 @@
+// The kernel of single-token attention and its launchers by head size: included by the files that instantiate
+// it (attention_decode.cu: the head sizes without tensor-map boxes; attention_decode_boxes.cu: 64 and 128).
+#pragma once
+
+#include <cooperative_groups.h>
+
+#include <cstring>
+
+#include "attention_mma.cuh"
+#include "common.cuh"
+#include "kernels.h"
+#include "launch.cuh"
+#include "tc_common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace vtb {
+
+// head sizes 64 and 128, compiled in a file of their own (attention_decode_boxes.cu)
+cudaError_t launch_decode_64_128(const AttnParams& p, int head_dim, int n_seqs, int* counters, cudaStream_t stream);
+
+namespace {
+
+
+// ---- single-token steps -----------------------------------------------------------------------------
+// A CTA of four warps serves one (sequence, KV head, run of keys).  The run's blocks of 32 keys go to
+// the warps in turn; each warp streams its blocks through its own two-stage cp.async ring and keeps a
+// running maximum, sum and output for the up to 16 rows (token, head of the group).  The four results
+// are merged in shared memory.  With more than one run a sequence (n_splits > 1) the CTA leaves its
+// merged result in scratch and counts itself in; the CTA that arrives last merges the runs and stores,
+// so there is no second kernel and no CTA waits for another.
+constexpr int DKB = 32;    // keys in a warp's block
+constexpr int DWARPS = 4;   // warps of a CTA; 3 where two CTAs are to fit an SM (more CTAs than SMs)
+// Head sizes of whole 128-byte lines (64, 128): a block's keys and values come as boxes of a tensor map, one
+// request of the copy engine for 16 or 32 rows of 128 bytes where the other head sizes issue a 16-byte cp.async
+// a lane and piece (whose issue rate, not the memory, bounded the kernel).  A box lands with the 128-byte swizzle:
+// piece c of row r at piece c ^ (r % 8), so that ldmatrix finds eight rows' pieces in eight different banks
+// without padding.
+constexpr bool decode_by_boxes(int d) { return d % 64 == 0; }
+constexpr int DTILE = DKB * 128;   // bytes of a box-loaded tile: 32 rows of 64 values
+// bytes of a warp's two stages of keys and values
+constexpr int decode_warp_bytes(int d, bool boxes) { return boxes ? 2 * 2 * (d / 64) * DTILE : 2 * 2 * DKB * (d + 8) * 2; }
+
+//
+// NARROW (at most 8 rows, that is one token of a group of up to 8 heads): the products are taken the other way
+// round, scores as K (16 keys) by q^T (8 rows) and the output as V^T (16 of d) by P^T (8 rows), so that the eight
+// columns of a tensor-core product hold the rows and none of its sixteen lines stay empty: half the products, half
+// the exponentials and half the registers of the output.
+//
+// BOXES: see decode_by_boxes.  A box takes longer to arrive than a cp.async; it pays where a warp has many blocks
+// to stream (long contexts), not where it has three.
+template <int D, int W, bool NARROW, bool BOXES>
+__global__ void __launch_bounds__(W * 32)
+attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v) {
+    static_assert(!BOXES || decode_by_boxes(D), "boxes are rows of whole 128-byte lines");
+    constexpr int LD = D + 8;                                 // row length without boxes: padded against bank conflicts
+    constexpr int WARP_BYTES = decode_warp_bytes(D, BOXES);   // K and V, two stages
+    constexpr int STAGE_BYTES = WARP_BYTES / 2;               // with boxes: [K tiles of 64 d][V tiles of 64 d]
+    extern __shared__ __align__(16) unsigned char smem_dyn[];
+    // swizzled tiles start on a 1,024-byte boundary
+    unsigned char* smem_raw = BOXES ? reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023) : smem_dyn;
+    __shared__ int last_flag;
+    __shared__ __align__(8) uint64_t arrived[DWARPS][2];      // with boxes: a warp's stage has arrived
+    // The kernels before this one in the stream may still be running (programmatic dependent launch).  What
+    // the step's description says (lengths, block tables: copied from the host before the step's first kernel)
+    // and the keys and values of earlier steps may be read at once; q, and a key or value written in this
+    // step, only after pdl_wait.
+    pdl_launch();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+    if constexpr (BOXES) {
+        if (threadIdx.x == 0) {                                // the maps' descriptors on their way before the first box
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_k) : "memory");
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_v) : "memory");
+        }
+    }
+    const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int q_begin = p.cu_q[seq];
+    const int q_len = p.cu_q[seq + 1] - q_begin;
+    const int ntok = min(p.tokens_per_tile, q_len);
+    if (ntok <= 0) {                                           // padding: a sequence without tokens
+        pdl_wait();
+        return;
+    }
+    const int group = p.heads / p.kv_heads;
+    const int rows_valid = ntok * group;
+    const int start = p.q_start[seq];
+    const int pos_lo = start, pos_hi = start + ntok - 1;
+    int key_lo = (p.window > 0) ? max(0, pos_lo - p.window + 1) : 0;
+    key_lo = key_lo / DKB * DKB;
+    const int key_hi = pos_hi + 1;
+    const int nblk = (key_hi - key_lo + DKB - 1) / DKB;
+    const int blk0 = (int)((long long)split * nblk / p.n_splits), blk1 = (int)((long long)(split + 1) * nblk / p.n_splits);
+
+    unsigned char* wbase = smem_raw + (size_t)warp * WARP_BYTES;
+    __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(wbase);                 // without boxes: [2][DKB][LD]
+    __nv_bfloat16* vs = ks + 2 * DKB * LD;
+    // the 16-byte piece c (d 8 c .. 8 c + 7) of row r of a stage's keys or values
+    auto kpiece = [&](int stage, int r, int c) -> __nv_bfloat16* {
+        if constexpr (BOXES)
+            return reinterpret_cast<__nv_bfloat16*>(wbase + stage * STAGE_BYTES + (c >> 3) * DTILE + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+        else
+            return ks + ((size_t)stage * DKB + r) * LD + c * 8;
+    };
+    auto vpiece = [&](int stage, int r, int c) -> __nv_bfloat16* {
+        if constexpr (BOXES)
+            return reinterpret_cast<__nv_bfloat16*>(wbase + stage * STAGE_BYTES + (D / 64 + (c >> 3)) * DTILE + r * 128 +
+                                                    (((c & 7) ^ (r & 7)) << 4));
+        else
+            return vs + ((size_t)stage * DKB + r) * LD + c * 8;
+    };
+    if constexpr (BOXES) {
+        if (lane == 0) {
+            mbar_init(&arrived[warp][0], 1);
+            mbar_init(&arrived[warp][1], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        }
+        __syncwarp();
+    }
+
+    int row[2], pos[2], tok[2], head[2];
+    bool valid[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        row[i] = gq + 8 * i;
+        valid[i] = row[i] < rows_valid;
+        const int tk = valid[i] ? row[i] / group : 0;
+        tok[i] = q_begin + tk;
+        pos[i] = pos_lo + tk;
+        head[i] = kvh * group + (valid[i] ? row[i] % group : 0);
+    }
+    const int* table = p.block_table + (size_t)seq * p.table_stride;
+    // the pages of a block's two runs of 16 keys (-1: none); looked up a block ahead of the block's loads
+    auto pages_of = [&](int blk, int (&pg)[2]) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int key = key_lo + blk * DKB + 16 * h;
+            pg[h] = (blk < blk1 && key < key_hi) ? table[key / p.page_size] : -1;
+        }
+    };
+    // Sends for a block's keys and values; the answer says which halves of 16 keys were asked for (bit h).
+    auto load_block = [&](int blk, int stage, const int (&pg)[2]) -> int {
+        const int kb = key_lo + blk * DKB;
+        if constexpr (BOXES) {
+            const int br = p.run_keys;               // rows of a box: 32, or 16 where a page is no multiple of 32
+            int asked = 0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                if (kb + 16 * h < key_hi && pg[h] >= 0 && pg[h] < p.n_pages) asked |= 1 << h;
+            if (br == 32) asked = (asked & 1) ? 3 : 0;   // one page holds the block: its first half decides
+            if (lane == 0) {
+                uint64_t* bar = &arrived[warp][stage];
+                const int boxes = br == 32 ? (asked ? 1 : 0) : __popc(asked);
+                if (boxes == 0) {
+                    mbar_arrive(bar);
+                } else {
+                    mbar_expect_tx(bar, (uint32_t)(boxes * 2 * (D / 64) * br * 128));
+                    for (int h = 0; h < 32 / br; ++h) {
+                        if (!(asked >> h & 1)) continue;
+                        const int key = kb + h * br;
+                        const int y = (pg[h] * p.kv_heads + kvh) * p.page_size + key % p.page_size;
+                        unsigned char* dst = wbase + stage * STAGE_BYTES + h * br * 128;
+#pragma unroll
+                        for (int t = 0; t < D / 64; ++t) {
+                            tma_load_2d(dst + t * DTILE, &map_k, t * 64, y, bar);
+                            tma_load_2d(dst + (D / 64 + t) * DTILE, &map_v, t * 64, y, bar);
+                        }
+                    }
+                }
+            }
+            return asked;
+        }
+        constexpr int CHUNKS = D / 8;
+        size_t base[2];
+        bool okp[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int key = kb + 16 * h;
+            okp[h] = key < key_hi && pg[h] >= 0 && pg[h] < p.n_pages;
+            base[h] = okp[h] ? (((size_t)pg[h] * p.kv_heads + kvh) * p.page_size + key % p.page_size) * D : 0;
+        }
+        if constexpr (32 % CHUNKS == 0) {
+            // A whole block of a head size whose rows are a power of two long: the lane's first row and its piece
+            // of it are found once; every further copy lies a constant number of bytes from them.
+            if (okp[0] && okp[1] && kb + DKB <= key_hi) {
+                constexpr int RPI = 32 / CHUNKS;         // rows that the warp's lanes cover in one turn
+                const int r0 = lane / CHUNKS, piece = lane % CHUNKS;
+                const unsigned ks0 = (unsigned)__cvta_generic_to_shared(ks + ((size_t)stage * DKB + r0) * LD + piece * 8);
+                const unsigned vs0 = (unsigned)__cvta_generic_to_shared(vs + ((size_t)stage * DKB + r0) * LD + piece * 8);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const __nv_bfloat16* kg0 = p.k_cache + base[h] + (size_t)r0 * D + piece * 8;
+                    const __nv_bfloat16* vg0 = p.v_cache + base[h] + (size_t)r0 * D + piece * 8;
+#pragma unroll
+                    for (int i = 0; i < 16 / RPI; ++i) {
+                        const int r = 16 * h + i * RPI;  // rows below the lane's first
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(ks0 + r * LD * 2), "l"(kg0 + i * RPI * D));
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(vs0 + r * LD * 2), "l"(vg0 + i * RPI * D));
+                    }
+                }
+                return 3;
+            }
+        }
+        for (int c = lane; c < DKB * CHUNKS; c += 32) {
+            const int r = c / CHUNKS, piece = c % CHUNKS;
+            const int h = r >> 4;
+            const bool ok = (h == 0 ? okp[0] : okp[1]) && (kb + r) < key_hi;
+            const size_t off = (h == 0 ? base[0] : base[1]) + (size_t)(r & 15) * D + piece * 8;
+            cp_async16(ks + ((size_t)stage * DKB + r) * LD + piece * 8, p.k_cache + (ok ? off : 0), ok);
+            cp_async16(vs + ((size_t)stage * DKB + r) * LD + piece * 8, p.v_cache + (ok ? off : 0), ok);
+        }
+        return 3;                                    // rows that were not asked for are filled with zeros
+    };
+
+    const int first = blk0 + warp;
+    // the warp's first block: its keys are of earlier steps, unless the step's own token lies in it and
+    // another kernel of this step has put it there
+    const bool own_in_first = pos_lo >= key_lo + first * DKB && pos_lo < key_lo + (first + 1) * DKB;
+    const bool early = first < blk1 && (!own_in_first || (p.fuse_rope && p.store_kv));
+    int pg_cur[2], pg_next[2];
+    pages_of(first, pg_cur);
+    pages_of(first + W, pg_next);
+    int asked[2] = {3, 3};                            // which halves of a stage's block were asked for
+    if (early) {
+        asked[0] = load_block(first, 0, pg_cur);
+        if constexpr (!BOXES) cp_async_commit();
+    }
+    pdl_wait();
+    if (first < blk1 && !early) {
+        asked[0] = load_block(first, 0, pg_cur);
+        if constexpr (!BOXES) cp_async_commit();
+    }
+    uint32_t qf[D / 16][4];
+    // With q, k and v as unadded shares (one token a sequence): this CTA's part of the token's row, that is its
+    // group's heads of q, then its head of k and of v, is added once, share by share, and kept as bfloat16 in the
+    // shared memory that later takes the merged result.
+    __nv_bfloat16* own = reinterpret_cast<__nv_bfloat16*>(smem_raw + (size_t)W * WARP_BYTES);     // [group + 2][D]
+    if (p.qkv_shares != nullptr) {
+        const size_t share_stride = (size_t)p.n_tokens * p.qkv_stride;
+        const float* row0 = p.qkv_shares + (size_t)q_begin * p.qkv_stride;
+        for (int e = threadIdx.x; e < (group + 2) * (D / 2); e += W * 32) {
+            const int j = e / (D / 2), d2 = (e % (D / 2)) * 2;
+            const int col = (j < group ? (kvh * group + j) : (j == group ? p.heads + kvh : p.heads + p.kv_heads + kvh)) * D + d2;
+            float2 v[8];                       // all shares' loads in flight together; added in order
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                v[q] = (q < p.n_shares) ? __ldcg(reinterpret_cast<const float2*>(row0 + q * share_stride + col)) : make_float2(0.f, 0.f);
+            float2 acc = v[0];
+#pragma unroll
+            for (int q = 1; q < 8; ++q) {
+                acc.x += v[q].x;
+                acc.y += v[q].y;
+            }
+            *reinterpret_cast<uint32_t*>(own + j * D + d2) = pack_bf16(acc.x, acc.y);
+        }
+        __syncthreads();
+    }
+    // two neighbouring values of q: row `t` of qkv, head `h`, at `d`
+    auto pair_at = [&](int t, int h, int d) -> uint32_t {
+        if (p.qkv_shares != nullptr) return *reinterpret_cast<const uint32_t*>(own + (h - kvh * group) * D + d);
+        return *reinterpret_cast<const uint32_t*>(p.qkv + (size_t)t * p.qkv_stride + (size_t)h * D + d);
+    };
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int ks_ = 0; ks_ < D / 16; ++ks_) {
+            qf[ks_][i] = valid[i] ? pair_at(tok[i], head[i], ks_ * 16 + 2 * tq) : 0u;
+            qf[ks_][i + 2] = valid[i] ? pair_at(tok[i], head[i], ks_ * 16 + 8 + 2 * tq) : 0u;
+        }
+    }
+    if (p.fuse_rope && p.cos_sin != nullptr) {
+        // rotate q in registers: the 8-wide chunk u of the first half pairs with chunk u + D / 16 (pairs (i, i + D/2),
+        // v1/tensortype/cuda_kernels/rotary_embed.cu:19-29); 32-bit arithmetic, one rounding, as the separate kernel does
+        constexpr int HC = D / 16;             // 8-wide chunks in half a head
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if (!valid[i]) continue;
+            if (pos[i] >= p.max_pos) {
+                if (tq == 0) set_status(p.status, kStatusBadPosition, pos[i]);
+                continue;
+            }
+            const float2* cs = p.cos_sin + (size_t)pos[i] * (D / 2);
+#pragma unroll
+            for (int u = 0; u < HC; ++u) {
+                const int v = u + HC;
+                uint32_t& xa = qf[u / 2][(u % 2) * 2 + i];
+                uint32_t& ya = qf[v / 2][(v % 2) * 2 + i];
+                const float2 x = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xa));
+                const float2 y = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&ya));
+                const float2 c0 = cs[u * 8 + 2 * tq], c1 = cs[u * 8 + 2 * tq + 1];
+                xa = pack_bf16(x.x * c0.x - y.x * c0.y, x.y * c1.x - y.y * c1.y);
+                ya = pack_bf16(y.x * c0.x + x.x * c0.y, y.y * c1.x + x.y * c1.y);
+            }
+        }
+    }
+    // The output: rows gq and gq + 8 by eight of d a tile; NARROW: d gq and gq + 8 of sixteen a tile by rows 2 tq and
+    // 2 tq + 1.  Maximum and sum: of rows gq and gq + 8; NARROW: of rows 2 tq and 2 tq + 1.
+    constexpr int OT = NARROW ? D / 16 : D / 8;
+    float o[OT][4];
+#pragma unroll
+    for (int i = 0; i < OT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+    // NARROW: the lane's two rows, 2 tq and 2 tq + 1
+    bool nvalid[2];
+    int npos[2];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        nvalid[c] = 2 * tq + c < rows_valid;
+        npos[c] = pos_lo + (nvalid[c] ? (2 * tq + c) / group : 0);
+    }
+
+    int it = 0;
+    for (int blk = first; blk < blk1; blk += W, ++it) {
+        const int stage = it & 1;
+        const int kb = key_lo + blk * DKB;
+        if (blk + W < blk1) {
+            const int a = load_block(blk + W, stage ^ 1, pg_next);
+            if (stage) asked[0] = a; else asked[1] = a;
+            if constexpr (!BOXES) cp_async_commit();
+            pages_of(blk + 2 * W, pg_next);        // for the next turn; the answer comes under this block's work
+            if constexpr (!BOXES) cp_async_wait<1>();
+        } else {
+            if constexpr (!BOXES) cp_async_wait<0>();
+        }
+        if constexpr (BOXES) {
+            if (!mbar_wait(&arrived[warp][stage], (it >> 1) & 1)) {         // the clock limit ran out: give up, say so
+                if (lane == 0) set_status(p.status, kStatusWaitTimeout, blk);
+                break;
+            }
+            // Rows that no box brought, and rows of a box behind the last key, hold what the memory held; a weight of
+            // zero times that may be no number: their values are cleared.
+            const int have = stage ? asked[1] : asked[0];
+            if (have != 3 || kb + DKB > key_hi) {
+                for (int r = 0; r < DKB; ++r) {
+                    if ((have >> (r >> 4) & 1) && kb + r < key_hi) continue;
+                    if (lane < D / 8) *reinterpret_cast<uint4*>(vpiece(stage, r, lane)) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");    // before a later box lands on these rows
+            }
+        }
+        __syncwarp();
+        if (p.fuse_rope && p.store_kv && pos_lo >= kb && pos_lo < kb + DKB) {
+            // the step's own token lies in this block: its k (rotated) and v come from qkv and go into the
+            // block in shared memory and into their page.  (A run of a layer that only reads another run's
+            // cache finds the token's k and v there already.)
+            const int r = pos_lo - kb;
+            const int kcol = (p.heads + kvh) * D, vcol = kcol + p.kv_heads * D;
+            auto value_at = [&](int col) -> __nv_bfloat16 {       // col: from the start of the token's k
+                if (p.qkv_shares != nullptr) return own[group * D + (col < kcol + D ? col - kcol : D + col - vcol)];
+                return p.qkv[(size_t)q_begin * p.qkv_stride + col];
+            };
+            auto ksm = [&](int d) -> __nv_bfloat16& { return kpiece(stage, r, d >> 3)[d & 7]; };
+            auto vsm = [&](int d) -> __nv_bfloat16& { return vpiece(stage, r, d >> 3)[d & 7]; };
+            __nv_bfloat16 *kg = nullptr, *vg = nullptr;
+            {
+                const int page = table[pos_lo / p.page_size];
+                if (page >= 0 && page < p.n_pages) {
+                    const size_t off = (((size_t)page * p.kv_heads + kvh) * p.page_size + pos_lo % p.page_size) * D;
+                    kg = p.k_out + off;
+                    vg = p.v_out + off;
+                } else if (lane == 0) {
+                    set_status(p.status, kStatusBadPage, page);
+                }
+            }
+            const bool rot = p.cos_sin != nullptr && pos_lo < p.max_pos;
+            const float2* cs = p.cos_sin + (size_t)(rot ? pos_lo : 0) * (D / 2);
+            for (int i = lane; i < D / 2; i += 32) {
+                __nv_bfloat16 ka = value_at(kcol + i), kb2 = value_at(kcol + i + D / 2);
+                const float a = __bfloat162float(ka), b = __bfloat162float(kb2);
+                if (rot) {
+                    const float2 c = cs[i];
+                    ka = __float2bfloat16_rn(a * c.x - b * c.y);
+                    kb2 = __float2bfloat16_rn(b * c.x + a * c.y);
+                }
+                ksm(i) = ka;
+                ksm(i + D / 2) = kb2;
+                if (kg) { kg[i] = ka; kg[i + D / 2] = kb2; }
+            }
+            for (int i = lane; i < D; i += 32) {
+                const __nv_bfloat16 vv = value_at(vcol + i);
+                vsm(i) = vv;
+                if (vg) vg[i] = vv;
+            }
+            __syncwarp();
+            if constexpr (BOXES) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        }
+        if constexpr (NARROW) {
+            const int mat = lane >> 3, r8 = lane & 7;
+            float st[DKB / 16][4];                 // keys gq and gq + 8 of a tile of 16 by rows 2 tq and 2 tq + 1
+#pragma unroll
+            for (int kt = 0; kt < DKB / 16; ++kt) st[kt][0] = st[kt][1] = st[kt][2] = st[kt][3] = 0.f;
+#pragma unroll
+            for (int ks_ = 0; ks_ < D / 16; ++ks_) {
+#pragma unroll
+                for (int kt = 0; kt < DKB / 16; ++kt) {
+                    // four 8x8 pieces of K: (keys 0..7, d 0..7), (keys 8..15, d 0..7), (keys 0..7, d 8..15), (keys 8..15, d 8..15)
+                    uint32_t kf[4];
+                    ldmatrix_x4(kf, kpiece(stage, kt * 16 + (mat & 1) * 8 + r8, ks_ * 2 + (mat >> 1)));
+                    mma_bf16(st[kt], kf, qf[ks_][0], qf[ks_][2]);
+                }
+            }
+            float mnew[2] = {mrow[0], mrow[1]};
+            const bool open = (kb + DKB - 1 <= pos_lo) && (p.window <= 0 || kb > pos_hi - p.window);
+#pragma unroll
+            for (int kt = 0; kt < DKB / 16; ++kt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int c = e & 1;
+                    const int key = kb + kt * 16 + gq + (e >> 1) * 8;
+                    const bool see = nvalid[c] && (open || (key <= npos[c] && (p.window <= 0 || key > npos[c] - p.window)));
+                    st[kt][e] = see ? st[kt][e] * p.scale_log2 : -INFINITY;
+                    mnew[c] = fmaxf(mnew[c], st[kt][e]);
+                }
+            }
+            float corr[2];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                mnew[c] = fmaxf(mnew[c], __shfl_xor_sync(0xffffffffu, mnew[c], 4));
+                mnew[c] = fmaxf(mnew[c], __shfl_xor_sync(0xffffffffu, mnew[c], 8));
+                mnew[c] = fmaxf(mnew[c], __shfl_xor_sync(0xffffffffu, mnew[c], 16));
+                corr[c] = (mnew[c] == -INFINITY) ? 1.f : exp2f(mrow[c] - mnew[c]);
+                mrow[c] = mnew[c];
+                lrow[c] *= corr[c];
+            }
+            const float base2[2] = {mnew[0] == -INFINITY ? 0.f : mnew[0], mnew[1] == -INFINITY ? 0.f : mnew[1]};
+#pragma unroll
+            for (int kt = 0; kt < DKB / 16; ++kt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float pv = exp2f(st[kt][e] - base2[e & 1]);
+                    st[kt][e] = pv;
+                    lrow[e & 1] += pv;
+                }
+            }
+            if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // no maximum moved: nothing to rescale
+#pragma unroll
+                for (int i = 0; i < OT; ++i) {
+                    o[i][0] *= corr[0]; o[i][1] *= corr[1];
+                    o[i][2] *= corr[0]; o[i][3] *= corr[1];
+                }
+            }
+#pragma unroll
+            for (int kt = 0; kt < DKB / 16; ++kt) {
+                // P^T of the tile's 16 keys as the second operand: the lane's (key gq, rows 2 tq, 2 tq + 1) becomes
+                // (row gq, keys 2 tq, 2 tq + 1) by a transposition within the warp
+                const uint32_t pb0 = movmatrix_trans(pack_bf16(st[kt][0], st[kt][1]));
+                const uint32_t pb1 = movmatrix_trans(pack_bf16(st[kt][2], st[kt][3]));
+#pragma unroll
+                for (int dt = 0; dt < D / 16; ++dt) {
+                    // V^T: (d 0..7, keys 0..7), (d 8..15, keys 0..7), (d 0..7, keys 8..15), (d 8..15, keys 8..15)
+                    uint32_t vf[4];
+                    ldmatrix_x4_trans(vf, vpiece(stage, kt * 16 + (mat >> 1) * 8 + r8, dt * 2 + (mat & 1)));
+                    mma_bf16(o[dt], vf, pb0, pb1);
+                }
+            }
+        } else {
+            float s[DKB / 8][4];
+#pragma unroll
+            for (int j = 0; j < DKB / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+            for (int ks_ = 0; ks_ < D / 16; ++ks_) {
+#pragma unroll
+                for (int j = 0; j < DKB / 8; j += 2) {
+                    // four 8x8 pieces of K: (keys of tile j, d 0..7), (tile j, d 8..15), (tile j+1, d 0..7), (tile j+1, d 8..15)
+                    uint32_t kf[4];
+                    const int mat = lane >> 3, r = lane & 7;
+                    ldmatrix_x4(kf, kpiece(stage, (j + (mat >> 1)) * 8 + r, ks_ * 2 + (mat & 1)));
+                    mma_bf16(s[j], qf[ks_], kf[0], kf[1]);
+                    mma_bf16(s[j + 1], qf[ks_], kf[2], kf[3]);
+                }
+            }
+            float mnew[2] = {mrow[0], mrow[1]};
+            // a block all of whose keys every token of the tile sees needs no comparison of positions
+            const bool open = (kb + DKB - 1 <= pos_lo) && (p.window <= 0 || kb > pos_hi - p.window);
+            if (open) {
+#pragma unroll
+                for (int j = 0; j < DKB / 8; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        s[j][e] = valid[e >> 1] ? s[j][e] * p.scale_log2 : -INFINITY;
+                        mnew[e >> 1] = fmaxf(mnew[e >> 1], s[j][e]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < DKB / 8; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = e >> 1;
+                        const int key = kb + j * 8 + 2 * tq + (e & 1);
+                        const bool see = valid[i] && key <= pos[i] && (p.window <= 0 || key > pos[i] - p.window);
+                        s[j][e] = see ? s[j][e] * p.scale_log2 : -INFINITY;
+                        mnew[i] = fmaxf(mnew[i], s[j][e]);
+                    }
+                }
+            }
+            float corr[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                mnew[i] = fmaxf(mnew[i], __shfl_xor_sync(0xffffffffu, mnew[i], 1));
+                mnew[i] = fmaxf(mnew[i], __shfl_xor_sync(0xffffffffu, mnew[i], 2));
+                corr[i] = (mnew[i] == -INFINITY) ? 1.f : exp2f(mrow[i] - mnew[i]);
+                mrow[i] = mnew[i];
+                lrow[i] *= corr[i];
+            }
+            const float base2[2] = {mnew[0] == -INFINITY ? 0.f : mnew[0], mnew[1] == -INFINITY ? 0.f : mnew[1]};
+#pragma unroll
+            for (int j = 0; j < DKB / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float pv = exp2f(s[j][e] - base2[e >> 1]);
+                    s[j][e] = pv;
+                    lrow[e >> 1] += pv;
+                }
+            }
+            if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // no maximum moved: nothing to rescale
+#pragma unroll
+                for (int i = 0; i < D / 8; ++i) {
+                    o[i][0] *= corr[0]; o[i][1] *= corr[0];
+                    o[i][2] *= corr[1]; o[i][3] *= corr[1];
+                }
+            }
+#pragma unroll
+            for (int kk = 0; kk < DKB / 16; ++kk) {
+                uint32_t pf[4];
+                pf[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                pf[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                pf[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pf[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int dn = 0; dn < D / 16; ++dn) {
+                    uint32_t vf[4];
+                    const int mat = lane >> 3, r = lane & 7;
+                    ldmatrix_x4_trans(vf, vpiece(stage, kk * 16 + (mat & 1) * 8 + r, dn * 2 + (mat >> 1)));
+                    mma_bf16(o[2 * dn], pf, vf[0], vf[1]);
+                    mma_bf16(o[2 * dn + 1], pf, vf[2], vf[3]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if constexpr (NARROW) {
+            lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 4);
+            lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 8);
+            lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 16);
+        } else {
+            lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 1);
+            lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 2);
+        }
+    }
+    // each warp leaves (output [16][D], maximum [16], sum [16]) at the start of its own buffers
+    float* wo = reinterpret_cast<float*>(wbase);
+    float* wm = wo + 16 * D;
+    float* wl = wm + 16;
+    if constexpr (NARROW) {
+#pragma unroll
+        for (int dt = 0; dt < D / 16; ++dt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) wo[(2 * tq + (e & 1)) * D + dt * 16 + gq + (e >> 1) * 8] = o[dt][e];
+        }
+        if (gq < 2) {                              // rows 0..7 from the lanes of gq 0; rows 8..15 are empty
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                wm[8 * gq + 2 * tq + c] = gq == 0 ? mrow[c] : -INFINITY;
+                wl[8 * gq + 2 * tq + c] = gq == 0 ? lrow[c] : 0.f;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+#pragma unroll
+            for (int dt = 0; dt < D / 8; ++dt)
+                *reinterpret_cast<float2*>(wo + row[i] * D + dt * 8 + 2 * tq) = make_float2(o[dt][2 * i], o[dt][2 * i + 1]);
+            if (tq == 0) {
+                wm[row[i]] = mrow[i];
+                wl[row[i]] = lrow[i];
+            }
+        }
+    }
+    __syncthreads();
+    // merge the warps: first one weight a (row, warp), the row's maximum and its sum; then every thread takes
+    // elements (row, d) of the [16][D] output
+    const int tile = seq * p.kv_heads + kvh;
+    float* res = reinterpret_cast<float*>(smem_raw + (size_t)W * WARP_BYTES);   // [16][D], then maxima [16], sums [16]
+    float* wwgt = res + 16 * D + 32;                                            // [16][W] weights, then [16][8] for the runs
+    if (threadIdx.x < 16) {
+        const int r = threadIdx.x;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < W; ++w) {
+            const float* b = reinterpret_cast<const float*>(smem_raw + (size_t)w * WARP_BYTES);
+            if (b[16 * D + 16 + r] > 0.f) mx = fmaxf(mx, b[16 * D + r]);
+        }
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < W; ++w) {
+            const float* b = reinterpret_cast<const float*>(smem_raw + (size_t)w * WARP_BYTES);
+            const float l = b[16 * D + 16 + r];
+            const float wg = (l > 0.f) ? exp2f(b[16 * D + r] - mx) : 0.f;
+            wwgt[r * W + w] = wg;
+            tot += l * wg;
+        }
+        res[16 * D + r] = mx;
+        res[16 * D + 16 + r] = tot;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 16 * D; e += W * 32) {
+        const int r = e / D, d = e % D;
+        if (r >= rows_valid) continue;
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < W; ++w)
+            acc += reinterpret_cast<const float*>(smem_raw + (size_t)w * WARP_BYTES)[e] * wwgt[r * W + w];
+        const float mx = res[16 * D + r], tot = res[16 * D + 16 + r];
+        const int t = q_begin + r / group, h = kvh * group + r % group;
+        if (p.n_splits == 1) {
+            p.out[((size_t)t * p.heads + h) * D + d] = __float2bfloat16_rn(tot > 0.f ? acc / tot : 0.f);
+        } else if (p.cluster_merge) {
+            res[e] = acc;
+        } else {
+            const size_t idx = ((size_t)split * p.n_tokens + t) * p.heads + h;
+            __stcg(p.part_o + idx * D + d, acc);
+            if (d == 0) {
+                __stcg(p.part_ml + idx * 2, mx);
+                __stcg(p.part_ml + idx * 2 + 1, tot);
+            }
+        }
+    }
+    if (p.n_splits == 1) return;
+    if (p.cluster_merge) {
+        // the runs are the CTAs of one cluster: each takes a share of the elements and reads every
+        // CTA's result through distributed shared memory, runs added in rank order
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        const int ranks = (int)cluster.num_blocks(), me = (int)cluster.block_rank();
+        // one weight a (row, run) and the row's sum, from the runs' maxima and sums (all read at once) ...
+        float* rwgt = wwgt + 16 * W;             // [16][8]
+        float* rtot = rwgt + 16 * 8;             // [16]
+        if (threadIdx.x < 16) {
+            const int r = threadIdx.x;
+            float m[8], l[8];
+#pragma unroll
+            for (int rk = 0; rk < 8; ++rk) {
+                const float* o_r = cluster.map_shared_rank(res, rk < ranks ? rk : me);
+                m[rk] = o_r[16 * D + r];
+                l[rk] = rk < ranks ? o_r[16 * D + 16 + r] : 0.f;
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int rk = 0; rk < 8; ++rk)
+                if (l[rk] > 0.f) mx = fmaxf(mx, m[rk]);
+            float tot = 0.f;
+#pragma unroll
+            for (int rk = 0; rk < 8; ++rk) {
+                const float wg = (l[rk] > 0.f) ? exp2f(m[rk] - mx) : 0.f;
+                rwgt[r * 8 + rk] = wg;
+                tot += l[rk] * wg;
+            }
+            rtot[r] = tot;
+        }
+        __syncthreads();
+        // ... then this CTA's share of the elements, the runs added in rank order
+        for (int e = me * W * 32 + threadIdx.x; e < 16 * D; e += ranks * W * 32) {
+            const int r = e / D, d = e % D;
+            if (r >= rows_valid) continue;
+            float v[8];
+#pragma unroll
+            for (int rk = 0; rk < 8; ++rk) v[rk] = rk < ranks ? cluster.map_shared_rank(res, rk)[e] : 0.f;
+            float acc = 0.f;
+#pragma unroll
+            for (int rk = 0; rk < 8; ++rk) acc += v[rk] * rwgt[r * 8 + rk];
+            const float tot = rtot[r];
+            const int t = q_begin + r / group, h = kvh * group + r % group;
+            p.out[((size_t)t * p.heads + h) * D + d] = __float2bfloat16_rn(tot > 0.f ? acc / tot : 0.f);
+        }
+        cluster.sync();    // nobody leaves while its shared memory is still being read
+        return;
+    }
+    if (p.n_splits == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last_flag = (atomicAdd(&counters[tile], 1) == p.n_splits - 1) ? 1 : 0;
+    __syncthreads();
+    if (!last_flag) return;
+    __threadfence();
+    // The last CTA merges the runs.  First the maxima and sums of all (row, run), loaded side by side and
+    // turned into one weight a (row, run) in shared memory; then the outputs, runs added in order.
+    constexpr int MAXS = 64;
+    float* wgt = reinterpret_cast<float*>(smem_raw);            // [16][MAXS] weights, then [16] totals
+    float* tot_s = wgt + 16 * MAXS;
+    const size_t stride = (size_t)p.n_tokens * p.heads;
+    for (int e = threadIdx.x; e < 16 * p.n_splits; e += W * 32) {
+        const int r = e / p.n_splits, sp = e % p.n_splits;
+        float m = -INFINITY, l = 0.f;
+        if (r < rows_valid) {
+            const size_t idx = sp * stride + (size_t)(q_begin + r / group) * p.heads + kvh * group + r % group;
+            m = __ldcg(p.part_ml + idx * 2);
+            l = __ldcg(p.part_ml + idx * 2 + 1);
+        }
+        wgt[r * MAXS + sp] = (l > 0.f) ? m : -INFINITY;      // for now the maximum (or -inf for an empty run)
+        wgt[16 * MAXS + 16 + r * MAXS + sp] = l;               // and the sum, behind the totals
+    }
+    __syncthreads();
+    if (threadIdx.x < 16) {
+        const int r = threadIdx.x;
+        float mx = -INFINITY;
+        for (int sp = 0; sp < p.n_splits; ++sp) mx = fmaxf(mx, wgt[r * MAXS + sp]);
+        float tot = 0.f;
+        for (int sp = 0; sp < p.n_splits; ++sp) {
+            const float m = wgt[r * MAXS + sp];
+            const float w = (m == -INFINITY) ? 0.f : exp2f(m - mx);
+            wgt[r * MAXS + sp] = w;
+            tot += wgt[16 * MAXS + 16 + r * MAXS + sp] * w;
+        }
+        tot_s[r] = tot;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 16 * D; e += W * 32) {
+        const int r = e / D, d = e % D;
+        if (r >= rows_valid) continue;
+        const size_t idx0 = (size_t)(q_begin + r / group) * p.heads + kvh * group + r % group;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int sp = 0; sp < p.n_splits; ++sp) acc += __ldcg(p.part_o + (sp * stride + idx0) * D + d) * wgt[r * MAXS + sp];
+        const float tot = tot_s[r];
+        p.out[idx0 * D + d] = __float2bfloat16_rn(tot > 0.f ? acc / tot : 0.f);
+    }
+    if (threadIdx.x == 0) counters[tile] = 0;
+}
+
+template <int D, int W, bool NARROW, bool BOXES>
+cudaError_t launch_decode_n(AttnParams p, int n_seqs, int* counters, cudaStream_t stream) {
+    constexpr int WARP_BYTES = decode_warp_bytes(D, BOXES);
+    // with boxes 1,024 bytes more: the swizzled tiles start on such a boundary
+    constexpr int smem = W * WARP_BYTES + (16 * D + 32 + 16 * W + 16 * 8 + 16) * 4 + (BOXES ? 1024 : 0);
+    static_assert(WARP_BYTES >= (16 * D + 32) * 4, "a warp's buffers must hold its merged result");
+    static_assert(W * WARP_BYTES >= (2 * 16 * 64 + 16) * 4, "the merge of the runs needs its weights");
+    static_assert(W <= DWARPS, "a barrier a warp and stage");
+    CUtensorMap map_k, map_v;
+    memset(&map_k, 0, sizeof(map_k));
+    memset(&map_v, 0, sizeof(map_v));
+    if constexpr (BOXES) {
+        // the caches as matrices [pages * kv_heads * page_size, D]; a box never crosses a page
+        p.run_keys = p.page_size % 32 == 0 ? 32 : 16;
+        const long long rows = (long long)p.n_pages * p.kv_heads * p.page_size;
+        if (!make_map(&map_k, p.k_cache, rows, D, p.run_keys) || !make_map(&map_v, p.v_cache, rows, D, p.run_keys))
+            return cudaErrorInvalidValue;
+    }
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, W, NARROW, BOXES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    return launch(attention_decode_kernel<D, W, NARROW, BOXES>, dim3(n_seqs, p.kv_heads, p.n_splits), dim3(W * 32, 1, 1), smem, stream,
+                  dim3(1, 1, p.cluster_merge ? p.n_splits : 1), p, counters, map_k, map_v);
+}
+
+template <int D, int W>
+cudaError_t launch_decode_w(const AttnParams& p, int n_seqs, int* counters, cudaStream_t stream) {
+    const bool narrow = p.tokens_per_tile * (p.heads / p.kv_heads) <= 8;
+    if constexpr (decode_by_boxes(D)) {
+        if (p.run_keys != 0)                       // the caller expects long runs of keys a warp
+            return narrow ? launch_decode_n<D, W, true, true>(p, n_seqs, counters, stream)
+                          : launch_decode_n<D, W, false, true>(p, n_seqs, counters, stream);
+    }
+    return narrow ? launch_decode_n<D, W, true, false>(p, n_seqs, counters, stream)
+                  : launch_decode_n<D, W, false, false>(p, n_seqs, counters, stream);
+}
+
+// With more CTAs than SMs the kernel runs with three warps a CTA where that lets two CTAs share an SM (head
+// sizes 64 and 128): the CTAs then need not run in rounds of one an SM, whose last round is partly empty.
+template <int D>
+cudaError_t launch_decode_d(const AttnParams& p, int n_seqs, int* counters, cudaStream_t stream) {
+    if constexpr (D == 128 || D == 64) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 0;
+        if (sms > 0 && (long long)n_seqs * p.kv_heads * p.n_splits > sms) return launch_decode_w<D, 3>(p, n_seqs, counters, stream);
+    }
+    return launch_decode_w<D, DWARPS>(p, n_seqs, counters, stream);
+}
+
+}  // namespace
+
+}  // namespace vtb

@@ -26,13 +26,15 @@ SOURCES = [
     "gemm_simt.cu",
     "attention_simt.cu",
     "attention_mma.cu",
+    "attention_decode.cu",
+    "attention_decode_boxes.cu",
     "attention_tc.cu",
     "gemm_skinny.cu",
     "gemm_tc.cu",
     "attention_noalloc.cu",
     "sampling.cu",
 ]
-HEADERS = ["common.cuh", "kernels.h", "launch.cuh", "tc_common.cuh", "attention_noalloc.h"]
+HEADERS = ["common.cuh", "kernels.h", "launch.cuh", "tc_common.cuh", "attention_mma.cuh", "attention_decode.cuh", "attention_noalloc.h"]
 
 CUDA_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
