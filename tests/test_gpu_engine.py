@@ -18,6 +18,19 @@ def test_cuts_equal_the_plain_implementation(folders, name, family, dtype):
     scenarios.replay_family(folders(name), name, family, DEV, dtype)
 
 
+@pytest.mark.parametrize("family", ["tail", "mixed"])
+def test_decoding_with_keys_and_values_fetched_as_tensor_map_boxes(folders, family):
+    """Head size 128 (one layer with a window): the engine fetches a decode step's keys as boxes only for long
+    contexts; here it is made to do so for these short ones, pages of 16, used again."""
+    from vt_transformer_b200 import ops as o
+    old = o.DECODE_BOXES
+    o.DECODE_BOXES = "always"
+    try:
+        scenarios.replay_family(folders("D"), "D", family, DEV, "bfloat16")
+    finally:
+        o.DECODE_BOXES = old
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_run_order_is_data(tmp_path, dtype):
     scenarios.run_order_case(str(tmp_path), DEV, dtype)

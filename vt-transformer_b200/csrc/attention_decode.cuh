@@ -21,17 +21,17 @@ cudaError_t launch_decode_64_128(const AttnParams& p, int head_dim, int n_seqs, 
 
 namespace {
 
-
 // ---- single-token steps -----------------------------------------------------------------------------
-// A CTA of four warps serves one (sequence, KV head, run of keys).  The run's blocks of 32 keys go to
-// the warps in turn; each warp streams its blocks through its own two-stage cp.async ring and keeps a
-// running maximum, sum and output for the up to 16 rows (token, head of the group).  The four results
-// are merged in shared memory.  With more than one run a sequence (n_splits > 1) the CTA leaves its
-// merged result in scratch and counts itself in; the CTA that arrives last merges the runs and stores,
-// so there is no second kernel and no CTA waits for another.
+// A CTA of four (or three) warps serves one (sequence, KV head, run of keys).  The run's blocks of 32 keys go
+// to the warps in turn; each warp streams its blocks through its own two-stage ring (cp.async, or tensor-map
+// boxes counted into an mbarrier) and keeps a running maximum, sum and output for the up to 16 rows (token,
+// head of the group).  The warps' results are merged in shared memory.  With more than one run a sequence
+// (n_splits > 1): up to 8 runs are the CTAs of a cluster and merge through distributed shared memory; with more
+// the CTA leaves its merged result in scratch and counts itself in, and the CTA that arrives last merges the
+// runs and stores, so there is no second kernel and no CTA waits for another.
 constexpr int DKB = 32;    // keys in a warp's block
 constexpr int DWARPS = 4;   // warps of a CTA; 3 where two CTAs are to fit an SM (more CTAs than SMs)
-// Head sizes of whole 128-byte lines (64, 128): a block's keys and values come as boxes of a tensor map, one
+// Head sizes of whole 128-byte lines (64, 128): a block's keys and values can come as boxes of a tensor map, one
 // request of the copy engine for 16 or 32 rows of 128 bytes where the other head sizes issue a 16-byte cp.async
 // a lane and piece (whose issue rate, not the memory, bounded the kernel).  A box lands with the 128-byte swizzle:
 // piece c of row r at piece c ^ (r % 8), so that ldmatrix finds eight rows' pieces in eight different banks
