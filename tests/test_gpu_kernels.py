@@ -291,6 +291,42 @@ def test_single_token_steps_with_more_ctas_than_sms(heads, kv_heads, d, page_siz
     assert not bool(torch.isnan(out.float()).any())
 
 
+@pytest.mark.parametrize("heads,kv_heads,d,page_size,window", [(28, 4, 128, 64, None), (12, 2, 128, 16, 700), (14, 2, 64, 32, None)])
+def test_keys_fetched_as_boxes_give_the_same_bits_as_copies(heads, kv_heads, d, page_size, window):
+    """The two ways of bringing a decode step's keys and values into shared memory feed the same arithmetic:
+    their outputs are equal bit for bit, with pages in a shuffled order and contexts that end anywhere in a page."""
+    import helpers
+    from vt_transformer_b200 import ops as o
+    dtype = torch.bfloat16
+    torch.manual_seed(21)
+    rng = random.Random(8)
+    seq_lens = [rng.randrange(900, 2300) for _ in range(47)] + [1, 33, 2304]
+    total = sum(seq_lens)
+    k = torch.randn(total, kv_heads, d, device=DEV).to(dtype)
+    v = torch.randn(total, kv_heads, d, device=DEV).to(dtype)
+    kc, vc, table = paged_cache(k, v, seq_lens, page_size, sum(-(-n // page_size) for n in seq_lens) + 5, dtype, seed=2)
+    T = len(seq_lens)
+    qkv = torch.randn(T, (heads + 2 * kv_heads) * d, device=DEV).to(dtype)
+    ctx = helpers.step_context([1] * T, [n - 1 for n in seq_lens], DEV)
+    outs = {}
+    old = o.DECODE_BOXES
+    try:
+        for mode in ("never", "always"):
+            o.DECODE_BOXES = mode
+            out = torch.full((T, heads * d), float("nan"), device=DEV, dtype=dtype)
+            o.paged_attention(qkv, out, kc, vc, ctx, table, heads, kv_heads, d, window, 1 / math.sqrt(d))
+            outs[mode] = out
+    finally:
+        o.DECODE_BOXES = old
+    assert not bool(torch.isnan(outs["never"].float()).any())
+    assert torch.equal(outs["never"], outs["always"])
+    # and the automatic choice takes boxes here
+    blocks = -(-(min(max(seq_lens), window + 31) if window else max(seq_lens)) // 32)
+    splits = o._decode_splits(T * kv_heads, blocks, torch.device(DEV))
+    if not window:
+        assert o._decode_long_runs(T * kv_heads, blocks, splits, d, torch.device(DEV))
+
+
 @pytest.mark.parametrize("heads,kv_heads,d,page_size,window,rotate", [(28, 4, 128, 16, None, True), (6, 2, 48, 32, 40, True),
                                                                       (4, 4, 16, 16, None, True), (8, 1, 64, 16, None, False),
                                                                       (24, 2, 64, 16, None, True), (9, 1, 128, 64, 70, True),
