@@ -5,8 +5,9 @@ with random weights, with their roofline fractions.
 
 A step is one decode step of a batch of 8 requests with 1,024-token prompts (the context grows
 from 1,024).  ``value`` is decoded tokens a second with the K steps timed on the device;
-``e2e`` is the same through the Python entry point (``LLM.step``), token ids crossing between
-host and device every step.  One JSON line is printed.  The engine runs on one GPU: for
+``e2e`` is the same through the Python entry point (``LLM.step``, with ``overlap``: the next step is
+enqueued before the tokens of the one before are read), the step's description going to the device
+and the sampled token ids coming to the host every step.  One JSON line is printed.  The engine runs on one GPU: for
 --gpus above 1 a line says so and the exit code is 2.
 """
 from __future__ import annotations
@@ -103,6 +104,8 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="tokens of every request's prompt (recorded in config)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the prefill")
     ap.add_argument("--skip-e2e", action="store_true", help="leave out the run through the Python entry point")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="end to end: read a step's tokens before the next step is enqueued (LLM(overlap=False))")
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prefill only (for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -242,7 +245,7 @@ def main() -> int:
                           "points": points, "prefill": prefill, "note": "partial run (--skip-e2e): not a bench line"}))
         return 0
     # end to end: the Python entry point, token ids in from the host and out to the host every step
-    llm = LLM(None, runner=runner, max_extend_tokens=2048)
+    llm = LLM(None, runner=runner, max_extend_tokens=2048, overlap=not args.no_overlap)
     params = SamplingParams(temperature=0.0, max_tokens=new_tokens, ignore_eos=True)
     for _ in range(args.batch):
         llm.add_request(random_tokens(prompt_len), params)
@@ -273,7 +276,7 @@ def main() -> int:
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "global_batch": args.batch, "seq_len": context, "prompt_len": prompt_len,
                    "mean_context": round(main_run["ctx_mean"], 1), "page_size": PAGE, "parallelism": "1 GPU",
-                   "l2": "inputs larger than L2 (every step reads all weights)", "peaks": pk["source"]},
+                   "l2": "inputs larger than L2 (every step reads all weights)", "peaks": pk["source"], "e2e_mode": "step by step" if args.no_overlap else "overlap"},
         "e2e": {"value": round(produced / e2e_s, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": main_run["launches"],
         "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"), "reasons": clocks.get("reasons", [])},

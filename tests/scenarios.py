@@ -420,3 +420,83 @@ def temperature_generation_case(folder, name, device, dtype, n_new=24):
                     assert lo - slack <= u <= float(c[tok]) + slack, (i, j, tok, u, lo, float(c[tok]))
     assert len({tuple(o) for o in results[0]}) > 1
     return results[0], preemptions
+
+
+# ----------------------------------------------------------------------------- the next step enqueued early
+
+
+def check_tokens_along_their_path(folder, prompt, out, temperature, seed, dtype):
+    """Every generated token against the plain implementation run over the engine's own tokens: greedy, its
+    plain logit lies within the tolerance of the largest; with a temperature, the draw's random number falls
+    into the token's interval of the plain cumulative distribution, give or take the tolerance."""
+    from vt_transformer_b200.sampling import uniform
+    ref = helpers.plain_logits(folder, list(prompt) + list(out))
+    for j, tok in enumerate(out):
+        row = ref[len(prompt) - 1 + j]
+        if temperature <= 0.0:
+            assert float(row.max() - row[tok]) <= 2 * helpers.TOL[dtype], (len(prompt), j, tok)
+        else:
+            c = torch.cumsum(plain.kept_probabilities(row, temperature), 0)
+            u, slack = uniform(seed, j), 4 * helpers.TOL[dtype]
+            lo = float(c[tok - 1]) if tok > 0 else 0.0
+            assert lo - slack <= u <= float(c[tok]) + slack, (len(prompt), j, tok, u, lo, float(c[tok]))
+
+
+def overlap_generation_case(folder, name, device, dtype, n_new=24):
+    """Generation with the next step enqueued before the tokens of the one before are read gives the tokens
+    of generation without: greedy and with a temperature, with requests that stop at an end token (found only
+    when their step lands, one step after they have run on), at their length, at different times, with
+    portions of prompts between decode steps, and with so few pages that requests are pre-empted."""
+    from vt_transformer_b200 import LLM, SamplingParams
+    prompts = helpers.prompts_for(name)[:4]
+    steps_with_overlap = 0
+    for kw in (dict(max_running_reqs=4, num_pages=40, max_extend_tokens=256, chunk_size=None),
+               dict(max_running_reqs=2, num_pages=40, max_extend_tokens=28, chunk_size=24),
+               dict(max_running_reqs=4, num_pages=11, max_extend_tokens=40, chunk_size=24)):
+        for temperature in (0.0, 0.7):
+            base = SamplingParams(temperature=temperature, max_tokens=n_new, ignore_eos=True, seed=5)
+            plain_llm = LLM(folder, dtype=dtype, device=device, max_seq_len=160, page_size=16, **kw)
+            want = plain_llm.generate(prompts, base)
+            # end tokens taken from what the requests generate: request i stops at its token number 3 + 4 i
+            # (or earlier, if the same id comes earlier), the last one runs to its length
+            params, stops = [], []
+            for i, o in enumerate(want):
+                if i == len(want) - 1:
+                    params.append(SamplingParams(temperature=temperature, max_tokens=n_new - 5, ignore_eos=True, seed=5 + i))
+                    stops.append(n_new - 5)
+                else:
+                    eos = o[min(3 + 4 * i, len(o) - 1)]
+                    params.append(SamplingParams(temperature=temperature, max_tokens=n_new, seed=5 + i, eos_token_ids=(eos,)))
+                    stops.append(o.index(eos) + 1)
+            outs = {}
+            for overlap in (False, True):
+                llm = LLM(folder, dtype=dtype, device=device, max_seq_len=160, page_size=16, overlap=overlap, **kw)
+                launched = []
+                if overlap:
+                    ahead = llm.scheduler._launch_ahead
+                    def counting(flight, ahead=ahead, launched=launched):
+                        got = ahead(flight)
+                        launched.append(got is not None)
+                        return got
+                    llm.scheduler._launch_ahead = counting
+                outs[overlap] = llm.generate(prompts, params)
+                llm.runner.cache.check()
+                assert llm.stats["free_pages"] == [kw["num_pages"]] * len(llm.runner.cache.groups)
+                assert not llm.scheduler.has_work()
+                steps_with_overlap += sum(launched)
+            if dtype == "float32":
+                assert outs[True] == outs[False], (kw, temperature)
+                for o, w, n in zip(outs[False], want, stops):
+                    assert o == w[:n], (kw, temperature)
+            else:
+                # In bfloat16 a logit may differ in its last place with the company in the batch, and the company
+                # differs (a request that has ended runs one step on, others have left earlier): every token is
+                # checked along its own path, and every request has stopped where its own rule says.
+                for res in outs.values():
+                    for i, (p, o, sp) in enumerate(zip(prompts, res, params)):
+                        check_tokens_along_their_path(folder, p, o, temperature, sp.seed, dtype)
+                        if sp.eos_token_ids and sp.eos_token_ids[0] in o:
+                            assert o.index(sp.eos_token_ids[0]) == len(o) - 1, (kw, temperature, i)
+                        else:
+                            assert len(o) == sp.max_tokens, (kw, temperature, i)
+    assert steps_with_overlap > 20, "hardly a step was enqueued early: the test does not test it"

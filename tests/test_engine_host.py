@@ -71,6 +71,10 @@ def test_temperature_generation_survives_recutting_and_preemption(fake_backend, 
     assert pre[0] == 0
 
 
+def test_the_next_step_enqueued_early_changes_no_token(fake_backend, folders):
+    scenarios.overlap_generation_case(folders("B"), "B", DEV, DT)
+
+
 def test_missing_extension_fails_loudly():
     from vt_transformer_b200 import ops
     ops.use_backend(None)

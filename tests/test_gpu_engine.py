@@ -58,6 +58,11 @@ def test_temperature_generation_survives_recutting_and_preemption(folders, dtype
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_the_next_step_enqueued_early_changes_no_token(folders, dtype):
+    scenarios.overlap_generation_case(folders("B"), "B", DEV, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_first_tokens_of_a_sequence(folders, dtype):
     """One token, two tokens, three: the first positions, where the cache is empty and a
     portion is shorter than any tile."""

@@ -57,6 +57,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--page-size", type=int, default=None, help="tokens in a page (default: the engine's, 64)")
     g.add_argument("--max-extend-tokens", type=int, default=8192, help="token budget of a step")
     g.add_argument("--chunk-size", type=int, default=None, help="longest portion of one prompt in a step")
+    g.add_argument("--overlap", action="store_true",
+                   help="enqueue the next decode step before the tokens of the one before are read")
     g.add_argument("--stats", action="store_true", help="print the scheduler's counters at the end")
 
     r = sub.add_parser("random-weights", help="write a model folder with seeded random weights")
@@ -79,7 +81,7 @@ def _generate(args) -> int:
     sizes = {} if args.page_size is None else {"page_size": args.page_size}
     llm = LLM(args.model, dtype=args.dtype, device=args.device, max_running_reqs=args.max_running_reqs,
               num_pages=args.num_pages, max_seq_len=args.max_seq_len,
-              max_extend_tokens=args.max_extend_tokens, chunk_size=args.chunk_size, **sizes)
+              max_extend_tokens=args.max_extend_tokens, chunk_size=args.chunk_size, overlap=args.overlap, **sizes)
     params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                             ignore_eos=args.ignore_eos, max_tokens=args.max_tokens, seed=args.seed)
 

@@ -143,10 +143,13 @@ def slices_of(entries: Sequence[StepEntry], cache) -> List[SeqSlice]:
     return seqs
 
 
-def build_context(entries: Sequence[StepEntry], cache, device, status=None) -> StepContext:
+def build_context(entries: Sequence[StepEntry], cache, device, status=None, carried=None) -> StepContext:
     """Packs the description of a step into one int32 buffer, copies it to the device in
     one transfer and returns views into it.  ``cache`` gives each row's cached length and
-    block-table rows; pages for the new tokens must have been allocated already."""
+    block-table rows; pages for the new tokens must have been allocated already.
+    ``carried``: an int32 tensor on the device whose element i is the token of entry i (every
+    entry then brings one token, whose id the host does not know yet: the step before sampled it
+    and may still be running); it is copied over the token ids on the device."""
     seqs = slices_of(entries, cache)
     T = sum(s.length for s in seqs)
     want_flat = [sl.offset + int(w) for e, sl in zip(entries, seqs) for w in e.want]
@@ -165,4 +168,8 @@ def build_context(entries: Sequence[StepEntry], cache, device, status=None) -> S
         host = np.empty(lay.total, dtype=np.int32)
         fill_host(host, lay, entries, seqs, want_flat, cache)
         buf = torch.from_numpy(host).to(dev)
+    if carried is not None:
+        if any(len(e.tokens) != 1 for e in entries) or carried.numel() < len(entries):
+            raise ValueError("carried tokens stand for one token of every entry")
+        buf[:len(entries)].copy_(carried[:len(entries)])
     return context_from(buf, lay, seqs, max((s.length for s in seqs), default=0), max_kv, status, want_inverse)

@@ -81,7 +81,7 @@ class DecodeGraph:
                 gc.enable()
         self.launches = runner.rt.ops.launches - launches_before
 
-    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def run(self, entries: Sequence[StepEntry], carried=None) -> torch.Tensor:
         cache = self.runner.cache
         seqs = [] if hasattr(cache, "book") else slices_of(entries, cache)     # the C++ side packs from its own lengths
         slot = self.turn
@@ -94,6 +94,8 @@ class DecodeGraph:
         if self.events[slot] is None:
             self.events[slot] = torch.cuda.Event()
         self.events[slot].record()
+        if carried is not None:                     # the ids that the step before sampled, still on the device
+            self.device_buf[:len(entries)].copy_(carried[:len(entries)])
         self.graph.replay()
         self.runner.rt.ops.launches += self.launches
         return self.logits[:len(entries)]

@@ -22,14 +22,25 @@ from .runner import ModelRunner
 from .scheduler import ReqResult, Scheduler, SchedulerConfig, StepResult
 
 
+class _InFlight:
+    """A step that has been enqueued: its sampled tokens on the device, the pinned memory they are copied to,
+    and the event after that copy."""
+    __slots__ = ("tokens", "host", "event", "n")
+
+    def __init__(self, tokens, host, event, n):
+        self.tokens, self.host, self.event, self.n = tokens, host, event, n
+
+
 class LLM:
     def __init__(self, model: str, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_running_reqs: int = 128, num_pages: Optional[int] = None, max_seq_len: int = 4096,
                  page_size: int = DEFAULT_PAGE_SIZE, max_extend_tokens: int = 8192, default_max_output: int = 1024,
-                 chunk_size: Optional[int] = None, runner: Optional[ModelRunner] = None):
+                 chunk_size: Optional[int] = None, runner: Optional[ModelRunner] = None, overlap: bool = False):
         """``model``: a folder with config.json and model.safetensors.  ``num_pages`` None
         sizes the pool for ``max_running_reqs`` requests of ``max_seq_len`` tokens, capped at
-        half a million tokens."""
+        half a million tokens.  ``overlap``: while all running requests decode, the next step is
+        enqueued before the tokens of the one before have been read (``Scheduler`` says how);
+        ``step()`` then reports a step's tokens one call later."""
         if runner is None:
             config = load_config(model)
             limit = getattr(config, "max_position_embeddings", None)
@@ -54,24 +65,50 @@ class LLM:
             eos = load_config(model).eos_token_id or () if model else ()
         except Exception:
             eos = ()
-        self.scheduler = Scheduler(cache, self.config, self._run_step, eos_token_ids=eos)
+        self.scheduler = Scheduler(cache, self.config, self._run_step, eos_token_ids=eos,
+                                   launch_step=self._launch_step, collect_step=self._collect_step, overlap=overlap)
+        self._landing = [None, None]     # two pinned buffers for the sampled tokens: one step may be read while the next runs
+        self._turn = 0
 
-    # the scheduler's hook: run the batch, sample one token for each request that wants one
-    def _run_step(self, entries, wanting) -> List[int]:
-        logits = self.runner.step(entries)
+    # The scheduler's hooks.  A step is enqueued (the batch, then one sampled token for each request that wants
+    # one, then their copy to pinned memory) and collected (wait for that copy); ``_run_step`` does both.
+    def _launch_step(self, entries, wanting, indices, before=None):
+        """``indices[i]``: which output of its request the token of ``wanting[i]`` is.  ``before``: the handle of
+        the step whose sampled tokens, in the same order, are this step's input tokens."""
+        logits = self.runner.step(entries, carried=before.tokens if before is not None else None)
         self.h2d_bytes_last_step = self.runner.last_h2d_bytes
         self.d2h_bytes_last_step = 0
         if not wanting:
-            return []
+            return _InFlight(None, None, None, 0)
         params = [r.params for r in wanting]
-        tokens = self.sampler.sample(logits, params, [len(r.output) for r in wanting])
+        tokens = self.sampler.sample(logits, params, list(indices))
         if not all(p.is_greedy for p in params):
             self.h2d_bytes_last_step += 16 * len(wanting)
         self.runner.stage_status()
-        host = tokens.tolist()          # waits for the step, and for the copy of the status word before it
+        n = len(wanting)
+        slot, self._turn = self._turn, self._turn ^ 1
+        if self._landing[slot] is None or self._landing[slot].numel() < n:
+            self._landing[slot] = torch.empty(max(n, self.runner.cache.max_requests), dtype=torch.int32,
+                                              pin_memory=tokens.is_cuda)
+        host = self._landing[slot]
+        host[:n].copy_(tokens, non_blocking=True)
+        event = None
+        if tokens.is_cuda:
+            event = torch.cuda.Event()
+            event.record()
+        self.d2h_bytes_last_step = 4 * n + 8
+        return _InFlight(tokens, host, event, n)
+
+    def _collect_step(self, flight) -> List[int]:
+        if flight.n == 0:
+            return []
+        if flight.event is not None:
+            flight.event.synchronize()      # the step, the copy of the status word and the copy of the tokens are done
         self.runner.check_status(staged=True)
-        self.d2h_bytes_last_step = 4 * len(host) + 8
-        return host
+        return flight.host[:flight.n].tolist()
+
+    def _run_step(self, entries, wanting) -> List[int]:
+        return self._collect_step(self._launch_step(entries, wanting, [len(r.output) for r in wanting]))
 
     # ---- requests one by one ---------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], sampling_params: Optional[SamplingParams] = None) -> int:

@@ -110,17 +110,21 @@ class ModelRunner:
         self.cache.release(row)
 
     # ---- the step ----------------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], carried: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs the entries as one batch and returns float32 logits [wanted, vocab] on the
         device, in the order of the entries and of their ``want``.  Raises ``OutOfPages``
-        (and changes nothing) if a group cannot cover the new tokens."""
+        (and changes nothing) if a group cannot cover the new tokens.
+
+        ``carried``: int32 token ids on the device, one for each entry in order, which stand in
+        for the entries' single tokens (the ids that the step before sampled, which the host has
+        not read yet: the step is enqueued behind it and reads them there)."""
         entries = [e for e in entries if len(e.tokens) > 0]
         vocab = self.model.spec.vocab
         if not entries:
             return torch.empty((0, vocab), dtype=torch.float32, device=self.rt.device)
         if (self.use_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries)
                 and all(len(e.want) == 0 or (len(e.want) == 1 and e.want[0] == 0) for e in entries)):
-            return self._graph_step(entries)
+            return self._graph_step(entries, carried)
         seen = set()
         for e in entries:
             if e.row in seen:
@@ -130,7 +134,7 @@ class ModelRunner:
                 if not 0 <= w < len(e.tokens):
                     raise ValueError(f"row {e.row}: wanted place {w} is outside its {len(e.tokens)} tokens")
         self.cache.extend([(e.row, self.cache.length(e.row) + len(e.tokens)) for e in entries])
-        ctx = build_context(entries, self.cache, self.rt.device, status=self.status)
+        ctx = build_context(entries, self.cache, self.rt.device, status=self.status, carried=carried)
         self.last_h2d_bytes = ctx.h2d_bytes
         logits = self.model.forward(ctx, self.cache.views(ctx.block_tables))
         if ctx.want_inverse is not None:
@@ -140,7 +144,7 @@ class ModelRunner:
         self.steps += 1
         return logits
 
-    def _graph_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def _graph_step(self, entries: Sequence[StepEntry], carried: Optional[torch.Tensor] = None) -> torch.Tensor:
         """A step of single tokens through a captured graph.  The logits lie in the graph's own
         buffer: they are valid until the next step."""
         from .graphs import DecodeGraph, batch_bucket, context_bucket
@@ -154,7 +158,7 @@ class ModelRunner:
         if graph is None:
             graph = DecodeGraph(self, *key)
             self._graphs[key] = graph
-        logits = graph.run(entries)
+        logits = graph.run(entries, carried)
         self.cache.book.commit_each(rows, 1)
         self.steps += 1
         self.last_h2d_bytes = graph.layout.total * 4

@@ -17,6 +17,15 @@ decided differently, because the reference leaves it open:
   with the same random numbers.  (The reference rolls a prompt batch back and otherwise
   stalls, vt_scheduler.cpp:386-402, and never evicts.)  The oldest request always goes on;
   a request that cannot fit the pool even alone is finished with reason "out_of_pages".
+
+With ``overlap`` (the reference's ``step_overlap``, vt_scheduler.cpp:148-226: it counts the tokens of the
+step in flight as cached, starts the next forward pass and takes the results of the one before at the next
+call) a step is enqueued and its tokens are read one call later.  While every running request decodes and
+none can be foreseen to finish (by its length), the next step is enqueued before the tokens of the step in
+flight have been read: its input tokens are that step's sampled tokens, which it finds on the device.  A
+request that then turns out to have ended (an end token) has run one token too far; that token is dropped
+when its step lands.  Everything else (prompts, admission, pre-emption, a foreseen end) happens with nothing
+in flight, as without overlap.
 """
 from __future__ import annotations
 
@@ -93,15 +102,31 @@ class StepResult:
     n_preempted: int = 0
 
 
+@dataclass
+class _Flight:
+    """A step that has been enqueued and whose tokens have not been read."""
+    plan: List[Tuple[Request, int]]
+    wanting: List[Request]
+    handle: object
+    n_preempted: int = 0
+
+
 class Scheduler:
     """``cache`` is the cache manager (pages and rows); ``run_step(entries)`` runs a batch and
     returns one sampled token for each entry that wants logits, in order (the engine binds it
     to ``ModelRunner.step`` plus the sampler; tests bind a fake)."""
 
-    def __init__(self, cache, config: SchedulerConfig, run_step, eos_token_ids: Sequence[int] = ()):
+    def __init__(self, cache, config: SchedulerConfig, run_step, eos_token_ids: Sequence[int] = (),
+                 launch_step=None, collect_step=None, overlap: bool = False):
+        """``launch_step(entries, wanting, indices, before) -> handle`` enqueues a step (``before``: the handle of
+        the step whose sampled tokens are this step's input tokens, or None) and ``collect_step(handle)`` waits
+        for it and returns its tokens; both are needed for ``overlap``."""
         self.cache = cache
         self.config = config
         self.run_step = run_step
+        self.launch_step, self.collect_step = launch_step, collect_step
+        self.overlap = bool(overlap) and launch_step is not None and collect_step is not None
+        self._flight: Optional[_Flight] = None
         self.eos = tuple(eos_token_ids)
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []
@@ -142,8 +167,12 @@ class Scheduler:
                 return True
         return False
 
+    def has_inflight(self) -> bool:
+        """A step has been enqueued whose tokens have not been read (vt_scheduler.hpp: ``has_inflight``)."""
+        return self._flight is not None
+
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self._flight is not None)
 
     def _finish(self, req: Request, reason: str) -> None:
         if req.row is not None:
@@ -207,6 +236,8 @@ class Scheduler:
         """One step: plan, run the batch, sample, finish and free."""
         if not self.has_work():
             return StepResult(False, [])
+        if self.overlap:
+            return self._step_overlap()
         plan, n_preempted = self.plan()
         if not plan:
             return StepResult(False, [], n_preempted=n_preempted)
@@ -227,8 +258,19 @@ class Scheduler:
             raise
         for req, n in plan:
             req.cached += n
+        results = self._take_tokens(wanting, tokens)
+        n_tok = sum(n for _, n in plan)
+        self.stats["steps"] += 1
+        self.stats["tokens"] += n_tok
+        return StepResult(True, results, n_tokens=n_tok, n_preempted=n_preempted)
+
+    def _take_tokens(self, wanting: List[Request], tokens) -> List[ReqResult]:
+        """Appends a step's sampled tokens to their requests and finishes those that have ended.  A request
+        that is no longer running (it ended or was aborted while the step was in flight) drops its token."""
         results = []
         for req, tok in zip(wanting, tokens):
+            if req.state != RUNNING:
+                continue
             tok = int(tok)
             req.output.append(tok)
             reason = None
@@ -243,7 +285,58 @@ class Scheduler:
                 self.running.remove(req)
                 self._finish(req, reason)
             results.append(ReqResult(req.uid, tok, reason is not None, reason))
-        n_tok = sum(n for _, n in plan)
+        return results
+
+    # ---- the step, with the next one enqueued before this one's tokens are read ---------------------------
+    def _step_overlap(self) -> StepResult:
+        flight = self._flight
+        self._flight = None
+        if flight is None:
+            plan, n_preempted = self.plan()
+            if not plan:
+                return StepResult(False, [], n_preempted=n_preempted)
+            entries, wanting = [], []
+            for req, n in plan:
+                last = (n == req.pending)
+                entries.append(StepEntry(req.row, req.token_slice(req.cached, req.cached + n), [n - 1] if last else []))
+                if last:
+                    wanting.append(req)
+            try:
+                handle = self.launch_step(entries, wanting, [len(r.output) for r in wanting], None)
+            except OutOfPages:
+                if len(self.running) > 1:
+                    self._preempt(max(self.running, key=lambda r: r.arrival))
+                    return StepResult(False, [], n_preempted=n_preempted + 1)
+                raise
+            for req, n in plan:
+                req.cached += n             # as the reference does: counted as cached when the step is enqueued
+            flight = _Flight(plan, wanting, handle, n_preempted)
+        ahead = self._launch_ahead(flight)
+        results = self._take_tokens(flight.wanting, self.collect_step(flight.handle))
+        self._flight = ahead
+        n_tok = sum(n for _, n in flight.plan)
         self.stats["steps"] += 1
         self.stats["tokens"] += n_tok
-        return StepResult(True, results, n_tokens=n_tok, n_preempted=n_preempted)
+        return StepResult(True, results, n_tokens=n_tok, n_preempted=flight.n_preempted)
+
+    def _launch_ahead(self, flight: "_Flight") -> Optional["_Flight"]:
+        """Enqueues the step after ``flight`` if that needs no decision: nobody waits, the running requests are
+        those that get a token from ``flight`` (each then has that one token to run), none of them ends by
+        its length with that token, and the pages for one more token each are there."""
+        wanting = flight.wanting
+        if self.waiting or not wanting or len(flight.plan) != len(wanting) or len(self.running) != len(wanting):
+            return None
+        running = {id(r) for r in self.running}
+        for r in wanting:
+            if r.state != RUNNING or id(r) not in running:
+                return None
+            if len(r.output) + 1 >= r.params.max_tokens or r.n_tokens + 1 >= self.config.max_seq_len:
+                return None
+        entries = [StepEntry(r.row, [0], [0]) for r in wanting]      # the ids are on the device: flight's tokens
+        try:
+            handle = self.launch_step(entries, wanting, [len(r.output) + 1 for r in wanting], flight.handle)
+        except OutOfPages:
+            return None
+        for r in wanting:
+            r.cached += 1
+        return _Flight([(r, 1) for r in wanting], list(wanting), handle, 0)
