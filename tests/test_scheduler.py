@@ -179,3 +179,121 @@ def test_random_load_every_request_gets_its_own_tokens(seed):
     for uid, out in want.items():
         assert s.finished[uid].output == out, (uid, s.finished[uid].finish_reason)
     assert cache.free_pages() == [cache.groups[0].pool.num_pages]
+
+
+# ---- overlap: the next step enqueued before the tokens of the one in flight are read --------------------------
+
+class FakeAsyncModel(FakeModel):
+    """The same fake behind the two hooks of the overlap mode.  A step that is enqueued behind another takes its
+    input tokens from that step's tokens, as the device does; the host's entries hold placeholders then."""
+
+    def __init__(self, cache):
+        super().__init__(cache)
+        self.early = 0
+        self.open_handles = 0
+
+    def launch(self, entries, wanting, indices, before=None):
+        if before is not None:
+            assert len(entries) == len(before["tokens"]) and all(len(e.tokens) == 1 for e in entries)
+            assert [r.uid for r in wanting] == before["uids"], "carried tokens must come in the order of the entries"
+            for e, tok in zip(entries, before["tokens"]):
+                e.tokens = [tok]
+            self.early += 1
+        self.cache.extend([(e.row, self.cache.length(e.row) + len(e.tokens)) for e in entries])
+        self.batches.append([(e.row, self.cache.length(e.row), len(e.tokens), list(e.want)) for e in entries])
+        for e in entries:
+            if self.cache.length(e.row) == 0:
+                self.history[e.row] = []
+            self.history.setdefault(e.row, [])
+            self.history[e.row] += list(e.tokens)
+            self.cache.commit(e.row, self.cache.length(e.row) + len(e.tokens))
+        out = []
+        for req, index in zip(wanting, indices):
+            seen = self.history[req.row]
+            known = req.prompt + req.output
+            assert seen[:len(known)] == known and len(seen) == len(req.prompt) + index
+            out.append((sum(seen) * 31 + len(seen)) % 97 + 3)
+        self.open_handles += 1
+        assert self.open_handles <= 2, "more than one step ahead"
+        return {"tokens": out, "uids": [r.uid for r in wanting]}
+
+    def collect(self, handle):
+        self.open_handles -= 1
+        return handle["tokens"]
+
+
+def make_overlap(num_pages=16, max_running=4, budget=64, chunk=None, max_seq_len=256, eos=()):
+    cache = CacheManager({0: KVCacheSpec(1, 16)}, page_size=16, num_pages=num_pages, max_requests=max_running,
+                         max_seq_len=max_seq_len, dtype=torch.float32, device="cpu", allocate=False)
+    cfg = SchedulerConfig(max_running_reqs=max_running, num_pages=num_pages, max_seq_len=max_seq_len, page_size=16,
+                          max_extend_tokens=budget, chunk_size=chunk)
+    model = FakeAsyncModel(cache)
+    s = Scheduler(cache, cfg, None, eos_token_ids=eos, launch_step=model.launch, collect_step=model.collect, overlap=True)
+    return s, model, cache
+
+
+def test_overlap_reports_every_token_once_and_stops_where_the_plain_loop_stops():
+    s, model, cache = make_overlap(num_pages=24)
+    # b's end token is the 7th it generates: it is found when that step lands, with the next step already enqueued
+    pb = [2] * 20
+    eos = expected_output(pb, 7)[6]
+    stop_b = expected_output(pb, 50).index(eos) + 1
+    a = s.add_request([1] * 20, SamplingParams(max_tokens=30, ignore_eos=True))
+    b = s.add_request(pb, SamplingParams(max_tokens=50, eos_token_ids=(eos,)))
+    c = s.add_request([3] * 9, SamplingParams(max_tokens=12, ignore_eos=True))
+    results = run_all(s)
+    assert s.finished[a].output == expected_output([1] * 20, 30) and s.finished[a].finish_reason == "length"
+    assert s.finished[b].output == expected_output(pb, stop_b) and s.finished[b].finish_reason == "stop"
+    assert s.finished[c].output == expected_output([3] * 9, 12)
+    for uid in (a, b, c):
+        assert [r.next_token for r in results[uid]] == s.finished[uid].output
+        assert [r.finished for r in results[uid]] == [False] * (len(results[uid]) - 1) + [True]
+    assert model.early > 20 and model.open_handles == 0 and not s.has_inflight()
+    cache.check()
+    assert cache.free_pages() == [24]
+
+
+def test_overlap_abort_while_a_step_is_in_flight():
+    s, model, cache = make_overlap()
+    a = s.add_request([1] * 20, SamplingParams(max_tokens=50, ignore_eos=True))
+    b = s.add_request([2] * 20, SamplingParams(max_tokens=50, ignore_eos=True))
+    for _ in range(4):
+        s.step()
+    assert s.has_inflight()
+    n = len(s.running[0].output)
+    assert s.abort(a)
+    assert s.finished[a].finish_reason == "abort" and len(s.finished[a].output) == n
+    res = s.step()                                      # lands the step that still held a: its token is dropped
+    assert [r.uid for r in res.results] == [b] and len(s.finished[a].output) == n
+    run_all(s)
+    assert s.finished[b].output == expected_output([2] * 20, 50)
+    cache.check()
+    assert cache.free_pages() == [16] and model.open_handles == 0
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_overlap_random_load_every_request_gets_its_own_tokens(seed):
+    rng = random.Random(100 + seed)
+    s, model, cache = make_overlap(num_pages=rng.choice([6, 9, 14]), max_running=rng.choice([2, 3, 4]),
+                                   budget=rng.choice([8, 24, 64]), chunk=rng.choice([None, 4, 16]))
+    want = {}
+    pending = [[rng.randrange(1, 90) for _ in range(rng.choice([1, 3, 17, 33, 50]))] for _ in range(10)]
+    steps = 0
+    while pending or s.has_work():
+        if pending and rng.random() < 0.25:
+            p = pending.pop()
+            n = rng.choice([1, 5, 12, 30])
+            full = expected_output(p, n)
+            if rng.random() < 0.5:
+                eos = full[rng.randrange(len(full))]
+                want[s.add_request(p, SamplingParams(max_tokens=n, eos_token_ids=(eos,)))] = full[:full.index(eos) + 1]
+            else:
+                want[s.add_request(p, SamplingParams(max_tokens=n, ignore_eos=True))] = full
+        if s.has_work():
+            s.step()
+            cache.check()
+        steps += 1
+        assert steps < 5000
+    for uid, out in want.items():
+        assert s.finished[uid].output == out, (uid, s.finished[uid].finish_reason)
+    assert cache.free_pages() == [cache.groups[0].pool.num_pages] and model.open_handles == 0
