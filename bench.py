@@ -23,7 +23,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# layer sizes of Qwen2-7B (BASELINE.json configs[2]); weights are random, N(0, 0.02)
+# layer sizes of Qwen2-7B (v1/models/qwen2-7b/inference_fp16.dag:1-14 of the reference); weights are random, N(0, 0.02)
 MODEL = dict(architectures=["Qwen2ForCausalLM"], vocab_size=152064, hidden_size=3584, intermediate_size=18944,
              num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, head_dim=128, rms_norm_eps=1e-6,
              rope_theta=1000000.0, max_position_embeddings=32768, tie_word_embeddings=False,
