@@ -129,9 +129,12 @@ def main() -> int:
     dev = "cuda:0"
     max_batch = max(64, args.batch)
     new_tokens = warmup + args.steps + 8
+    # end to end the requests' prompts run 2,048 tokens a step beside the decoding of those that are through: the
+    # first request decodes that many steps more than the last, and none may end inside the timed steps
+    e2e_tokens = new_tokens + (args.batch * args.prompt_len + 2047) // 2048 + 8
     prompt_len = args.prompt_len
-    context = max(CONTEXT, prompt_len + max(new_tokens, 256) + PAGE)
-    per_req = prompt_len + max(new_tokens, 256) + PAGE
+    context = max(CONTEXT, prompt_len + max(e2e_tokens, 256) + PAGE)
+    per_req = prompt_len + max(e2e_tokens, 256) + PAGE
     pool_tokens = max_batch * per_req + PREFILL_TOKENS
     t0 = time.time()
     runner = ModelRunner.from_random(cfg, seed=0, sigma=0.02, dtype="bfloat16", device=dev, page_size=PAGE,
@@ -246,7 +249,7 @@ def main() -> int:
         return 0
     # end to end: the Python entry point, token ids in from the host and out to the host every step
     llm = LLM(None, runner=runner, max_extend_tokens=2048, overlap=not args.no_overlap)
-    params = SamplingParams(temperature=0.0, max_tokens=new_tokens, ignore_eos=True)
+    params = SamplingParams(temperature=0.0, max_tokens=e2e_tokens, ignore_eos=True)
     for _ in range(args.batch):
         llm.add_request(random_tokens(prompt_len), params)
     while any(len(r.output) == 0 for r in llm.scheduler.running) or llm.scheduler.waiting:
@@ -260,6 +263,8 @@ def main() -> int:
         produced += len(llm.step().results)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t1
+    if produced != args.batch * args.steps:
+        raise RuntimeError(f"end to end: {produced} tokens from {args.steps} steps of {args.batch} requests: a request ended early")
     h2d = llm.h2d_bytes_last_step
     d2h = llm.d2h_bytes_last_step
     for req in list(llm.scheduler.running):
