@@ -34,7 +34,7 @@ def replay_family(folder, name, family, device, dtype):
     pages = helpers.tokens_needed(trace, round_to=16) // 16
     runner = runner_for(folder, device, dtype, num_pages=pages)
     got = helpers.run_trace_inproc(runner, trace)
-    worst = helpers.compare_trace(folder, prompts, trace, got, helpers.TOL[dtype])
+    worst = helpers.compare_trace(folder, prompts, trace, got, helpers.tol(dtype, name))
     assert runner.cache.free_pages() == [g.pool.num_pages for g in runner.cache.groups]
     return worst
 
@@ -78,9 +78,9 @@ def run_order_case(tmp, device, dtype):
             a += k
         runner.check_status()
         err = float((torch.cat(got).double() - ref).abs().max())
-        assert err <= helpers.TOL[dtype], err
+        assert err <= helpers.tol(dtype, ref=ref), err
         plain_default = plain.forward(cfg, w, ids)
-        assert float((ref - plain_default).abs().max()) > 5 * helpers.TOL[dtype]    # the order matters
+        assert float((ref - plain_default).abs().max()) > 5 * helpers.tol(dtype, ref=ref)    # the order matters
         return err
     finally:
         unregister_architecture("OrderTestLM")
@@ -194,8 +194,9 @@ def toy_state_case(tmp, device, dtype):
             runner.check_status()
             for i, ids in enumerate((first, second)):
                 assert done[i] == len(ids)
-                err = float((torch.cat(got[i]).double() - reference(ids)).abs().max())
-                assert err <= helpers.TOL[dtype], (i, err)
+                ref = reference(ids)
+                err = float((torch.cat(got[i]).double() - ref).abs().max())
+                assert err <= helpers.tol(dtype, ref=ref), (i, err)
                 worst = max(worst, err)
             for r in rows:
                 runner.release(r)
@@ -337,7 +338,9 @@ def toy_routed_case(tmp, device, dtype):
             runner.check_status()
             runner.release(row)
             err = float((torch.cat(got).double() - ref).abs().max())
-            assert err <= 3 * helpers.TOL[dtype] * max(1.0, float(ref.abs().max())), (sizes, err)
+            # the toy rounds its experts' intermediate results and the weighted output to bfloat16 itself, at weights
+            # of sigma 0.3: measured 0.57 at a spread of the logits of 2.5 (32-bit: 3.2e-5)
+            assert err <= helpers.tol(dtype, ref=ref) * (1.0 if dtype == "float32" else 3.0), (sizes, err)
             worst = max(worst, err)
         return worst
     finally:
@@ -377,7 +380,7 @@ def greedy_generation_case(folder, name, device, dtype, n_new=16):
             ref = helpers.plain_logits(folder, list(p) + o)
             for i, tok in enumerate(o):
                 row = ref[len(p) - 1 + i]
-                assert float(row.max() - row[tok]) <= 2 * helpers.TOL[dtype], (len(p), i, tok)
+                assert float(row.max() - row[tok]) <= 2 * helpers.tol(dtype, name), (len(p), i, tok)
     llm.runner.cache.check()
     assert llm.stats["free_pages"] == [24] * len(llm.runner.cache.groups)
     return outs
@@ -409,7 +412,7 @@ def temperature_generation_case(folder, name, device, dtype, n_new=24):
         for i, (p, o) in enumerate(zip(prompts, results[0])):
             assert o == plain_generate(folder, p, n_new, temperature=0.7, seed=77 + i), i
     else:
-        slack = 4 * helpers.TOL[dtype]
+        slack = 4 * helpers.tol(dtype, name)
         for res in results:
             for i, (p, o) in enumerate(zip(prompts, res)):
                 ref = helpers.plain_logits(folder, list(p) + o)
@@ -425,7 +428,7 @@ def temperature_generation_case(folder, name, device, dtype, n_new=24):
 # ----------------------------------------------------------------------------- the next step enqueued early
 
 
-def check_tokens_along_their_path(folder, prompt, out, temperature, seed, dtype):
+def check_tokens_along_their_path(folder, prompt, out, temperature, seed, dtype, name):
     """Every generated token against the plain implementation run over the engine's own tokens: greedy, its
     plain logit lies within the tolerance of the largest; with a temperature, the draw's random number falls
     into the token's interval of the plain cumulative distribution, give or take the tolerance."""
@@ -434,10 +437,10 @@ def check_tokens_along_their_path(folder, prompt, out, temperature, seed, dtype)
     for j, tok in enumerate(out):
         row = ref[len(prompt) - 1 + j]
         if temperature <= 0.0:
-            assert float(row.max() - row[tok]) <= 2 * helpers.TOL[dtype], (len(prompt), j, tok)
+            assert float(row.max() - row[tok]) <= 2 * helpers.tol(dtype, name), (len(prompt), j, tok)
         else:
             c = torch.cumsum(plain.kept_probabilities(row, temperature), 0)
-            u, slack = uniform(seed, j), 4 * helpers.TOL[dtype]
+            u, slack = uniform(seed, j), 4 * helpers.tol(dtype, name)
             lo = float(c[tok - 1]) if tok > 0 else 0.0
             assert lo - slack <= u <= float(c[tok]) + slack, (len(prompt), j, tok, u, lo, float(c[tok]))
 
@@ -494,9 +497,97 @@ def overlap_generation_case(folder, name, device, dtype, n_new=24):
                 # checked along its own path, and every request has stopped where its own rule says.
                 for res in outs.values():
                     for i, (p, o, sp) in enumerate(zip(prompts, res, params)):
-                        check_tokens_along_their_path(folder, p, o, temperature, sp.seed, dtype)
+                        check_tokens_along_their_path(folder, p, o, temperature, sp.seed, dtype, name)
                         if sp.eos_token_ids and sp.eos_token_ids[0] in o:
                             assert o.index(sp.eos_token_ids[0]) == len(o) - 1, (kw, temperature, i)
                         else:
                             assert len(o) == sp.max_tokens, (kw, temperature, i)
     assert steps_with_overlap > 20, "hardly a step was enqueued early: the test does not test it"
+
+
+# ----------------------------------------------------------------------------- real layer widths, wide steps
+
+_models = {}
+
+
+def shared_runner(folder, device, dtype, num_pages, max_requests=4, max_seq_len=None, page_size=16):
+    """A runner over a model that is loaded once for each (folder, dtype) and shared: the model folders of real
+    widths hold gigabytes.  The cache manager, and with it the pool, the block tables and the captured graphs,
+    is the runner's own."""
+    from vt_transformer_b200.cache.manager import CacheManager
+    from vt_transformer_b200.engine.runner import ModelRunner
+    key = (folder, str(device), dtype)
+    if key not in _models:
+        base = ModelRunner.from_folder(folder, dtype=dtype, device=device, page_size=16, num_pages=1, max_requests=1,
+                                       max_seq_len=16)
+        _models[key] = (base.model, base.rt)
+    model, rt = _models[key]
+    if max_seq_len is None:
+        max_seq_len = model.spec.max_positions
+    cache = CacheManager(model.cache_slots(), page_size=page_size, num_pages=num_pages, max_requests=max_requests,
+                         max_seq_len=max_seq_len, dtype=rt.dtype, device=rt.device)
+    return ModelRunner(model, cache, rt)
+
+
+def forget_shared_models():
+    _models.clear()
+
+
+def replay_family_shared(folder, name, family, device, dtype, n_prompts=4, sizes=None, page_size=16):
+    """``replay_family`` for a model of real widths: the first ``n_prompts`` requests, the model shared."""
+    prompts = helpers.prompts_for(name)[:n_prompts]
+    make = {"whole": helpers.trace_whole, "tail": helpers.trace_tail,
+            "portions": (lambda p: helpers.trace_portions(p, sizes=sizes)) if sizes else helpers.trace_portions,
+            "mixed": lambda p: helpers.trace_mixed(p, max_live=4, seed=3)}[family]
+    trace = make(prompts)
+    pages = helpers.tokens_needed(trace, round_to=page_size) // page_size
+    runner = shared_runner(folder, device, dtype, num_pages=pages, page_size=page_size)
+    got = helpers.run_trace_inproc(runner, trace)
+    worst = helpers.compare_trace(folder, prompts, trace, got, helpers.tol(dtype, name))
+    assert runner.cache.free_pages() == [g.pool.num_pages for g in runner.cache.groups]
+    return worst
+
+
+def wide_decode_case(folder, name, device, dtype, sequences, decode_steps, runner=None, page_size=16, budget=512,
+                     bound=None):
+    """Decode steps of many live requests.  ``sequences``: token lists of different lengths.  Each request's
+    tokens but the last ``decode_steps`` run as prompt portions (several requests a step, up to ``budget`` tokens);
+    then every request brings one token a step, all in one step, and every row of logits is compared with the
+    plain implementation.  Returns (worst difference, the graph keys (batch bucket, context bucket) that ran)."""
+    from vt_transformer_b200.engine.batch import StepEntry
+    n = len(sequences)
+    if runner is None:
+        pages = sum(-(-len(s) // page_size) for s in sequences)
+        runner = shared_runner(folder, device, dtype, num_pages=pages, max_requests=n, page_size=page_size)
+    rows = [runner.admit() for _ in range(n)]
+    done = [0] * n
+    heads = [max(1, len(s) - decode_steps) for s in sequences]
+    while any(d < h for d, h in zip(done, heads)):
+        entries, left = [], budget
+        for i in range(n):
+            if done[i] < heads[i] and left > 0:
+                k = min(heads[i] - done[i], left)
+                entries.append(StepEntry(rows[i], sequences[i][done[i]:done[i] + k], []))
+                done[i] += k
+                left -= k
+        runner.step(entries)
+    worst, bound = 0.0, (helpers.tol(dtype, name) if bound is None else bound)
+    for step in range(decode_steps):
+        live = [i for i in range(n) if done[i] < len(sequences[i])]
+        if not live:
+            break
+        logits = runner.step([StepEntry(rows[i], [sequences[i][done[i]]], [0]) for i in live]).double().cpu()
+        runner.check_status()
+        for j, i in enumerate(live):
+            ref = helpers.plain_logits(folder, sequences[i])[done[i]]
+            d = float((logits[j] - ref).abs().max())
+            assert d == d and d <= bound, (f"decode step {step} of {len(live)} requests: request {i} (length "
+                                          f"{len(sequences[i])}) at position {done[i]}: |dlogit| {d:.3e} > {bound:.1e}")
+            worst = max(worst, d)
+            done[i] += 1
+    keys = sorted(runner._graphs)
+    for r in rows:
+        runner.release(r)
+    runner.cache.check()
+    assert runner.cache.free_pages() == [g.pool.num_pages for g in runner.cache.groups]
+    return worst, keys

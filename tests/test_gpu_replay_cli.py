@@ -23,7 +23,7 @@ def test_trace_run_replays_every_family(folders, tmp_path, name, dtype):
     # the engine's own page size (64) for A and D, smaller pages for B and C
     extra = {"B": ("--page-size", "16"), "C": ("--page-size", "32")}.get(name, ())
     got = helpers.run_trace_cli(folder, trace, dtype, str(tmp_path / "out"), helpers.tokens_needed(trace, 64), extra)
-    helpers.compare_trace(folder, prompts, trace, got, helpers.TOL[dtype])
+    helpers.compare_trace(folder, prompts, trace, got, helpers.tol(dtype, name))
 
 
 def test_trace_run_skips_files_for_steps_that_want_nothing(folders, tmp_path):
@@ -35,5 +35,5 @@ def test_trace_run_skips_files_for_steps_that_want_nothing(folders, tmp_path):
                    {"step": 1, "entries": [{"id": "a", "tokens": prompts[1][9:], "want": [7]}], "end": ["a"]}]
     trace.expect = {1: [(1, 16)]}
     got = helpers.run_trace_cli(folder, trace, "float32", str(tmp_path / "o"), 64)
-    helpers.compare_trace(folder, prompts, trace, got, helpers.TOL["float32"])
+    helpers.compare_trace(folder, prompts, trace, got, helpers.tol("float32", "A"))
     assert sorted(os.listdir(tmp_path / "o")) == ["1.f32"]
