@@ -83,13 +83,141 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def reference_arm():
-    # viitrix/vt-transformer has no Python package at its root (no setup.py / pyproject.toml beside its
-    # C++ trees), so `pip install <checkout>` has nothing to install; its engine is a C++ program that
-    # needs cuDNN, a Rust tokenizer library and a per-tensor weight dump made with network access.
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "vt-transformer is a C++ program without a Python package to install offline; it needs cuDNN, "
-                      "a Rust tokenizer library and a weight dump that cannot be made here"}))
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+def write_reference_weights(folder, model):
+    """Random fp16 files with the names and sizes that v1/models/qwen2-7b/inference_fp16.dag:87-142 loads."""
+    import torch
+    V, H, I, L = model["vocab_size"], model["hidden_size"], model["intermediate_size"], model["num_hidden_layers"]
+    KV = model["num_key_value_heads"] * model["head_dim"]
+    g = torch.Generator(device="cuda").manual_seed(0)
+
+    def put(name, shape, around_one=False):
+        t = torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * 0.02
+        if around_one:
+            t += 1.0
+        t.half().cpu().numpy().tofile(os.path.join(folder, name + ".fp16"))
+
+    put("wte", (V, H))
+    put("ln_f", (H,), True)
+    put("lm_head", (V, H))
+    for i in range(L):
+        p = f"h_{i}."
+        put(p + "ln_1.weight", (H,), True)
+        put(p + "ln_2.weight", (H,), True)
+        for proj, rows in (("query", H), ("key", KV), ("value", KV)):
+            put(p + f"attn.{proj}.weight", (rows, H))
+            put(p + f"attn.{proj}.bias", (rows,))
+        put(p + "attn.o_proj.weight", (H, H))
+        put(p + "mlp.w1.weight", (I, H))
+        put(p + "mlp.w2.weight", (I, H))
+        put(p + "mlp.o_proj.weight", (H, I))
+
+
+def reference_arm(args) -> int:
+    """The unmodified vt-transformer v1 engine (its tensor library, CUDA kernels, cuBLASLt and cuDNN calls and its graph
+    v1/models/qwen2-7b/inference_fp16.dag), built by baseline/build_reference.sh and driven by baseline/ref_driver.cpp
+    as v1/models/qwen2-7b/chat.cpp drives it: the same model sizes, random fp16 weights, 1,024-token prompts, a step
+    being one call of its `gpu_main` for the whole batch.  Its step takes the whole token lists from the host and
+    gives the sampled ids back to the host, so its figure is an end-to-end one.  MAX_BATCH is set by a second graph
+    file, as chat.cpp's command line allows; batch 64 does not fit (its activation buffer for 64 x 4,096 tokens
+    alone is 182 GB)."""
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+
+    if args.gpus != 1:
+        return unavailable("vt-transformer's v1 engine runs this model on one GPU")
+    driver = os.path.join(REF_DIR, "ref_driver")
+    dag = os.path.join(REF_DIR, "src", "models", "qwen2-7b", "inference_fp16.dag")
+    if not os.path.isfile(driver) or not os.path.isfile(dag):
+        if os.path.isdir("/root/reference/v1"):
+            res = subprocess.run(["bash", os.path.join(ROOT, "baseline", "build_reference.sh")], capture_output=True, text=True)
+            if res.returncode != 0:
+                return unavailable("baseline/build_reference.sh failed: " + (res.stderr.strip().splitlines() or ["no message"])[-1][:200])
+        else:
+            return unavailable("baseline/_ref/ref_driver is not built and there is no checkout to build it from "
+                               "(baseline/build_reference.sh <checkout>)")
+    import shutil
+    import tempfile
+    import torch
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device")
+    pk = peaks()
+    warmup = max(3, args.warmup)
+    steps = min(args.steps, 3000 - warmup)               # its cache holds 4,096 tokens a sequence
+    root = tempfile.mkdtemp(prefix="vt_ref_", dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
+    try:
+        os.makedirs(os.path.join(root, "weights"))
+        t0 = time.time()
+        write_reference_weights(os.path.join(root, "weights"), MODEL)
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        build_s = time.time() - t0
+
+        def run(batch, k, prefill_runs):
+            extra = []
+            if batch > 1:
+                with open(os.path.join(root, f"batch{batch}.dag"), "w") as f:
+                    f.write(f'{batch} "MAX_BATCH" !\n')
+                extra = ["--dag", os.path.join(root, f"batch{batch}.dag")]
+            cmd = [driver, "--dag", dag, *extra, "--batch", str(batch), "--prompt-len", str(args.prompt_len), "--steps", str(k),
+                   "--warmup", str(warmup), "--prefill", str(PREFILL_TOKENS if prefill_runs else 0), "--prefill-runs", str(prefill_runs)]
+            res = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=1500)
+            lines = [l for l in res.stdout.splitlines() if l.startswith("{")]
+            if res.returncode != 0 or not lines:
+                raise RuntimeError(f"ref_driver ended with {res.returncode}: {(res.stderr.strip().splitlines() or ['no message'])[-1][:300]}")
+            return json.loads(lines[-1])
+
+        clocks = ClockSampler()
+        clocks.start()
+        try:
+            main = run(args.batch, steps, 3)
+            info = clocks.stop()
+            one = run(1, min(steps, 64), 0) if args.batch != 1 and not args.skip_points else None
+        except (RuntimeError, subprocess.TimeoutExpired) as e:
+            clocks.stop()
+            return unavailable(str(e)[:400])
+    finally:
+        shutil.rmtree(root, ignore_errors=True)
+    cfg = MODEL
+    T, H, I, L = PREFILL_TOKENS, cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    q_dim, kv_dim = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    flops = L * (2 * T * H * (q_dim + 2 * kv_dim) + 2 * T * q_dim * H + 6 * T * H * I
+                 + 4 * (T * (T + 1) // 2) * cfg["head_dim"] * cfg["num_attention_heads"]) + 2 * H * cfg["vocab_size"]
+    pm = main["prefill_ms"]
+    ctx_mean = args.prompt_len + warmup + (steps - 1) / 2.0 + 1
+    weight_bytes = 2 * (L * (H * (q_dim + 2 * kv_dim) + q_dim + 2 * kv_dim + q_dim * H + 3 * H * I + 2 * H) + H
+                        + cfg["vocab_size"] * H + args.batch * H)
+    step_bytes = weight_bytes + 2 * 2 * kv_dim * L * ctx_mean * args.batch
+    achieved = step_bytes / (main["decode_ms_per_step"] / 1e3) / 1e9
+    line = {
+        "metric": f"decode tok/s at batch {args.batch} (Qwen2-7B layer sizes, random weights, {args.prompt_len:,}-token prompts)",
+        "value": round(main["decode_tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(main["decode_ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp16", "data": "synthetic", "impl": "reference",
+        "config": {"model": "Qwen2-7B sizes, random N(0,0.02)", "layers": L, "layers_full": L, "hidden": H,
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": I, "vocab": cfg["vocab_size"], "global_batch": args.batch, "seq_len": 4096,
+                   "prompt_len": args.prompt_len, "mean_context": round(ctx_mean, 1), "parallelism": "1 GPU",
+                   "l2": "inputs larger than L2 (every step reads all weights)", "peaks": pk["source"],
+                   "timing": "wall clock around whole steps, device idle on both sides",
+                   "engine": "vt-transformer v1, inference_fp16.dag, unmodified, MAX_BATCH from a second graph file"},
+        "e2e": {"value": round(main["decode_tok_s"], 1), "unit": "tok/s",
+                "h2d_bytes_per_step": int(2 * 4 * args.batch * ctx_mean), "d2h_bytes_per_step": 4 * args.batch,
+                "note": "the engine's step takes the whole token lists and masks from the host and returns the sampled ids"},
+        "clocks": {"sm_mhz": info.get("sm_mhz"), "sm_max_mhz": info.get("sm_max_mhz"), "reasons": info.get("reasons", []),
+                   "note": "sampled over the whole run of the engine, its loading of the weights included"},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
+        "prefill": {"value": round(T / (pm / 1e3), 1), "tokens": T, "ms": round(pm, 3),
+                    "frac": round(flops / (pm / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(flops / pm / 1e9, 1),
+                    "ms_all": main["prefill_ms_all"]},
+        "points": {"decode_b1": round(one["decode_tok_s"], 1)} if one else {},
+        "build_s": round(build_s, 1),
+    }
+    print(json.dumps(line))
     return 0
 
 
@@ -109,7 +237,7 @@ def main() -> int:
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prefill only (for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -128,3 +128,97 @@ def test_samplers():
     # the counter random numbers are uniform and differ by request and index
     u = [plain.uniform_from_counter(7, r, i) for r in range(20) for i in range(50)]
     assert 0.45 < float(np.mean(u)) < 0.55 and len(set(u)) > 990 and all(0 <= x < 1 for x in u)
+
+
+# ----------------------------------------------------------------------------- the reference's own kernels
+# tests/golden/reference_kernels.npz holds inputs and outputs of vt-transformer's CUDA kernels, compiled unchanged
+# and run on a B200 (tests/golden/make_kernel_golden.py).  They are float kernels: the plain functions run in
+# float64 and must agree to float rounding.
+
+
+def _kernels():
+    return np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_kernels.npz"))
+
+
+def test_rms_norm_equals_the_reference_kernel():
+    """v1/tensortype/cuda_kernels/rmsnorm.cu:10-49: out = w * x * rsqrt(mean(x^2) + eps), and norm2 is that rsqrt."""
+    g = _kernels()
+    for n in range(2):
+        x, w = torch.from_numpy(g[f"rms{n}_x"]).double(), torch.from_numpy(g[f"rms{n}_w"]).double()
+        eps = float(g[f"rms{n}_eps"])
+        got = plain.rms_norm(x, w, eps)
+        want = torch.from_numpy(g[f"rms{n}_out"]).double()
+        assert float((got - want).abs().max()) <= 2e-6 * float(want.abs().max())
+        r = torch.rsqrt((x * x).mean(dim=-1) + eps)
+        assert float((r - torch.from_numpy(g[f"rms{n}_norm2"]).double()).abs().max()) <= 1e-6
+        # the weight multiplies as it is: with 1 + w the result would differ by the size of the result itself
+        assert float((plain.rms_norm(x, 1.0 + w, eps) - want).abs().max()) > 0.5
+
+
+def test_rotation_equals_the_reference_kernel():
+    """v1/tensortype/cuda_kernels/rotary_embed.cu:9-30 with the table of fill_rotary_cache: pairs (i, i + d/2), the
+    row at index l of sequence b rotated by position pos[b] + l."""
+    g = _kernels()
+    x, want = torch.from_numpy(g["rot_x"]).double(), torch.from_numpy(g["rot_out"]).double()
+    table, pos = g["rot_table"], g["rot_pos"]
+    bs, length, hnum, dims = x.shape
+    cos, sin = plain.rotation_table(table.shape[0], dims, 1000000.0)          # the table's case: 24 positions, base 1e6
+    assert np.abs(cos.float().numpy() - table[:, :dims // 2, 0]).max() <= 1e-7
+    for b in range(bs):
+        got = plain.rotate(x[b], range(int(pos[b]), int(pos[b]) + length), cos, sin)
+        assert float((got - want[b]).abs().max()) <= 5e-6, b
+    # another pairing (neighbours 2i, 2i + 1) is another function
+    a, c = x[1, :, :, 0::2], x[1, :, :, 1::2]
+    p = torch.arange(int(pos[1]), int(pos[1]) + length)
+    co, si = cos[p][:, None, :], sin[p][:, None, :]
+    other = torch.stack([a * co - c * si, c * co + a * si], dim=-1).reshape(length, hnum, dims)
+    assert float((other - want[1]).abs().max()) > 0.1
+
+
+def test_the_activation_of_swiglu_equals_the_reference_kernel():
+    """v1/tensortype/cuda_kernels/silu_product.cu:9-18: out = act / (1 + exp(-act)) * in, the activation on the first
+    argument, which the graph gives the product with w1, the gate (inference_fp16.dag:333-335)."""
+    g = _kernels()
+    act, inp = torch.from_numpy(g["silu_act"]).double(), torch.from_numpy(g["silu_in"]).double()
+    n = act.numel()
+    eye, zero = torch.eye(n, dtype=torch.float64), torch.zeros(n, n, dtype=torch.float64)
+    x = torch.cat([act, inp])[None, :]
+    got = plain.swiglu(x, torch.cat([eye, zero], dim=1), torch.cat([zero, eye], dim=1), eye)[0]   # gate picks act, up picks in
+    want = torch.from_numpy(g["silu_out"]).double()
+    assert float((got - want).abs().max()) <= 2e-6 * max(1.0, float(want.abs().max()))
+    swapped = plain.swiglu(x, torch.cat([zero, eye], dim=1), torch.cat([eye, zero], dim=1), eye)[0]
+    assert float((swapped - want).abs().max()) > 0.5
+
+
+def test_the_mask_rule_of_attention_equals_the_reference_kernel():
+    """v1/tensortype/cuda_kernels/causal_mask.cu:12-57: new row t of `new` rows after `full - new` cached ones sees
+    key j if j <= full - new + t (and the key is not masked out).  The plain attention's rule is read off its
+    output: with all scores equal and one-hot values, out[t, j] > 0 exactly where row t sees key j."""
+    g = _kernels()
+    m, want = g["mask_in"], g["mask_out"]
+    batch, new, full = want.shape
+    q = torch.zeros(full, 1, full, dtype=torch.float64)
+    k = torch.zeros(full, 1, full, dtype=torch.float64)
+    v = torch.eye(full, dtype=torch.float64)[:, None, :]
+    seen = (plain.attention(q, k, v)[:, 0, :] > 0).numpy()[full - new:]        # the last `new` rows of the whole sequence
+    assert np.array_equal(want[0] == 0.0, seen)
+    assert (want[0][~seen] < -1e30).all()
+    # the second sequence has key 2 masked out (a padding key of the reference's rectangular batch; the engine has
+    # no padding keys): everything else follows the same rule
+    expect = seen.copy()
+    expect[:, 2] = False
+    assert np.array_equal(want[1] == 0.0, expect) and int(m[1, 2]) == 0
+
+
+def test_the_samplers_equal_the_reference_kernels():
+    """v1/tensortype/cuda_kernels/easy_sampling.cu:141-169 (the largest logit) and :32-104 (the three largest,
+    softmax over them at a temperature, walked from the third to the first against one uniform number)."""
+    g = _kernels()
+    logits = torch.from_numpy(g["top_logits"])
+    for b in range(logits.shape[0]):
+        assert plain.sample_greedy(logits[b]) == int(g["top1_ids"][b])
+    temp = float(g["top3_temperature"])
+    for n, u in enumerate(g["top3_draws"]):
+        for b in range(logits.shape[0]):
+            assert plain.sample_top3_reference(logits[b], temp, float(u)) == int(g["top3_ids"][n, b]), (n, b)
+    assert len({int(i) for i in g["top3_ids"].flatten()}) > logits.shape[0]   # the draws did pick different ranks
