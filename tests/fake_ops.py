@@ -11,13 +11,19 @@ from __future__ import annotations
 import torch
 
 
-def embedding(table, ids, out, status=None):
+def embedding(table, ids, out, status=None, scale=1.0):
     idx = ids.long()
     ok = (idx >= 0) & (idx < table.shape[0])
     out.zero_()
-    out[ok] = table[idx[ok]].float()
+    out[ok] = table[idx[ok]].float() * scale
     if status is not None and bool((idx >= table.shape[0]).any()):
         status[0] = 1
+
+
+def logits_scale_cap(logits, scale, cap):
+    logits.mul_(scale)
+    if cap > 0:
+        logits.copy_(cap * torch.tanh(logits / cap))
 
 
 def rmsnorm(x, delta, weight, eps, out, rows=None, status=None):

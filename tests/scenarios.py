@@ -349,6 +349,167 @@ def toy_routed_case(tmp, device, dtype):
         unregister_part("position", "toy_linear_angles")
 
 
+# ----------------------------------------------------------------------------- another norm, a cache kind, the model's two ends
+
+
+def define_toy_seam_parts():
+    """A norm that is no RMS norm and knows nothing of a product's unadded shares (it centres the row and has a
+    bias), and a mixer with a cache kind of its own: it keeps a narrow latent for every token in pages and answers
+    with the mean of the latents so far.  Defined here, registered through the public registries."""
+    from vt_transformer_b200.parts import (Mixer, MixerSpec, Norm, NormSpec, PagedLayout, ParamSpec, register_cache_kind,
+                                           register_part)
+
+    @dataclass(frozen=True)
+    class CentredSpec(NormSpec):
+        kind: str = "toy_centred"
+
+    class Centred(Norm):
+        def param_specs(self):
+            return {self.prefix + ".weight": ParamSpec((self.spec.size,), role="vector", init="one_plus_normal"),
+                    self.prefix + ".bias": ParamSpec((self.spec.size,), role="vector")}
+
+        def load(self, get):
+            self.w = self.rt.param(get(self.prefix + ".weight"), "vector")
+            self.b = self.rt.param(get(self.prefix + ".bias"), "vector")
+
+        def __call__(self, x, delta=None, rows=None, status=None):
+            if delta is not None:
+                assert isinstance(delta, torch.Tensor) and delta.shape == x.shape     # never a product's shares
+                x += delta.float()
+            v = x if rows is None else x[rows.long()]
+            return ((v - v.mean(dim=-1, keepdim=True)) * self.w + self.b).to(self.rt.dtype)
+
+    @dataclass(frozen=True)
+    class LatentCacheSpec:
+        width: int
+
+    @dataclass(frozen=True)
+    class LatentSpec(MixerSpec):
+        hidden: int = 0
+        width: int = 8
+        kind: str = "toy_latent_memory"
+
+    class LatentMemory(Mixer):
+        def cache_spec(self):
+            return LatentCacheSpec(self.spec.width)
+
+        def param_specs(self):
+            s = self.spec
+            return {self.prefix + "down.weight": ParamSpec((s.width, s.hidden)),
+                    self.prefix + "up.weight": ParamSpec((s.hidden, s.width))}
+
+        def load(self, get):
+            self.down = self.rt.param(get(self.prefix + "down.weight")).float()
+            self.up = self.rt.param(get(self.prefix + "up.weight")).float()
+
+        def forward(self, h, ctx, cache):
+            z = cache.pages["z"]                                   # [pages, 1, page_size, width]
+            out = torch.empty_like(h)
+            for i, s in enumerate(ctx.seqs):
+                new = h[s.offset:s.offset + s.length].float() @ self.down.t()
+                end = s.start + s.length
+                pos = torch.arange(end, device=h.device)
+                page = cache.block_table[i, pos // cache.page_size].long()
+                z[page[s.start:], 0, pos[s.start:] % cache.page_size] = new.to(z.dtype)
+                mean = torch.cumsum(z[page, 0, pos % cache.page_size].float(), dim=0)[s.start:] / (pos[s.start:, None] + 1)
+                out[s.offset:s.offset + s.length] = (mean @ self.up.t()).to(h.dtype)
+            return out
+
+    register_part("norm", "toy_centred", Centred, replace=True)
+    register_part("mixer", "toy_latent_memory", LatentMemory, replace=True)
+    register_cache_kind(LatentCacheSpec, lambda spec: PagedLayout((("z", 1, spec.width),), None))
+    return CentredSpec, LatentSpec, LatentCacheSpec
+
+
+def toy_seams_case(tmp, device, dtype):
+    """An architecture whose embedding is scaled and whose logits are scaled and capped (fields of the model's
+    spec), whose second layer's first norm and whose last norm are the toy norm, and whose second layer's mixer
+    keeps latents in pages of its own kind: registered from here, built from a folder, stepped whole, in portions
+    beside another request and token by token, with so few pages that they are used again."""
+    from vt_transformer_b200.config import Qwen2Config, config_from_dict, register_architecture, unregister_architecture
+    from vt_transformer_b200.models.qwen2 import qwen2_model_spec
+    from vt_transformer_b200.parts import unregister_cache_kind, unregister_part
+    from vt_transformer_b200.weights import write_random_model
+    Centred, Latent, LatentCache = define_toy_seam_parts()
+    scale, logit_scale, cap, width = 3.0, 3.0, 1.5, 8
+
+    def spec(cfg):
+        base = qwen2_model_spec(cfg)
+        blocks = list(base.blocks)
+        blocks[1] = replace(blocks[1], norm1=Centred(size=cfg.hidden_size, eps=0.0),
+                            mixer=Latent(hidden=cfg.hidden_size, width=width), mixer_prefix="memory.")
+        return replace(base, blocks=tuple(blocks), embedding=replace(base.embedding, scale=scale),
+                       head=replace(base.head, norm=Centred(size=cfg.hidden_size, eps=0.0), logit_scale=logit_scale,
+                                    logit_cap=cap))
+
+    register_architecture("ToySeamsLM", Qwen2Config, spec, replace=True)
+    try:
+        d = copy.deepcopy(helpers.CONFIGS["B"])
+        d["architectures"] = ["ToySeamsLM"]
+        folder = write_random_model(config_from_dict(d), os.path.join(tmp, "seams"), seed=12, sigma=0.05)
+        cfg, w = plain.read_config(folder), plain.read_weights(folder)
+        assert "model.layers.1.memory.down.weight" in w and "model.norm.bias" in w
+
+        def centred(x, name):
+            return (x - x.mean(dim=-1, keepdim=True)) * w[name + ".weight"] + w[name + ".bias"]
+
+        def reference(ids):
+            cos, sin = plain.rotation_table(cfg.max_pos, cfg.head_dim, cfg.theta)
+            x = plain.embed(w["model.embed_tokens.weight"], ids) * scale
+            x = plain.layer(cfg, w, 0, x, cos, sin)
+            h = centred(x, "model.layers.1.input_layernorm")
+            z = h @ w["model.layers.1.memory.down.weight"].t()
+            mean = torch.cumsum(z, 0) / torch.arange(1, len(ids) + 1, dtype=z.dtype)[:, None]
+            x = x + mean @ w["model.layers.1.memory.up.weight"].t()
+            h = plain.rms_norm(x, w["model.layers.1.post_attention_layernorm.weight"], cfg.eps)
+            x = x + plain.swiglu(h, w["model.layers.1.mlp.gate_proj.weight"], w["model.layers.1.mlp.up_proj.weight"],
+                                 w["model.layers.1.mlp.down_proj.weight"])
+            x = plain.layer(cfg, w, 2, x, cos, sin)
+            logits = plain.linear(centred(x, "model.norm"), w["lm_head.weight"]) * logit_scale
+            return cap * torch.tanh(logits / cap)
+
+        runner = runner_for(folder, device, dtype, num_pages=9, max_requests=2)
+        slots = runner.model.cache_slots()
+        assert isinstance(slots[1], LatentCache) and len(runner.cache.groups) == 2     # keys and values; latents
+        assert runner.cache.bytes_per_token() == (2 * 2 * 32 + width) * (4 if dtype == "float32" else 2)
+        prompts = helpers.prompts_for("B")
+        worst = 0.0
+        for first, second in ((prompts[3], prompts[2]), (prompts[2], prompts[1])):   # the second pair uses rows and pages again
+            rows = [runner.admit(), runner.admit()]
+            got, done = [[], []], [0, 0]
+            sizes = [[9, 2, 30, 1, 1, 27], [5, 1, 1, 13, 11]]
+            for step in range(6):
+                entries = []
+                for i, ids in enumerate((first, second)):
+                    if step < len(sizes[i]) and done[i] < len(ids):
+                        k = min(sizes[i][step], len(ids) - done[i])
+                        entries.append((i, helpers_entry(rows[i], ids[done[i]:done[i] + k])))
+                        done[i] += k
+                logits = runner.step([e for _, e in entries]).float().cpu()
+                at = 0
+                for i, e in entries:
+                    got[i].append(logits[at:at + len(e.tokens)])
+                    at += len(e.tokens)
+            runner.check_status()
+            for i, ids in enumerate((first, second)):
+                assert done[i] == len(ids)
+                ref = reference(ids)
+                assert float(ref.abs().max()) > 0.8 * cap > float(ref.abs().median())       # the cap bends some logits, not all
+                err = float((torch.cat(got[i]).double() - ref).abs().max())
+                assert err <= helpers.tol(dtype, ref=ref), (i, err)
+                worst = max(worst, err)
+            for r in rows:
+                runner.release(r)
+            runner.cache.check()
+        assert runner.cache.free_pages() == [9, 9]
+        return worst
+    finally:
+        unregister_architecture("ToySeamsLM")
+        unregister_part("norm", "toy_centred")
+        unregister_part("mixer", "toy_latent_memory")
+        unregister_cache_kind(LatentCache)
+
+
 # ----------------------------------------------------------------------------- generation
 
 

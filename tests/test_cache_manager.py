@@ -40,7 +40,7 @@ def test_groups_by_need():
     assert len(m.groups) == 2
     assert m.slot_group[0][0] == m.slot_group[1][0] != m.slot_group[2][0]
     full, win = m.groups[m.slot_group[0][0]], m.groups[m.slot_group[2][0]]
-    assert full.kv.shape == (2, 2, 8, 2, 16, 16) and win.kv.shape == (1, 2, 8, 2, 16, 16)
+    assert full.tensors["k"].shape == (2, 8, 2, 16, 16) and win.tensors["v"].shape == (1, 8, 2, 16, 16)
     assert full.spec.window is None and win.spec.window == 20
 
 

@@ -93,6 +93,9 @@ def test_window_by_layer():
     d["layer_types"] = ["sliding_attention", "full_attention", "full_attention", "sliding_attention"]
     cfg = config_from_dict(d)
     assert [cfg.layer_window(i) for i in range(4)] == [20, None, None, 20]
+    d["use_sliding_window"] = False                      # switched off: layer_types gives no layer a window
+    assert [config_from_dict(d).layer_window(i) for i in range(4)] == [None] * 4
+    d["use_sliding_window"] = True
     d["layer_types"] = ["full_attention"]
     with pytest.raises(ConfigError, match="layer_types"):
         config_from_dict(d)

@@ -44,6 +44,25 @@ def test_toy_feed_forward_with_routing_and_another_position_encoding(fake_backen
     scenarios.toy_routed_case(str(tmp_path), DEV, DT)
 
 
+def test_toy_norm_cache_kind_and_the_models_two_ends(fake_backend, tmp_path):
+    scenarios.toy_seams_case(str(tmp_path), DEV, DT)
+
+
+def test_an_unknown_kind_of_cache_spec_is_refused_by_name():
+    from vt_transformer_b200.cache import CacheManager
+    with pytest.raises(TypeError, match="cache slot 3: unknown kind of cache spec.*register_cache_kind"):
+        CacheManager({3: object()}, page_size=16, num_pages=2, max_requests=1, max_seq_len=32, dtype=torch.float32,
+                     device="cpu", allocate=False)
+
+
+def test_attention_refuses_a_rotation_of_part_of_the_head():
+    from vt_transformer_b200.parts import AttentionSpec, PositionSpec, Runtime, build_part
+    rt = Runtime(torch.device("cpu"), torch.float32, None)
+    spec = AttentionSpec(hidden=64, heads=4, kv_heads=2, head_dim=16, position=PositionSpec(dim=8, base=1e4, max_positions=32))
+    with pytest.raises(ValueError, match="covers 8 of the head's 16"):
+        build_part("mixer", spec, "x.", rt)
+
+
 def test_step_refuses_bad_entries_and_leaves_the_cache_alone(fake_backend, folders):
     from vt_transformer_b200.cache import OutOfPages
     from vt_transformer_b200.engine import StepEntry

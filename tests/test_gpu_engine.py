@@ -47,6 +47,11 @@ def test_toy_feed_forward_with_routing_and_another_position_encoding(tmp_path, d
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_norm_cache_kind_and_the_models_two_ends(tmp_path, dtype):
+    scenarios.toy_seams_case(str(tmp_path), DEV, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "C"])
 def test_greedy_generation_through_the_entry_point(folders, name, dtype):
     scenarios.greedy_generation_case(folders(name), name, DEV, dtype)
@@ -179,6 +184,35 @@ def test_window_edge(folders, dtype):
     runner.check_status()
     err = (torch.cat(got) - ref).abs().max(dim=1).values
     assert float(err.max()) <= helpers.tol(dtype, "C"), (int(err.argmax()), float(err.max()))
+
+
+def test_a_folder_stored_in_32_bit_rounded_at_load_runs_the_bfloat16_kernels(tmp_path):
+    """A model stored in float32, loaded in bfloat16 mode: with fp32_weights="round" its matrices are bfloat16 (the
+    tcgen05 products run) and the logits are those of a folder that stores the rounded values, bit for bit; kept in
+    32-bit (the default, with a warning) the products run the 32-bit kernel and the logits are within the bound."""
+    import warnings
+    from test_weights import wide_and_rounded_folders
+    from vt_transformer_b200.engine import ModelRunner, StepEntry
+    wide, rounded = wide_and_rounded_folders(str(tmp_path))
+    ids = helpers.prompts_for("B")[4]
+    kw = dict(dtype="bfloat16", device=DEV, page_size=16, num_pages=10, max_requests=1)
+
+    def logits(runner):
+        out = runner.step([StepEntry(runner.admit(), ids, list(range(len(ids))))])
+        runner.check_status()
+        return out
+
+    cut = ModelRunner.from_folder(wide, fp32_weights="round", **kw)
+    ref = ModelRunner.from_folder(rounded, **kw)
+    assert cut.model.blocks[0].mixer.w_qkv.dtype == torch.bfloat16 and cut.model.blocks[0].ffn.w_gate_up.dtype == torch.bfloat16
+    got, want = logits(cut), logits(ref)
+    assert torch.equal(got, want)
+    with pytest.warns(UserWarning, match="stay so"):
+        kept = ModelRunner.from_folder(wide, **kw)
+    assert kept.model.blocks[0].mixer.w_qkv.dtype == torch.float32
+    plain_ref = helpers.plain_logits(rounded, ids)
+    assert float((logits(kept).double().cpu() - plain_ref).abs().max()) <= helpers.tol("bfloat16", ref=plain_ref)
+    assert float((want.double().cpu() - plain_ref).abs().max()) <= helpers.tol("bfloat16", ref=plain_ref)
 
 
 def test_status_word_reports_a_bad_token_id(folders):

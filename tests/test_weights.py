@@ -128,3 +128,79 @@ def test_writer_checks_its_layout(tmp_path):
         st.write_file(str(tmp_path / "f.safetensors"), iter([("a", torch.zeros(2, 4, dtype=torch.bfloat16))]), layout)
     with pytest.raises(SafetensorsError, match="fewer"):
         st.write_file(str(tmp_path / "f.safetensors"), iter([]), layout)
+
+
+def _rewrite(src_folder, dst_folder, change, extra=None):
+    """A copy of a model folder whose tensors went through ``change(name, tensor)``, plus ``extra`` tensors."""
+    src = SafetensorsSource(src_folder)
+    tensors = {n: change(n, src.get(n).clone()) for n in src.entries()}
+    tensors.update(extra or {})
+    os.makedirs(dst_folder, exist_ok=True)
+    with open(os.path.join(src_folder, "config.json")) as f, open(os.path.join(dst_folder, "config.json"), "w") as g:
+        g.write(f.read())
+    st.write_file(os.path.join(dst_folder, "model.safetensors"), iter(tensors.items()),
+                  [(n, t.dtype, tuple(t.shape)) for n, t in tensors.items()])
+    return dst_folder
+
+
+def wide_and_rounded_folders(tmp):
+    """A folder stored in float32 whose values bfloat16 cannot hold exactly, and one that stores those values
+    rounded to bfloat16."""
+    g = torch.Generator().manual_seed(3)
+    base = helpers.make_folder("B", os.path.join(tmp, "bf16"))
+    wide = _rewrite(base, os.path.join(tmp, "f32"), lambda n, t: t.float() + 1e-4 * torch.randn(t.shape, generator=g))
+    rounded = _rewrite(wide, os.path.join(tmp, "rounded"), lambda n, t: t.to(torch.bfloat16))
+    return wide, rounded
+
+
+def test_matrices_stored_in_32_bit_are_kept_with_a_warning_or_rounded_with_a_report(fake_backend, tmp_path, capsys):
+    """In bfloat16 mode matrices stored in float32 stay 32-bit by default and a warning says what that costs; with
+    fp32_weights="round" they become bfloat16 and a line reports it; in 32-bit mode nothing is said.  (What the
+    logits then are is compared on the GPU: tests/test_gpu_engine.py.)"""
+    import warnings
+    from vt_transformer_b200.engine import ModelRunner
+    wide, rounded = wide_and_rounded_folders(str(tmp_path))
+    kw = dict(device="cpu", page_size=16, num_pages=8, max_requests=1)
+    with pytest.warns(UserWarning, match="stored in float32 and stay so.*fp32_weights='round'"):
+        kept = ModelRunner.from_folder(wide, dtype="bfloat16", **kw)
+    assert kept.model.blocks[0].mixer.w_qkv.dtype == torch.float32
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        capsys.readouterr()
+        cut = ModelRunner.from_folder(wide, dtype="bfloat16", fp32_weights="round", **kw)
+        assert "rounded to bfloat16 (to nearest even): 0 values became infinite, 0 became zero" in capsys.readouterr().err
+        ref = ModelRunner.from_folder(rounded, dtype="bfloat16", **kw)
+        full = ModelRunner.from_folder(wide, dtype="float32", **kw)
+        assert capsys.readouterr().err == ""
+    assert cut.model.blocks[0].mixer.w_qkv.dtype == torch.bfloat16 and cut.model.blocks[2].ffn.w_down.dtype == torch.bfloat16
+    assert cut.model.head.weight.dtype == torch.bfloat16 and full.model.head.weight.dtype == torch.float32
+    for a, b in ((cut.model.blocks[1].mixer.w_qkv, ref.model.blocks[1].mixer.w_qkv), (cut.model.head.weight, ref.model.head.weight)):
+        assert torch.equal(a, b)                            # rounded at load = rounded in the file
+    with pytest.raises(ValueError, match="fp32_weights"):
+        ModelRunner.from_folder(wide, dtype="bfloat16", fp32_weights="maybe", **kw)
+
+
+def test_rounding_counts_the_values_that_change_class():
+    from vt_transformer_b200.parts import Runtime
+    rt = Runtime(torch.device("cpu"), torch.bfloat16, None, fp32_weights="round")
+    t = torch.tensor([[1.0, 3.4e38, -3.4e38, 1e-44], [0.0, 2.5, 1e-40, -7.0]], dtype=torch.float32)
+    out = rt.param(t)
+    assert out.dtype == torch.bfloat16 and rt.notes == {"rounded": 1, "rounded_values": 8, "to_inf": 2, "to_zero": 1}
+    assert torch.equal(out, t.to(torch.bfloat16))
+    assert rt.param(t, "vector").dtype == torch.float32 and rt.notes["rounded"] == 1     # vectors are read in 32-bit anyway
+
+
+def test_float16_is_rounded_with_a_report_and_known_extras_are_left_aside_with_a_warning(fake_backend, tmp_path, capsys):
+    from vt_transformer_b200.engine import ModelRunner
+    base = helpers.make_folder("A", str(tmp_path / "bf16"))
+    extra = {f"model.layers.{i}.self_attn.rotary_emb.inv_freq": torch.ones(8) for i in range(2)}
+    half = _rewrite(base, str(tmp_path / "f16"), lambda n, t: t.to(torch.float16), extra)
+    with pytest.warns(UserWarning, match="2 tensors that the model does not read were left aside: .*rotary_emb.inv_freq"):
+        runner = ModelRunner.from_folder(half, dtype="bfloat16", device="cpu", page_size=16, num_pages=2, max_requests=1)
+    err = capsys.readouterr().err
+    assert "tensors stored in float16 were rounded to bfloat16" in err
+    assert runner.model.blocks[0].mixer.w_qkv.dtype == torch.bfloat16
+    # a tensor that is no known extra is still a difference
+    odd = _rewrite(base, str(tmp_path / "odd"), lambda n, t: t, {"model.layers.0.self_attn.rotary_emb.other": torch.ones(8)})
+    with pytest.raises(WeightError, match="unexpected"):
+        ModelRunner.from_folder(odd, dtype="bfloat16", device="cpu", page_size=16, num_pages=2, max_requests=1)

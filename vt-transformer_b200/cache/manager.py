@@ -24,7 +24,7 @@ from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..parts.base import CacheView, KVCacheSpec, StateSpec
+from ..parts.base import CacheView, KVCacheSpec, PagedLayout, StateLayout, StateSpec, cache_layout
 
 
 class OutOfPages(RuntimeError):
@@ -93,15 +93,21 @@ class _GroupPool:
 @dataclass
 class _Group:
     index: int
-    spec: KVCacheSpec
+    layout: PagedLayout
     slots: List[int]
     pool: _GroupPool
-    kv: Optional[torch.Tensor]          # [slots, 2, pages, kv_heads, page_size, head_dim]
+    tensors: Optional[Dict[str, torch.Tensor]]   # name -> [slots, pages, outer, page_size, inner]
     table: np.ndarray                   # [rows, max_pages] int32, -1 where no page is held: a view of the book's table
+
+    @property
+    def spec(self):
+        """The group's layout (its ``tensors`` and its ``window``)."""
+        return self.layout
 
 
 class CacheManager:
-    """``slot_specs``: cache slot id -> ``KVCacheSpec`` or ``StateSpec`` (``DecoderModel.cache_slots()``).
+    """``slot_specs``: cache slot id -> a cache spec (``DecoderModel.cache_slots()``): ``KVCacheSpec``, ``StateSpec``,
+    or any kind that ``parts.register_cache_kind`` has given a layout.  Slots with equal paged layouts form a group.
 
     A request lives in a *row*.  ``admit`` takes a row, ``extend`` makes sure that pages
     cover its positions below a new length (all-or-nothing over a list of requests),
@@ -123,33 +129,34 @@ class CacheManager:
         self.groups: List[_Group] = []
         self.slot_group: Dict[int, Tuple[int, int]] = {}     # slot -> (group index, index inside the group)
         self.state: Dict[int, torch.Tensor] = {}
-        self.state_specs: Dict[int, StateSpec] = {}
-        by_key: Dict[Tuple, List[int]] = {}
+        self.state_specs: Dict[int, object] = {}
+        by_layout: Dict[PagedLayout, List[int]] = {}
+        self.slot_specs = dict(slot_specs)
         for slot in sorted(slot_specs):
-            spec = slot_specs[slot]
-            if isinstance(spec, KVCacheSpec):
-                by_key.setdefault((spec.kv_heads, spec.head_dim, spec.window), []).append(slot)
-            elif isinstance(spec, StateSpec):
-                self.state_specs[slot] = spec
-                self.state[slot] = (torch.zeros((max_requests,) + tuple(spec.shape), dtype=spec.dtype, device=device)
+            try:
+                layout = cache_layout(slot_specs[slot])
+            except TypeError as e:
+                raise TypeError(f"cache slot {slot}: {e}") from None
+            if isinstance(layout, PagedLayout):
+                by_layout.setdefault(layout, []).append(slot)
+            elif isinstance(layout, StateLayout):
+                self.state_specs[slot] = slot_specs[slot]
+                self.state[slot] = (torch.zeros((max_requests,) + tuple(layout.shape), dtype=layout.dtype, device=device)
                                     if allocate else None)
             else:
-                raise TypeError(f"cache slot {slot}: unknown kind of cache spec {spec!r}")
-        plan = []
-        for key, slots in by_key.items():
-            kv_heads, head_dim, window = key
-            n = num_pages if (window is None or window_pages is None) else window_pages
-            plan.append((key, slots, n))
+                raise TypeError(f"cache slot {slot}: a layout must be a PagedLayout or a StateLayout, found {layout!r}")
+        plan = [(layout, slots, num_pages if (layout.window is None or window_pages is None) else window_pages)
+                for layout, slots in by_layout.items()]
         # the bookkeeping (rows, lengths, free lists, block tables) is the C++ object; the tensors stay here
         self.book = _host().CacheBook(page_size, max_requests, max_seq_len,
-                                      [(-1 if key[2] is None else int(key[2]), n) for key, _, n in plan])
-        for (kv_heads, head_dim, window), slots, n in plan:
-            kv = None
+                                      [(-1 if layout.window is None else int(layout.window), n) for layout, _, n in plan])
+        for layout, slots, n in plan:
+            tensors = None
             if allocate:
-                kv = torch.zeros((len(slots), 2, n, kv_heads, page_size, head_dim), dtype=dtype, device=device)
+                tensors = {name: torch.zeros((len(slots), n, outer, page_size, inner), dtype=dtype, device=device)
+                           for name, outer, inner in layout.tensors}
             index = len(self.groups)
-            g = _Group(index, KVCacheSpec(kv_heads, head_dim, window), slots, _GroupPool(self.book, index), kv,
-                       self.book.table(index))
+            g = _Group(index, layout, slots, _GroupPool(self.book, index), tensors, self.book.table(index))
             for i, s in enumerate(slots):
                 self.slot_group[s] = (g.index, i)
             self.groups.append(g)
@@ -217,8 +224,9 @@ class CacheManager:
         out: Dict[int, CacheView] = {}
         for slot, (gi, si) in self.slot_group.items():
             g = self.groups[gi]
-            out[slot] = CacheView(spec=g.spec, k=g.kv[si, 0], v=g.kv[si, 1], block_table=block_tables[gi],
-                                  page_size=self.page_size)
+            pages = {name: t[si] for name, t in g.tensors.items()}
+            out[slot] = CacheView(spec=self.slot_specs[slot], k=pages.get("k"), v=pages.get("v"), pages=pages,
+                                  block_table=block_tables[gi], page_size=self.page_size)
         for slot, t in self.state.items():
             out[slot] = CacheView(spec=self.state_specs[slot], state=t)
         return out
@@ -226,7 +234,7 @@ class CacheManager:
     def bytes_per_token(self) -> int:
         """Bytes of keys and values one cached token takes, over all slots."""
         item = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * g.spec.kv_heads * g.spec.head_dim * item * len(g.slots) for g in self.groups)
+        return sum(outer * inner * item * len(g.slots) for g in self.groups for _, outer, inner in g.layout.tensors)
 
     # ---- invariants (tests) --------------------------------------------------------------
     def check(self) -> None:

@@ -42,6 +42,9 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--model", "--model-path", required=True, help="folder with config.json and model.safetensors")
     g.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     g.add_argument("--device", default="cuda:0")
+    g.add_argument("--fp32-weights", default="keep", choices=["keep", "round"],
+                   help="matrices stored in 32-bit, with --dtype bfloat16: keep them (their products run the 32-bit "
+                        "kernels) or round them to bfloat16 at load")
     g.add_argument("--prompt-ids", action="append", default=[], help="a prompt as token ids, e.g. 1,2,3 (repeatable)")
     g.add_argument("--prompt-file", help="a file with one prompt a line, as token ids")
     g.add_argument("--shell-mode", action="store_true", help="read prompts (token ids) line by line from standard input")
@@ -81,7 +84,8 @@ def _generate(args) -> int:
     sizes = {} if args.page_size is None else {"page_size": args.page_size}
     llm = LLM(args.model, dtype=args.dtype, device=args.device, max_running_reqs=args.max_running_reqs,
               num_pages=args.num_pages, max_seq_len=args.max_seq_len,
-              max_extend_tokens=args.max_extend_tokens, chunk_size=args.chunk_size, overlap=args.overlap, **sizes)
+              max_extend_tokens=args.max_extend_tokens, chunk_size=args.chunk_size, overlap=args.overlap,
+              fp32_weights=args.fp32_weights, **sizes)
     params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                             ignore_eos=args.ignore_eos, max_tokens=args.max_tokens, seed=args.seed)
 

@@ -52,15 +52,16 @@ class Qwen2Config(ModelConfig):
         of the config keys themselves: ``layer_types[layer]`` if the list is given
         ("full_attention" or "sliding_attention"); else, with ``use_sliding_window``, the
         layers from ``max_window_layers`` on see the last ``sliding_window`` keys: key j
-        is seen from position p if p - sliding_window < j <= p.
+        is seen from position p if p - sliding_window < j <= p.  With ``use_sliding_window`` false no layer has
+        a window, whatever ``layer_types`` and ``sliding_window`` say (the architecture's own reading of its keys:
+        the 7B checkpoint's config carries sliding_window 131072 beside use_sliding_window false).
         """
+        if not self.use_sliding_window or self.sliding_window is None:
+            return None
         if self.layer_types is not None:
             return self.sliding_window if self.layer_types[layer] == "sliding_attention" else None
-        if self.use_sliding_window and self.sliding_window is not None:
-            first = self.num_hidden_layers if self.max_window_layers is None else self.max_window_layers
-            if layer >= first:
-                return self.sliding_window
-        return None
+        first = self.num_hidden_layers if self.max_window_layers is None else self.max_window_layers
+        return self.sliding_window if layer >= first else None
 
     # ---- reading -------------------------------------------------------------------
     @classmethod

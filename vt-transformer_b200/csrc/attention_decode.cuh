@@ -749,12 +749,9 @@ cudaError_t launch_decode_n(AttnParams p, int n_seqs, int* counters, cudaStream_
         if (!make_map(&map_k, p.k_cache, rows, D, p.run_keys) || !make_map(&map_v, p.v_cache, rows, D, p.run_keys))
             return cudaErrorInvalidValue;
     }
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, W, NARROW, BOXES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static std::atomic<unsigned long long> configured{0};
+    cudaError_t e = allow_dynamic_smem(attention_decode_kernel<D, W, NARROW, BOXES>, smem, configured);
+    if (e != cudaSuccess) return e;
     return launch(attention_decode_kernel<D, W, NARROW, BOXES>, dim3(n_seqs, p.kv_heads, p.n_splits), dim3(W * 32, 1, 1), smem, stream,
                   dim3(1, 1, p.cluster_merge ? p.n_splits : 1), p, counters, map_k, map_v);
 }

@@ -309,14 +309,11 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
 template <int D, int WARPS>
 cudaError_t launch_one(const AttnParams& p, int n_tiles, cudaStream_t stream) {
     constexpr int smem = 2 * 2 * KB * (D + 8) * (int)sizeof(__nv_bfloat16);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<D, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static std::atomic<unsigned long long> configured{0};
+    cudaError_t e = allow_dynamic_smem(attention_mma_kernel<D, WARPS>, smem, configured);
+    if (e != cudaSuccess) return e;
     dim3 grid(n_tiles, p.kv_heads, p.n_splits);
-    cudaError_t e = launch(attention_mma_kernel<D, WARPS>, grid, WARPS * 32, smem, stream, p);
+    e = launch(attention_mma_kernel<D, WARPS>, grid, WARPS * 32, smem, stream, p);
     if (e != cudaSuccess) return e;
     if (p.n_splits > 1) {
         const long long pairs = (long long)p.n_tokens * p.heads;

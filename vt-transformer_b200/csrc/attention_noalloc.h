@@ -6,10 +6,13 @@
 // plug-in that runs under someone else's memory budget, a service loop in which the implicit
 // synchronisation of an allocation is not acceptable.
 //
-// It is the engine's single-token attention over the paged cache with the keys of each sequence cut
-// into `n_splits` runs (the kernel behind `attention_mma` with n_splits > 1).  The partial results of
-// the runs, which the ordinary entry point puts into scratch tensors that its caller allocates, go
-// into a fixed array that is part of this library's device image instead:
+// It computes single-token attention over the paged cache with the keys of each sequence cut into `n_splits`
+// runs: `attention_mma_kernel<head_dim, 1>` (one warp a (sequence, KV head, run)) followed by
+// `attention_combine_kernel`, which merges the runs; the same two kernels as the extension's `attention_mma`
+// with n_splits > 1.  (Generation itself decodes with another kernel, `attention_decode_kernel`, which merges its
+// runs inside thread-block clusters; this pair is the form whose scratch is one plain array.)  The partial results
+// of the runs, which the ordinary entry point puts into scratch tensors that its caller allocates, go into a
+// fixed array that is part of this library's device image instead:
 //
 //     VTB_NOALLOC_SCRATCH_FLOATS = 2,097,152 floats (8 MiB), held by every GPU that loads the
 //     library, from load until the process exits.
@@ -19,8 +22,9 @@
 // only; nothing is allocated or freed, by this function or by anything it calls.
 //
 // Set-up: the first call on a device looks up the array's device address (cudaGetSymbolAddress, with
-// that device current) and remembers it for the device; the first use of the kernel in the process
-// also sets its shared-memory attribute.  Make that first call before any stream capture begins.
+// that device current) and remembers it for the device; the first launch of the kernel on a device
+// also sets its shared-memory attribute there.  Make that first call before any stream capture begins.
+// First calls from two host threads at once are harmless (both look up the same address).
 //
 // Sharing: every call uses the same array and finds the last call's contents in it.  Nothing has to
 // start at zero -- each (run, sequence, head) of a call writes its own partial result before the
@@ -35,9 +39,10 @@
 //   q_start     int32 [n_seqs], position of each sequence's token (= keys cached before it)
 //   block_table int32 [n_seqs, table_stride], page of every 16.. tokens of a sequence
 //   window      keys a token sees (0: all);  scale: multiplier of q.k;  stream: a cudaStream_t
-// Returns 0, or 1 (too large for the array), 2 (a shape the kernel does not take: head_dim a multiple
-// of 16 up to 128, at most 16 heads a KV head, page_size a multiple of 16, 1 <= n_splits <= 64),
-// 3 (a CUDA call failed; its message goes to stderr).
+// Returns 0, or 1 (too large for the array), 2 (arguments the kernel does not take: a null pointer, head_dim
+// not a multiple of 16 up to 128, more than 16 heads a KV head, page_size not a positive multiple of 16,
+// n_splits outside 1..64, qkv_stride below heads * head_dim, table_stride or n_pages below 1; nothing is
+// launched), 3 (a CUDA call failed; its message goes to stderr).
 #pragma once
 
 #ifdef __cplusplus

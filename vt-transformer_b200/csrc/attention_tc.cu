@@ -442,12 +442,9 @@ cudaError_t launch_attention_tc(const void* qkv, int qkv_stride, void* out, cons
     const int halves = head_dim / 64;
     const int smem = max((1 + 2 * 2) * halves * HALF_BYTES + 1024 + 256 + 2 * 128 * 2 * 4, 120 * 1024);
     auto kernel = head_dim == 128 ? attention_tc_kernel<128> : attention_tc_kernel<64>;
-    static bool configured[2] = {false, false};
-    if (!configured[halves - 1]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return e;
-        configured[halves - 1] = true;
-    }
+    static std::atomic<unsigned long long> configured[2] = {{0}, {0}};
+    cudaError_t e = allow_dynamic_smem(kernel, smem, configured[halves - 1]);
+    if (e != cudaSuccess) return e;
     return launch(kernel, dim3(n_tiles, kv_heads, 1), dim3(ATC_THREADS, 1, 1), smem, stream, map_k, map_v, p);
 }
 

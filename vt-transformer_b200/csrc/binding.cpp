@@ -44,7 +44,7 @@ int* status_ptr(const c10::optional<Tensor>& status) {
     return status->data_ptr<int>();
 }
 
-void embedding(const Tensor& table, const Tensor& ids, Tensor& out, c10::optional<Tensor> status) {
+void embedding(const Tensor& table, const Tensor& ids, Tensor& out, c10::optional<Tensor> status, double scale) {
     check_cuda(table, "table"); check_i32(ids, "ids"); check_f32(out, "out");
     TORCH_CHECK(table.dim() == 2 && out.dim() == 2, "embedding: table and out must be 2-d");
     const int hidden = table.size(1);
@@ -52,8 +52,17 @@ void embedding(const Tensor& table, const Tensor& ids, Tensor& out, c10::optiona
     TORCH_CHECK(out.size(1) == hidden && out.size(0) == ids.numel(), "embedding: out must be [tokens, hidden]");
     c10::cuda::CUDAGuard guard(table.device());
     check_launch(vtb::launch_embedding(dtype_code(table, "table"), table.data_ptr(), ids.data_ptr<int>(),
-                                       out.data_ptr<float>(), ids.numel(), hidden, table.size(0),
+                                       out.data_ptr<float>(), ids.numel(), hidden, table.size(0), (float)scale,
                                        status_ptr(status), stream_of(table)), "embedding");
+}
+
+void logits_scale_cap(Tensor& logits, double scale, double cap) {
+    check_f32(logits, "logits");
+    TORCH_CHECK(logits.is_contiguous(), "logits_scale_cap: logits must be contiguous");
+    TORCH_CHECK(cap >= 0.0, "logits_scale_cap: the cap must not be negative");
+    c10::cuda::CUDAGuard guard(logits.device());
+    check_launch(vtb::launch_logits_scale_cap(logits.data_ptr<float>(), logits.numel(), (float)scale, (float)cap,
+                                              stream_of(logits)), "logits_scale_cap");
 }
 
 void rmsnorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, double eps, Tensor& out,
@@ -429,7 +438,9 @@ void sample(const Tensor& logits, const Tensor& temperature, const Tensor& top_k
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     namespace py = pybind11;
-    m.def("embedding", &embedding, py::arg("table"), py::arg("ids"), py::arg("out"), py::arg("status") = py::none());
+    m.def("embedding", &embedding, py::arg("table"), py::arg("ids"), py::arg("out"), py::arg("status") = py::none(),
+          py::arg("scale") = 1.0);
+    m.def("logits_scale_cap", &logits_scale_cap, py::arg("logits"), py::arg("scale"), py::arg("cap"));
     m.def("rmsnorm", &rmsnorm, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("eps"), py::arg("out"),
           py::arg("rows") = py::none(), py::arg("status") = py::none());
     m.def("silu_mul", &silu_mul, py::arg("gu"), py::arg("out"), py::arg("interleave") = 0);

@@ -17,7 +17,7 @@ namespace vtb {
 
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
-                                 int hidden, int vocab, int* status) {
+                                 int hidden, int vocab, float scale, int* status) {
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
@@ -36,17 +36,41 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
     for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
         float f[8];
         Vec8<T>::load(row + i, f);
+        if (scale != 1.0f) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] *= scale;
+        }
         Vec8<float>::store(o + i, f);
     }
 }
 
 cudaError_t launch_embedding(int table_dtype, const void* table, const int* ids, float* out, int n_tokens,
-                             int hidden, int vocab, int* status, cudaStream_t stream) {
+                             int hidden, int vocab, float scale, int* status, cudaStream_t stream) {
     if (n_tokens == 0) return cudaSuccess;
     int threads = min(256, max(32, ((hidden / 8 + 31) / 32) * 32));
     if (table_dtype == kBF16)
-        return launch(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
-    return launch(embedding_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab, status);
+        return launch(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab, scale, status);
+    return launch(embedding_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab, scale, status);
+}
+
+// ------------------------------------------------------------------------- logits: scale and soft cap
+
+// logits = cap * tanh(scale * logits / cap) in place (cap 0: the scale alone), 32-bit.
+__global__ void logits_scale_cap_kernel(float* __restrict__ logits, long long n, float scale, float cap) {
+    pdl_launch();
+    pdl_wait();
+    const float inv = cap > 0.f ? 1.f / cap : 0.f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float v = logits[i] * scale;
+        if (cap > 0.f) v = cap * tanhf(v * inv);
+        logits[i] = v;
+    }
+}
+
+cudaError_t launch_logits_scale_cap(float* logits, long long n, float scale, float cap, cudaStream_t stream) {
+    if (n == 0) return cudaSuccess;
+    const int blocks = (int)min((n + 255) / 256, (long long)148 * 8);
+    return launch(logits_scale_cap_kernel, blocks, 256, 0, stream, logits, n, scale, cap);
 }
 
 // ------------------------------------------------------------------------- rmsnorm

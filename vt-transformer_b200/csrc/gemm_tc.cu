@@ -344,12 +344,9 @@ cudaError_t launch_cfg(const void* a, int rows_a, const void* b, int rows_b, int
     CUtensorMap map_a, map_b;
     if (!make_map(&map_a, a, rows_a, k, BM) || !make_map(&map_b, b, rows_b, k, BN)) return cudaErrorInvalidValue;
     constexpr int smem = STAGES * (A_STAGE + BN * BK * 2) + 1024 + 256;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, EPI, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static std::atomic<unsigned long long> configured{0};
+    cudaError_t e = allow_dynamic_smem(gemm_tc_kernel<BN, STAGES, SWAP, EPI, TOut>, smem, configured);
+    if (e != cudaSuccess) return e;
     const int tiles = ((rows_a + BM - 1) / BM) * ((rows_b + BN - 1) / BN);
     const int units = n_full + (tiles - n_full) * s_tail;
     return launch(gemm_tc_kernel<BN, STAGES, SWAP, EPI, TOut>, dim3(units < sm_count() ? units : sm_count(), 1, 1),

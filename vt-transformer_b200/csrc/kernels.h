@@ -12,7 +12,9 @@ enum DType : int { kF32 = 0, kBF16 = 1 };
 
 // out[t, :] = float(table[ids[t], :]).  hidden % 8 == 0.
 cudaError_t launch_embedding(int table_dtype, const void* table, const int* ids, float* out, int n_tokens,
-                             int hidden, int vocab, int* status, cudaStream_t stream);
+                             int hidden, int vocab, float scale, int* status, cudaStream_t stream);
+// logits = cap * tanh(scale * logits / cap) in place; cap 0 applies the scale alone
+cudaError_t launch_logits_scale_cap(float* logits, long long n, float scale, float cap, cudaStream_t stream);
 
 // For r in 0..n_rows: t = rows ? rows[r] : r; v = x[t] (+ delta[t], written back to x[t]);
 // out[r] = weight * v * rsqrt(mean(v^2) + eps).  x float, weight float, delta/out of out_dtype.  Instead of

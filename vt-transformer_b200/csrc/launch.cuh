@@ -4,6 +4,7 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdlib>
 
 namespace vtb {
@@ -15,6 +16,22 @@ inline bool pdl_enabled() {
         on = (v != nullptr && v[0] == '0') ? 0 : 1;
     }
     return on == 1;
+}
+
+// A kernel's limit of dynamic shared memory is an attribute of the kernel on one device.  `done` is the caller's
+// static flag word, one bit a device: the attribute is set at the kernel's first launch on each device.  Setting it
+// twice is harmless, so two host threads that both find the bit clear may both set it.
+template <typename K>
+cudaError_t allow_dynamic_smem(K kernel, int bytes, std::atomic<unsigned long long>& done) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    const unsigned long long bit = 1ull << (device & 63);
+    if (done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    done.fetch_or(bit, std::memory_order_release);
+    return cudaSuccess;
 }
 
 template <typename... KArgs, typename... Args>

@@ -35,12 +35,14 @@ class LLM:
     def __init__(self, model: str, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_running_reqs: int = 128, num_pages: Optional[int] = None, max_seq_len: int = 4096,
                  page_size: int = DEFAULT_PAGE_SIZE, max_extend_tokens: int = 8192, default_max_output: int = 1024,
-                 chunk_size: Optional[int] = None, runner: Optional[ModelRunner] = None, overlap: bool = False):
+                 chunk_size: Optional[int] = None, runner: Optional[ModelRunner] = None, overlap: bool = False,
+                 fp32_weights: str = "keep"):
         """``model``: a folder with config.json and model.safetensors.  ``num_pages`` None
         sizes the pool for ``max_running_reqs`` requests of ``max_seq_len`` tokens, capped at
         half a million tokens.  ``overlap``: while all running requests decode, the next step is
         enqueued before the tokens of the one before have been read (``Scheduler`` says how);
-        ``step()`` then reports a step's tokens one call later."""
+        ``step()`` then reports a step's tokens one call later.  ``fp32_weights``: "keep" or "round", what becomes
+        of matrices stored in 32-bit when ``dtype`` is bfloat16 (``ModelRunner.build``)."""
         if runner is None:
             config = load_config(model)
             limit = getattr(config, "max_position_embeddings", None)
@@ -50,7 +52,7 @@ class LLM:
                 num_pages = -(-min(max_running_reqs * max_seq_len, 1 << 19) // page_size)
             runner = ModelRunner.from_folder(model, dtype=dtype, device=device, page_size=page_size,
                                              num_pages=num_pages, max_requests=max_running_reqs,
-                                             max_seq_len=max_seq_len)
+                                             max_seq_len=max_seq_len, fp32_weights=fp32_weights)
         self.runner = runner
         cache = runner.cache
         self.config = SchedulerConfig(max_running_reqs=cache.max_requests, num_pages=cache.groups[0].pool.num_pages

@@ -11,6 +11,8 @@ logits and leaves sampling to the caller.
 from __future__ import annotations
 
 import os
+import sys
+import warnings
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -63,14 +65,19 @@ class ModelRunner:
     @classmethod
     def build(cls, config, source_factory, *, dtype="bfloat16", device="cuda:0", page_size: int = DEFAULT_PAGE_SIZE,
               num_pages: Optional[int] = None, max_tokens: Optional[int] = None, max_requests: int = 8,
-              max_seq_len: Optional[int] = None, ops=None) -> "ModelRunner":
+              max_seq_len: Optional[int] = None, ops=None, fp32_weights: str = "keep") -> "ModelRunner":
         """``source_factory(param_table)`` returns the ``WeightSource``.  The pool holds
-        ``num_pages`` pages in each group, or enough for ``max_tokens`` tokens."""
+        ``num_pages`` pages in each group, or enough for ``max_tokens`` tokens.  ``fp32_weights``: what becomes of
+        a matrix stored in 32-bit when ``dtype`` is bfloat16: "keep" (it stays 32-bit and its products run the
+        32-bit kernels; a warning says so) or "round" (to bfloat16, to nearest even; a line reports how many values
+        became infinite or zero)."""
+        if fp32_weights not in ("keep", "round"):
+            raise ValueError(f"fp32_weights must be 'keep' or 'round', found {fp32_weights!r}")
         dt = parse_dtype(dtype)
         if torch.device(device).type == "cuda" and not torch.cuda.is_available():
             raise RuntimeError("vt_transformer_b200 runs on a CUDA device (B200, sm_100a) only; "
                                "torch.cuda.is_available() is False and there is no CPU path")
-        rt = Runtime(device=torch.device(device), dtype=dt, ops=ops if ops is not None else _ops)
+        rt = Runtime(device=torch.device(device), dtype=dt, ops=ops if ops is not None else _ops, fp32_weights=fp32_weights)
         spec = get_architecture(config.architecture).model_spec(config)
         model = DecoderModel(spec, rt)
         source = source_factory(model.param_specs())
@@ -78,6 +85,10 @@ class ModelRunner:
             model.load(source)
         finally:
             source.close()
+        for line in model.load_info:
+            print(f"[vt_transformer_b200] {line}", file=sys.stderr, flush=True)
+        for line in model.load_warnings:
+            warnings.warn(line, stacklevel=2)
         limit = spec.max_positions or None
         if max_seq_len is None:
             max_seq_len = limit or 4096

@@ -1,5 +1,5 @@
-"""A decoder model put together from a ``ModelSpec``: embedding, blocks in their run
-order, final norm, output head.  It names no architecture."""
+"""A decoder model put together from a ``ModelSpec``: an embedding part, blocks in their run
+order, a head part.  It names no architecture and knows no part's kind."""
 from __future__ import annotations
 
 from typing import Dict, List, Optional
@@ -8,7 +8,7 @@ import torch
 
 from ..parts.base import CacheView, ParamSpec, ResidualStream, Runtime, build_part
 from ..parts.specs import ModelSpec
-from ..weights.loader import WeightSource, check_against
+from ..weights.loader import WeightSource, check_against, load_report
 
 
 class DecoderModel:
@@ -22,10 +22,10 @@ class DecoderModel:
     def __init__(self, spec: ModelSpec, rt: Runtime):
         self.spec = spec
         self.rt = rt
+        self.embedding = build_part("embedding", spec.embedding, spec.embedding.name, rt)
         self.blocks = [build_part("block", b, b.prefix, rt) for b in spec.blocks]
-        self.final_norm = build_part("norm", spec.final_norm, spec.final_norm_name, rt)
-        self.embed = None
-        self.head = None
+        self.head = build_part("head", spec.head, spec.head.name, rt)
+        self.load_info, self.load_warnings = [], []
         self._check_order()
 
     # ---- structure -----------------------------------------------------------------
@@ -57,60 +57,43 @@ class DecoderModel:
 
     def graph_safe(self) -> bool:
         """True if a step of this model may be captured as a CUDA graph and replayed."""
-        return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+        return all(p.graph_safe for p in (self.embedding, *self.blocks, self.head))
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        s = self.spec
-        out = {s.embed_name: ParamSpec((s.vocab, s.hidden))}
-        out[s.head_name] = ParamSpec((s.vocab, s.hidden), optional=s.tied_head)
+        out = dict(self.embedding.param_specs())
         for b in self.blocks:
             out.update(b.param_specs())
-        out.update(self.final_norm.param_specs())
+        for name, spec in self.head.param_specs().items():
+            out.setdefault(name, spec)          # a head tied to the embedding names the same tensor
         return out
 
     # ---- weights -------------------------------------------------------------------
     def load(self, source: WeightSource) -> None:
         """Checks the source against the parameter table (one error for all differences),
         then hands each part its tensors."""
-        check_against(source, self.param_specs())
-        s = self.spec
-        self.embed = self.rt.param(source.get(s.embed_name))
-        if s.head_name in source.entries() and not s.tied_head:
-            self.head = self.rt.param(source.get(s.head_name))
-        else:
-            self.head = self.embed
-        for b in self.blocks:
-            b.load(source.get)
-        self.final_norm.load(source.get)
+        aside = check_against(source, self.param_specs(), self.spec.ignored)
+        self.rt.notes.clear()
+        for part in (self.embedding, *self.blocks, self.head):
+            part.load(source.get)
+        self.rt.loaded.clear()                  # the parts hold what they share; nothing else needs the table
+        self.load_info, self.load_warnings = load_report(source, self.rt.notes, aside)
 
     def weight_bytes(self, n_tokens: int = 1) -> int:
         """Bytes of weights a step reads: every block's weights once for each of its runs,
-        the head, the final norm, and the embedding rows of the step's tokens."""
+        the head with its norm, and the embedding rows of the step's tokens."""
         n = sum(self.blocks[r.block].weight_bytes() for r in self.spec.order)
-        n += self.final_norm.weight_bytes()
-        n += self.head.numel() * self.head.element_size()
-        n += n_tokens * self.spec.hidden * self.embed.element_size()
-        return n
+        return n + self.head.weight_bytes() + self.embedding.step_bytes(n_tokens)
 
     # ---- forward -------------------------------------------------------------------
     def forward(self, ctx, views: Dict[int, CacheView]) -> torch.Tensor:
         """Runs the step's tokens and returns float32 logits [wanted rows, vocab].
         ``views[slot]`` is the cache view of a slot for this step."""
-        ops, s = self.rt.ops, self.spec
-        x = torch.empty((ctx.n_tokens, s.hidden), dtype=torch.float32, device=self.rt.device)
-        ops.embedding(self.embed, ctx.token_ids, x, status=ctx.status)
-        stream = ResidualStream(x, status=ctx.status)
-        for run in s.order:
+        stream = ResidualStream(self.embedding.forward(ctx), status=ctx.status)
+        for run in self.spec.order:
             view: Optional[CacheView] = None
             if run.cache is not None and run.cache in views:
                 view = views[run.cache]
                 if view.writes != run.writes:
                     view = CacheView(**{**view.__dict__, "writes": run.writes})
             self.blocks[run.block].forward(stream, ctx, view)
-        n_want = ctx.want_rows.numel()
-        logits = torch.empty((n_want, s.vocab), dtype=torch.float32, device=self.rt.device)
-        if n_want == 0:
-            return logits
-        h = stream.normed(self.final_norm, rows=ctx.want_rows)
-        ops.linear(h, self.head, None, logits)
-        return logits
+        return self.head.forward(stream, ctx)

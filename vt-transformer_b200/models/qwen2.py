@@ -8,7 +8,8 @@ from __future__ import annotations
 
 from ..config.qwen2 import Qwen2Config
 from ..config.registry import register_architecture
-from ..parts.specs import AttentionSpec, BlockSpec, GatedMLPSpec, ModelSpec, NormSpec, PositionSpec
+from ..parts.specs import (AttentionSpec, BlockSpec, EmbeddingSpec, GatedMLPSpec, HeadSpec, ModelSpec, NormSpec,
+                           PositionSpec)
 
 
 def qwen2_model_spec(cfg: Qwen2Config) -> ModelSpec:
@@ -23,9 +24,14 @@ def qwen2_model_spec(cfg: Qwen2Config) -> ModelSpec:
                                 out_bias=False, window=cfg.layer_window(i), position=position),
             ffn=GatedMLPSpec(hidden=cfg.hidden_size, inter=cfg.intermediate_size, activation=cfg.hidden_act),
             norm1=norm, norm2=norm, prefix=f"model.layers.{i}."))
+    embedding = EmbeddingSpec(vocab=cfg.vocab_size, hidden=cfg.hidden_size, name="model.embed_tokens.weight")
+    # the output head is a tensor of its own, or (tie_word_embeddings) the embedding's
+    head = HeadSpec(vocab=cfg.vocab_size, hidden=cfg.hidden_size, norm=norm, norm_name="model.norm", name="lm_head.weight",
+                    tied_to=embedding.name if cfg.tie_word_embeddings else None)
     return ModelSpec(vocab=cfg.vocab_size, hidden=cfg.hidden_size, blocks=tuple(blocks),
-                     order=ModelSpec.default_order(len(blocks)), final_norm=norm,
-                     tied_head=cfg.tie_word_embeddings, max_positions=cfg.max_position_embeddings)
+                     order=ModelSpec.default_order(len(blocks)), embedding=embedding, head=head,
+                     max_positions=cfg.max_position_embeddings,
+                     ignored=("*.rotary_emb.inv_freq",))      # older checkpoints store the rotation's frequencies
 
 
 register_architecture("Qwen2ForCausalLM", Qwen2Config, qwen2_model_spec, replace=True)

@@ -41,9 +41,16 @@ def use_backend(obj) -> None:
 # --------------------------------------------------------------------------- elementwise
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status=None) -> torch.Tensor:
-    backend().embedding(table, ids, out, status)
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status=None, scale: float = 1.0) -> torch.Tensor:
+    """out[t] = scale * table[ids[t]] as float32 rows (id -1: a row of zeros)."""
+    backend().embedding(table, ids, out, status, float(scale))
     return out
+
+
+def logits_scale_cap(logits: torch.Tensor, scale: float = 1.0, cap: float = 0.0) -> torch.Tensor:
+    """logits = cap * tanh(scale * logits / cap) in place, in 32-bit; cap 0 applies the scale alone."""
+    backend().logits_scale_cap(logits, float(scale), float(cap))
+    return logits
 
 
 class SplitSum:
@@ -401,5 +408,5 @@ def _counted(fn):
     return wrapper
 
 
-for _name in ("embedding", "rmsnorm", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # the others count where they launch
+for _name in ("embedding", "logits_scale_cap", "rmsnorm", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # the others count where they launch
     globals()[_name] = _counted(globals()[_name])

@@ -21,6 +21,10 @@ class PagedAttention(Mixer):
 
     def __init__(self, spec, prefix, rt):
         super().__init__(spec, prefix, rt)
+        if spec.position.kind != "none" and spec.position.dim != spec.head_dim:
+            # the rotation kernels turn the whole head, pairs (i, i + head_dim / 2), from a table [positions, head_dim / 2, 2]
+            raise ValueError(f"attention: the position encoding covers {spec.position.dim} of the head's {spec.head_dim} "
+                             f"dimensions; a rotation of part of the head is not built")
         self.position = build_part("position", spec.position, prefix, rt)
         self.q_dim = spec.heads * spec.head_dim
         self.kv_dim = spec.kv_heads * spec.head_dim

@@ -1,6 +1,6 @@
 """Interfaces of the parts a model is put together from, and their registry.
 
-Five categories: ``norm``, ``position``, ``mixer``, ``feed_forward``, ``block``.  A part is
+Seven categories: ``embedding``, ``norm``, ``position``, ``mixer``, ``feed_forward``, ``block``, ``head``.  A part is
 built from its spec (sizes and constants), the prefix of its tensor names and the
 ``Runtime`` (device, compute dtype, kernels).  It says which tensors it wants
 (``param_specs``), takes them (``load``) and runs on the flat token batch of one step.
@@ -47,18 +47,43 @@ class Runtime:
     device: torch.device
     dtype: torch.dtype
     ops: object
+    loaded: Dict[Tuple[str, str], torch.Tensor] = field(default_factory=dict)
+    # what happens to a matrix that is stored in 32-bit when the compute dtype is bfloat16: "keep" (it stays 32-bit
+    # and its products run the 32-bit kernels) or "round" (to bfloat16, round to nearest even)
+    fp32_weights: str = "keep"
+    notes: Dict[str, int] = field(default_factory=dict)      # counts of what ``param`` did, for the load report
+
+    def load(self, get: Callable, name: str, role: str = "matrix") -> torch.Tensor:
+        """``param(get(name), role)``, made once for each (name, role): parts that read the same tensor (an
+        output head tied to the embedding) share one copy on the device."""
+        key = (name, role)
+        if key not in self.loaded:
+            self.loaded[key] = self.param(get(name), role)
+        return self.loaded[key]
 
     def param(self, t: torch.Tensor, role: str = "matrix") -> torch.Tensor:
         """A stored tensor as the kernels read it.  Matrices are used in the compute
         dtype (a bfloat16 tensor is widened exactly for the 32-bit path; a tensor stored
-        in 32-bit stays 32-bit and its products run through the 32-bit kernels).
+        in 32-bit stays 32-bit and its products run through the 32-bit kernels, unless
+        ``fp32_weights`` is "round").
         Vectors are read in 32-bit by every kernel.  Tables are int32."""
         if role == "table":
             return t.to(device=self.device, dtype=torch.int32).contiguous()
         if role == "vector":
             return t.to(device=self.device, dtype=torch.float32).contiguous()
-        if self.dtype == torch.float32 or t.dtype == torch.float32:
+        if self.dtype == torch.float32:
             return t.to(device=self.device, dtype=torch.float32).contiguous()
+        if t.dtype == torch.float32:
+            if self.fp32_weights != "round":
+                self.notes["kept_fp32"] = self.notes.get("kept_fp32", 0) + 1
+                return t.to(device=self.device, dtype=torch.float32).contiguous()
+            wide = t.to(device=self.device)
+            out = wide.to(self.dtype).contiguous()             # round to nearest even
+            for key, n in (("rounded", 1), ("rounded_values", t.numel()),
+                           ("to_inf", int((torch.isinf(out) & torch.isfinite(wide)).sum())),
+                           ("to_zero", int(((out == 0) & (wide != 0)).sum()))):
+                self.notes[key] = self.notes.get(key, 0) + n
+            return out
         return t.to(device=self.device, dtype=self.dtype).contiguous()
 
 
@@ -81,15 +106,57 @@ class StateSpec:
     dtype: torch.dtype = torch.float32
 
 
+@dataclass(frozen=True)
+class PagedLayout:
+    """What a kind of cache spec keeps for every token, in pages.  ``tensors``: (name, outer, inner) for each
+    tensor; the pool's tensor of that name is [pages, outer, page_size, inner] for a slot (keys: outer = KV heads,
+    inner = head size, so that a (page, head) run of keys is contiguous).  ``window`` None keeps all tokens, w
+    the last w: pages that the window has passed go back to the pool."""
+    tensors: Tuple[Tuple[str, int, int], ...]
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateLayout:
+    """A block of fixed size for each request, zero at admission."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+_CACHE_KINDS: Dict[type, Callable] = {}
+
+
+def register_cache_kind(spec_class: type, layout: Callable) -> None:
+    """Tells the cache manager what a kind of cache spec needs: ``layout(spec)`` returns a ``PagedLayout`` or a
+    ``StateLayout``.  Slots whose paged layouts are equal share a pool and a block table for each request."""
+    _CACHE_KINDS[spec_class] = layout
+
+
+def unregister_cache_kind(spec_class: type) -> None:
+    _CACHE_KINDS.pop(spec_class, None)
+
+
+def cache_layout(spec):
+    for cls in type(spec).__mro__:
+        if cls in _CACHE_KINDS:
+            return _CACHE_KINDS[cls](spec)
+    raise TypeError(f"unknown kind of cache spec {spec!r}; known: {', '.join(c.__name__ for c in _CACHE_KINDS) or 'none'} "
+                    f"(parts.register_cache_kind adds one)")
+
+
+register_cache_kind(KVCacheSpec, lambda s: PagedLayout((("k", s.kv_heads, s.head_dim), ("v", s.kv_heads, s.head_dim)), s.window))
+register_cache_kind(StateSpec, lambda s: StateLayout(tuple(s.shape), s.dtype))
+
+
 @dataclass
 class CacheView:
     """What one run of a block sees of the cache.
 
-    For a ``KVCacheSpec`` slot: ``k`` and ``v`` are [pages, kv_heads, page_size, head_dim],
-    ``block_table`` is the int32 device table [sequences of this step, stride] of the slot's
-    group, ``page_size`` the tokens in a page.  For a ``StateSpec`` slot: ``state`` is
-    [request rows, *shape]; the step's ``rows`` index it.  ``writes`` is False for a run
-    that only reads another run's slot."""
+    For a paged slot: ``pages[name]`` is [pages, outer, page_size, inner] for every tensor of the slot's layout
+    (``k`` and ``v``, [pages, kv_heads, page_size, head_dim], are those of a ``KVCacheSpec``), ``block_table`` is the
+    int32 device table [sequences of this step, stride] of the slot's group, ``page_size`` the tokens in a page.
+    For a state slot: ``state`` is [request rows, *shape]; the step's ``rows`` index it.  ``writes`` is False for
+    a run that only reads another run's slot."""
     spec: object = None
     k: Optional[torch.Tensor] = None
     v: Optional[torch.Tensor] = None
@@ -97,6 +164,7 @@ class CacheView:
     page_size: int = 0
     state: Optional[torch.Tensor] = None
     writes: bool = True
+    pages: Optional[Dict[str, torch.Tensor]] = None
 
 
 # ----------------------------------------------------------------------------- parts
@@ -129,10 +197,14 @@ class Part:
 
 class Norm(Part):
     """``__call__(x, delta=None, rows=None)``: x is the 32-bit residual stream [T, H].
-    With ``delta`` the sum x + delta is formed in 32-bit, written back to x, and normed.
-    With ``rows`` (int32 indices) only those rows are done, packed in that order.
-    Returns the normed rows in the compute dtype."""
+    With ``delta`` (a tensor [T, H] of the compute dtype) the sum x + delta is formed in 32-bit, written back to
+    x, and normed.  With ``rows`` (int32 indices) only those rows are done, packed in that order.
+    Returns the normed rows in the compute dtype.
+
+    A norm whose kernel can add the unadded 32-bit shares of a matrix product itself sets ``takes_shares``; it is
+    then given what ``ops.linear_to_stream`` returned as it is.  Any other norm gets an ordinary tensor."""
     category = "norm"
+    takes_shares = False
 
     def __call__(self, x, delta=None, rows=None, status=None):
         raise NotImplementedError
@@ -175,6 +247,27 @@ class Block(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    """``forward(ctx) -> x``: the step's token ids (``ctx.token_ids``, -1 for padding) as the 32-bit residual
+    stream [T, hidden].  ``prefix`` is the tensor's full name.  ``step_bytes(n_tokens)``: bytes it reads a step."""
+    category = "embedding"
+
+    def forward(self, ctx):
+        raise NotImplementedError
+
+    def step_bytes(self, n_tokens: int) -> int:
+        return 0
+
+
+class Head(Part):
+    """``forward(stream, ctx) -> logits``: float32 [wanted rows, vocab] for the rows ``ctx.want_rows`` of the
+    ``ResidualStream`` (whose pending delta it must add: ``stream.normed`` does)."""
+    category = "head"
+
+    def forward(self, stream, ctx):
+        raise NotImplementedError
+
+
 class ResidualStream:
     """The 32-bit residual stream [T, H] and a delta not yet added to it.
 
@@ -191,6 +284,8 @@ class ResidualStream:
 
     def normed(self, norm: Norm, rows=None):
         delta, self.pending = self.pending, None
+        if delta is not None and not isinstance(delta, torch.Tensor) and not getattr(norm, "takes_shares", False):
+            delta = norm.rt.ops.dense(delta, norm.rt.dtype)       # unadded shares, for a norm that wants a tensor
         return norm(self.x, delta=delta, rows=rows, status=self.status)
 
     def add(self, delta) -> None:
@@ -201,7 +296,7 @@ class ResidualStream:
 
 # ----------------------------------------------------------------------------- registry
 
-_CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block")
+_CATEGORIES = ("embedding", "norm", "position", "mixer", "feed_forward", "block", "head")
 _PARTS: Dict[str, Dict[str, Callable]] = {c: {} for c in _CATEGORIES}
 
 

@@ -14,6 +14,7 @@ class RMSNorm(Norm):
     without ".weight"."""
 
     graph_safe = True
+    takes_shares = True        # the kernel adds a product's unadded shares while it reads them
 
     def param_specs(self):
         return {self.prefix + ".weight": ParamSpec((self.spec.size,), role="vector", init="one_plus_normal")}

@@ -105,17 +105,44 @@ class RunSpec:
 
 
 @dataclass(frozen=True)
+class EmbeddingSpec:
+    """How token ids become the residual stream.  ``table``: x[t] = scale * table[id[t]] in 32-bit."""
+    vocab: int
+    hidden: int
+    name: str = "model.embed_tokens.weight"
+    scale: float = 1.0
+    kind: str = "table"
+
+
+@dataclass(frozen=True)
+class HeadSpec:
+    """How the stream's wanted rows become logits.  ``linear``: norm, then the product with a [vocab, hidden]
+    matrix: its own (``name``), or, with ``tied_to``, the tensor of that name (the embedding's; one under ``name``
+    is then allowed in the weights and not read); then logits * logit_scale and, with ``logit_cap`` c > 0,
+    c * tanh(logits / c)."""
+    vocab: int
+    hidden: int
+    norm: NormSpec
+    norm_name: str = "model.norm"
+    name: str = "lm_head.weight"
+    tied_to: Optional[str] = None
+    logit_scale: float = 1.0
+    logit_cap: float = 0.0
+    kind: str = "linear"
+
+
+@dataclass(frozen=True)
 class ModelSpec:
+    """Embedding, blocks in their run order, head: each a part chosen by its spec's kind."""
     vocab: int
     hidden: int
     blocks: Tuple[BlockSpec, ...]
     order: Tuple[RunSpec, ...]
-    final_norm: NormSpec
-    embed_name: str = "model.embed_tokens.weight"
-    final_norm_name: str = "model.norm"
-    head_name: str = "lm_head.weight"
-    tied_head: bool = False
+    embedding: EmbeddingSpec
+    head: HeadSpec
     max_positions: int = 0
+    # patterns (fnmatch) of tensor names that a checkpoint of the architecture may hold and the model does not read
+    ignored: Tuple[str, ...] = ()
 
     @staticmethod
     def default_order(n_blocks: int) -> Tuple[RunSpec, ...]:

@@ -9,12 +9,15 @@ model does not know, wrong shapes and wrong kinds of dtype.
 
 Tensors are handed out as they are stored: bfloat16 stays bfloat16, a tensor stored in
 32-bit stays 32-bit; float16 and float64 (which no kernel reads) become bfloat16 and
-float32; integer tables become int32.
+float32; integer tables become int32.  What was converted is counted (``WeightSource.converted``) and
+reported after loading (``load_report``): vt-transformer's own dump rounds everything to fp16 without a word
+(v1/models/qwen2-7b/dump_from_huggingface.py:35).
 """
 from __future__ import annotations
 
+import fnmatch
 import hashlib
-from typing import Dict, Iterator, Mapping, Tuple
+from typing import Dict, Iterator, List, Mapping, Sequence, Tuple
 
 import torch
 
@@ -53,6 +56,7 @@ class WeightSource:
     data, ``get(name)`` the tensor as stored."""
 
     where = "weights"
+    converted: Dict[str, int]        # stored dtype -> tensors that ``get`` converted from it
 
     def entries(self) -> Dict[str, Tuple[torch.dtype, Tuple[int, ...]]]:
         raise NotImplementedError
@@ -69,12 +73,13 @@ class SafetensorsSource(WeightSource):
         self.where = folder
         self.index = st.index_folder(folder)
         self.files = st.MappedFiles()
+        self.converted = {}
 
     def entries(self):
         return {n: (e.dtype, e.shape) for n, e in self.index.items()}
 
     def get(self, name: str) -> torch.Tensor:
-        return normalise_dtype(self.files.tensor(self.index[name]))
+        return normalise_dtype(self.files.tensor(self.index[name]), self.converted)
 
     def close(self) -> None:
         self.files.close()
@@ -84,19 +89,23 @@ class DictSource(WeightSource):
     def __init__(self, tensors: Mapping[str, torch.Tensor], where: str = "tensors"):
         self.tensors = tensors
         self.where = where
+        self.converted = {}
 
     def entries(self):
         return {n: (t.dtype, tuple(t.shape)) for n, t in self.tensors.items()}
 
     def get(self, name: str) -> torch.Tensor:
-        return normalise_dtype(self.tensors[name])
+        return normalise_dtype(self.tensors[name], self.converted)
 
 
-def normalise_dtype(t: torch.Tensor) -> torch.Tensor:
+def normalise_dtype(t: torch.Tensor, counts: Dict[str, int] = None) -> torch.Tensor:
     if t.dtype in (torch.bfloat16, torch.float32, torch.int32):
         return t
+    if counts is not None:
+        key = str(t.dtype).replace("torch.", "")
+        counts[key] = counts.get(key, 0) + 1
     if t.dtype == torch.float16:
-        return t.to(torch.bfloat16)
+        return t.to(torch.bfloat16)          # round to nearest even; bfloat16's range holds float16's
     if t.dtype == torch.float64:
         return t.to(torch.float32)
     if t.dtype in _INTS:
@@ -104,12 +113,38 @@ def normalise_dtype(t: torch.Tensor) -> torch.Tensor:
     raise TypeError(f"no kernel reads dtype {t.dtype}")
 
 
-def check_against(source: WeightSource, expected: Mapping[str, ParamSpec]) -> None:
+def load_report(source: "WeightSource", notes: Mapping[str, int], ignored: Sequence[str] = ()) -> Tuple[List[str], List[str]]:
+    """(lines to tell, lines to warn of) about what loading changed: tensors converted by the source, matrices
+    rounded from 32-bit or kept in it (``Runtime.notes``), tensors of the folder that the model does not read."""
+    info, warn = [], []
+    conv = getattr(source, "converted", None) or {}
+    if conv.get("float16"):
+        info.append(f"{source.where}: {conv['float16']} tensors stored in float16 were rounded to bfloat16 (to nearest even; "
+                    f"no value can overflow or vanish, bfloat16's range holds float16's)")
+    for key in sorted(k for k in conv if k != "float16"):
+        info.append(f"{source.where}: {conv[key]} tensors stored in {key} were converted")
+    if notes.get("rounded"):
+        info.append(f"{source.where}: {notes['rounded']} matrices stored in float32 ({notes.get('rounded_values', 0):,} values) were "
+                    f"rounded to bfloat16 (to nearest even): {notes.get('to_inf', 0)} values became infinite, "
+                    f"{notes.get('to_zero', 0)} became zero")
+    if notes.get("kept_fp32"):
+        warn.append(f"{source.where}: {notes['kept_fp32']} matrices are stored in float32 and stay so: their products run the "
+                    f"32-bit kernels, many times slower than the bfloat16 ones; fp32_weights='round' (--fp32-weights round) "
+                    f"rounds them to bfloat16 at load")
+    if ignored:
+        warn.append(f"{source.where}: {len(ignored)} tensors that the model does not read were left aside: "
+                    + ", ".join(sorted(ignored)[:6]) + (" ..." if len(ignored) > 6 else ""))
+    return info, warn
+
+
+def check_against(source: WeightSource, expected: Mapping[str, ParamSpec], ignored: Sequence[str] = ()) -> List[str]:
     """Raises one ``WeightError`` that lists every difference between the source and the
-    model's parameter table."""
+    model's parameter table.  Tensors whose names match a pattern of ``ignored`` (names that checkpoints of the
+    architecture are known to carry and the model does not read) are no difference: they are returned."""
     found = source.entries()
     missing = [n for n, s in expected.items() if n not in found and not s.optional]
-    unexpected = [n for n in found if n not in expected]
+    aside = [n for n in found if n not in expected and any(fnmatch.fnmatchcase(n, pat) for pat in ignored)]
+    unexpected = [n for n in found if n not in expected and n not in aside]
     wrong_shape, wrong_dtype = {}, {}
     for name, spec in expected.items():
         if name not in found:
@@ -124,6 +159,7 @@ def check_against(source: WeightSource, expected: Mapping[str, ParamSpec]) -> No
             wrong_dtype[name] = ("a floating-point type", str(dtype))
     if missing or unexpected or wrong_shape or wrong_dtype:
         raise WeightError(source.where, missing, unexpected, wrong_shape, wrong_dtype)
+    return aside
 
 
 # ----------------------------------------------------------------------------- random weights
@@ -156,6 +192,7 @@ class RandomSource(WeightSource):
     def __init__(self, expected: Mapping[str, ParamSpec], seed: int, sigma: float, device="cpu"):
         self.expected = {n: s for n, s in expected.items() if not s.optional}
         self.seed, self.sigma, self.device = seed, sigma, device
+        self.converted = {}
         self.where = f"random weights (seed {seed}, sigma {sigma})"
 
     def entries(self):
