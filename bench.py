@@ -221,6 +221,137 @@ def reference_arm(args) -> int:
     return 0
 
 
+# layer sizes of the two smaller models of the family, for the workloads measured beside the headline
+MODEL_1_5B = dict(MODEL, hidden_size=1536, intermediate_size=8960, num_attention_heads=12, num_key_value_heads=2,
+                  vocab_size=151936, tie_word_embeddings=True, max_window_layers=28)
+MODEL_0_5B = dict(MODEL, hidden_size=896, intermediate_size=4864, num_hidden_layers=24, num_attention_heads=14,
+                  num_key_value_heads=2, head_dim=64, vocab_size=151936, tie_word_embeddings=True, max_window_layers=24)
+
+
+def other_points(pk, dev="cuda:0"):
+    """Three workloads at the sizes of the family's smaller models (random weights, bfloat16, pages of 64), as flat
+    numbers for `points`:
+
+    q15_*: 1.5B sizes, 32 requests at once with prompt lengths uniform in [64, 8192] (seeded) and 128 new tokens
+    each, through ``LLM`` with a budget of 2,048 tokens a step: prompt portions beside decoded tokens.
+    q05_decode_b256*: 0.5B sizes, decode steps of 256 requests after 512-token prompts, with the step's fraction of
+    the HBM roofline.  q05_prefill32k_*: 0.5B sizes, one prompt of 32,768 tokens in portions of 2,048."""
+    import random
+
+    import torch
+    from vt_transformer_b200 import LLM, SamplingParams, ops
+    from vt_transformer_b200.config import config_from_dict
+    from vt_transformer_b200.engine import ModelRunner, StepEntry
+    out = {}
+    gen = torch.Generator().manual_seed(2)
+
+    # ---- 1.5B sizes: 32 concurrent requests, mixed steps
+    cfg = config_from_dict(MODEL_1_5B)
+    rng = random.Random(7)
+    lens = [rng.randint(64, 8192) for _ in range(32)]
+    new = 128
+    runner = ModelRunner.from_random(cfg, seed=0, sigma=0.02, dtype="bfloat16", device=dev, page_size=PAGE,
+                                     num_pages=sum(-(-(n + new + 2) // PAGE) for n in lens) + 8, max_requests=32,
+                                     max_seq_len=8192 + new + PAGE)
+    best = None
+    for rep in range(2):                                    # the first run captures the graphs of its steps
+        llm = LLM(None, runner=runner, max_extend_tokens=2048, overlap=True)
+        for n in lens:
+            llm.add_request(torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist(),
+                            SamplingParams(temperature=0.0, max_tokens=new, ignore_eos=True))
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        produced, mixed, decode = 0, [], []
+        while llm.has_work():
+            t1 = time.perf_counter()
+            res = llm.step()
+            dt = (time.perf_counter() - t1) * 1e3
+            produced += len(res.results)
+            if res.results and res.n_tokens > len(res.results) + 32:
+                mixed.append(dt)
+            elif res.results:
+                decode.append(dt)
+        torch.cuda.synchronize()
+        el = time.perf_counter() - t0
+        if produced != 32 * new:
+            raise RuntimeError(f"1.5B workload: {produced} tokens generated, {32 * new} expected")
+        best = dict(el=el, mixed=mixed, decode=decode) if best is None or el < best["el"] else best
+    out["q15_generated_tok_s"] = round(32 * new / best["el"], 1)
+    out["q15_all_tok_s"] = round((sum(lens) + 32 * new) / best["el"], 1)
+    out["q15_mixed_step_ms"] = round(statistics.median(best["mixed"]), 3) if best["mixed"] else None
+    out["q15_decode_step_ms"] = round(statistics.median(best["decode"]), 3) if best["decode"] else None
+    del llm, runner
+    torch.cuda.empty_cache()
+
+    # ---- 0.5B sizes: decode steps of 256 requests
+    cfg = config_from_dict(MODEL_0_5B)
+    B, P, steps, warm = 256, 512, 64, 6
+    runner = ModelRunner.from_random(cfg, seed=0, sigma=0.02, dtype="bfloat16", device=dev, page_size=PAGE,
+                                     num_pages=B * (P + steps + warm + PAGE) // PAGE + 8, max_requests=B, max_seq_len=1024)
+    rows = [runner.admit() for _ in range(B)]
+    for i in range(0, B, 4):
+        runner.step([StepEntry(r, torch.randint(0, cfg.vocab_size, (P,), generator=gen).tolist(), []) for r in rows[i:i + 4]])
+    tok = torch.empty(B, dtype=torch.int32, device=dev)
+    feeds = [torch.randint(0, cfg.vocab_size, (B,), generator=gen).tolist() for _ in range(steps + warm)]
+
+    def one(i):
+        ops.argmax(runner.step([StepEntry(r, [feeds[i][j]], [0]) for j, r in enumerate(rows)]), tok)
+
+    for i in range(warm):
+        one(i)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for i in range(warm, warm + steps):
+        one(i)
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / steps
+    step_bytes = runner.weight_bytes(B) + runner.cache.bytes_per_token() * (P + warm + (steps - 1) / 2.0 + 1) * B
+    out["q05_decode_b256"] = round(B / (ms / 1e3), 1)
+    out["q05_decode_b256_ms"] = round(ms, 4)
+    out["q05_decode_b256_hbm_frac"] = round(step_bytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+    runner.check_status()
+    del runner
+    torch.cuda.empty_cache()
+
+    # ---- 0.5B sizes: a prompt of 32,768 tokens in portions of 2,048
+    T, C = 32768, 2048
+    runner = ModelRunner.from_random(cfg, seed=0, sigma=0.02, dtype="bfloat16", device=dev, page_size=PAGE,
+                                     num_pages=T // PAGE + 8, max_requests=2, max_seq_len=T)
+    toks = torch.randint(0, cfg.vocab_size, (T,), generator=gen).tolist()
+    best = None
+    for rep in range(2):
+        row = runner.admit()
+        times = []
+        for a in range(0, T, C):
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            runner.step([StepEntry(row, toks[a:a + C], [C - 1] if a + C == T else [])])
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e))
+        runner.release(row)
+        best = times if best is None or sum(times) < sum(best) else best
+    runner.check_status()
+    H, I, L = cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers
+    gemm = L * (2 * T * H * (cfg.q_dim + 2 * cfg.kv_dim) + 2 * T * cfg.q_dim * H + 6 * T * H * I) + 2 * H * cfg.vocab_size
+    attn = L * 4 * (T * (T + 1) // 2) * cfg.head_dim * cfg.num_attention_heads
+    total = sum(best)
+    out["q05_prefill32k_tok_s"] = round(T / (total / 1e3), 1)
+    out["q05_prefill32k_tflops"] = round((gemm + attn) / total / 1e9, 1)
+    out["q05_prefill32k_last_portion_ms"] = round(best[-1], 3)
+    # the last portion: 2,048 tokens over 32,768 keys; its products take what the first portion's take, the rest is attention
+    last_attn = L * 4 * (C * (T - C) + C * (C + 1) // 2) * cfg.head_dim * cfg.num_attention_heads
+    first_attn = L * 4 * (C * (C + 1) // 2) * cfg.head_dim * cfg.num_attention_heads
+    if best[-1] > best[0]:
+        out["q05_attention_last_portion_tflops"] = round((last_attn - first_attn) / (best[-1] - best[0]) / 1e9, 1)
+    del runner
+    torch.cuda.empty_cache()
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -316,8 +447,8 @@ def main() -> int:
         return dict(tok_s=batch * steps / (ms / 1e3), ms_per_step=ms / steps, launches=launched, ctx_mean=ctx_mean,
                     clocks=info)
 
-    def prefill_ms(warm, timed):
-        """One request of 2,048 tokens, one step, logits of the last token: median of `timed` steps in ms."""
+    def prefill_times(warm, timed):
+        """One request of 2,048 tokens, one step, logits of the last token: the times of `timed` steps in ms."""
         times = []
         for i in range(warm + timed):
             row = runner.admit()
@@ -332,22 +463,28 @@ def main() -> int:
                 times.append(s.elapsed_time(e))
             runner.release(row)
         runner.check_status()
-        return statistics.median(times)
+        return times
 
-    points, prefill = {}, None
+    points, prefill, prefill_all = {}, None, []
+    T, H, I, L = PREFILL_TOKENS, cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers
+    per_layer = 2 * T * H * (cfg.q_dim + 2 * cfg.kv_dim) + 2 * T * cfg.q_dim * H + 2 * T * H * 2 * I + 2 * T * I * H
+    attn = 2 * 2 * (T * (T + 1) // 2) * cfg.head_dim * cfg.num_attention_heads
+    flops = L * (per_layer + attn) + 2 * H * vocab
+
+    def prefill_record(times):
+        """The median of all timed prefill steps.  Steps back to back are a load under which the GPU reaches its
+        power cap: `frac` is against the burst peak of the matrix product, `frac_sustained` against the peak of a
+        seconds-long loop."""
+        ms = statistics.median(times)
+        return {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
+                "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(flops / ms / 1e9, 1),
+                "frac_sustained": round(flops / (ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4),
+                "timed_steps": len(times), "ms_min": round(min(times), 3), "ms_max": round(max(times), 3)}
+
     if not args.skip_points:
-        # The prefill is timed first and once more after the decode runs.  Eight steps back to back are a load of
-        # 0.2 s: the GPU reaches its power cap within them, so the median is nearer to a sustained figure than to a
-        # burst (a single step after one warm-up takes about a tenth less).  `frac` is against the burst peak,
-        # `frac_sustained` against the peak of a seconds-long loop.
-        ms = prefill_ms(1, 1) if args.only_prefill else prefill_ms(3, 5)
-        T, H, I, L = PREFILL_TOKENS, cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers
-        per_layer = 2 * T * H * (cfg.q_dim + 2 * cfg.kv_dim) + 2 * T * cfg.q_dim * H + 2 * T * H * 2 * I + 2 * T * I * H
-        attn = 2 * 2 * (T * (T + 1) // 2) * cfg.head_dim * cfg.num_attention_heads
-        flops = L * (per_layer + attn) + 2 * H * vocab
-        prefill = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
-                   "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(flops / ms / 1e9, 1),
-                   "frac_sustained": round(flops / (ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4)}
+        # the prefill is timed before the decode runs and once more after them; the figure is the median of all
+        prefill_all += prefill_times(1, 1) if args.only_prefill else prefill_times(3, 5)
+        prefill = prefill_record(prefill_all)
 
     if args.only_prefill:
         main_run = dict(tok_s=0.0, ms_per_step=1.0, launches=0, ctx_mean=0.0, clocks=None)
@@ -362,15 +499,8 @@ def main() -> int:
         for b in (() if args.only_prefill else (1, 64)):
             points[f"decode_b{b}"] = round(decode_run(b, min(args.steps, 64), 5)["tok_s"], 1)
         if not args.only_prefill:
-            # the better of the two medians is the figure; both are kept
-            after = prefill_ms(1, 3)
-            prefill["ms_before_decode_runs"] = prefill["ms"]
-            prefill["ms_after_decode_runs"] = round(after, 3)
-            if after < ms:
-                scale = ms / after
-                prefill.update(value=round(T / (after / 1e3), 1), ms=round(after, 3), frac=round(prefill["frac"] * scale, 4),
-                               tflops=round(prefill["tflops"] * scale, 1),
-                               frac_sustained=round(prefill["frac_sustained"] * scale, 4))
+            prefill_all += prefill_times(1, 3)
+            prefill = prefill_record(prefill_all)
     if args.skip_e2e:
         print(json.dumps({"value": round(main_run["tok_s"], 1), "ms_per_step": round(main_run["ms_per_step"], 4),
                           "points": points, "prefill": prefill, "note": "partial run (--skip-e2e): not a bench line"}))
@@ -397,6 +527,10 @@ def main() -> int:
     d2h = llm.d2h_bytes_last_step
     for req in list(llm.scheduler.running):
         llm.abort(req.uid)
+    if not args.skip_points and args.layers is None:
+        del llm, runner
+        torch.cuda.empty_cache()
+        points.update(other_points(pk, dev))
 
     clocks = main_run["clocks"] or {}
     line = {
@@ -408,7 +542,8 @@ def main() -> int:
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "global_batch": args.batch, "seq_len": context, "prompt_len": prompt_len,
-                   "mean_context": round(main_run["ctx_mean"], 1), "page_size": PAGE, "parallelism": "1 GPU",
+                   "mean_context": round(main_run["ctx_mean"], 1),
+                   "baseline_mean_context": prompt_len + 128, "page_size": PAGE, "parallelism": "1 GPU",
                    "l2": "inputs larger than L2 (every step reads all weights)", "peaks": pk["source"], "e2e_mode": "step by step" if args.no_overlap else "overlap"},
         "e2e": {"value": round(produced / e2e_s, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": main_run["launches"],
