@@ -102,23 +102,38 @@ def test_missing_extension_fails_loudly():
             ops.backend()
 
 
-def test_single_token_steps_fetch_by_boxes_only_where_a_warp_streams_many_blocks():
-    """The choice between cp.async copies and tensor-map boxes for a decode step's keys is made on the host."""
+def test_single_token_steps_cut_their_keys_by_the_work_and_fetch_by_boxes_where_that_pays():
+    """How a decode step's keys are cut over CTAs, and the choice between cp.async copies and tensor-map boxes for
+    them, are made on the host (148 SMs assumed where there is no device)."""
     import torch
     from vt_transformer_b200 import ops as o
     dev = torch.device("cpu")
-    # batch 8 at 1,024 keys, 3 runs: 32 blocks for 12 warps: copies
-    assert not o._decode_long_runs(32, 32, 3, 128, dev)
-    # batch 64 at 4,096 keys: 128 blocks for the three warps of a CTA: boxes
-    assert o._decode_long_runs(256, 128, 1, 128, dev)
-    assert o._decode_long_runs(256, 128, 1, 64, dev)
-    # other head sizes have no boxes
-    assert not o._decode_long_runs(256, 128, 1, 80, dev)
-    old = o.DECODE_BOXES
+    o._sm_counts[dev] = 148
     try:
-        o.DECODE_BOXES = "never"
-        assert not o._decode_long_runs(256, 128, 1, 128, dev)
-        o.DECODE_BOXES = "always"
-        assert o._decode_long_runs(32, 32, 3, 128, dev) and not o._decode_long_runs(32, 32, 3, 96, dev)
+        # batch 8 of 4 KV heads under a bound of 2,048 keys: a typical sequence (64 blocks) is cut into a cluster of
+        # three runs of 22 blocks; a sequence of 1,040 keys (65 blocks) takes all three, one at the bound longer runs
+        assert o._decode_plan(32, 2048, dev) == (3, 22, False)
+        # batch 64: a CTA a (sequence, KV head) already fills the SMs: no cut
+        assert o._decode_plan(256, 2048, dev) == (1, 0, False)
+        # one sequence of up to 4,096 keys: runs of 8 blocks, more than a cluster holds, met in scratch memory
+        assert o._decode_plan(2, 4096, dev) == (32, 8, True)
+        # 32 sequences of 2 KV heads under a bound of 16,384 keys: their lengths may differ by thousands of keys, so
+        # up to 7 runs of 148 blocks meet in scratch memory and a short sequence takes one CTA
+        assert o._decode_plan(64, 16384, dev) == (7, 148, True)
+        # a short bound is not cut
+        assert o._decode_plan(8, 200, dev) == (1, 0, False)
+        # boxes: where the CTAs run in several rounds (batch 64, any context), or a warp streams many blocks
+        assert o._decode_long_runs(256, 1040, 1, 0, 128, dev) and o._decode_long_runs(256, 1040, 1, 0, 64, dev)
+        assert not o._decode_long_runs(32, 2048, 3, 22, 128, dev)
+        assert o._decode_long_runs(8, 32768, 1, 0, 128, dev)
+        assert not o._decode_long_runs(256, 1040, 1, 0, 80, dev)          # other head sizes have no boxes
+        old = o.DECODE_BOXES
+        try:
+            o.DECODE_BOXES = "never"
+            assert not o._decode_long_runs(256, 1040, 1, 0, 128, dev)
+            o.DECODE_BOXES = "always"
+            assert o._decode_long_runs(32, 2048, 3, 22, 128, dev) and not o._decode_long_runs(32, 2048, 3, 22, 96, dev)
+        finally:
+            o.DECODE_BOXES = old
     finally:
-        o.DECODE_BOXES = old
+        del o._sm_counts[dev]

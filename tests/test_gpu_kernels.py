@@ -259,6 +259,57 @@ def test_single_token_steps_split_the_keys(heads, kv_heads, d, page_size, window
         at += n
 
 
+def last_row_attention(q, k, v, window):
+    """The plain attention's last row, q [heads, d] against all n keys: the plain function itself for short
+    sequences; for long ones (whose n x n scores would take it seconds a head) its formula for that one row."""
+    n, heads = k.shape[0], q.shape[0]
+    if n <= 800:
+        qq = torch.zeros(n, heads, q.shape[1], dtype=torch.float64)
+        qq[n - 1] = q
+        return plain.attention(qq, k, v, window)[n - 1]
+    g = heads // k.shape[1]
+    lo = max(0, n - window) if window else 0
+    out = torch.empty_like(q)
+    for h in range(heads):
+        p = torch.softmax((k[lo:, h // g] @ q[h]) / math.sqrt(q.shape[1]), dim=0)
+        out[h] = p @ v[lo:, h // g]
+    return out
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,page_size,window", [(28, 4, 128, 64, None), (12, 2, 128, 16, None), (14, 2, 64, 32, None),
+                                                               (6, 2, 80, 16, None), (8, 1, 128, 48, 3000)])
+def test_single_token_steps_of_very_different_lengths_meet_in_scratch_memory(heads, kv_heads, d, page_size, window, key_fetch):
+    """A step whose sequences hold from one key to thousands: under a long bound the keys are cut into runs of a
+    fixed number of blocks, so the long sequences take many CTAs (whose results meet in scratch memory and are merged
+    by the CTA that arrives last), the short ones one (which stores its result itself), and CTAs without keys leave
+    at once.  Run twice: the arrival counters are left at zero."""
+    import helpers
+    from vt_transformer_b200 import ops as o
+    dtype = torch.bfloat16
+    torch.manual_seed(31)
+    seq_lens = [5000, 64, 1, 4097, 700, 17, 2300, 129]
+    total = sum(seq_lens)
+    k = torch.randn(total, kv_heads, d, device=DEV).to(dtype)
+    v = torch.randn(total, kv_heads, d, device=DEV).to(dtype)
+    kc, vc, table = paged_cache(k, v, seq_lens, page_size, sum(-(-n // page_size) for n in seq_lens) + 5, dtype, seed=6)
+    T = len(seq_lens)
+    q = (torch.randn(T, heads, d, device=DEV) * 2).to(dtype)
+    qkv = torch.cat([q.view(T, -1), torch.zeros(T, 2 * kv_heads * d, device=DEV, dtype=dtype)], dim=1).contiguous()
+    ctx = helpers.step_context([1] * T, [n - 1 for n in seq_lens], DEV)
+    splits, run, scratch = o._decode_plan(T * kv_heads, min(max(seq_lens), window + 31) if window else max(seq_lens), torch.device(DEV))
+    assert scratch == (window is None) and splits > 1 and run > 0
+    for _ in range(2):
+        out = torch.full((T, heads * d), float("nan"), device=DEV, dtype=dtype)
+        o.paged_attention(qkv, out, kc, vc, ctx, table, heads, kv_heads, d, window, 1 / math.sqrt(d))
+        at = 0
+        for i, n in enumerate(seq_lens):
+            ref = last_row_attention(q[i].cpu().double(), k[at:at + n].cpu().double(), v[at:at + n].cpu().double(), window)
+            close(out[i].view(heads, d), ref, dtype, 4)
+            at += n
+    counters = o._counters.get(torch.device(DEV))
+    assert counters is None or int(counters.abs().sum()) == 0
+
+
 @pytest.mark.parametrize("heads,kv_heads,d,page_size,n_seqs,longest", [(28, 4, 128, 16, 50, 300), (8, 2, 64, 32, 90, 200),
                                                                         (14, 2, 128, 64, 40, 1500), (6, 2, 80, 16, 80, 100)])
 def test_single_token_steps_with_more_ctas_than_sms(heads, kv_heads, d, page_size, n_seqs, longest, key_fetch):
@@ -321,10 +372,10 @@ def test_keys_fetched_as_boxes_give_the_same_bits_as_copies(heads, kv_heads, d, 
     assert not bool(torch.isnan(outs["never"].float()).any())
     assert torch.equal(outs["never"], outs["always"])
     # and the automatic choice takes boxes here
-    blocks = -(-(min(max(seq_lens), window + 31) if window else max(seq_lens)) // 32)
-    splits = o._decode_splits(T * kv_heads, blocks, torch.device(DEV))
+    span = min(max(seq_lens), window + 31) if window else max(seq_lens)
+    splits, run, _ = o._decode_plan(T * kv_heads, span, torch.device(DEV))
     if not window:
-        assert o._decode_long_runs(T * kv_heads, blocks, splits, d, torch.device(DEV))
+        assert o._decode_long_runs(T * kv_heads, span, splits, run, d, torch.device(DEV))
 
 
 @pytest.mark.parametrize("heads,kv_heads,d,page_size,window,rotate", [(28, 4, 128, 16, None, True), (6, 2, 48, 32, 40, True),
@@ -467,6 +518,15 @@ def test_tcgen05_product_leaves_its_shares_unadded_and_the_norm_adds_them(m, n, 
     bias = torch.randn(n, device=DEV)
     ref = plain.linear(x.cpu().double(), w.cpu().double(), bias.cpu().double())
     got = o.linear_to_stream(x, w, bias)
+    if m > 128 and n * k * 2 <= o.STREAM_SMALL_WEIGHT_BYTES:
+        # a small matrix under a wide batch: an ordinary tensor from the kernel with x as the 128-row operand
+        assert isinstance(got, torch.Tensor) and got.dtype == torch.bfloat16 and tuple(got.shape) == (m, n)
+        close(got, ref, torch.bfloat16, 2)
+        forced, o.STREAM_SMALL_WEIGHT_BYTES = o.STREAM_SMALL_WEIGHT_BYTES, 0          # and the shares, as for the other sizes
+        try:
+            got = o.linear_to_stream(x, w, bias)
+        finally:
+            o.STREAM_SMALL_WEIGHT_BYTES = forced
     assert isinstance(got, o.SplitSum) and got.shares.dtype == torch.float32
     assert got.shares.shape == (o.backend().gemm_tc_shares(m, n, k), m, n) and tuple(got.shape) == (m, n)
     close(o.dense(got), ref, torch.float32, 40)

@@ -94,7 +94,7 @@ def test_decode_with_keys_cut_into_more_runs_than_a_cluster_holds(tmp_path, dtyp
     seqs = _sequences("D", 1, seed=7, shortest=2100, longest=2100)
     ref = helpers.plain_logits(folder, seqs[0])
     bound = helpers.tol(dtype, ref=ref)
-    assert ops._decode_splits(2, 4096 // 32, DEV) > 8
+    assert ops._decode_plan(2, 4096, torch.device(DEV))[0] > 8 and ops._decode_plan(2, 4096, torch.device(DEV))[2]
     for others in (0, 2):
         batch = seqs + _sequences("D", others, seed=8, longest=90)
         runner = scenarios.shared_runner(folder, DEV, dtype, num_pages=sum(-(-len(s) // 16) for s in batch),

@@ -144,12 +144,12 @@ def _rewrite(src_folder, dst_folder, change, extra=None):
 
 
 def wide_and_rounded_folders(tmp):
-    """A folder stored in float32 whose values bfloat16 cannot hold exactly, and one that stores those values
-    rounded to bfloat16."""
+    """A folder stored in float32 whose values bfloat16 cannot hold exactly, and one that stores its matrices
+    rounded to bfloat16 (vectors, that is norm weights and biases, are read in 32-bit in both modes and stay)."""
     g = torch.Generator().manual_seed(3)
     base = helpers.make_folder("B", os.path.join(tmp, "bf16"))
     wide = _rewrite(base, os.path.join(tmp, "f32"), lambda n, t: t.float() + 1e-4 * torch.randn(t.shape, generator=g))
-    rounded = _rewrite(wide, os.path.join(tmp, "rounded"), lambda n, t: t.to(torch.bfloat16))
+    rounded = _rewrite(wide, os.path.join(tmp, "rounded"), lambda n, t: t.to(torch.bfloat16) if t.dim() == 2 else t)
     return wide, rounded
 
 

@@ -11,14 +11,17 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
                                     int n_seqs, int n_pages, int n_tokens, int heads, int kv_heads, int head_dim,
                                     int page_size, int window, float scale, int n_splits, float* part_o, float* part_ml,
                                     int* counters, int fuse_rope, const float2* cos_sin, int max_pos, int store_kv,
-                                    const float* qkv_shares, int n_shares, int long_runs, int* status, cudaStream_t stream) {
+                                    const float* qkv_shares, int n_shares, int long_runs, int run_blocks, int* status,
+                                    cudaStream_t stream) {
     if (n_seqs == 0 || n_tokens == 0) return cudaSuccess;
     if (!attention_mma_supports(head_dim, heads, kv_heads, 1) || page_size % 16 != 0) return cudaErrorInvalidValue;
     if (n_splits < 1) n_splits = 1;
     if (n_splits > 64) return cudaErrorInvalidValue;   // the merge keeps a weight a run in shared memory
-    // up to 8 runs are the CTAs of a cluster and need no scratch; more go through scratch and a counter
-    const bool cluster = n_splits > 1 && n_splits <= 8;
+    // up to 8 runs are the CTAs of a cluster and need no scratch; more, or any number where the caller gives scratch,
+    // go through scratch and a counter
     if (n_splits > 8 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return cudaErrorInvalidValue;
+    const bool with_scratch = part_o != nullptr && part_ml != nullptr && counters != nullptr;
+    const bool cluster = n_splits > 1 && n_splits <= 8 && !with_scratch;
     AttnParams p;
     p.cluster_merge = cluster ? 1 : 0;
     p.qkv = (const __nv_bfloat16*)qkv;
@@ -40,6 +43,7 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
     p.tokens_per_tile = fuse_rope ? 1 : 16 / (heads / kv_heads);
     p.run_keys = long_runs ? 1 : 0;                  // the launcher of a head size with boxes sets the rows of a box
     p.n_splits = n_splits;
+    p.run_blocks = run_blocks > 0 ? run_blocks : 0;
     p.part_o = part_o;
     p.part_ml = part_ml;
     p.n_tokens = n_tokens;

@@ -29,17 +29,22 @@ namespace {
 // (n_splits > 1): up to 8 runs are the CTAs of a cluster and merge through distributed shared memory; with more
 // the CTA leaves its merged result in scratch and counts itself in, and the CTA that arrives last merges the
 // runs and stores, so there is no second kernel and no CTA waits for another.
-constexpr int DKB = 32;    // keys in a warp's block
-constexpr int DWARPS = 4;   // warps of a CTA; 3 where two CTAs are to fit an SM (more CTAs than SMs)
+constexpr int DKB = 16;    // keys in a warp's block
+constexpr int DHALVES = DKB / 16;   // runs of 16 keys in a block: each lies in one page
+constexpr int DFULL = (1 << DHALVES) - 1;
+constexpr int DWARPS_MAX = 8;     // most warps of a CTA
+constexpr int DSTAGES_MAX = 4;    // most stages of a warp's ring
 // Head sizes of whole 128-byte lines (64, 128): a block's keys and values can come as boxes of a tensor map, one
 // request of the copy engine for 16 or 32 rows of 128 bytes where the other head sizes issue a 16-byte cp.async
 // a lane and piece (whose issue rate, not the memory, bounded the kernel).  A box lands with the 128-byte swizzle:
 // piece c of row r at piece c ^ (r % 8), so that ldmatrix finds eight rows' pieces in eight different banks
 // without padding.
 constexpr bool decode_by_boxes(int d) { return d % 64 == 0; }
-constexpr int DTILE = DKB * 128;   // bytes of a box-loaded tile: 32 rows of 64 values
-// bytes of a warp's two stages of keys and values
-constexpr int decode_warp_bytes(int d, bool boxes) { return boxes ? 2 * 2 * (d / 64) * DTILE : 2 * 2 * DKB * (d + 8) * 2; }
+constexpr int DTILE = DKB * 128;   // bytes of a box-loaded tile: DKB rows of 64 values
+// bytes of the stages of a warp's ring, keys and values
+constexpr int decode_warp_bytes(int d, bool boxes, int stages) {
+    return boxes ? stages * 2 * (d / 64) * DTILE : stages * 2 * DKB * (d + 8) * 2;
+}
 
 //
 // NARROW (at most 8 rows, that is one token of a group of up to 8 heads): the products are taken the other way
@@ -49,19 +54,20 @@ constexpr int decode_warp_bytes(int d, bool boxes) { return boxes ? 2 * 2 * (d /
 //
 // BOXES: see decode_by_boxes.  A box takes longer to arrive than a cp.async; it pays where a warp has many blocks
 // to stream (long contexts), not where it has three.
-template <int D, int W, bool NARROW, bool BOXES>
+template <int D, int W, int S, bool NARROW, bool BOXES>
 __global__ void __launch_bounds__(W * 32)
 attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v) {
     static_assert(!BOXES || decode_by_boxes(D), "boxes are rows of whole 128-byte lines");
     constexpr int LD = D + 8;                                 // row length without boxes: padded against bank conflicts
-    constexpr int WARP_BYTES = decode_warp_bytes(D, BOXES);   // K and V, two stages
-    constexpr int STAGE_BYTES = WARP_BYTES / 2;               // with boxes: [K tiles of 64 d][V tiles of 64 d]
+    static_assert(S >= 2 && S <= DSTAGES_MAX && W <= DWARPS_MAX, "a barrier a warp and stage");
+    constexpr int WARP_BYTES = decode_warp_bytes(D, BOXES, S);   // K and V, S stages
+    constexpr int STAGE_BYTES = WARP_BYTES / S;                  // with boxes: [K tiles of 64 d][V tiles of 64 d]
     extern __shared__ __align__(16) unsigned char smem_dyn[];
     // swizzled tiles start on a 1,024-byte boundary
     unsigned char* smem_raw = BOXES ? reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023) : smem_dyn;
     __shared__ int last_flag;
-    __shared__ __align__(8) uint64_t arrived[DWARPS][2];      // with boxes: a warp's stage has arrived
+    __shared__ __align__(8) uint64_t arrived[DWARPS_MAX][DSTAGES_MAX];      // with boxes: a warp's stage has arrived
     // The kernels before this one in the stream may still be running (programmatic dependent launch).  What
     // the step's description says (lengths, block tables: copied from the host before the step's first kernel)
     // and the keys and values of earlier steps may be read at once; q, and a key or value written in this
@@ -90,11 +96,22 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
     key_lo = key_lo / DKB * DKB;
     const int key_hi = pos_hi + 1;
     const int nblk = (key_hi - key_lo + DKB - 1) / DKB;
-    const int blk0 = (int)((long long)split * nblk / p.n_splits), blk1 = (int)((long long)(split + 1) * nblk / p.n_splits);
+    // The runs of this sequence: n_splits equal ones, or, with run_blocks, as many as make runs of about that many
+    // blocks (between two thirds and one and a half of it), so that sequences of different lengths give CTAs of
+    // like work; the CTAs beyond them have no keys.
+    int runs = p.n_splits;
+    if (p.run_blocks > 0) runs = min(p.n_splits, max(1, (nblk + p.run_blocks / 2) / p.run_blocks));
+    const bool idle = split >= runs;
+    if (idle && !p.cluster_merge) {                            // nobody waits for this CTA
+        pdl_wait();
+        return;
+    }
+    const int blk0 = idle ? 0 : (int)((long long)split * nblk / runs), blk1 = idle ? 0 : (int)((long long)(split + 1) * nblk / runs);
+    const bool alone = p.n_splits == 1 || (!p.cluster_merge && runs == 1);   // this CTA's result is the sequence's
 
     unsigned char* wbase = smem_raw + (size_t)warp * WARP_BYTES;
-    __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(wbase);                 // without boxes: [2][DKB][LD]
-    __nv_bfloat16* vs = ks + 2 * DKB * LD;
+    __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(wbase);                 // without boxes: [S][DKB][LD]
+    __nv_bfloat16* vs = ks + S * DKB * LD;
     // the 16-byte piece c (d 8 c .. 8 c + 7) of row r of a stage's keys or values
     auto kpiece = [&](int stage, int r, int c) -> __nv_bfloat16* {
         if constexpr (BOXES)
@@ -111,8 +128,8 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
     };
     if constexpr (BOXES) {
         if (lane == 0) {
-            mbar_init(&arrived[warp][0], 1);
-            mbar_init(&arrived[warp][1], 1);
+#pragma unroll
+            for (int st = 0; st < S; ++st) mbar_init(&arrived[warp][st], 1);
             asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         }
@@ -131,35 +148,39 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
         head[i] = kvh * group + (valid[i] ? row[i] % group : 0);
     }
     const int* table = p.block_table + (size_t)seq * p.table_stride;
-    // the pages of a block's two runs of 16 keys (-1: none); looked up a block ahead of the block's loads
-    auto pages_of = [&](int blk, int (&pg)[2]) {
+    // the page and the place in it of a key: by shift and mask where a page holds a power of two of tokens
+    const int pshift = (p.page_size & (p.page_size - 1)) == 0 ? 31 - __clz(p.page_size) : -1;
+    auto page_index = [&](int key) -> int { return pshift >= 0 ? key >> pshift : key / p.page_size; };
+    auto in_page = [&](int key) -> int { return pshift >= 0 ? key & (p.page_size - 1) : key % p.page_size; };
+    // the pages of a block's runs of 16 keys (-1: none); looked up a block ahead of the block's loads
+    auto pages_of = [&](int blk, int (&pg)[DHALVES]) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < DHALVES; ++h) {
             const int key = key_lo + blk * DKB + 16 * h;
-            pg[h] = (blk < blk1 && key < key_hi) ? table[key / p.page_size] : -1;
+            pg[h] = (blk < blk1 && key < key_hi) ? table[page_index(key)] : -1;
         }
     };
     // Sends for a block's keys and values; the answer says which halves of 16 keys were asked for (bit h).
-    auto load_block = [&](int blk, int stage, const int (&pg)[2]) -> int {
+    auto load_block = [&](int blk, int stage, const int (&pg)[DHALVES]) -> int {
         const int kb = key_lo + blk * DKB;
         if constexpr (BOXES) {
-            const int br = p.run_keys;               // rows of a box: 32, or 16 where a page is no multiple of 32
+            const int br = p.run_keys;               // rows of a box: the block's, or 16 where a page is no multiple of the block
             int asked = 0;
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int h = 0; h < DHALVES; ++h)
                 if (kb + 16 * h < key_hi && pg[h] >= 0 && pg[h] < p.n_pages) asked |= 1 << h;
-            if (br == 32) asked = (asked & 1) ? 3 : 0;   // one page holds the block: its first half decides
+            if (br == DKB) asked = (asked & 1) ? DFULL : 0;   // one page holds the block: its first run decides
             if (lane == 0) {
                 uint64_t* bar = &arrived[warp][stage];
-                const int boxes = br == 32 ? (asked ? 1 : 0) : __popc(asked);
+                const int boxes = br == DKB ? (asked ? 1 : 0) : __popc(asked);
                 if (boxes == 0) {
                     mbar_arrive(bar);
                 } else {
                     mbar_expect_tx(bar, (uint32_t)(boxes * 2 * (D / 64) * br * 128));
-                    for (int h = 0; h < 32 / br; ++h) {
-                        if (!(asked >> h & 1)) continue;
+                    for (int h = 0; h < DKB / br; ++h) {
+                        if (!(asked >> (h * (br / 16)) & 1)) continue;
                         const int key = kb + h * br;
-                        const int y = (pg[h] * p.kv_heads + kvh) * p.page_size + key % p.page_size;
+                        const int y = (pg[h * (br / 16)] * p.kv_heads + kvh) * p.page_size + in_page(key);
                         unsigned char* dst = wbase + stage * STAGE_BYTES + h * br * 128;
 #pragma unroll
                         for (int t = 0; t < D / 64; ++t) {
@@ -172,24 +193,26 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
             return asked;
         }
         constexpr int CHUNKS = D / 8;
-        size_t base[2];
-        bool okp[2];
+        size_t base[DHALVES];
+        bool okp[DHALVES];
+        bool all_ok = true;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < DHALVES; ++h) {
             const int key = kb + 16 * h;
             okp[h] = key < key_hi && pg[h] >= 0 && pg[h] < p.n_pages;
-            base[h] = okp[h] ? (((size_t)pg[h] * p.kv_heads + kvh) * p.page_size + key % p.page_size) * D : 0;
+            base[h] = okp[h] ? (((size_t)pg[h] * p.kv_heads + kvh) * p.page_size + in_page(key)) * D : 0;
+            all_ok = all_ok && okp[h];
         }
         if constexpr (32 % CHUNKS == 0) {
             // A whole block of a head size whose rows are a power of two long: the lane's first row and its piece
             // of it are found once; every further copy lies a constant number of bytes from them.
-            if (okp[0] && okp[1] && kb + DKB <= key_hi) {
+            if (all_ok && kb + DKB <= key_hi) {
                 constexpr int RPI = 32 / CHUNKS;         // rows that the warp's lanes cover in one turn
                 const int r0 = lane / CHUNKS, piece = lane % CHUNKS;
                 const unsigned ks0 = (unsigned)__cvta_generic_to_shared(ks + ((size_t)stage * DKB + r0) * LD + piece * 8);
                 const unsigned vs0 = (unsigned)__cvta_generic_to_shared(vs + ((size_t)stage * DKB + r0) * LD + piece * 8);
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
+                for (int h = 0; h < DHALVES; ++h) {
                     const __nv_bfloat16* kg0 = p.k_cache + base[h] + (size_t)r0 * D + piece * 8;
                     const __nv_bfloat16* vg0 = p.v_cache + base[h] + (size_t)r0 * D + piece * 8;
 #pragma unroll
@@ -199,37 +222,54 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
                         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(vs0 + r * LD * 2), "l"(vg0 + i * RPI * D));
                     }
                 }
-                return 3;
+                return DFULL;
             }
         }
         for (int c = lane; c < DKB * CHUNKS; c += 32) {
             const int r = c / CHUNKS, piece = c % CHUNKS;
             const int h = r >> 4;
-            const bool ok = (h == 0 ? okp[0] : okp[1]) && (kb + r) < key_hi;
-            const size_t off = (h == 0 ? base[0] : base[1]) + (size_t)(r & 15) * D + piece * 8;
+            const bool ok = okp[h] && (kb + r) < key_hi;
+            const size_t off = base[h] + (size_t)(r & 15) * D + piece * 8;
             cp_async16(ks + ((size_t)stage * DKB + r) * LD + piece * 8, p.k_cache + (ok ? off : 0), ok);
             cp_async16(vs + ((size_t)stage * DKB + r) * LD + piece * 8, p.v_cache + (ok ? off : 0), ok);
         }
-        return 3;                                    // rows that were not asked for are filled with zeros
+        return DFULL;                                // rows that were not asked for are filled with zeros
     };
 
     const int first = blk0 + warp;
-    // the warp's first block: its keys are of earlier steps, unless the step's own token lies in it and
-    // another kernel of this step has put it there
-    const bool own_in_first = pos_lo >= key_lo + first * DKB && pos_lo < key_lo + (first + 1) * DKB;
-    const bool early = first < blk1 && (!own_in_first || (p.fuse_rope && p.store_kv));
-    int pg_cur[2], pg_next[2];
-    pages_of(first, pg_cur);
-    pages_of(first + W, pg_next);
-    int asked[2] = {3, 3};                            // which halves of a stage's block were asked for
-    if (early) {
-        asked[0] = load_block(first, 0, pg_cur);
-        if constexpr (!BOXES) cp_async_commit();
+    // The warp's ring: block j of the warp (first + j W) lies in stage j % S.  Before the loop the first S - 1 blocks
+    // are sent for, and every turn of the loop sends for the block S - 1 turns ahead, so that S - 1 blocks are on
+    // their way while one is worked on.  A block of earlier steps' keys may be sent for before the dependency wait;
+    // the block with the step's own token only if this kernel itself puts the token there (otherwise another kernel
+    // of the step may still be writing it): the early blocks are a prefix of the warp's blocks.
+    auto early_ok = [&](int blk) -> bool {
+        const int kb_ = key_lo + blk * DKB;
+        return blk < blk1 && (!(pos_lo >= kb_ && pos_lo < kb_ + DKB) || (p.fuse_rope && p.store_kv));
+    };
+    unsigned asked_bits = 0;                          // which runs of 16 keys of a stage's block were asked for
+    auto set_asked = [&](int stage, int a) {
+        asked_bits = (asked_bits & ~((unsigned)DFULL << (stage * DHALVES))) | ((unsigned)a << (stage * DHALVES));
+    };
+    int pg_pro[S - 1][DHALVES], pg_next[DHALVES];
+#pragma unroll
+    for (int j = 0; j < S - 1; ++j) pages_of(first + j * W, pg_pro[j]);
+    pages_of(first + (S - 1) * W, pg_next);
+    int sent = 0;                                     // blocks of the prologue sent for before the wait
+#pragma unroll
+    for (int j = 0; j < S - 1; ++j) {
+        if (sent == j && early_ok(first + j * W)) {
+            set_asked(j, load_block(first + j * W, j, pg_pro[j]));
+            if constexpr (!BOXES) cp_async_commit();
+            sent = j + 1;
+        }
     }
     pdl_wait();
-    if (first < blk1 && !early) {
-        asked[0] = load_block(first, 0, pg_cur);
-        if constexpr (!BOXES) cp_async_commit();
+#pragma unroll
+    for (int j = 0; j < S - 1; ++j) {
+        if (j >= sent) {
+            if (first + j * W < blk1) set_asked(j, load_block(first + j * W, j, pg_pro[j]));
+            if constexpr (!BOXES) cp_async_commit();  // a group a block of the prologue, empty where there is no block
+        }
     }
     uint32_t qf[D / 16][4];
     // With q, k and v as unadded shares (one token a sequence): this CTA's part of the token's row, that is its
@@ -310,28 +350,25 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
         npos[c] = pos_lo + (nvalid[c] ? (2 * tq + c) / group : 0);
     }
 
-    int it = 0;
-    for (int blk = first; blk < blk1; blk += W, ++it) {
-        const int stage = it & 1;
+    int stage = 0, phase = 0;
+    for (int blk = first; blk < blk1; blk += W) {
         const int kb = key_lo + blk * DKB;
-        if (blk + W < blk1) {
-            const int a = load_block(blk + W, stage ^ 1, pg_next);
-            if (stage) asked[0] = a; else asked[1] = a;
-            if constexpr (!BOXES) cp_async_commit();
-            pages_of(blk + 2 * W, pg_next);        // for the next turn; the answer comes under this block's work
-            if constexpr (!BOXES) cp_async_wait<1>();
-        } else {
-            if constexpr (!BOXES) cp_async_wait<0>();
+        {
+            const int nb = blk + (S - 1) * W, ns = stage == 0 ? S - 1 : stage - 1;   // the stage worked on a turn ago
+            if (nb < blk1) set_asked(ns, load_block(nb, ns, pg_next));
+            if constexpr (!BOXES) cp_async_commit();   // a group a turn, empty where there was nothing to send for
+            pages_of(nb + W, pg_next);                 // for the next turn; the answer comes under this block's work
+            if constexpr (!BOXES) cp_async_wait<S - 1>();
         }
         if constexpr (BOXES) {
-            if (!mbar_wait(&arrived[warp][stage], (it >> 1) & 1)) {         // the clock limit ran out: give up, say so
+            if (!mbar_wait(&arrived[warp][stage], phase)) {         // the clock limit ran out: give up, say so
                 if (lane == 0) set_status(p.status, kStatusWaitTimeout, blk);
                 break;
             }
             // Rows that no box brought, and rows of a box behind the last key, hold what the memory held; a weight of
             // zero times that may be no number: their values are cleared.
-            const int have = stage ? asked[1] : asked[0];
-            if (have != 3 || kb + DKB > key_hi) {
+            const int have = (asked_bits >> (stage * DHALVES)) & DFULL;
+            if (have != DFULL || kb + DKB > key_hi) {
                 for (int r = 0; r < DKB; ++r) {
                     if ((have >> (r >> 4) & 1) && kb + r < key_hi) continue;
                     if (lane < D / 8) *reinterpret_cast<uint4*>(vpiece(stage, r, lane)) = make_uint4(0u, 0u, 0u, 0u);
@@ -401,16 +438,29 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
                 }
             }
             float mnew[2] = {mrow[0], mrow[1]};
+            // a block all of whose keys every token sees needs no comparison of positions (rows beyond the valid
+            // ones hold q = 0 and are never stored: they may run along)
             const bool open = (kb + DKB - 1 <= pos_lo) && (p.window <= 0 || kb > pos_hi - p.window);
+            if (open) {
 #pragma unroll
-            for (int kt = 0; kt < DKB / 16; ++kt) {
+                for (int kt = 0; kt < DKB / 16; ++kt) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int c = e & 1;
-                    const int key = kb + kt * 16 + gq + (e >> 1) * 8;
-                    const bool see = nvalid[c] && (open || (key <= npos[c] && (p.window <= 0 || key > npos[c] - p.window)));
-                    st[kt][e] = see ? st[kt][e] * p.scale_log2 : -INFINITY;
-                    mnew[c] = fmaxf(mnew[c], st[kt][e]);
+                    for (int e = 0; e < 4; ++e) {
+                        st[kt][e] *= p.scale_log2;
+                        mnew[e & 1] = fmaxf(mnew[e & 1], st[kt][e]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int kt = 0; kt < DKB / 16; ++kt) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = e & 1;
+                        const int key = kb + kt * 16 + gq + (e >> 1) * 8;
+                        const bool see = nvalid[c] && key <= npos[c] && (p.window <= 0 || key > npos[c] - p.window);
+                        st[kt][e] = see ? st[kt][e] * p.scale_log2 : -INFINITY;
+                        mnew[c] = fmaxf(mnew[c], st[kt][e]);
+                    }
                 }
             }
             float corr[2];
@@ -419,7 +469,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
                 mnew[c] = fmaxf(mnew[c], __shfl_xor_sync(0xffffffffu, mnew[c], 4));
                 mnew[c] = fmaxf(mnew[c], __shfl_xor_sync(0xffffffffu, mnew[c], 8));
                 mnew[c] = fmaxf(mnew[c], __shfl_xor_sync(0xffffffffu, mnew[c], 16));
-                corr[c] = (mnew[c] == -INFINITY) ? 1.f : exp2f(mrow[c] - mnew[c]);
+                corr[c] = (mnew[c] == -INFINITY) ? 1.f : fast_exp2(mrow[c] - mnew[c]);
                 mrow[c] = mnew[c];
                 lrow[c] *= corr[c];
             }
@@ -428,7 +478,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
             for (int kt = 0; kt < DKB / 16; ++kt) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float pv = exp2f(st[kt][e] - base2[e & 1]);
+                    const float pv = fast_exp2(st[kt][e] - base2[e & 1]);
                     st[kt][e] = pv;
                     lrow[e & 1] += pv;
                 }
@@ -500,7 +550,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
             for (int i = 0; i < 2; ++i) {
                 mnew[i] = fmaxf(mnew[i], __shfl_xor_sync(0xffffffffu, mnew[i], 1));
                 mnew[i] = fmaxf(mnew[i], __shfl_xor_sync(0xffffffffu, mnew[i], 2));
-                corr[i] = (mnew[i] == -INFINITY) ? 1.f : exp2f(mrow[i] - mnew[i]);
+                corr[i] = (mnew[i] == -INFINITY) ? 1.f : fast_exp2(mrow[i] - mnew[i]);
                 mrow[i] = mnew[i];
                 lrow[i] *= corr[i];
             }
@@ -509,7 +559,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
             for (int j = 0; j < DKB / 8; ++j) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float pv = exp2f(s[j][e] - base2[e >> 1]);
+                    const float pv = fast_exp2(s[j][e] - base2[e >> 1]);
                     s[j][e] = pv;
                     lrow[e >> 1] += pv;
                 }
@@ -539,7 +589,12 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
             }
         }
         __syncwarp();
+        if (++stage == S) {
+            stage = 0;
+            phase ^= 1;
+        }
     }
+    if constexpr (!BOXES) cp_async_wait<0>();         // (only empty groups are left)
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         if constexpr (NARROW) {
@@ -599,7 +654,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
         for (int w = 0; w < W; ++w) {
             const float* b = reinterpret_cast<const float*>(smem_raw + (size_t)w * WARP_BYTES);
             const float l = b[16 * D + 16 + r];
-            const float wg = (l > 0.f) ? exp2f(b[16 * D + r] - mx) : 0.f;
+            const float wg = (l > 0.f) ? fast_exp2(b[16 * D + r] - mx) : 0.f;
             wwgt[r * W + w] = wg;
             tot += l * wg;
         }
@@ -616,7 +671,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
             acc += reinterpret_cast<const float*>(smem_raw + (size_t)w * WARP_BYTES)[e] * wwgt[r * W + w];
         const float mx = res[16 * D + r], tot = res[16 * D + 16 + r];
         const int t = q_begin + r / group, h = kvh * group + r % group;
-        if (p.n_splits == 1) {
+        if (alone) {
             p.out[((size_t)t * p.heads + h) * D + d] = __float2bfloat16_rn(tot > 0.f ? acc / tot : 0.f);
         } else if (p.cluster_merge) {
             res[e] = acc;
@@ -629,7 +684,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
             }
         }
     }
-    if (p.n_splits == 1) return;
+    if (alone) return;
     if (p.cluster_merge) {
         // the runs are the CTAs of one cluster: each takes a share of the elements and reads every
         // CTA's result through distributed shared memory, runs added in rank order
@@ -655,7 +710,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
             float tot = 0.f;
 #pragma unroll
             for (int rk = 0; rk < 8; ++rk) {
-                const float wg = (l[rk] > 0.f) ? exp2f(m[rk] - mx) : 0.f;
+                const float wg = (l[rk] > 0.f) ? fast_exp2(m[rk] - mx) : 0.f;
                 rwgt[r * 8 + rk] = wg;
                 tot += l[rk] * wg;
             }
@@ -679,10 +734,9 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
         cluster.sync();    // nobody leaves while its shared memory is still being read
         return;
     }
-    if (p.n_splits == 1) return;
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) last_flag = (atomicAdd(&counters[tile], 1) == p.n_splits - 1) ? 1 : 0;
+    if (threadIdx.x == 0) last_flag = (atomicAdd(&counters[tile], 1) == runs - 1) ? 1 : 0;
     __syncthreads();
     if (!last_flag) return;
     __threadfence();
@@ -692,8 +746,8 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
     float* wgt = reinterpret_cast<float*>(smem_raw);            // [16][MAXS] weights, then [16] totals
     float* tot_s = wgt + 16 * MAXS;
     const size_t stride = (size_t)p.n_tokens * p.heads;
-    for (int e = threadIdx.x; e < 16 * p.n_splits; e += W * 32) {
-        const int r = e / p.n_splits, sp = e % p.n_splits;
+    for (int e = threadIdx.x; e < 16 * runs; e += W * 32) {
+        const int r = e / runs, sp = e % runs;
         float m = -INFINITY, l = 0.f;
         if (r < rows_valid) {
             const size_t idx = sp * stride + (size_t)(q_begin + r / group) * p.heads + kvh * group + r % group;
@@ -707,11 +761,11 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
     if (threadIdx.x < 16) {
         const int r = threadIdx.x;
         float mx = -INFINITY;
-        for (int sp = 0; sp < p.n_splits; ++sp) mx = fmaxf(mx, wgt[r * MAXS + sp]);
+        for (int sp = 0; sp < runs; ++sp) mx = fmaxf(mx, wgt[r * MAXS + sp]);
         float tot = 0.f;
-        for (int sp = 0; sp < p.n_splits; ++sp) {
+        for (int sp = 0; sp < runs; ++sp) {
             const float m = wgt[r * MAXS + sp];
-            const float w = (m == -INFINITY) ? 0.f : exp2f(m - mx);
+            const float w = (m == -INFINITY) ? 0.f : fast_exp2(m - mx);
             wgt[r * MAXS + sp] = w;
             tot += wgt[16 * MAXS + 16 + r * MAXS + sp] * w;
         }
@@ -724,61 +778,74 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
         const size_t idx0 = (size_t)(q_begin + r / group) * p.heads + kvh * group + r % group;
         float acc = 0.f;
 #pragma unroll 8
-        for (int sp = 0; sp < p.n_splits; ++sp) acc += __ldcg(p.part_o + (sp * stride + idx0) * D + d) * wgt[r * MAXS + sp];
+        for (int sp = 0; sp < runs; ++sp) acc += __ldcg(p.part_o + (sp * stride + idx0) * D + d) * wgt[r * MAXS + sp];
         const float tot = tot_s[r];
         p.out[idx0 * D + d] = __float2bfloat16_rn(tot > 0.f ? acc / tot : 0.f);
     }
     if (threadIdx.x == 0) counters[tile] = 0;
 }
 
-template <int D, int W, bool NARROW, bool BOXES>
+template <int D, int W, int S, bool NARROW, bool BOXES>
 cudaError_t launch_decode_n(AttnParams p, int n_seqs, int* counters, cudaStream_t stream) {
-    constexpr int WARP_BYTES = decode_warp_bytes(D, BOXES);
+    constexpr int WARP_BYTES = decode_warp_bytes(D, BOXES, S);
     // with boxes 1,024 bytes more: the swizzled tiles start on such a boundary
     constexpr int smem = W * WARP_BYTES + (16 * D + 32 + 16 * W + 16 * 8 + 16) * 4 + (BOXES ? 1024 : 0);
     static_assert(WARP_BYTES >= (16 * D + 32) * 4, "a warp's buffers must hold its merged result");
     static_assert(W * WARP_BYTES >= (2 * 16 * 64 + 16) * 4, "the merge of the runs needs its weights");
-    static_assert(W <= DWARPS, "a barrier a warp and stage");
     CUtensorMap map_k, map_v;
     memset(&map_k, 0, sizeof(map_k));
     memset(&map_v, 0, sizeof(map_v));
     if constexpr (BOXES) {
         // the caches as matrices [pages * kv_heads * page_size, D]; a box never crosses a page
-        p.run_keys = p.page_size % 32 == 0 ? 32 : 16;
+        p.run_keys = p.page_size % DKB == 0 ? DKB : 16;
         const long long rows = (long long)p.n_pages * p.kv_heads * p.page_size;
         if (!make_map(&map_k, p.k_cache, rows, D, p.run_keys) || !make_map(&map_v, p.v_cache, rows, D, p.run_keys))
             return cudaErrorInvalidValue;
     }
     static std::atomic<unsigned long long> configured{0};
-    cudaError_t e = allow_dynamic_smem(attention_decode_kernel<D, W, NARROW, BOXES>, smem, configured);
+    cudaError_t e = allow_dynamic_smem(attention_decode_kernel<D, W, S, NARROW, BOXES>, smem, configured);
     if (e != cudaSuccess) return e;
-    return launch(attention_decode_kernel<D, W, NARROW, BOXES>, dim3(n_seqs, p.kv_heads, p.n_splits), dim3(W * 32, 1, 1), smem, stream,
+    return launch(attention_decode_kernel<D, W, S, NARROW, BOXES>, dim3(n_seqs, p.kv_heads, p.n_splits), dim3(W * 32, 1, 1), smem, stream,
                   dim3(1, 1, p.cluster_merge ? p.n_splits : 1), p, counters, map_k, map_v);
 }
 
-template <int D, int W>
+template <int D, int W, int S>
 cudaError_t launch_decode_w(const AttnParams& p, int n_seqs, int* counters, cudaStream_t stream) {
     const bool narrow = p.tokens_per_tile * (p.heads / p.kv_heads) <= 8;
     if constexpr (decode_by_boxes(D)) {
         if (p.run_keys != 0)                       // the caller expects long runs of keys a warp
-            return narrow ? launch_decode_n<D, W, true, true>(p, n_seqs, counters, stream)
-                          : launch_decode_n<D, W, false, true>(p, n_seqs, counters, stream);
+            return narrow ? launch_decode_n<D, W, S, true, true>(p, n_seqs, counters, stream)
+                          : launch_decode_n<D, W, S, false, true>(p, n_seqs, counters, stream);
     }
-    return narrow ? launch_decode_n<D, W, true, false>(p, n_seqs, counters, stream)
-                  : launch_decode_n<D, W, false, false>(p, n_seqs, counters, stream);
+    return narrow ? launch_decode_n<D, W, S, true, false>(p, n_seqs, counters, stream)
+                  : launch_decode_n<D, W, S, false, false>(p, n_seqs, counters, stream);
 }
 
-// With more CTAs than SMs the kernel runs with three warps a CTA where that lets two CTAs share an SM (head
-// sizes 64 and 128): the CTAs then need not run in rounds of one an SM, whose last round is partly empty.
+// The shape of a CTA: warps and stages of a warp's ring.  The ring's bytes bound both: W * S blocks of keys and
+// values fit an SM once (8 x 2 or 4 x 4 at head size 128) or, for two CTAs an SM, half as many each (6 x 2 or
+// 3 x 4).  With more CTAs than SMs the kernel runs the shape of which two fit an SM (head sizes 64 and 128): the
+// CTAs then need not run in rounds of one an SM, whose last round is partly empty.
+inline int decode_shape() {
+    static int shape = -1;
+    if (shape < 0) {
+        const char* v = std::getenv("VTB200_DECODE_SHAPE");     // "deep": fewer warps with deeper rings (for measurements)
+        shape = (v != nullptr && v[0] == 'd') ? 1 : 0;
+    }
+    return shape;
+}
+
 template <int D>
 cudaError_t launch_decode_d(const AttnParams& p, int n_seqs, int* counters, cudaStream_t stream) {
     if constexpr (D == 128 || D == 64) {
         int dev = 0, sms = 0;
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 0;
-        if (sms > 0 && (long long)n_seqs * p.kv_heads * p.n_splits > sms) return launch_decode_w<D, 3>(p, n_seqs, counters, stream);
+        const bool two = sms > 0 && (long long)n_seqs * p.kv_heads * p.n_splits > sms;
+        if (decode_shape() == 1)
+            return two ? launch_decode_w<D, 3, 4>(p, n_seqs, counters, stream) : launch_decode_w<D, 4, 4>(p, n_seqs, counters, stream);
+        return two ? launch_decode_w<D, 6, 2>(p, n_seqs, counters, stream) : launch_decode_w<D, 8, 2>(p, n_seqs, counters, stream);
     }
-    return launch_decode_w<D, DWARPS>(p, n_seqs, counters, stream);
+    return launch_decode_w<D, 8, 2>(p, n_seqs, counters, stream);
 }
 
 }  // namespace

@@ -374,6 +374,7 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
     p.scale_log2 = scale * 1.4426950408889634f;
     p.tokens_per_tile = (16 * warps) / (heads / kv_heads);
     p.n_splits = n_splits < 1 ? 1 : n_splits;
+    p.run_blocks = 0;
     p.part_o = part_o;
     p.part_ml = part_ml;
     p.n_tokens = n_tokens;

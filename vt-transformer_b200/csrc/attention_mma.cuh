@@ -27,6 +27,9 @@ struct AttnParams {
     int tokens_per_tile;
     int run_keys;              // single-token steps, head sizes 64 and 128: rows of a box of the keys' and values' tensor maps
     int n_splits;
+    // single-token steps: blocks of keys that a run is to hold; a sequence then takes about (its blocks / run_blocks)
+    // of the n_splits CTAs, the others stay idle.  0: every sequence is cut into n_splits equal runs.
+    int run_blocks;
     float* part_o;          // [splits, tokens, heads, D] unnormalised sums, when n_splits > 1
     float* part_ml;         // [splits, tokens, heads, 2] running maximum (log2 domain) and sum
     int n_tokens;

@@ -328,7 +328,7 @@ void attention_decode(const Tensor& qkv, Tensor& out, const Tensor& k_cache, con
                       int64_t window, double scale, int64_t n_splits, c10::optional<Tensor> part_o,
                       c10::optional<Tensor> part_ml, c10::optional<Tensor> counters, bool fuse_rope,
                       c10::optional<Tensor> cos_sin, bool store_kv, c10::optional<Tensor> status,
-                      c10::optional<Tensor> qkv_shares, bool long_runs) {
+                      c10::optional<Tensor> qkv_shares, bool long_runs, int64_t run_blocks) {
     check_cuda(qkv, "qkv"); check_cuda(out, "out"); check_i32(cu_q, "cu_q"); check_i32(q_start, "q_start");
     check_i32(block_table, "block_table");
     TORCH_CHECK(qkv.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16,
@@ -346,7 +346,7 @@ void attention_decode(const Tensor& qkv, Tensor& out, const Tensor& k_cache, con
                 "attention_decode: one q_start and one block-table row for each sequence");
     float *po = nullptr, *pm = nullptr;
     int* pc = nullptr;
-    if (n_splits > 8) {
+    if (n_splits > 8 || part_o.has_value()) {
         TORCH_CHECK(part_o.has_value() && part_ml.has_value() && counters.has_value(),
                     "attention_decode: more than 8 runs need scratch tensors and counters");
         check_f32(*part_o, "part_o"); check_f32(*part_ml, "part_ml"); check_i32(*counters, "counters");
@@ -386,7 +386,8 @@ void attention_decode(const Tensor& qkv, Tensor& out, const Tensor& k_cache, con
                                               block_table.data_ptr<int>(), block_table.size(1), n_seqs, k_cache.size(0),
                                               n_tokens, heads, kv_heads, head_dim, k_cache.size(2), window, (float)scale,
                                               n_splits, po, pm, pc, fuse_rope ? 1 : 0, cs, max_pos, store_kv ? 1 : 0,
-                                              shp, n_shares, long_runs ? 1 : 0, status_ptr(status), stream_of(qkv)), "attention_decode");
+                                              shp, n_shares, long_runs ? 1 : 0, (int)run_blocks, status_ptr(status),
+                                              stream_of(qkv)), "attention_decode");
 }
 
 void attention_simt(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache,
@@ -470,7 +471,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("n_splits"), py::arg("part_o") = py::none(),
           py::arg("part_ml") = py::none(), py::arg("counters") = py::none(), py::arg("fuse_rope") = false,
           py::arg("cos_sin") = py::none(), py::arg("store_kv") = false, py::arg("status") = py::none(),
-          py::arg("qkv_shares") = py::none(), py::arg("long_runs") = false);
+          py::arg("qkv_shares") = py::none(), py::arg("long_runs") = false, py::arg("run_blocks") = 0);
     m.def("argmax", &argmax, py::arg("logits"), py::arg("out"));
     m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"),
           py::arg("u"), py::arg("out"));

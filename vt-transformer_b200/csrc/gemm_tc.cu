@@ -376,10 +376,25 @@ int small_batch_ksplit(int n, int k, int bn, bool have_scratch, long long scratc
     return ksplit;
 }
 
+// Which operand has the 128 rows, for up to 256 rows of x.  Swapped (w has them) every weight is streamed once and
+// the batch rides along as columns; its epilogue then holds a feature a thread and writes the batch's rows with a
+// stride, which costs more the wider the batch is.  Measured on a B200 (products alone, from cold caches): up to 32
+// rows swapped always wins; beyond, it wins only where the weights are large enough that streaming them is the
+// whole cost (from about 64 MB; the product with SiLU(gate) * up, whose swapped epilogue pairs rows across
+// lanes, from 100 MB and up to 64 rows).  Shares left unadded for the norm (EPI 2) exist swapped only.
+template <int EPI>
+bool swapped_for(int m, int n, int k) {
+    if (m > 256) return false;
+    if (EPI == 2 || m <= 32) return true;
+    const long long weight_bytes = (long long)n * k * 2;
+    if (EPI == 1) return m <= 64 && weight_bytes >= (100LL << 20);
+    return weight_bytes >= (64LL << 20);
+}
+
 template <int EPI, typename TOut>
 cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* out, int m, int n, int k, float* scratch,
                          long long scratch_floats, int* counters, int n_counters, int* status, cudaStream_t stream) {
-    if (m <= 256) {
+    if (swapped_for<EPI>(m, n, k)) {
         // swapped: w is the 128-row operand and every weight is streamed once; the batch rides along as 16 to 256
         // columns.  (At 256 columns a k-block's MMAs take about as long as its 16 KB of weights take to arrive.)
         const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)));

@@ -107,7 +107,8 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
                                     int n_seqs, int n_pages, int n_tokens, int heads, int kv_heads, int head_dim,
                                     int page_size, int window, float scale, int n_splits, float* part_o, float* part_ml,
                                     int* counters, int fuse_rope, const float2* cos_sin, int max_pos, int store_kv,
-                                    const float* qkv_shares, int n_shares, int long_runs, int* status, cudaStream_t stream);
+                                    const float* qkv_shares, int n_shares, int long_runs, int run_blocks, int* status,
+                                    cudaStream_t stream);
 
 // out[r] = index of the largest logit of row r (the lowest index among equals).
 cudaError_t launch_argmax(const float* logits, int* out, int n_rows, int vocab, cudaStream_t stream);

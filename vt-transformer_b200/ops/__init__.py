@@ -181,8 +181,11 @@ def linear_to_stream(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
     tensor [T, N] of x's dtype, or, for bfloat16 batches small enough that the kernel cuts the inner dimension
     over CTAs, a ``SplitSum`` of the unadded 32-bit shares, which the next norm adds."""
     m = x.shape[0]
+    # (a small matrix under a wide batch is faster with x as the 128-row operand and no shares: measured on a B200,
+    # 256 rows by [1152, 896]: 21 us with shares, 15 us without; at 128 rows they are level)
+    small_under_wide = m > 128 and w.shape[0] * w.shape[1] * 2 <= STREAM_SMALL_WEIGHT_BYTES
     if (STREAM_SHARES and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < m <= STREAM_MAX_ROWS
-            and not (SMALL_BATCH_KERNEL == "skinny" and m <= SKINNY_MAX_ROWS)):
+            and not small_under_wide and not (SMALL_BATCH_KERNEL == "skinny" and m <= SKINNY_MAX_ROWS)):
         be = backend()
         n, k = w.shape
         shares = torch.empty((be.gemm_tc_shares(m, n, k), m, n), dtype=torch.float32, device=x.device)
@@ -209,6 +212,7 @@ def _split_workspace(device):
 
 SKINNY_MAX_ROWS = 64            # rows of x up to which the small-batch kernel may run
 STREAM_MAX_ROWS = 256           # rows up to which w is the 128-row operand and products may leave their shares of k unadded
+STREAM_SMALL_WEIGHT_BYTES = 8 << 20   # ... unless the matrix is this small and the batch has more than 128 rows
 # "tc": the tcgen05 kernel with w as the 128-row operand; "skinny": mma.sync weight streaming.
 # The environment variable VTB200_SMALL_BATCH_KERNEL overrides it (for measurements).
 import os as _os
@@ -265,16 +269,16 @@ def rope_attention(qkv, out, cos_sin, k_cache, v_cache, ctx, block_table, heads:
         launches += 1
         w = int(window) if window else 0
         span = ctx.max_kv_len if not w else min(ctx.max_kv_len, w + 31)
-        splits = _decode_splits(ctx.n_seqs * kv_heads, max(1, -(-span // 32)), qkv.device)
+        splits, run, scratch = _decode_plan(ctx.n_seqs * kv_heads, span, qkv.device)
         part_o = part_ml = counters = None
-        if splits > 8:
+        if scratch or splits > 8:
             part_o = torch.empty((splits, ctx.n_tokens, heads, head_dim), dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty((splits, ctx.n_tokens, heads, 2), dtype=torch.float32, device=qkv.device)
             counters = _attention_counters(qkv.device, ctx.n_seqs * kv_heads)
-        long_runs = _decode_long_runs(ctx.n_seqs * kv_heads, max(1, -(-span // 32)), splits, head_dim, qkv.device)
+        long_runs = _decode_long_runs(ctx.n_seqs * kv_heads, span, splits, run, head_dim, qkv.device)
         be.attention_decode(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, heads, kv_heads, head_dim, w,
                             float(scale), splits, part_o, part_ml, counters, True, cos_sin, bool(store), status, shares,
-                            long_runs)
+                            long_runs, run)
         return out
     rope_store(qkv, ctx.positions, cos_sin, k_cache, v_cache, ctx.token_seq, block_table, heads, kv_heads, head_dim,
                store=store, status=status)
@@ -298,15 +302,16 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
     if qkv.dtype == torch.bfloat16 and ATTENTION_KERNEL in ("auto", "mma"):
         if ctx.max_q_len == 1 and be.attention_mma_supports(head_dim, heads, kv_heads, 1):
             span = ctx.max_kv_len if not w else min(ctx.max_kv_len, w + 31)
-            splits = _decode_splits(ctx.n_seqs * kv_heads, max(1, -(-span // 32)), qkv.device)
+            splits, run, scratch = _decode_plan(ctx.n_seqs * kv_heads, span, qkv.device)
             part_o = part_ml = counters = None
-            if splits > 8:
+            if scratch or splits > 8:
                 part_o = torch.empty((splits, ctx.n_tokens, heads, head_dim), dtype=torch.float32, device=qkv.device)
                 part_ml = torch.empty((splits, ctx.n_tokens, heads, 2), dtype=torch.float32, device=qkv.device)
                 counters = _attention_counters(qkv.device, ctx.n_seqs * kv_heads)
-            long_runs = _decode_long_runs(ctx.n_seqs * kv_heads, max(1, -(-span // 32)), splits, head_dim, qkv.device)
+            long_runs = _decode_long_runs(ctx.n_seqs * kv_heads, span, splits, run, head_dim, qkv.device)
             be.attention_decode(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, heads, kv_heads,
-                                head_dim, w, float(scale), splits, part_o, part_ml, counters, long_runs=long_runs)
+                                head_dim, w, float(scale), splits, part_o, part_ml, counters, long_runs=long_runs,
+                                run_blocks=run)
             return out
         # portions long enough to fill tiles of 128 rows: the tcgen05 kernel where it takes the sizes
         if (ATTENTION_KERNEL == "auto" and ctx.max_q_len * group >= 128
@@ -331,48 +336,68 @@ _sm_counts = {}
 _counters = {}
 
 
-def _decode_splits(pairs: int, blocks: int, device) -> int:
-    """Into how many runs the keys of a sequence are cut in a single-token step.  With up to one CTA an SM
-    the CTAs have four warps and run in waves of one an SM; with more, three warps, two CTAs an SM, each
-    slower for the company.  Least waves * (rounds of one 32-key block a warp + a fixed cost of a CTA,
-    counted as three rounds)."""
+DECODE_BLOCK = 16         # keys in a block of the single-token attention kernel (one warp's unit of work)
+# CTAs a step's attention aims at, in SMs (the fixed cost of a CTA against the spread of the work): where the runs of
+# a sequence are a thread-block cluster, and where they meet in scratch memory
+DECODE_CTAS_PER_SM = float(os.environ.get("VTB200_DECODE_CTAS_PER_SM", "0.65"))
+DECODE_CTAS_PER_SM_LONG = float(os.environ.get("VTB200_DECODE_CTAS_PER_SM_LONG", "1.5"))
+DECODE_MIN_RUN = int(os.environ.get("VTB200_DECODE_MIN_RUN", "8"))        # blocks below which a run of keys is not cut further
+DECODE_LONG_BOUND = int(os.environ.get("VTB200_DECODE_LONG_BOUND", "4096"))   # keys from which the runs meet in scratch memory
+
+
+def _decode_plan(pairs: int, span: int, device):
+    """How a single-token step's keys are cut over CTAs: (runs a sequence at most, blocks a run, whether the runs
+    meet in scratch memory).  ``pairs``: sequences times KV heads; ``span``: the most keys a sequence of the step can
+    hold (the bound of a captured graph).  A sequence takes about (its blocks / blocks a run) CTAs, so that
+    sequences of different lengths give CTAs of like work; a step's typical sequence is taken to hold half the bound
+    (a graph serves lengths between half its bound and the bound at the top, shorter ones below).
+
+    Short bounds: the runs of a sequence are the CTAs of a thread-block cluster, which merge through shared memory;
+    the cluster is sized for the typical sequence (a CTA without keys still has to be placed and to wait at the
+    cluster's barriers, which costs the step more than a longer run does), and longer sequences get longer runs.
+    Long bounds (the lengths of a step then differ by thousands of keys): as many runs as the longest sequence needs,
+    met in scratch memory and merged by the CTA that arrives last; a CTA without keys leaves at once, a sequence of
+    one run stores its result itself."""
     sms = _sm_counts.get(device)
     if sms is None:
         sms = torch.cuda.get_device_properties(device).multi_processor_count
         _sm_counts[device] = sms
-    best, best_cost = 1, None
-    for s in range(1, 33):
-        if s > 1 and blocks // s < 2:
-            break
-        two = pairs * s > sms
-        warps = 3 if two else 4
-        # up to 8 runs are the CTAs of a thread-block cluster (merged through shared memory; clusters
-        # pack into the GPCs with some loss); more runs meet in scratch, which costs more
-        slots = sms if s == 1 else (int(sms * 0.86) // s * s if s <= 8 else sms)
-        if two:
-            slots *= 2
-        waves = -(-pairs * s // max(slots, 1))
-        rounds = -(-blocks // (warps * s)) * (1.5 if two else 1.0)
-        cost = waves * (rounds + 3 + (0 if s == 1 else 0.5 if s <= 8 else 2))
-        if best_cost is None or cost < best_cost:
-            best, best_cost = s, cost
-    return best
+    blocks = max(1, -(-span // DECODE_BLOCK))
+    typical = blocks / 2
+    if blocks < 2 * DECODE_MIN_RUN:
+        return 1, 0, False
+    if span < DECODE_LONG_BOUND:
+        per_pair = DECODE_CTAS_PER_SM * sms / max(pairs, 1)
+        if per_pair < 1.5:
+            return 1, 0, False
+        run = max(DECODE_MIN_RUN, int(-(-typical // per_pair)))
+        splits = min(8, int(-(-typical // run)))
+        return (splits, run, False) if splits > 1 else (1, 0, False)
+    per_pair = DECODE_CTAS_PER_SM_LONG * sms / max(pairs, 1)
+    run = max(DECODE_MIN_RUN, int(-(-typical // max(per_pair, 1.0))))
+    splits = min(64, -(-blocks // run))
+    return (splits, run, True) if splits > 1 else (1, 0, False)
 
 
-DECODE_BOXES = "auto"    # "auto" | "always" | "never": tensor-map boxes for the keys and values of single-token steps
-LONG_RUN_BLOCKS = 16     # blocks of 32 keys a warp from which the boxes pay
+# "auto" | "always" | "never": tensor-map boxes for the keys and values of single-token steps
+DECODE_BOXES = os.environ.get("VTB200_DECODE_BOXES", "auto")
+LONG_RUN_BLOCKS = 16     # blocks of 16 keys a warp from which the boxes pay where the CTAs run in one round
 
 
-def _decode_long_runs(pairs: int, blocks: int, splits: int, head_dim: int, device) -> bool:
+def _decode_long_runs(pairs: int, span: int, splits: int, run: int, head_dim: int, device) -> bool:
     """Whether a single-token step's keys and values come as boxes of a tensor map (head sizes 64 and 128):
-    a box arrives later than a cp.async copy but costs the warp one instruction, not 64, so it pays where a
-    warp streams many blocks and loses where it has a few."""
+    a box arrives later than a cp.async copy but costs the warp one instruction, not 32, so it pays where a
+    warp streams many blocks, or where the CTAs run in several rounds and another CTA's work hides the wait; it
+    loses where a warp has a few blocks and the SMs one CTA each."""
     if head_dim not in (64, 128) or DECODE_BOXES == "never":
         return False
     if DECODE_BOXES == "always":
         return True
-    warps = 3 if pairs * splits > _sm_counts.get(device, 148) else 4
-    return blocks >= LONG_RUN_BLOCKS * warps * splits
+    sms = _sm_counts.get(device, 148)
+    if pairs * splits > sms:
+        return True
+    blocks = max(1, -(-span // DECODE_BLOCK))
+    return (run if run else blocks) >= LONG_RUN_BLOCKS * 8
 
 
 def _attention_counters(device, n: int) -> torch.Tensor:
