@@ -215,6 +215,43 @@ def test_a_folder_stored_in_32_bit_rounded_at_load_runs_the_bfloat16_kernels(tmp
     assert float((want.double().cpu() - plain_ref).abs().max()) <= helpers.tol("bfloat16", ref=plain_ref)
 
 
+def test_mixed_step_with_decoding_requests_first(folders):
+    """A step as a scheduler makes it: five decoding requests first (one token each, contexts of 43 to 332 tokens),
+    then portions of two prompts.  At head size 128 the portions run the tcgen05 kernel and the single tokens at the
+    head of the batch a launch of the single-token kernel of their own; a second such step has a single token behind
+    a portion as well (that one runs with the portions).  Every row against the plain implementation."""
+    from vt_transformer_b200 import ops
+    from vt_transformer_b200.engine import StepEntry
+    folder = folders("D")
+    prompts = helpers.prompts_for("D") + helpers.prompts_for("D", seed=3)[:3]      # 44, 150, 333, 64, 44, 150, 333 tokens
+    runner = scenarios.runner_for(folder, DEV, "bfloat16", num_pages=80, max_requests=7, page_size=16)
+    rows = [runner.admit() for _ in prompts]
+    for r, p in zip(rows[:5], prompts[:5]):
+        runner.step([StepEntry(r, p[:-2], [])])
+    before = ops.launches
+    entries = [StepEntry(r, [p[-2]], [0]) for r, p in zip(rows[:5], prompts[:5])]
+    entries += [StepEntry(rows[5], prompts[5][:100], list(range(100))), StepEntry(rows[6], prompts[6][:60], list(range(60)))]
+    got = runner.step(entries).double().cpu()
+    layers = len(runner.model.blocks)
+    assert ops._leading_single_tokens(scenarios.helpers.step_context([1] * 5 + [100, 60], [0] * 7, "cpu")) == 5
+    entries2 = [StepEntry(r, [p[-1]], [0]) for r, p in zip(rows[:4], prompts[:4])]
+    entries2 += [StepEntry(rows[5], prompts[5][100:], [len(prompts[5]) - 101]), StepEntry(rows[4], [prompts[4][-1]], [0])]
+    got2 = runner.step(entries2).double().cpu()
+    runner.check_status()
+    bound = helpers.tol("bfloat16", "D")
+    at = 0
+    for i, p in enumerate(prompts[:5]):
+        assert float((got[at] - helpers.plain_logits(folder, p)[len(p) - 2]).abs().max()) <= bound, i
+        at += 1
+    for i, n in ((5, 100), (6, 60)):
+        assert float((got[at:at + n] - helpers.plain_logits(folder, prompts[i])[:n]).abs().max()) <= bound, i
+        at += n
+    for j, i in enumerate((0, 1, 2, 3)):
+        assert float((got2[j] - helpers.plain_logits(folder, prompts[i])[-1]).abs().max()) <= bound, i
+    assert float((got2[4] - helpers.plain_logits(folder, prompts[5])[-1]).abs().max()) <= bound
+    assert float((got2[5] - helpers.plain_logits(folder, prompts[4])[-1]).abs().max()) <= bound
+
+
 def test_status_word_reports_a_bad_token_id(folders):
     from vt_transformer_b200.engine import DeviceStatusError, StepEntry
     runner = scenarios.runner_for(folders("A"), DEV, "float32", num_pages=2, max_requests=1)

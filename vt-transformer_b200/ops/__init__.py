@@ -224,13 +224,14 @@ ATTENTION_KERNEL = "auto"
 # --------------------------------------------------------------------------- attention
 
 
-def _attention_tiles(ctx, tokens_per_tile: int, device):
+def _attention_tiles(ctx, tokens_per_tile: int, device, first_seq: int = 0):
     """(sequence, first token) for every tile of the step: each sequence's new tokens in runs of
-    ``tokens_per_tile``, ordered by falling number of keys.  Built once a step and kept in ``ctx.extras``."""
-    key = ("attention_tiles", tokens_per_tile)
+    ``tokens_per_tile``, ordered by falling number of keys; the sequences before ``first_seq`` are left out.
+    Built once a step and kept in ``ctx.extras``."""
+    key = ("attention_tiles", tokens_per_tile, first_seq)
     tiles = ctx.extras.get(key)
     if tiles is None:
-        pairs = [(i, a) for i, s in enumerate(ctx.seqs) for a in range(0, s.length, tokens_per_tile)]
+        pairs = [(i, a) for i, s in enumerate(ctx.seqs) if i >= first_seq for a in range(0, s.length, tokens_per_tile)]
         # the tiles with the most keys first: the CTAs that start last are then the short ones
         pairs.sort(key=lambda p: -(ctx.seqs[p[0]].start + p[1]))
         host = torch.tensor(pairs, dtype=torch.int32).view(-1, 2)
@@ -239,6 +240,19 @@ def _attention_tiles(ctx, tokens_per_tile: int, device):
         tiles = host.to(device, non_blocking=True)
         ctx.extras[key] = tiles
     return tiles
+
+
+MIXED_STEP_MIN_SINGLES = 2    # single tokens at the head of a mixed step from which they get a launch of their own
+
+
+def _leading_single_tokens(ctx) -> int:
+    """How many entries at the head of the step bring one token each (0 if all do: that is no mixed step)."""
+    n = 0
+    for s in ctx.seqs:
+        if s.length != 1:
+            break
+        n += 1
+    return n if n < len(ctx.seqs) else 0
 
 
 def single_token_step_is_one_kernel(ctx, dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
@@ -296,6 +310,7 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
     takes the sizes (head_dim a multiple of 16 up to 128; tcgen05 for prompt portions at 64 and 128): single-token steps with the keys of a
     sequence split over several CTAs, other steps in tiles of 64 or 128 rows of (token, head of
     the group).  Everything else, and all of float32, runs the plain kernel."""
+    global launches
     be = backend()
     w = int(window) if window else 0
     group = heads // kv_heads
@@ -316,7 +331,27 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
         # portions long enough to fill tiles of 128 rows: the tcgen05 kernel where it takes the sizes
         if (ATTENTION_KERNEL == "auto" and ctx.max_q_len * group >= 128
                 and be.attention_tc_supports(head_dim, heads, kv_heads) and k_cache.shape[2] % 16 == 0):
-            tiles = _attention_tiles(ctx, 128 // group, qkv.device)
+            # A mixed step: the single tokens at the head of the batch (a scheduler puts the decoding requests first)
+            # would each be a tile of 128 rows with 7 of them live, its keys walked by one CTA.  They go to the
+            # single-token kernel instead, which cuts their keys over CTAs; the two launches write disjoint rows.
+            lead = _leading_single_tokens(ctx)
+            if lead >= MIXED_STEP_MIN_SINGLES and be.attention_mma_supports(head_dim, heads, kv_heads, 1):
+                longest = max(s.start + 1 for s in ctx.seqs[:lead])
+                span = longest if not w else min(longest, w + 31)
+                splits, run, scratch = _decode_plan(lead * kv_heads, span, qkv.device)
+                part_o = part_ml = counters = None
+                if scratch or splits > 8:
+                    part_o = torch.empty((splits, lead, heads, head_dim), dtype=torch.float32, device=qkv.device)
+                    part_ml = torch.empty((splits, lead, heads, 2), dtype=torch.float32, device=qkv.device)
+                    counters = _attention_counters(qkv.device, lead * kv_heads)
+                long_runs = _decode_long_runs(lead * kv_heads, span, splits, run, head_dim, qkv.device)
+                launches += 1
+                be.attention_decode(qkv[:lead], out[:lead], k_cache, v_cache, ctx.cu_q[:lead + 1], ctx.q_start[:lead],
+                                    block_table[:lead], heads, kv_heads, head_dim, w, float(scale), splits, part_o, part_ml,
+                                    counters, long_runs=long_runs, run_blocks=run)
+            else:
+                lead = 0
+            tiles = _attention_tiles(ctx, 128 // group, qkv.device, first_seq=lead)
             be.attention_tc(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, tiles, heads, kv_heads,
                             head_dim, w, float(scale), status)
             return out
