@@ -29,6 +29,7 @@ MODEL = dict(architectures=["Qwen2ForCausalLM"], vocab_size=152064, hidden_size=
              rope_theta=1000000.0, max_position_embeddings=32768, tie_word_embeddings=False,
              sliding_window=131072, use_sliding_window=False, max_window_layers=28, torch_dtype="bfloat16")
 PROMPT_LEN, CONTEXT, PREFILL_TOKENS, PAGE = 1024, 4096, 2048, 64
+E2E_SETTLE = 24      # tokens every request decodes between its prompt and the end-to-end run's warm-up steps
 
 
 def peaks():
@@ -390,7 +391,7 @@ def main() -> int:
     new_tokens = warmup + args.steps + 8
     # end to end the requests' prompts run 2,048 tokens a step beside the decoding of those that are through: the
     # first request decodes that many steps more than the last, and none may end inside the timed steps
-    e2e_tokens = new_tokens + (args.batch * args.prompt_len + 2047) // 2048 + 8
+    e2e_tokens = new_tokens + (args.batch * args.prompt_len + 2047) // 2048 + 8 + E2E_SETTLE
     prompt_len = args.prompt_len
     context = max(CONTEXT, prompt_len + max(e2e_tokens, 256) + PAGE)
     per_req = prompt_len + max(e2e_tokens, 256) + PAGE
@@ -495,6 +496,32 @@ def main() -> int:
     step_bytes = runner.weight_bytes(args.batch) + kv_bytes
     achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
 
+    e2e_s = produced = h2d = d2h = None
+    if not args.skip_e2e:
+        # end to end: the Python entry point, token ids in from the host and out to the host every step
+        llm = LLM(None, runner=runner, max_extend_tokens=2048, overlap=not args.no_overlap)
+        params = SamplingParams(temperature=0.0, max_tokens=e2e_tokens, ignore_eos=True)
+        for _ in range(args.batch):
+            llm.add_request(random_tokens(prompt_len), params)
+        # the prompts run first (compute-bound steps under which the GPU lowers its clocks); the requests then decode
+        # E2E_SETTLE tokens before the warm-up steps, so that the timed steps are steady decoding as the device-timed ones are
+        while any(len(r.output) < E2E_SETTLE for r in llm.scheduler.running) or llm.scheduler.waiting:
+            llm.step()
+        for _ in range(warmup):
+            llm.step()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        produced = 0
+        for _ in range(args.steps):
+            produced += len(llm.step().results)
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t1
+        if produced != args.batch * args.steps:
+            raise RuntimeError(f"end to end: {produced} tokens from {args.steps} steps of {args.batch} requests: a request ended early")
+        h2d = llm.h2d_bytes_last_step
+        d2h = llm.d2h_bytes_last_step
+        for req in list(llm.scheduler.running):
+            llm.abort(req.uid)
     if not args.skip_points:
         for b in (() if args.only_prefill else (1, 64)):
             points[f"decode_b{b}"] = round(decode_run(b, min(args.steps, 64), 5)["tok_s"], 1)
@@ -505,28 +532,6 @@ def main() -> int:
         print(json.dumps({"value": round(main_run["tok_s"], 1), "ms_per_step": round(main_run["ms_per_step"], 4),
                           "points": points, "prefill": prefill, "note": "partial run (--skip-e2e): not a bench line"}))
         return 0
-    # end to end: the Python entry point, token ids in from the host and out to the host every step
-    llm = LLM(None, runner=runner, max_extend_tokens=2048, overlap=not args.no_overlap)
-    params = SamplingParams(temperature=0.0, max_tokens=e2e_tokens, ignore_eos=True)
-    for _ in range(args.batch):
-        llm.add_request(random_tokens(prompt_len), params)
-    while any(len(r.output) == 0 for r in llm.scheduler.running) or llm.scheduler.waiting:
-        llm.step()
-    for _ in range(warmup):
-        llm.step()
-    torch.cuda.synchronize()
-    t1 = time.perf_counter()
-    produced = 0
-    for _ in range(args.steps):
-        produced += len(llm.step().results)
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t1
-    if produced != args.batch * args.steps:
-        raise RuntimeError(f"end to end: {produced} tokens from {args.steps} steps of {args.batch} requests: a request ended early")
-    h2d = llm.h2d_bytes_last_step
-    d2h = llm.d2h_bytes_last_step
-    for req in list(llm.scheduler.running):
-        llm.abort(req.uid)
     if not args.skip_points and args.layers is None:
         del llm, runner
         torch.cuda.empty_cache()
