@@ -6,12 +6,16 @@ code with the package: it reads config.json with ``json`` and the weights with t
 ``float32``) from the formulas of viitrix/vt-transformer's own files, cited at each
 function by the file's path in that project.
 
-It rests on those formulas only: vt-transformer's own model code cannot run on a
-CPU (every op of its host tensor returns OP_TODO_ERROR,
-v1/tensortype/computing.hpp:32-150, and the CUDA ops need cuDNN), so there is no
-golden output of the reference to compare with.  The one piece that does compile
-on a CPU, the rotation table of v1/tensortype/common.cpp:6-24, is compared in
-tests/golden/.
+vt-transformer's own model code cannot run on a CPU (every op of its host tensor
+returns OP_TODO_ERROR, v1/tensortype/computing.hpp:32-150), so there is no golden output
+of its whole forward pass to compare with.  What of it does run anchors the functions
+below (tests/golden/, compared in tests/test_plain.py): the rotation table of
+v1/tensortype/common.cpp:6-24, compiled on the CPU; and its CUDA kernels for the RMS norm,
+the rotation, silu(a) * b, the causal mask and the samplers
+(v1/tensortype/cuda_kernels/{rmsnorm,rotary_embed,silu_product,causal_mask,easy_sampling}.cu),
+compiled unchanged and run once on a B200 on small seeded inputs.  The matrix products,
+the softmax and the order of the parts in a layer rest on the formulas of the graph
+(v1/models/qwen2-7b/inference_fp16.dag) and of v1/tensortype/cuda_tensor.cpp.
 
 What vt-transformer does not have (a window on the keys, a run order that names
 a layer twice or shares a cache) is defined here in the simplest way and marked.
