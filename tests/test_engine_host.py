@@ -48,6 +48,30 @@ def test_toy_norm_cache_kind_and_the_models_two_ends(fake_backend, tmp_path):
     scenarios.toy_seams_case(str(tmp_path), DEV, DT)
 
 
+def test_end_tokens_and_position_limit_come_from_the_model_spec(fake_backend, tmp_path):
+    """An architecture whose configuration names things its own way: the engine reads the positions a model can
+    hold and the tokens that end a request from the ModelSpec, not from a configuration key."""
+    import copy
+    from dataclasses import dataclass, replace
+    from vt_transformer_b200 import LLM, SamplingParams
+    from vt_transformer_b200.config import Qwen2Config, config_from_dict, register_architecture, unregister_architecture
+    from vt_transformer_b200.models.qwen2 import qwen2_model_spec
+    from vt_transformer_b200.weights import write_random_model
+
+    def spec(cfg):
+        return replace(qwen2_model_spec(cfg), max_positions=48, eos_token_ids=(7, 9))
+
+    register_architecture("ToyLimitsLM", Qwen2Config, spec, replace=True)
+    try:
+        d = copy.deepcopy(helpers.CONFIGS["A"])
+        d["architectures"] = ["ToyLimitsLM"]
+        folder = write_random_model(config_from_dict(d), str(tmp_path / "limits"), seed=2, sigma=0.05)
+        llm = LLM(folder, dtype=DT, device=DEV, max_running_reqs=2, page_size=16)
+        assert llm.scheduler.eos == (7, 9) and llm.runner.cache.max_seq_len == 48
+    finally:
+        unregister_architecture("ToyLimitsLM")
+
+
 def test_an_unknown_kind_of_cache_spec_is_refused_by_name():
     from vt_transformer_b200.cache import CacheManager
     with pytest.raises(TypeError, match="cache slot 3: unknown kind of cache spec.*register_cache_kind"):

@@ -204,3 +204,22 @@ def test_float16_is_rounded_with_a_report_and_known_extras_are_left_aside_with_a
     odd = _rewrite(base, str(tmp_path / "odd"), lambda n, t: t, {"model.layers.0.self_attn.rotary_emb.other": torch.ones(8)})
     with pytest.raises(WeightError, match="unexpected"):
         ModelRunner.from_folder(odd, dtype="bfloat16", device="cpu", page_size=16, num_pages=2, max_requests=1)
+
+
+def test_a_part_may_bring_an_initialiser_of_its_own():
+    """The random-weights mode fills a tensor by the function its ParamSpec names; a new one is registered, not
+    edited in."""
+    from vt_transformer_b200.parts import ParamSpec
+    from vt_transformer_b200.weights import random_tensor, register_initialiser, unregister_initialiser
+    spec = ParamSpec((4, 6), init="toy_ramp")
+    with pytest.raises(ValueError, match="unknown initialiser 'toy_ramp'.*known: normal, one_plus_normal, zeros"):
+        random_tensor("x", spec, 0, 0.02)
+    register_initialiser("toy_ramp", lambda shape, g, sigma, device: torch.arange(shape[0] * shape[1], dtype=torch.float32).view(shape) * sigma)
+    try:
+        t = random_tensor("x", spec, 0, 0.5)
+        assert t.dtype == torch.bfloat16 and torch.equal(t.float(), (torch.arange(24.0) * 0.5).view(4, 6))
+        with pytest.raises(ValueError, match="registered already"):
+            register_initialiser("toy_ramp", lambda *a: None)
+    finally:
+        unregister_initialiser("toy_ramp")
+    assert float(random_tensor("b", ParamSpec((8,), role="vector", init="zeros"), 1, 0.3).abs().sum()) == 0.0

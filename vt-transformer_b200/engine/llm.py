@@ -15,7 +15,7 @@ from typing import Dict, List, Optional, Sequence, Union
 import torch
 
 from ..cache.manager import DEFAULT_PAGE_SIZE
-from ..config.registry import load_config
+from ..config.registry import get_architecture, load_config
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .runner import ModelRunner
@@ -44,8 +44,10 @@ class LLM:
         ``step()`` then reports a step's tokens one call later.  ``fp32_weights``: "keep" or "round", what becomes
         of matrices stored in 32-bit when ``dtype`` is bfloat16 (``ModelRunner.build``)."""
         if runner is None:
+            # what the engine needs to know of a model beyond its parts is in its ModelSpec, whatever the
+            # architecture's configuration calls it: the positions it can hold, the tokens that end a request
             config = load_config(model)
-            limit = getattr(config, "max_position_embeddings", None)
+            limit = get_architecture(config.architecture).model_spec(config).max_positions
             if limit:
                 max_seq_len = min(max_seq_len, limit)
             if num_pages is None:
@@ -62,11 +64,7 @@ class LLM:
         self.sampler = Sampler(runner.rt.ops, runner.rt.device)
         self.h2d_bytes_last_step = 0
         self.d2h_bytes_last_step = 0
-        eos = ()
-        try:
-            eos = load_config(model).eos_token_id or () if model else ()
-        except Exception:
-            eos = ()
+        eos = tuple(runner.model.spec.eos_token_ids)
         self.scheduler = Scheduler(cache, self.config, self._run_step, eos_token_ids=eos,
                                    launch_step=self._launch_step, collect_step=self._collect_step, overlap=overlap)
         self._landing = [None, None]     # two pinned buffers for the sampled tokens: one step may be read while the next runs

@@ -31,7 +31,8 @@ def qwen2_model_spec(cfg: Qwen2Config) -> ModelSpec:
     return ModelSpec(vocab=cfg.vocab_size, hidden=cfg.hidden_size, blocks=tuple(blocks),
                      order=ModelSpec.default_order(len(blocks)), embedding=embedding, head=head,
                      max_positions=cfg.max_position_embeddings,
-                     ignored=("*.rotary_emb.inv_freq",))      # older checkpoints store the rotation's frequencies
+                     ignored=("*.rotary_emb.inv_freq",),      # older checkpoints store the rotation's frequencies
+                     eos_token_ids=tuple(cfg.eos_token_id or ()))
 
 
 register_architecture("Qwen2ForCausalLM", Qwen2Config, qwen2_model_spec, replace=True)

@@ -28,7 +28,7 @@ class ParamSpec:
     ``role``: "matrix" and "vector" are floating point (stored in bfloat16 by the random
     initialiser; a file may hold them in 32-bit); "table" is an integer table (int32).
     ``init``: how the random initialiser fills it: "normal" is N(0, sigma),
-    "one_plus_normal" is 1 + N(0, sigma).
+    "one_plus_normal" is 1 + N(0, sigma), "zeros"; or a name given to ``weights.register_initialiser``.
     """
     shape: Tuple[int, ...]
     role: str = "matrix"

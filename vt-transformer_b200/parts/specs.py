@@ -143,6 +143,8 @@ class ModelSpec:
     max_positions: int = 0
     # patterns (fnmatch) of tensor names that a checkpoint of the architecture may hold and the model does not read
     ignored: Tuple[str, ...] = ()
+    # token ids at which generation ends unless a request says otherwise (from the architecture's configuration)
+    eos_token_ids: Tuple[int, ...] = ()
 
     @staticmethod
     def default_order(n_blocks: int) -> Tuple[RunSpec, ...]:

@@ -170,20 +170,42 @@ def _tensor_seed(seed: int, name: str) -> int:
     return int.from_bytes(digest[:8], "little") & ((1 << 63) - 1)
 
 
+# How the random-weights mode fills a tensor: ``ParamSpec.init`` names a function (shape, generator, sigma, device) ->
+# float32 tensor.  A part whose tensors want another start registers one under a name of its own.
+_INITIALISERS = {
+    "normal": lambda shape, g, sigma, device: torch.randn(shape, generator=g, dtype=torch.float32, device=device) * sigma,
+    "one_plus_normal": lambda shape, g, sigma, device: torch.randn(shape, generator=g, dtype=torch.float32,
+                                                                   device=device) * sigma + 1.0,
+    "zeros": lambda shape, g, sigma, device: torch.zeros(shape, dtype=torch.float32, device=device),
+}
+
+
+def register_initialiser(name: str, fn, replace: bool = False) -> None:
+    """``fn(shape, generator, sigma, device)`` returns the float32 tensor that the random-weights mode stores (in
+    bfloat16) for every ``ParamSpec`` whose ``init`` is ``name``."""
+    if name in _INITIALISERS and not replace:
+        raise ValueError(f"initialiser '{name}' is registered already")
+    _INITIALISERS[name] = fn
+
+
+def unregister_initialiser(name: str) -> None:
+    _INITIALISERS.pop(name, None)
+
+
 def random_tensor(name: str, spec: ParamSpec, seed: int, sigma: float, device="cpu") -> torch.Tensor:
     """The tensor ``name`` of a random model: N(0, sigma) for matrices and vectors,
-    1 + N(0, sigma) for norm weights, stored in bfloat16; tables are zeros.  The numbers
-    depend on (seed, name) only, not on the order in which tensors are made."""
+    1 + N(0, sigma) for norm weights (or what the initialiser that ``spec.init`` names gives), stored in
+    bfloat16; tables are zeros.  The numbers depend on (seed, name) only, not on the order in which tensors
+    are made."""
     if spec.role == "table":
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
+    try:
+        fill = _INITIALISERS[spec.init]
+    except KeyError:
+        raise ValueError(f"unknown initialiser '{spec.init}' for {name}; known: {', '.join(sorted(_INITIALISERS))}") from None
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, name))
-    t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device) * sigma
-    if spec.init == "one_plus_normal":
-        t = t + 1.0
-    elif spec.init != "normal":
-        raise ValueError(f"unknown initialiser '{spec.init}' for {name}")
-    return t.to(torch.bfloat16)
+    return fill(tuple(spec.shape), g, sigma, device).to(torch.bfloat16)
 
 
 class RandomSource(WeightSource):
