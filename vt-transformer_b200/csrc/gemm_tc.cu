@@ -421,7 +421,12 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
         // 288 tiles of 208 are 1.95 rounds of narrower tiles).  Cost of a width: rounds * (width + a fixed part
         // for the 128-row operand of every k-block).
         int bn = wide ? 256 : 128;
-        if (wide) {
+        // a small product (a wide batch of a small model: 256 rows by a matrix of a megabyte or two) has a dozen tiles
+        // of 128 x 192: tiles of 64 features give four times the CTAs, each done in a quarter of the time
+        const long tiles_128 = (long)((m + BM - 1) / BM) * ((n + 127) / 128);
+        if (tiles_128 * 2 <= sms) {
+            bn = 64;
+        } else if (wide) {
             long best = -1;
             for (int cand : {256, 240, 224, 208, 192}) {
                 const long t = (long)((m + BM - 1) / BM) * ((n + cand - 1) / cand);
@@ -455,6 +460,7 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
             case 208: return launch_cfg<208, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
             case 192: return launch_cfg<192, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
         }
+        if (bn == 64) return launch_cfg<64, 8, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
         return launch_cfg<128, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
     }
 }
