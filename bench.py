@@ -148,11 +148,20 @@ def reference_arm(args) -> int:
     pk = peaks()
     warmup = max(3, args.warmup)
     steps = min(args.steps, 3000 - warmup)               # its cache holds 4,096 tokens a sequence
-    root = tempfile.mkdtemp(prefix="vt_ref_", dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
+    # 15 GB of weight files: in memory (/dev/shm) where that has the room, else in the temporary folder
+    root, t0 = None, time.time()
+    for where in (["/dev/shm"] if os.path.isdir("/dev/shm") else []) + [None]:
+        root = tempfile.mkdtemp(prefix="vt_ref_", dir=where)
+        try:
+            os.makedirs(os.path.join(root, "weights"))
+            write_reference_weights(os.path.join(root, "weights"), MODEL)
+            break
+        except OSError as e:
+            shutil.rmtree(root, ignore_errors=True)
+            root, why = None, f"the weight files could not be written ({e.__class__.__name__}: {e.strerror})"
+    if root is None:
+        return unavailable(why)
     try:
-        os.makedirs(os.path.join(root, "weights"))
-        t0 = time.time()
-        write_reference_weights(os.path.join(root, "weights"), MODEL)
         torch.cuda.synchronize()
         torch.cuda.empty_cache()
         build_s = time.time() - t0
