@@ -576,6 +576,77 @@ def test_tcgen05_product_takes_each_element_once():
     close(act, g / (1 + torch.exp(-g)) * u, torch.bfloat16, 2)
 
 
+@pytest.mark.parametrize("bn", [256, 224, 192])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 520, 200), (777, 3000, 136), (1000, 1160, 72), (1990, 3500, 264),
+                                   (512, 768, 3592)])
+def test_tcgen05_product_of_a_pair_of_ctas(m, n, k, bn):
+    """A tile of 256 rows of x to two CTAs (tcgen05.mma.cta_group::2), alone: every width of tile, tiles that hang over
+    every edge (the second CTA's rows of x or of w may lie wholly outside), k that is no multiple of 64, more tiles
+    than pairs and fewer; small integers first, so that a k-block or a half of w read from the wrong place shows as a
+    wrong integer, then random numbers against the plain product with bias."""
+    be = ops().backend()
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    torch.manual_seed(16)
+    x = torch.randint(-3, 4, (m, k), device=DEV).to(torch.bfloat16)
+    w = torch.randint(-3, 4, (n, k), device=DEV).to(torch.bfloat16)
+    out = torch.full((m, n), float("nan"), device=DEV, dtype=torch.bfloat16)
+    be.gemm_tc_pair(x, w, None, out, 0, bn, status)
+    assert torch.equal(out.cpu().float(), (x.cpu().float() @ w.cpu().float().t()).to(torch.bfloat16).float())
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    bias = torch.randn(n, device=DEV)
+    for _ in range(2):                                        # twice: the barriers' phases start over every launch
+        out.fill_(float("nan"))
+        be.gemm_tc_pair(x, w, bias, out, 0, bn, status)
+        close(out, plain.linear(x.cpu().double(), w.cpu().double(), bias.cpu().double()), torch.bfloat16, 2)
+    assert status.tolist() == [0, 0]
+
+
+@pytest.mark.parametrize("m,inter,k,bn", [(600, 752, 200, 224), (512, 18944 // 4, 1544, 0), (1100, 344, 72, 256), (300, 96, 64, 192)])
+def test_gate_up_product_of_a_pair_of_ctas(m, inter, k, bn):
+    """silu(x Wg^T) * (x Wu^T) in the epilogue of the kernel of two CTAs a tile; and the same bits as the kernel of one
+    CTA a tile gives, which adds a tile's k-blocks in the same order."""
+    o = ops()
+    torch.manual_seed(17)
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    wg = (torch.randn(inter, k, device=DEV) / math.sqrt(k) * 2).to(torch.bfloat16)
+    wu = (torch.randn(inter, k, device=DEV) / math.sqrt(k) * 2).to(torch.bfloat16)
+    g, u = x.cpu().double() @ wg.cpu().double().t(), x.cpu().double() @ wu.cpu().double().t()
+    packed = o.interleave_gate_up(wg, wu)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    out = torch.full((m, inter), float("nan"), device=DEV, dtype=torch.bfloat16)
+    o.backend().gemm_tc_pair(x, packed, None, out, 1, bn, status)
+    close(out, g / (1 + torch.exp(-g)) * u, torch.bfloat16, 2)
+    assert status.tolist() == [0, 0]
+    if k < 1536:                                              # below that the dispatch keeps the kernel of one CTA a tile
+        one = torch.full((m, inter), float("nan"), device=DEV, dtype=torch.bfloat16)
+        o.backend().gemm_tc(x, packed, None, one, None, *o._split_workspace(torch.device(DEV)), 1)
+        assert torch.equal(one, out)
+
+
+def test_products_of_many_rows_go_to_pairs_of_ctas_and_give_the_same_numbers():
+    """What the dispatch sends to the kernel of two CTAs a tile (many rows, a long k, a tile for every pair) equals,
+    bit for bit, what that kernel gives when called by name; with 32-bit results and for fewer rows the dispatch
+    keeps the kernel of one CTA a tile."""
+    o = ops()
+    torch.manual_seed(18)
+    m, n, k = 1536, 4608, 1536
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    bias = torch.randn(n, device=DEV)
+    ref = plain.linear(x.cpu().double(), w.cpu().double(), bias.cpu().double())
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    by_name = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    o.backend().gemm_tc_pair(x, w, bias, by_name, 0, 0, status)
+    out = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    o.linear(x, w, bias, out)
+    close(out, ref, torch.bfloat16, 2)
+    assert torch.equal(out, by_name) and status.tolist() == [0, 0]
+    out32 = torch.empty(m, n, device=DEV, dtype=torch.float32)
+    o.linear(x, w, bias, out32)
+    close(out32, ref, torch.float32, 40)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,d,page_size", [(6, 2, 48, 16), (4, 4, 128, 32)])
 def test_rotation_and_cache_store(dtype, heads, kv_heads, d, page_size):

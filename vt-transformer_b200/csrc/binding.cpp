@@ -235,6 +235,32 @@ void gemm_tc(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tenso
                                      (int)epilogue, sp, sn, cp, cn, status_ptr(status), stream_of(x)), "gemm_tc");
 }
 
+void gemm_tc_pair(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tensor& out, int64_t epilogue, int64_t bn,
+                  c10::optional<Tensor> status) {
+    check_cuda(x, "x"); check_cuda(w, "w"); check_cuda(out, "out");
+    TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16,
+                "gemm_tc_pair: x, w and out must be bfloat16");
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm_tc_pair: x, w and out must be 2-d");
+    const int m = x.size(0), k = x.size(1), n = w.size(0);
+    TORCH_CHECK(epilogue == 0 || epilogue == 1, "gemm_tc_pair: epilogue must be 0 (bias) or 1 (silu(gate) * up)");
+    TORCH_CHECK(bn == 0 || bn == 256 || bn == 224 || bn == 192, "gemm_tc_pair: tiles of 256, 224 or 192 rows of w (0: chosen by the sizes)");
+    TORCH_CHECK(w.size(1) == k && out.size(0) == m && out.size(1) == (epilogue == 1 ? n / 2 : n),
+                "gemm_tc_pair: shapes [m,k] x [n,k] -> [m,n] (or [m,n/2] with the silu epilogue)");
+    TORCH_CHECK(epilogue != 1 || (n % 16 == 0 && !bias.has_value()), "gemm_tc_pair: the silu epilogue takes n % 16 == 0 and no bias");
+    TORCH_CHECK(k % 8 == 0, "gemm_tc_pair: inner size ", k, " must be a multiple of 8 (TMA rows start on 16-byte boundaries)");
+    TORCH_CHECK(((uintptr_t)x.data_ptr() & 15) == 0 && ((uintptr_t)w.data_ptr() & 15) == 0,
+                "gemm_tc_pair: x and w must start on 16-byte boundaries");
+    const float* bp = nullptr;
+    if (bias.has_value()) {
+        check_f32(*bias, "bias");
+        TORCH_CHECK(bias->numel() == n, "gemm_tc_pair: bias must have one entry for each output column");
+        bp = bias->data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    check_launch(vtb::launch_gemm_tc_pair(x.data_ptr(), w.data_ptr(), bp, out.data_ptr(), m, n, k, (int)epilogue, (int)bn,
+                                          status_ptr(status), stream_of(x)), "gemm_tc_pair");
+}
+
 bool attention_mma_supports(int64_t head_dim, int64_t heads, int64_t kv_heads, int64_t warps) {
     return vtb::attention_mma_supports(head_dim, heads, kv_heads, warps);
 }
@@ -455,6 +481,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_skinny", &gemm_skinny, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"));
     m.def("gemm_tc", &gemm_tc, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"), py::arg("status") = py::none(),
           py::arg("scratch") = py::none(), py::arg("counters") = py::none(), py::arg("epilogue") = 0);
+    m.def("gemm_tc_pair", &gemm_tc_pair, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"), py::arg("epilogue") = 0,
+          py::arg("bn") = 256, py::arg("status") = py::none());
     m.def("gemm_tc_shares", [](int64_t m, int64_t n, int64_t k) { return (int64_t)vtb::gemm_tc_shares(m, n, k); });
     m.def("attention_mma_supports", &attention_mma_supports);
     m.def("attention_mma", &attention_mma, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),

@@ -31,10 +31,11 @@ SOURCES = [
     "attention_tc.cu",
     "gemm_skinny.cu",
     "gemm_tc.cu",
+    "gemm_tc_pair.cu",
     "attention_noalloc.cu",
     "sampling.cu",
 ]
-HEADERS = ["common.cuh", "kernels.h", "launch.cuh", "tc_common.cuh", "attention_mma.cuh", "attention_decode.cuh", "attention_noalloc.h"]
+HEADERS = ["common.cuh", "kernels.h", "launch.cuh", "tc_common.cuh", "gemm_epilogue.cuh", "attention_mma.cuh", "attention_decode.cuh", "attention_noalloc.h"]
 
 CUDA_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -1,0 +1,279 @@
+// out = x w^T (+ bias, or SiLU(gate) * up) for many rows of x, a tile to a PAIR of CTAs: tcgen05.mma.cta_group::2.
+//
+// The kernel of gemm_tc.cu gives a tile of 128 rows of x by 256 rows of w to one CTA; every k-block of 64 it brings
+// 16 KB of x and 32 KB of w from L2 for 524 cycles of MMAs, and the products stand at 74 to 81 % of the tensor
+// pipe.  Here two CTAs on neighbouring SMs (a cluster of two) share a tile of 256 rows of x by BN rows of w: each
+// loads its own 128 rows of x and HALF of the rows of w (loads of its own: no multicast), and one thread of the
+// first CTA issues MMAs that read both CTAs' shared memory and write both CTAs' tensor memory (each CTA ends up with
+// its 128 rows by all BN columns).  A k-block then costs a CTA 16 + 16 KB, so the ring is six stages deep where it
+// was four, and L2 delivers a third less.
+//
+// What crosses between the two CTAs, and how:
+//   full[s]      lives in the first CTA.  It arms it for the bytes of both CTAs' loads; the second CTA's TMA loads
+//                complete on it too (cp.async.bulk.tensor ... cta_group::2 with the barrier's address in the first
+//                CTA, from mapa).
+//   empty[s]     one in each CTA; the MMA thread's commit arrives on both (tcgen05.commit ... multicast::cluster).
+//   acc_full[b]  one in each CTA, both signalled by the commit after a tile's last MMA.
+//   acc_empty[b] lives in the first CTA; the four epilogue warps of each CTA arrive on it (a remote arrive from the
+//                second CTA), eight arrivals a phase.
+// The rest is the structure of gemm_tc.cu: persistent pairs taking tiles in turn, warp 0 loads, warp 1 owns the
+// tensor memory (and, in the first CTA, issues the MMAs), warps 2..5 are the epilogue under the next tile's MMAs;
+// every wait is bounded.  The two CTAs meet at a cluster barrier after set-up and before they free their tensor
+// memory: neither may leave while the other's MMAs or loads still name its memory.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_epilogue.cuh"
+#include "kernels.h"
+#include "launch.cuh"
+#include "tc_common.cuh"
+
+namespace vtb {
+
+namespace {
+
+constexpr int PBM = 128;                 // rows of x a CTA holds of the pair's 256
+constexpr int PBK = 64;
+constexpr int PA_STAGE = PBM * PBK * 2;  // 16 KB
+constexpr int PTHREADS = 192;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// the address, in the cluster's shared window, of the same place in CTA `rank`
+__device__ __forceinline__ uint32_t in_cta(uint32_t local, uint32_t rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(a) : "r"(local), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+// a box of a tensor map into this CTA's shared memory, its bytes counted on a barrier that may lie in the pair's other CTA
+__device__ __forceinline__ void tma_load_2d_pair(void* smem, const CUtensorMap* map, int x, int y, uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(
+            smem_u32(smem)),
+        "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives, when the MMAs issued so far are done, on the barrier at this place in both CTAs of the pair
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(
+                     smem_u32(bar)),
+                 "h"(both)
+                 : "memory");
+}
+
+template <int BN, int STAGES, int EPI, typename TOut>
+__global__ void __launch_bounds__(PTHREADS)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo, int* status) {
+    static_assert(BN % 32 == 0 && BN <= 256, "each CTA holds half of the tile's rows of w, in whole swizzle groups");
+    constexpr int BH = BN / 2;                       // rows of w a CTA loads
+    constexpr int B_STAGE = BH * PBK * 2;
+    constexpr int COLS = BN;                         // tensor-memory columns of an accumulator
+    constexpr int ALLOC = 2 * COLS <= 256 ? 256 : 512;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* a_s = smem;
+    unsigned char* b_s = smem + STAGES * PA_STAGE;
+    uint64_t* full = reinterpret_cast<uint64_t*>(b_s + STAGES * B_STAGE);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();            // 0: the CTA that issues the MMAs
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int a_tiles = (rows_a + 2 * PBM - 1) / (2 * PBM), b_tiles = (rows_b + BN - 1) / BN;
+    const int tiles = a_tiles * b_tiles;
+    const int nkb = (k + PBK - 1) / PBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);                  // the first CTA's arrival with the bytes to expect
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 8);             // four epilogue warps of each CTA
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(ALLOC));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                              // both CTAs' barriers and tensor memory are there
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    bool timed_out = false;
+    pdl_launch();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int kit = 0;
+            bool waited = false;
+            for (int t = pair; t < tiles && !timed_out; t += n_pairs) {
+                const int a_row0 = (t % a_tiles) * 2 * PBM + (int)rank * PBM, b_row0 = (t / a_tiles) * BN + (int)rank * BH;
+                for (int kb = 0; kb < nkb; ++kb, ++kit) {
+                    const int s = kit % STAGES;
+                    if (kit >= STAGES && !mbar_wait(&empty[s], ((kit / STAGES) & 1) ^ 1)) { timed_out = true; break; }
+                    const uint32_t bar = in_cta(smem_u32(&full[s]), 0);
+                    if (rank == 0) mbar_expect_tx(&full[s], 2 * (PA_STAGE + B_STAGE));
+                    // the weights are written by no kernel: they go out before the dependency wait
+                    tma_load_2d_pair(b_s + s * B_STAGE, &map_b, kb * PBK, b_row0, bar);
+                    if (!waited) {
+                        pdl_wait();
+                        waited = true;
+                    }
+                    tma_load_2d_pair(a_s + s * PA_STAGE, &map_a, kb * PBK, a_row0, bar);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = instr_desc(2 * PBM, BN);
+            int kit = 0, ui = 0;
+            for (int t = pair; t < tiles && !timed_out; t += n_pairs, ++ui) {
+                const int buf = ui & 1;
+                if (ui >= 2 && !mbar_wait(&acc_empty[buf], ((ui >> 1) & 1) ^ 1)) { timed_out = true; break; }
+                tc_fence_after();
+                const uint32_t acc = tmem + (uint32_t)(buf * COLS);
+                for (int kb = 0; kb < nkb; ++kb, ++kit) {
+                    const int s = kit % STAGES;
+                    if (!mbar_wait(&full[s], (kit / STAGES) & 1)) { timed_out = true; break; }
+                    tc_fence_after();
+                    const uint64_t ad = smem_desc(a_s + s * PA_STAGE), bd = smem_desc(b_s + s * B_STAGE);
+#pragma unroll
+                    for (int kk = 0; kk < PBK / 16; ++kk)
+                        tc_mma_pair(acc, ad + 2 * kk, bd + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                    tc_commit_pair(&empty[s]);
+                }
+                tc_commit_pair(&acc_full[buf]);
+            }
+        }
+    }
+    __syncwarp();
+    pdl_wait();
+
+    if (warp >= 2) {
+        const int q = warp & 3;
+        const int r = q * 32 + lane;
+        const uint32_t acc_empty_first = in_cta(smem_u32(&acc_empty[0]), 0);
+        int ui = 0;
+        for (int t = pair; t < tiles; t += n_pairs, ++ui) {
+            const int a_row0 = (t % a_tiles) * 2 * PBM + (int)rank * PBM, b_row0 = (t / a_tiles) * BN;
+            const int buf = ui & 1;
+            bool ok = !timed_out && mbar_wait(&acc_full[buf], (ui >> 1) & 1);
+            if (!ok) timed_out = true;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                if (ok) {
+                    uint32_t raw[16];
+                    tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * COLS + c0), raw);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(raw[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                }
+                if (c0 + 16 >= BN) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_remote(acc_empty_first + (uint32_t)(buf * 8));
+                }
+                emit16<false, EPI, TOut>(v, r, a_row0, b_row0, c0, rows_a, rows_b, bias, out, ldo);
+            }
+        }
+    }
+    if (timed_out && status) set_status(status, kStatusWaitTimeout, blockIdx.x);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                              // neither CTA's memory is named by the other any more
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(ALLOC));
+    }
+}
+
+template <int BN, int STAGES, int EPI, typename TOut>
+cudaError_t launch_pair_cfg(const void* x, int m, const void* w, int n, int k, const float* bias, TOut* out, int ldo, int* status,
+                            cudaStream_t stream) {
+    CUtensorMap map_a, map_b;
+    if (!make_map(&map_a, x, m, k, PBM) || !make_map(&map_b, w, n, k, BN / 2)) return cudaErrorInvalidValue;
+    constexpr int smem = STAGES * (PA_STAGE + (BN / 2) * PBK * 2) + 1024 + 256;
+    static std::atomic<unsigned long long> configured{0};
+    cudaError_t e = allow_dynamic_smem(gemm_tc_pair_kernel<BN, STAGES, EPI, TOut>, smem, configured);
+    if (e != cudaSuccess) return e;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    const int tiles = ((m + 2 * PBM - 1) / (2 * PBM)) * ((n + BN - 1) / BN);
+    const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+    return launch(gemm_tc_pair_kernel<BN, STAGES, EPI, TOut>, dim3(2 * pairs, 1, 1), dim3(PTHREADS, 1, 1), smem, stream, dim3(2, 1, 1),
+                  map_a, map_b, bias, out, m, n, k, ldo, status);
+}
+
+}  // namespace
+
+// bfloat16 out [m, n] (epilogue 0, with bias) or [m, n / 2] (epilogue 1: SiLU(gate) * up over rows of w interleaved
+// in runs of 8).  `bn`: rows of w in a tile: 256, 224 or 192; 0: the one whose rounds of one tile a pair come out best.
+cudaError_t launch_gemm_tc_pair(const void* x, const void* w, const float* bias, void* out, int m, int n, int k, int epilogue,
+                                int bn, int* status, cudaStream_t stream) {
+    if (m == 0 || n == 0) return cudaSuccess;
+    if (k % 8 != 0 || k < 8) return cudaErrorInvalidValue;
+    __nv_bfloat16* o = (__nv_bfloat16*)out;
+    if (bn == 0) {
+        // rounds of one tile a pair, times the width of a tile and a fixed part for the 128 rows of x of every
+        // k-block; a narrower tile also has a little less of the tensor pipe (measured: 192 is a fifth slower a column)
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        const int pairs = sms / 2;
+        long best = -1;
+        for (int cand : {256, 224}) {
+            const long t = (long)((m + 2 * PBM - 1) / (2 * PBM)) * ((n + cand - 1) / cand);
+            const long cost = ((t + pairs - 1) / pairs) * (cand + 32 + (256 - cand) / 2);
+            if (best < 0 || cost < best) {
+                best = cost;
+                bn = cand;
+            }
+        }
+    }
+    if (epilogue == 1) {
+        if (n % 16 != 0 || bias != nullptr) return cudaErrorInvalidValue;
+        if (bn == 192) return launch_pair_cfg<192, 7, 1, __nv_bfloat16>(x, m, w, n, k, nullptr, o, n / 2, status, stream);
+        if (bn == 224) return launch_pair_cfg<224, 6, 1, __nv_bfloat16>(x, m, w, n, k, nullptr, o, n / 2, status, stream);
+        return launch_pair_cfg<256, 6, 1, __nv_bfloat16>(x, m, w, n, k, nullptr, o, n / 2, status, stream);
+    }
+    if (epilogue != 0) return cudaErrorInvalidValue;
+    if (bn == 192) return launch_pair_cfg<192, 7, 0, __nv_bfloat16>(x, m, w, n, k, bias, o, n, status, stream);
+    if (bn == 224) return launch_pair_cfg<224, 6, 0, __nv_bfloat16>(x, m, w, n, k, bias, o, n, status, stream);
+    return launch_pair_cfg<256, 6, 0, __nv_bfloat16>(x, m, w, n, k, bias, o, n, status, stream);
+}
+
+}  // namespace vtb
