@@ -11,9 +11,11 @@
 //          cycles whatever its size: pages of 16 keys hold this kernel to about half of what pages of 64 allow
 //   S      = Q K^T: A = Q (K-major), B = K block (K-major, N = 128 keys), accumulator [128 x 128] floats in
 //          tensor memory; two buffers, one for the even and one for the odd blocks
-//   P      two groups of four warps, one for the even and one for the odd blocks, a thread a row:
-//          tcgen05.ld of the row of S, scale, mask, maximum, 2^x, sum; P rounded to bfloat16 and stored
-//          (tcgen05.st) over the columns of S that have been read: it is the A operand of the next product
+//   P      two groups of four warps, one for the even and one for the odd blocks, a thread a row: the row of S
+//          into registers (four tcgen05.ld on their way together), mask, maximum, scale, 2^x, sum; P rounded to
+//          bfloat16 and stored (tcgen05.st) over the first 64 columns of S: it is the A operand of the next
+//          product.  The half of P over the first 64 keys is announced by itself, so that its product with V
+//          runs while the warps still compute the other half
 //   PV     O += P V: A = P in tensor memory, B = V block as it lies ([key][dim]: MN-major); each group has
 //          its own accumulator O [128 x 128] and its own running maximum and sum, which meet at the end
 //
@@ -65,58 +67,76 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// Largest raw score of a row of S (128 columns of tensor memory at s_addr; kb: their first key).  MASKED:
-// keys this row does not see (beyond its position, or before its window) count as -infinity.
-template <bool MASKED>
-__device__ __forceinline__ float row_max(uint32_t s_addr, int kb, int pos, int window, bool valid) {
-    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-    for (int c0 = 0; c0 < TK; c0 += 32) {
-        uint32_t raw[32];
-        tc_ld32(s_addr + c0, raw);
-        if (MASKED) {
-            // keys [lo, hi) of this chunk are seen
-            const int hi = valid ? min(32, pos - (kb + c0) + 1) : 0;
-            const int lo = (window > 0) ? max(0, pos - window + 1 - (kb + c0)) : 0;
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-                mx[i & 3] = fmaxf(mx[i & 3], (i >= lo && i < hi) ? __uint_as_float(raw[i]) : -INFINITY);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(raw[i]));
-        }
-    }
-    return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
-// P = 2^(raw * scale - base) of a row, rounded to bfloat16 and stored over the first 64 columns of the row of S
-// (two keys a column; 32 keys are read before their 16 columns are written); returns the sum of the unrounded values.
+// The 128 scores of a row of S from tensor memory into registers: four loads on their way together, one wait.
+#define VTB_TC_LD32_ASYNC(taddr, r, o)                                                                                   \
+    asm volatile(                                                                                                        \
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"                 \
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"                                     \
+        : "=r"(r[o + 0]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]), "=r"(r[o + 4]), "=r"(r[o + 5]), "=r"(r[o + 6]),   \
+          "=r"(r[o + 7]), "=r"(r[o + 8]), "=r"(r[o + 9]), "=r"(r[o + 10]), "=r"(r[o + 11]), "=r"(r[o + 12]),              \
+          "=r"(r[o + 13]), "=r"(r[o + 14]), "=r"(r[o + 15]), "=r"(r[o + 16]), "=r"(r[o + 17]), "=r"(r[o + 18]),           \
+          "=r"(r[o + 19]), "=r"(r[o + 20]), "=r"(r[o + 21]), "=r"(r[o + 22]), "=r"(r[o + 23]), "=r"(r[o + 24]),           \
+          "=r"(r[o + 25]), "=r"(r[o + 26]), "=r"(r[o + 27]), "=r"(r[o + 28]), "=r"(r[o + 29]), "=r"(r[o + 30]),           \
+          "=r"(r[o + 31])                                                                                                \
+        : "r"(taddr))
+
+__device__ __forceinline__ void load_row(uint32_t s_addr, uint32_t (&raw)[TK]) {
+    VTB_TC_LD32_ASYNC(s_addr, raw, 0);
+    VTB_TC_LD32_ASYNC(s_addr + 32, raw, 32);
+    VTB_TC_LD32_ASYNC(s_addr + 64, raw, 64);
+    VTB_TC_LD32_ASYNC(s_addr + 96, raw, 96);
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// Largest raw score of a row (its 128 scores in registers; kb: their first key).  MASKED: keys [lo, hi) of the
+// block are seen by this row; the others count as -infinity.
 template <bool MASKED>
-__device__ __forceinline__ float write_p(uint32_t s_addr, int kb, int pos, int window, bool valid, float scale_log2,
-                                         float base) {
-    float sum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-    for (int c0 = 0; c0 < TK; c0 += 32) {
-        uint32_t raw[32];
-        tc_ld32(s_addr + c0, raw);
-        const int hi = valid ? min(32, pos - (kb + c0) + 1) : 0;
-        const int lo = (window > 0) ? max(0, pos - window + 1 - (kb + c0)) : 0;
+__device__ __forceinline__ float row_max(const uint32_t (&raw)[TK], int lo, int hi) {
+    float mx[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) mx[c] = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < TK; i += 2) {
+        const float a = (!MASKED || (i >= lo && i < hi)) ? __uint_as_float(raw[i]) : -INFINITY;
+        const float b = (!MASKED || (i + 1 >= lo && i + 1 < hi)) ? __uint_as_float(raw[i + 1]) : -INFINITY;
+        mx[(i >> 1) & 7] = max3(mx[(i >> 1) & 7], a, b);
+    }
+    return fmaxf(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], max3(mx[5], mx[6], mx[7])));
+}
+
+// P = 2^(raw * scale - base) of half a row (the 64 keys from H * 64 on), rounded to bfloat16 and stored over 32 of the
+// first 64 columns of the row of S (two keys a column); adds the unrounded values to `sum`.  Two values at a time
+// where the hardware has an instruction for two (the scaling, the sum, the rounding); 2^x comes from the
+// special-function unit.  (A quarter or a half of the 2^x as a polynomial on the FMA pipe instead was slower, and
+// so was the kernel with no 2^x at all no faster: what the kernel waits for is the tensor pipe's queue, which one
+// thread feeds, and the traffic of tensor memory, not these warps' arithmetic.)
+template <bool MASKED, int H>
+__device__ __forceinline__ void write_p_half(const uint32_t (&raw)[TK], uint32_t s_addr, int lo, int hi, float scale_log2, float base,
+                                             float2 (&sum)[2]) {
+    const float2 sc = make_float2(scale_log2, scale_log2), nb = make_float2(-base, -base);
+#pragma unroll
+    for (int c0 = H * 64; c0 < H * 64 + 64; c0 += 32) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-            float pv[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                pv[e] = ex2(fmaf(__uint_as_float(raw[i + e]), scale_log2, -base));
-                if (MASKED) pv[e] = (i + e >= lo && i + e < hi) ? pv[e] : 0.f;
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(raw[c0 + i]), __uint_as_float(raw[c0 + i + 1])), sc, nb);
+            float2 pv = make_float2(ex2(x.x), ex2(x.y));
+            if (MASKED) {
+                pv.x = (c0 + i >= lo && c0 + i < hi) ? pv.x : 0.f;
+                pv.y = (c0 + i + 1 >= lo && c0 + i + 1 < hi) ? pv.y : 0.f;
             }
-            sum[(i >> 1) & 3] += pv[0] + pv[1];
-            __nv_bfloat162 b = __floats2bfloat162_rn(pv[0], pv[1]);
+            sum[(i >> 1) & 1] = __fadd2_rn(sum[(i >> 1) & 1], pv);
+            __nv_bfloat162 b = __floats2bfloat162_rn(pv.x, pv.y);
             pk[i >> 1] = *reinterpret_cast<uint32_t*>(&b);
         }
         tc_st16(s_addr + (c0 >> 1), pk);
     }
-    return (sum[0] + sum[1]) + (sum[2] + sum[3]);
 }
 
 template <int D>
@@ -132,20 +152,36 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     unsigned char* k_s = q_s + TILE_BYTES;               // [2][TILE_BYTES]
     unsigned char* v_s = k_s + 2 * TILE_BYTES;           // [2][TILE_BYTES]
     uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * TILE_BYTES);
-    uint64_t *k_full = bars, *k_empty = bars + 2, *v_full = bars + 4, *v_empty = bars + 6, *s_full = bars + 8,
-             *p_full = bars + 10, *o_done = bars + 12, *q_full = bars + 14, *pair = bars + 15;
+    // s_full[b]: S of a block with parity b is there (and its stage of K free); p_full[2 b + h]: half h of its P is
+    // stored; o_done[b]: its product with V is done (and its stage of V free)
+    uint64_t *k_full = bars, *v_full = bars + 2, *s_full = bars + 4, *p_full = bars + 6, *o_done = bars + 10,
+             *q_full = bars + 12, *pair = bars + 13;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
     float* xch = reinterpret_cast<float*>(bars + 20);     // [2 groups][128 rows][maximum, sum]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // what the step's own inputs say about this tile (they are there before the step's first kernel starts)
+    const int kvh = blockIdx.y;
+    const int2 tl = p.tiles[blockIdx.x];
+    const int seq = tl.x, tok0 = tl.y;
+    const int q_begin = p.cu_q[seq];
+    const int q_len = p.cu_q[seq + 1] - q_begin;
+    const int ntok = min(p.tokens_per_tile, q_len - tok0);
+    const int group = p.heads / p.kv_heads;
+    const int rows_valid = max(0, ntok) * group;
+    const int start = p.q_start[seq];
+    const int pos_lo = start + tok0, pos_hi = pos_lo + max(1, ntok) - 1;
+    int key_lo = (p.window > 0) ? max(0, pos_lo - p.window + 1) : 0;
+    key_lo = key_lo / TK * TK;
+    const int key_hi = pos_hi + 1;
+    const int nb = (ntok > 0) ? (key_hi - key_lo + TK - 1) / TK : 0;
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) {
             mbar_init(&k_full[i], 1);
-            mbar_init(&k_empty[i], 1);
             mbar_init(&v_full[i], 1);
-            mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 4);
+            mbar_init(&p_full[2 * i], 4);
+            mbar_init(&p_full[2 * i + 1], 4);
             mbar_init(&o_done[i], 1);
         }
         mbar_init(q_full, 8);
@@ -166,20 +202,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     pdl_launch();
     pdl_wait();                                 // q, and the keys and values of this step, come from kernels before
 
-    const int kvh = blockIdx.y;
-    const int2 tl = p.tiles[blockIdx.x];
-    const int seq = tl.x, tok0 = tl.y;
-    const int q_begin = p.cu_q[seq];
-    const int q_len = p.cu_q[seq + 1] - q_begin;
-    const int ntok = min(p.tokens_per_tile, q_len - tok0);
-    const int group = p.heads / p.kv_heads;
-    const int rows_valid = max(0, ntok) * group;
-    const int start = p.q_start[seq];
-    const int pos_lo = start + tok0, pos_hi = pos_lo + max(1, ntok) - 1;
-    int key_lo = (p.window > 0) ? max(0, pos_lo - p.window + 1) : 0;
-    key_lo = key_lo / TK * TK;
-    const int key_hi = pos_hi + 1;
-    const int nb = (ntok > 0) ? (key_hi - key_lo + TK - 1) / TK : 0;
     bool timed_out = false;
 
     if (warp == 0) {
@@ -216,11 +238,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             };
             // in the order in which the products want them: K0, K1, V0, K2, V1, ...
             int row_cur = row_of(0), row_next = row_of(1);
-            if (!load(0, row_cur, &map_k, k_s, k_full, k_empty)) timed_out = true;
+            if (!load(0, row_cur, &map_k, k_s, k_full, s_full)) timed_out = true;
             for (int j = 0; j < nb && !timed_out; ++j) {
                 const int row_after = row_of(j + 2);
-                if (j + 1 < nb && !load(j + 1, row_next, &map_k, k_s, k_full, k_empty)) { timed_out = true; break; }
-                if (!load(j, row_cur, &map_v, v_s, v_full, v_empty)) timed_out = true;
+                if (j + 1 < nb && !load(j + 1, row_next, &map_k, k_s, k_full, s_full)) { timed_out = true; break; }
+                if (!load(j, row_cur, &map_v, v_s, v_full, o_done)) timed_out = true;
                 row_cur = row_next;
                 row_next = row_after;
             }
@@ -230,37 +252,45 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             const uint32_t idesc_s = instr_desc(TQ, TK), idesc_pv = instr_desc(TQ, D, true);
             // descriptors of the tiles' first bytes; a tile further on adds its distance / 16 to the address field
             const uint64_t desc_q = smem_desc(q_s), desc_k = smem_desc(k_s), desc_v = smem_desc_lbo(v_s, HALF_BYTES);
-            auto issue_s = [&](int j) -> bool {
+            auto issue_s = [&](int j, bool keys_there) -> bool {
                 const int st = j & 1;
-                if (!mbar_wait(&k_full[st], (j >> 1) & 1)) return false;
-                tc_fence_after();
+                if (!keys_there) {
+                    if (!mbar_wait(&k_full[st], (j >> 1) & 1)) return false;
+                    tc_fence_after();
+                }
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h)
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)     // 16 dims = 32 bytes further along the swizzled rows
                         tc_mma(tmem + (uint32_t)(st * TK), desc_q + (uint64_t)((h * HALF_BYTES >> 4) + 2 * kk),
                                desc_k + (uint64_t)(((st * TILE_BYTES + h * HALF_BYTES) >> 4) + 2 * kk), idesc_s, (h | kk) ? 1u : 0u);
-                tc_commit(&k_empty[st]);
                 tc_commit(&s_full[st]);
                 return true;
             };
             if (!mbar_wait(q_full, 0)) timed_out = true;
             tc_fence_after();
-            if (!timed_out && !issue_s(0)) timed_out = true;
-            if (!timed_out && nb > 1 && !issue_s(1)) timed_out = true;
+            if (!timed_out && !issue_s(0, false)) timed_out = true;
+            if (!timed_out && nb > 1 && !issue_s(1, false)) timed_out = true;
             for (int j = 0; j < nb && !timed_out; ++j) {
                 const int st = j & 1;
-                if (!mbar_wait(&p_full[st], (j >> 1) & 1) || !mbar_wait(&v_full[st], (j >> 1) & 1)) { timed_out = true; break; }
-                tc_fence_after();
+                // (the barriers whose turn came long ago first: the keys of the block after next, this block's values)
+                if (j + 2 < nb && !mbar_wait(&k_full[st], ((j + 2) >> 1) & 1)) { timed_out = true; break; }
+                // the product over the first 64 keys runs while the softmax warps still write the P of the other 64
+                if (!mbar_wait(&v_full[st], (j >> 1) & 1)) { timed_out = true; break; }
 #pragma unroll
-                for (int ks = 0; ks < TK / 16; ++ks)   // 16 keys: 8 columns of P, 16 rows of V further
-                    tc_mma_ta(tmem + 2 * TK + st * D, tmem + (uint32_t)(st * TK + ks * 8),
-                              desc_v + (uint64_t)((st * TILE_BYTES + ks * STEP_BYTES) >> 4), idesc_pv, (j >= 2 || ks) ? 1u : 0u);
-                tc_commit(&v_empty[st]);
+                for (int h = 0; h < 2; ++h) {
+                    if (!mbar_wait(&p_full[2 * st + h], (j >> 1) & 1)) { timed_out = true; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = h * 4; ks < h * 4 + 4; ++ks)   // 16 keys: 8 columns of P, 16 rows of V further
+                        tc_mma_ta(tmem + 2 * TK + st * D, tmem + (uint32_t)(st * TK + ks * 8),
+                                  desc_v + (uint64_t)((st * TILE_BYTES + ks * STEP_BYTES) >> 4), idesc_pv, (j >= 2 || ks) ? 1u : 0u);
+                }
+                if (timed_out) break;
                 tc_commit(&o_done[st]);
                 // the scores of the group's next block go where this P lies: the tensor cores run the
                 // products in the order in which they were issued
-                if (j + 2 < nb && !issue_s(j + 2)) { timed_out = true; break; }
+                if (j + 2 < nb && !issue_s(j + 2, true)) { timed_out = true; break; }
             }
         }
     } else {
@@ -298,8 +328,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             const int kb = key_lo + j * TK;
             // a block all of whose keys every row of the tile sees needs no mask
             const bool open = (kb + TK - 1 <= pos_lo) && (p.window <= 0 || kb > pos_hi - p.window);
-            const float raw_max = open ? row_max<false>(s_addr, kb, pos, p.window, valid)
-                                       : row_max<true>(s_addr, kb, pos, p.window, valid);
+            uint32_t raw[TK];
+            load_row(s_addr, raw);
+            // keys [lo, hi) of the block are seen by this row
+            const int hi = valid ? pos - kb + 1 : 0;
+            const int lo = (p.window > 0) ? pos - p.window + 1 - kb : 0;
+            const float raw_max = open ? row_max<false>(raw, lo, hi) : row_max<true>(raw, lo, hi);
             const float mx = fmaxf(m, raw_max * p.scale_log2);          // the scale is positive
             // a row that has seen no key yet takes the maximum as it is: its O is still zero
             const bool raise = (m != -INFINITY) && (mx > m + RAISE);
@@ -321,10 +355,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             }
             if (m == -INFINITY) m = mx;
             const float base = (m == -INFINITY) ? 0.f : m;
-            const float lsum = open ? write_p<false>(s_addr, kb, pos, p.window, valid, p.scale_log2, base)
-                                    : write_p<true>(s_addr, kb, pos, p.window, valid, p.scale_log2, base);
-            l += lsum;
-            tc_wait_st();
             if (j == nb - 1) {
                 // The last run of keys may reach beyond the last key, into rows of the page that hold
                 // whatever was there before.  Their P is 0, but 0 times a stale NaN or infinity is not:
@@ -340,10 +370,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 }
             }
-            // P is in tensor memory: tell the MMA warp
+            float2 sum[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+            if (open) write_p_half<false, 0>(raw, s_addr, lo, hi, p.scale_log2, base, sum);
+            else write_p_half<true, 0>(raw, s_addr, lo, hi, p.scale_log2, base, sum);
+            // half of P is in tensor memory: tell the MMA warp
+            tc_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[g]);
+            if (lane == 0) mbar_arrive(&p_full[2 * g]);
+            if (open) write_p_half<false, 1>(raw, s_addr, lo, hi, p.scale_log2, base, sum);
+            else write_p_half<true, 1>(raw, s_addr, lo, hi, p.scale_log2, base, sum);
+            l += (sum[0].x + sum[0].y) + (sum[1].x + sum[1].y);
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[2 * g + 1]);
         }
         if (nb > 0 && !timed_out) {
             // the two groups' maxima and sums of the row meet; each thread then writes 64 dims of it
