@@ -213,17 +213,23 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   const int* __restrict__ block_table, int table_stride, int n_seqs, int n_pages,
                                   int heads, int kv_heads, int head_dim, int page_size, int rotate, int store,
                                   int* status) {
+    // Positions, sequences and block tables are the step's own inputs, there before its first kernel starts: they are
+    // read while the kernel before this one may still run; qkv, which that kernel writes, waits.  (Every thread
+    // waits before it leaves: a kernel all of whose blocks left early would be done before the one before it.)
     pdl_launch();
-    pdl_wait();
     const int t = blockIdx.x;
     const int seq = token_seq[t];
+    const bool seq_ok = seq >= 0 && seq < n_seqs;
+    const int pos = seq_ok ? positions[t] : 0;
+    const bool pos_ok = pos >= 0 && (!rotate || pos < max_pos);
+    const int page = (store && seq_ok && pos_ok) ? block_table[(size_t)seq * table_stride + pos / page_size] : 0;
+    pdl_wait();
     if (seq < 0) return;  // padding
-    if (seq >= n_seqs) {
+    if (!seq_ok) {
         if (threadIdx.x == 0) set_status(status, kStatusBadSequence, seq);
         return;
     }
-    const int pos = positions[t];
-    if (pos < 0 || (rotate && pos >= max_pos)) {
+    if (!pos_ok) {
         if (threadIdx.x == 0) set_status(status, kStatusBadPosition, pos);
         return;
     }
@@ -235,7 +241,6 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
     size_t page_base = 0;
     int slot = 0;
     if (store) {
-        const int page = block_table[(size_t)seq * table_stride + pos / page_size];
         if (page < 0 || page >= n_pages) {
             if (threadIdx.x == 0) set_status(status, kStatusBadPage, page);
             store = 0;

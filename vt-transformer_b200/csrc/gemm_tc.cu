@@ -327,8 +327,8 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
         const bool have_scratch = scratch != nullptr && counters != nullptr;
         const int ksplit = (EPI == 2) ? gemm_tc_shares(m, n, k)
                                       : small_batch_ksplit(n, k, bn, have_scratch, scratch_floats, n_counters);
-        if (bn == 16) return launch_cfg<16, 11, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
-        if (bn == 32) return launch_cfg<32, 10, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
+        if (bn == 16) return launch_cfg<16, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
+        if (bn == 32) return launch_cfg<32, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
         if (bn == 64) return launch_cfg<64, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
         if (bn == 128) return launch_cfg<128, 6, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
         return launch_cfg<256, 4, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
