@@ -4,13 +4,10 @@ and dtype: the host-side tests run them on the CPU with the stand-in kernels
 from __future__ import annotations
 
 import copy
-import math
 import os
-import random
 from dataclasses import dataclass, replace
 from typing import List
 
-import numpy as np
 import torch
 
 import helpers

@@ -52,8 +52,8 @@ def test_end_tokens_and_position_limit_come_from_the_model_spec(fake_backend, tm
     """An architecture whose configuration names things its own way: the engine reads the positions a model can
     hold and the tokens that end a request from the ModelSpec, not from a configuration key."""
     import copy
-    from dataclasses import dataclass, replace
-    from vt_transformer_b200 import LLM, SamplingParams
+    from dataclasses import replace
+    from vt_transformer_b200 import LLM
     from vt_transformer_b200.config import Qwen2Config, config_from_dict, register_architecture, unregister_architecture
     from vt_transformer_b200.models.qwen2 import qwen2_model_spec
     from vt_transformer_b200.weights import write_random_model

@@ -124,7 +124,6 @@ def test_a_far_key_among_hundreds_is_found(tmp_path, dtype):
     token attends to a few keys that differ from token to token: a key missed at a page's
     edge, in a page that was used before, or far back, changes the logits by far more than
     the tolerance."""
-    from safetensors import safe_open
     from vt_transformer_b200.engine import StepEntry
     from vt_transformer_b200.weights import SafetensorsSource, write_random_model
     from vt_transformer_b200.weights import safetensors_io as st
@@ -190,7 +189,6 @@ def test_a_folder_stored_in_32_bit_rounded_at_load_runs_the_bfloat16_kernels(tmp
     """A model stored in float32, loaded in bfloat16 mode: with fp32_weights="round" its matrices are bfloat16 (the
     tcgen05 products run) and the logits are those of a folder that stores the rounded values, bit for bit; kept in
     32-bit (the default, with a warning) the products run the 32-bit kernel and the logits are within the bound."""
-    import warnings
     from test_weights import wide_and_rounded_folders
     from vt_transformer_b200.engine import ModelRunner, StepEntry
     wide, rounded = wide_and_rounded_folders(str(tmp_path))

@@ -1,7 +1,5 @@
 """Each part alone on the GPU, built from its spec and fed its own tensors, against the plain
 implementation's function for it, at sizes of its own."""
-import math
-
 import pytest
 import torch
 

@@ -4,7 +4,6 @@ import math
 import os
 
 import numpy as np
-import pytest
 import torch
 
 import helpers

@@ -24,7 +24,7 @@ from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..parts.base import CacheView, KVCacheSpec, PagedLayout, StateLayout, StateSpec, cache_layout
+from ..parts.base import CacheView, PagedLayout, StateLayout, cache_layout
 
 
 class OutOfPages(RuntimeError):

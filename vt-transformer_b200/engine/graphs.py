@@ -11,9 +11,8 @@ from __future__ import annotations
 
 import gc
 
-from typing import Dict, List, Sequence, Tuple
+from typing import Sequence
 
-import numpy as np
 import torch
 
 from .batch import Layout, StepEntry, context_from, fill_host, slices_of

@@ -19,7 +19,7 @@ from ..config.registry import get_architecture, load_config
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .runner import ModelRunner
-from .scheduler import ReqResult, Scheduler, SchedulerConfig, StepResult
+from .scheduler import Scheduler, SchedulerConfig, StepResult
 
 
 class _InFlight:

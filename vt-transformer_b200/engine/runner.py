@@ -10,10 +10,9 @@ logits and leaves sampling to the caller.
 """
 from __future__ import annotations
 
-import os
 import sys
 import warnings
-from typing import Dict, List, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 
@@ -22,8 +21,8 @@ from ..cache.manager import DEFAULT_PAGE_SIZE, CacheManager
 from ..config.registry import get_architecture, load_config
 from ..models.base import DecoderModel
 from ..parts.base import Runtime
-from ..weights.loader import RandomSource, SafetensorsSource, WeightSource
-from .batch import StepContext, StepEntry, build_context
+from ..weights.loader import RandomSource, SafetensorsSource
+from .batch import StepEntry, build_context
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}

@@ -2,7 +2,7 @@
 order, a head part.  It names no architecture and knows no part's kind."""
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict, Optional
 
 import torch
 

@@ -9,7 +9,7 @@ seed and the index of the output token.
 """
 from __future__ import annotations
 
-from typing import List, Sequence
+from typing import Sequence
 
 import torch
 
