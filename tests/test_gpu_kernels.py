@@ -728,6 +728,52 @@ def test_sampling_kernel_draws_what_the_plain_sampler_draws(vocab):
     assert len(set(out.tolist())) > rows // 2
 
 
+@pytest.mark.parametrize("vocab", [152064, 151937])
+def test_sampling_kernel_on_peaked_flat_and_tied_rows(vocab):
+    """The sampling kernel's ways through a row, each against the plain sampler: a peaked row (few tokens hold the
+    mass: thresholds and draw finished among a few gathered candidates), a flat row (top_p keeps tens of thousands:
+    further passes over the row), top_k beyond what is gathered, thousands of values equal to the k-th (all kept),
+    top_p of 0 (the largest alone) and a row whose length is no multiple of four (its start is on no 16-byte
+    boundary)."""
+    from vt_transformer_b200.sampling import uniform
+    torch.manual_seed(9)
+    peaked = torch.randn(vocab) * 2
+    peaked[torch.randperm(vocab)[:40]] += 12.0
+    flat = torch.randn(vocab) * 0.5
+    tied = torch.randn(vocab)
+    tied[torch.randperm(vocab)[:3000]] = 2.5                    # thousands of equals at the edge of top_k
+    tied[torch.randperm(vocab)[:10]] += 6.0
+    rows, params = [], []
+    for base in (peaked, flat, tied):
+        for (t, k, p) in [(0.7, 20, 0.8), (1.0, -1, 0.9), (0.8, 50, 1.0), (1.0, 5000, 0.95), (1.2, -1, 0.0), (0.9, 300, 0.999),
+                          (1.0, -1, 1.0), (0.5, 2000, 1.0)]:
+            rows.append(base)
+            params.append((t, k, p))
+    logits = torch.stack(rows).to(DEV)
+    n = len(rows)
+    for trial in range(3):
+        us = [uniform(11 + trial, r) for r in range(n)]
+        out = torch.empty(n, dtype=torch.int32, device=DEV)
+        ops().sample(logits, torch.tensor([q[0] for q in params], device=DEV),
+                     torch.tensor([q[1] for q in params], dtype=torch.int32, device=DEV),
+                     torch.tensor([q[2] for q in params], device=DEV), torch.tensor(us, device=DEV), out)
+        host = logits.cpu()
+        want = [plain.sample(host[r], params[r][0], float(torch.tensor(us[r], dtype=torch.float32)), params[r][1], params[r][2])
+                for r in range(n)]
+        assert out.tolist() == want, [(r, params[r]) for r in range(n) if out.tolist()[r] != want[r]]
+    # the ends of the kept sets: u = 0 draws the first kept index, u just below 1 one of the last
+    for uval in (0.0, 0.99999994):
+        out = torch.empty(n, dtype=torch.int32, device=DEV)
+        ops().sample(logits, torch.tensor([q[0] for q in params], device=DEV),
+                     torch.tensor([q[1] for q in params], dtype=torch.int32, device=DEV),
+                     torch.tensor([q[2] for q in params], device=DEV), torch.full((n,), uval, device=DEV), out)
+        uu = float(torch.tensor(uval, dtype=torch.float32))
+        for r in range(n):
+            kept = torch.nonzero(plain.kept_probabilities(logits[r].cpu(), *params[r])).flatten()
+            assert int(out[r]) == plain.sample(logits[r].cpu(), params[r][0], uu, params[r][1], params[r][2]), (r, params[r])
+            assert int(out[r]) in kept.tolist() and (uval > 0 or int(out[r]) == int(kept[0]))
+
+
 def test_sampling_kernel_follows_the_distribution():
     logits = torch.tensor([0.0, math.log(2.0), math.log(5.0), -40.0] + [-60.0] * 96, device=DEV).repeat(4000, 1)
     n = logits.shape[0]

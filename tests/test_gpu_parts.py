@@ -26,6 +26,11 @@ def tensors_for(part, sigma=0.1, seed=0):
     return {name: random_tensor(name, spec, seed, sigma) for name, spec in part.param_specs().items()}
 
 
+@pytest.fixture(autouse=True)
+def _same_numbers_whatever_ran_before():
+    torch.manual_seed(1234)
+
+
 def tol(dtype):
     return 3e-5 if dtype == torch.float32 else 3e-2
 
@@ -141,4 +146,4 @@ def test_a_matrix_stored_in_32_bit_stays_32_bit_on_the_bfloat16_path():
     h = torch.randn(5, 64, device=DEV).to(torch.bfloat16)
     out = ops_module().dense(part.forward(h, None))
     ref = plain.swiglu(h.cpu().double(), *(w[f"m.{n}_proj.weight"].double() for n in ("gate", "up", "down")))
-    assert float((out.cpu().double() - ref).abs().max()) <= 3e-2
+    close(out, ref, torch.bfloat16)          # the bound of every other part here: at the scale of the reference
