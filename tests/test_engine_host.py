@@ -139,8 +139,10 @@ def test_single_token_steps_cut_their_keys_by_the_work_and_fetch_by_boxes_where_
         assert o._decode_plan(32, 2048, dev) == (3, 22, False)
         # batch 64: a CTA a (sequence, KV head) already fills the SMs: no cut
         assert o._decode_plan(256, 2048, dev) == (1, 0, False)
-        # one sequence of up to 4,096 keys: runs of 8 blocks, more than a cluster holds, met in scratch memory
-        assert o._decode_plan(2, 4096, dev) == (32, 8, True)
+        # one sequence of up to 4,096 keys: runs of 32 blocks (not shorter: a run has its fixed cost), met in scratch memory
+        assert o._decode_plan(2, 4096, dev) == (8, 32, True)
+        # one sequence of 4 KV heads of up to 32,768 keys: no more runs than give every SM one CTA of eight warps
+        assert o._decode_plan(4, 32768, dev) == (37, 32, True)
         # 32 sequences of 2 KV heads under a bound of 16,384 keys: their lengths may differ by thousands of keys, so
         # up to 7 runs of 148 blocks meet in scratch memory and a short sequence takes one CTA
         assert o._decode_plan(64, 16384, dev) == (7, 148, True)

@@ -80,7 +80,7 @@ def test_decode_steps_of_many_requests(folders, n_live, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_decode_with_keys_cut_into_more_runs_than_a_cluster_holds(tmp_path, dtype):
+def test_decode_with_keys_cut_into_more_runs_than_a_cluster_holds(tmp_path, dtype, request):
     """One request of 2,100 tokens decodes alone (head size 128, two KV heads): its keys are cut into more than
     eight runs, which meet in scratch memory and are merged by the CTA that arrives last; beside it, the same
     request in a step of three (fewer runs, merged inside a cluster)."""
@@ -94,6 +94,9 @@ def test_decode_with_keys_cut_into_more_runs_than_a_cluster_holds(tmp_path, dtyp
     seqs = _sequences("D", 1, seed=7, shortest=2100, longest=2100)
     ref = helpers.plain_logits(folder, seqs[0])
     bound = helpers.tol(dtype, ref=ref)
+    # (runs as short as a cluster's, so that this sequence is cut into more of them than a cluster holds)
+    shortest, ops.DECODE_MIN_RUN_LONG = ops.DECODE_MIN_RUN_LONG, 8
+    request.addfinalizer(lambda: setattr(ops, "DECODE_MIN_RUN_LONG", shortest))
     assert ops._decode_plan(2, 4096, torch.device(DEV))[0] > 8 and ops._decode_plan(2, 4096, torch.device(DEV))[2]
     for others in (0, 2):
         batch = seqs + _sequences("D", others, seed=8, longest=90)

@@ -772,15 +772,45 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
         tot_s[r] = tot;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < 16 * D; e += W * 32) {
-        const int r = e / D, d = e % D;
-        if (r >= rows_valid) continue;
+    // four dims of a row a thread (the rows that hold a query only), the runs' parts added in order, eight 16-byte
+    // loads on their way at a time: with one value a load and the rows without a query gone through as well, a
+    // single long sequence (64 runs) spent more time here than on its keys
+    for (int e = threadIdx.x; e < rows_valid * (D / 4); e += W * 32) {
+        const int r = e / (D / 4), d = (e % (D / 4)) * 4;
         const size_t idx0 = (size_t)(q_begin + r / group) * p.heads + kvh * group + r % group;
-        float acc = 0.f;
-#pragma unroll 8
-        for (int sp = 0; sp < runs; ++sp) acc += __ldcg(p.part_o + (sp * stride + idx0) * D + d) * wgt[r * MAXS + sp];
+        const float* src = p.part_o + idx0 * D + d;
+        const float* w_r = wgt + r * MAXS;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        int sp = 0;
+        for (; sp + 8 <= runs; sp += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + i) * stride * D));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float w = w_r[sp + i];
+                acc.x += v[i].x * w;
+                acc.y += v[i].y * w;
+                acc.z += v[i].z * w;
+                acc.w += v[i].w * w;
+            }
+        }
+        for (; sp < runs; ++sp) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * stride * D));
+            const float w = w_r[sp];
+            acc.x += v.x * w;
+            acc.y += v.y * w;
+            acc.z += v.z * w;
+            acc.w += v.w * w;
+        }
         const float tot = tot_s[r];
-        p.out[idx0 * D + d] = __float2bfloat16_rn(tot > 0.f ? acc / tot : 0.f);
+        // (a / tot as before, not a * (1 / tot): the same bits as the merge inside a cluster gives)
+        __nv_bfloat162 lo = __floats2bfloat162_rn(tot > 0.f ? acc.x / tot : 0.f, tot > 0.f ? acc.y / tot : 0.f);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(tot > 0.f ? acc.z / tot : 0.f, tot > 0.f ? acc.w / tot : 0.f);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p.out + idx0 * D + d) = packed;
     }
     if (threadIdx.x == 0) counters[tile] = 0;
 }

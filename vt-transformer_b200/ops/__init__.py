@@ -377,6 +377,7 @@ DECODE_BLOCK = 16         # keys in a block of the single-token attention kernel
 DECODE_CTAS_PER_SM = float(os.environ.get("VTB200_DECODE_CTAS_PER_SM", "0.65"))
 DECODE_CTAS_PER_SM_LONG = float(os.environ.get("VTB200_DECODE_CTAS_PER_SM_LONG", "1.5"))
 DECODE_MIN_RUN = int(os.environ.get("VTB200_DECODE_MIN_RUN", "8"))        # blocks below which a run of keys is not cut further
+DECODE_MIN_RUN_LONG = int(os.environ.get("VTB200_DECODE_MIN_RUN_LONG", "32"))   # the same where the runs meet in scratch memory
 DECODE_LONG_BOUND = int(os.environ.get("VTB200_DECODE_LONG_BOUND", "4096"))   # keys from which the runs meet in scratch memory
 
 
@@ -408,9 +409,14 @@ def _decode_plan(pairs: int, span: int, device):
         run = max(DECODE_MIN_RUN, int(-(-typical // per_pair)))
         splits = min(8, int(-(-typical // run)))
         return (splits, run, False) if splits > 1 else (1, 0, False)
+    # (measured on a B200, every sequence at the bound: a run below 32 blocks costs a lone sequence of 8,192 keys a
+    # third more (27 against 20 us), two of them twice (37 against 19); with few sequences, one CTA an SM with all
+    # eight warps beats two with six (one sequence of 32,768 keys: 24 against 33 us))
     per_pair = DECODE_CTAS_PER_SM_LONG * sms / max(pairs, 1)
-    run = max(DECODE_MIN_RUN, int(-(-typical // max(per_pair, 1.0))))
+    run = max(DECODE_MIN_RUN_LONG, int(-(-typical // max(per_pair, 1.0))))
     splits = min(64, -(-blocks // run))
+    if pairs * 16 <= sms:
+        splits = min(splits, max(1, sms // pairs))
     return (splits, run, True) if splits > 1 else (1, 0, False)
 
 
