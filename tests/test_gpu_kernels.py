@@ -624,6 +624,39 @@ def test_gate_up_product_of_a_pair_of_ctas(m, inter, k, bn):
         assert torch.equal(one, out)
 
 
+@pytest.mark.parametrize("m,n,k,epi", [(300, 520, 8200, 0), (512, 3584, 18944, 0), (272, 1000, 8264, 0), (400, 1504, 8192, 1)])
+def test_pairs_of_ctas_with_k_in_two_shares(m, n, k, epi):
+    """Few tiles and a long inner dimension: the kernel of two CTAs a tile cuts k into two shares for twice the pairs;
+    the shares meet in scratch memory and the pair that arrives last adds them.  Twice: the counters must be back at
+    zero; against the plain product, and close to the same kernel without shares (which adds in another order)."""
+    o = ops()
+    torch.manual_seed(19)
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) / math.sqrt(k) * (2 if epi else 1)).to(torch.bfloat16)
+    bias = torch.randn(n, device=DEV) if epi == 0 else None
+    if epi == 0:
+        ref = plain.linear(x.cpu().double(), w.cpu().double(), bias.cpu().double())
+        packed = w
+    else:
+        inter = n // 2
+        g, u = x.cpu().double() @ w[:inter].cpu().double().t(), x.cpu().double() @ w[inter:].cpu().double().t()
+        ref = g / (1 + torch.exp(-g)) * u
+        packed = o.interleave_gate_up(w[:inter], w[inter:])
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    scratch, counters = o._split_workspace(torch.device(DEV))
+    cols = n if epi == 0 else n // 2
+    whole = torch.full((m, cols), float("nan"), device=DEV, dtype=torch.bfloat16)
+    o.backend().gemm_tc_pair(x, packed, bias, whole, epi, 0, status)
+    for _ in range(2):
+        out = torch.full((m, cols), float("nan"), device=DEV, dtype=torch.bfloat16)
+        o.backend().gemm_tc_pair(x, packed, bias, out, epi, 0, status, scratch, counters)
+        close(out, ref, torch.bfloat16, 2)
+        assert int(counters.abs().sum()) == 0 and status.tolist() == [0, 0]
+    # two orders of adding the same 32-bit products: a last bit of bfloat16 here and there, no more
+    assert float((out.float() - whole.float()).abs().max()) <= float(ref.abs().max()) / 128
+    assert float((out.float() != whole.float()).float().mean()) < 0.2
+
+
 def test_products_of_many_rows_go_to_pairs_of_ctas_and_give_the_same_numbers():
     """What the dispatch sends to the kernel of two CTAs a tile (many rows, a long k, a tile for every pair) equals,
     bit for bit, what that kernel gives when called by name; with 32-bit results and for fewer rows the dispatch

@@ -236,7 +236,7 @@ void gemm_tc(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tenso
 }
 
 void gemm_tc_pair(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tensor& out, int64_t epilogue, int64_t bn,
-                  c10::optional<Tensor> status) {
+                  c10::optional<Tensor> status, c10::optional<Tensor> scratch, c10::optional<Tensor> counters) {
     check_cuda(x, "x"); check_cuda(w, "w"); check_cuda(out, "out");
     TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16,
                 "gemm_tc_pair: x, w and out must be bfloat16");
@@ -256,9 +256,23 @@ void gemm_tc_pair(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, 
         TORCH_CHECK(bias->numel() == n, "gemm_tc_pair: bias must have one entry for each output column");
         bp = bias->data_ptr<float>();
     }
+    // scratch and counters (zeroed once; the kernel leaves them zero): with them, k is cut over pairs where the tiles are few
+    float* sp = nullptr;
+    int* cp = nullptr;
+    long long scratch_floats = 0;
+    int n_counters = 0;
+    if (scratch.has_value() && counters.has_value()) {
+        check_f32(*scratch, "scratch");
+        check_cuda(*counters, "counters");
+        TORCH_CHECK(counters->scalar_type() == torch::kInt32 && counters->is_contiguous(), "gemm_tc_pair: counters must be contiguous int32");
+        sp = scratch->data_ptr<float>();
+        scratch_floats = scratch->numel();
+        cp = counters->data_ptr<int>();
+        n_counters = (int)counters->numel();
+    }
     c10::cuda::CUDAGuard guard(x.device());
-    check_launch(vtb::launch_gemm_tc_pair(x.data_ptr(), w.data_ptr(), bp, out.data_ptr(), m, n, k, (int)epilogue, (int)bn,
-                                          status_ptr(status), stream_of(x)), "gemm_tc_pair");
+    check_launch(vtb::launch_gemm_tc_pair(x.data_ptr(), w.data_ptr(), bp, out.data_ptr(), m, n, k, (int)epilogue, (int)bn, sp,
+                                          scratch_floats, cp, n_counters, status_ptr(status), stream_of(x)), "gemm_tc_pair");
 }
 
 bool attention_mma_supports(int64_t head_dim, int64_t heads, int64_t kv_heads, int64_t warps) {
@@ -482,7 +496,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_tc", &gemm_tc, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"), py::arg("status") = py::none(),
           py::arg("scratch") = py::none(), py::arg("counters") = py::none(), py::arg("epilogue") = 0);
     m.def("gemm_tc_pair", &gemm_tc_pair, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"), py::arg("epilogue") = 0,
-          py::arg("bn") = 256, py::arg("status") = py::none());
+          py::arg("bn") = 256, py::arg("status") = py::none(), py::arg("scratch") = py::none(), py::arg("counters") = py::none());
     m.def("gemm_tc_shares", [](int64_t m, int64_t n, int64_t k) { return (int64_t)vtb::gemm_tc_shares(m, n, k); });
     m.def("attention_mma_supports", &attention_mma_supports);
     m.def("attention_mma", &attention_mma, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),

@@ -344,8 +344,9 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
         const bool wide = !(n <= 128 || m <= 128);
         // The width of a tile: 256 features, or fewer where that makes the rounds of one tile an SM come out
         // better (n = 3584 and 2,048 tokens: 224 tiles of 256 features are 1.5 rounds and take the time of 2;
-        // 288 tiles of 208 are 1.95 rounds of narrower tiles).  Cost of a width: rounds * (width + a fixed part
-        // for the 128-row operand of every k-block).
+        // 288 tiles of 208 are 1.95 rounds of narrower tiles; a few hundred tokens: tiles of 160 or 128 features,
+        // so that most SMs have one: 640 tokens by 3584 x 18944 in 109 us where tiles of 192 took 165).  Cost of a
+        // width: rounds * (width + a fixed part for the 128-row operand of every k-block).
         int bn = wide ? 256 : 128;
         // a small product (a wide batch of a small model: 256 rows by a matrix of a megabyte or two) has a dozen tiles
         // of 128 x 192: tiles of 64 features give four times the CTAs, each done in a quarter of the time
@@ -354,7 +355,7 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
             bn = 64;
         } else if (wide) {
             long best = -1;
-            for (int cand : {256, 240, 224, 208, 192}) {
+            for (int cand : {256, 240, 224, 208, 192, 160, 128}) {
                 const long t = (long)((m + BM - 1) / BM) * ((n + cand - 1) / cand);
                 const long cost = ((t + sms - 1) / sms) * (cand + 24);
                 if (best < 0 || cost < best) {
@@ -385,6 +386,8 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
             case 224: return launch_cfg<224, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
             case 208: return launch_cfg<208, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
             case 192: return launch_cfg<192, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
+            case 160: return launch_cfg<160, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
+            case 128: if (wide) return launch_cfg<128, 6, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
         }
         if (bn == 64) return launch_cfg<64, 8, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
         return launch_cfg<128, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
@@ -404,8 +407,13 @@ int gemm_tc_shares(int m, int n, int k) {
 // rows on, the feed-forward's from 512; 1.5B: the feed-forward's from 1,024 rows, by 1 to 7 %); with k = 896 or fewer
 // tiles than pairs it is level or loses.
 static bool pair_for(int m, int n, int k) {
-    if (m < 512 || k < 1536) return false;
+    if (k < 1536 || m <= 256) return false;
     const long pair_tiles = (long)((m + 255) / 256) * ((n + 255) / 256);
+    // a long inner dimension under a few hundred rows (the feed-forward's second product of a short portion): the pairs
+    // take it with k in two shares, 76 to 92 us where the kernel of one CTA a tile takes 97 to 104 (272 to 512 rows by
+    // 3584 x 18944); with more tiles than half the pairs there are no shares and the kernel of one CTA a tile is ahead again
+    if (k >= 8192 && 4 * pair_tiles <= sm_count()) return true;
+    if (m < 512) return false;
     return pair_tiles * 2 >= sm_count();
 }
 
@@ -415,7 +423,7 @@ cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const fl
     if (m == 0 || n == 0) return cudaSuccess;
     if (k % 8 != 0 || k < 8) return cudaErrorInvalidValue;
     if (out_dtype == kBF16 && (epilogue == 0 || epilogue == 1) && pair_for(m, n, k))
-        return launch_gemm_tc_pair(x, w, bias, out, m, n, k, epilogue, 0, status, stream);
+        return launch_gemm_tc_pair(x, w, bias, out, m, n, k, epilogue, 0, scratch, scratch_floats, counters, n_counters, status, stream);
     if (epilogue == 1) {
         if (n % 16 != 0 || bias != nullptr || out_dtype != kBF16) return cudaErrorInvalidValue;
         return launch_typed<1, __nv_bfloat16>(x, w, nullptr, (__nv_bfloat16*)out, m, n, k, scratch, scratch_floats,

@@ -85,7 +85,8 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
 template <int BN, int STAGES, int EPI, typename TOut>
 __global__ void __launch_bounds__(PTHREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo, int* status) {
+                    const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo, int ksplit,
+                    float* __restrict__ scratch, int* __restrict__ counters, int* status) {
     static_assert(BN % 32 == 0 && BN <= 256, "each CTA holds half of the tile's rows of w, in whole swizzle groups");
     constexpr int BH = BN / 2;                       // rows of w a CTA loads
     constexpr int B_STAGE = BH * PBK * 2;
@@ -100,6 +101,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t* acc_full = empty + STAGES;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();            // 0: the CTA that issues the MMAs
@@ -107,6 +109,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int a_tiles = (rows_a + 2 * PBM - 1) / (2 * PBM), b_tiles = (rows_b + BN - 1) / BN;
     const int tiles = a_tiles * b_tiles;
     const int nkb = (k + PBK - 1) / PBK;
+    // A unit is (tile, share of k): with fewer tiles than pairs of SMs and a long k, the k-blocks of a tile are cut
+    // into `ksplit` shares for as many pairs; unit u is share u / tiles of tile u % tiles.
+    const int units = tiles * ksplit;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -136,9 +141,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             int kit = 0;
             bool waited = false;
-            for (int t = pair; t < tiles && !timed_out; t += n_pairs) {
+            for (int u = pair; u < units && !timed_out; u += n_pairs) {
+                const int t = u % tiles, krank = u / tiles;
+                const int kb0 = (int)((long long)krank * nkb / ksplit), kb1 = (int)((long long)(krank + 1) * nkb / ksplit);
                 const int a_row0 = (t % a_tiles) * 2 * PBM + (int)rank * PBM, b_row0 = (t / a_tiles) * BN + (int)rank * BH;
-                for (int kb = 0; kb < nkb; ++kb, ++kit) {
+                for (int kb = kb0; kb < kb1; ++kb, ++kit) {
                     const int s = kit % STAGES;
                     if (kit >= STAGES && !mbar_wait(&empty[s], ((kit / STAGES) & 1) ^ 1)) { timed_out = true; break; }
                     const uint32_t bar = in_cta(smem_u32(&full[s]), 0);
@@ -157,19 +164,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0 && rank == 0) {
             const uint32_t idesc = instr_desc(2 * PBM, BN);
             int kit = 0, ui = 0;
-            for (int t = pair; t < tiles && !timed_out; t += n_pairs, ++ui) {
+            for (int u = pair; u < units && !timed_out; u += n_pairs, ++ui) {
+                const int krank = u / tiles;
+                const int kb0 = (int)((long long)krank * nkb / ksplit), kb1 = (int)((long long)(krank + 1) * nkb / ksplit);
                 const int buf = ui & 1;
                 if (ui >= 2 && !mbar_wait(&acc_empty[buf], ((ui >> 1) & 1) ^ 1)) { timed_out = true; break; }
                 tc_fence_after();
                 const uint32_t acc = tmem + (uint32_t)(buf * COLS);
-                for (int kb = 0; kb < nkb; ++kb, ++kit) {
+                for (int kb = kb0; kb < kb1; ++kb, ++kit) {
                     const int s = kit % STAGES;
                     if (!mbar_wait(&full[s], (kit / STAGES) & 1)) { timed_out = true; break; }
                     tc_fence_after();
                     const uint64_t ad = smem_desc(a_s + s * PA_STAGE), bd = smem_desc(b_s + s * B_STAGE);
 #pragma unroll
                     for (int kk = 0; kk < PBK / 16; ++kk)
-                        tc_mma_pair(acc, ad + 2 * kk, bd + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                        tc_mma_pair(acc, ad + 2 * kk, bd + 2 * kk, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
                     tc_commit_pair(&empty[s]);
                 }
                 tc_commit_pair(&acc_full[buf]);
@@ -184,12 +193,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int r = q * 32 + lane;
         const uint32_t acc_empty_first = in_cta(smem_u32(&acc_empty[0]), 0);
         int ui = 0;
-        for (int t = pair; t < tiles; t += n_pairs, ++ui) {
+        for (int u = pair; u < units; u += n_pairs, ++ui) {
+            const int t = u % tiles, krank = u / tiles;
             const int a_row0 = (t % a_tiles) * 2 * PBM + (int)rank * PBM, b_row0 = (t / a_tiles) * BN;
             const int buf = ui & 1;
             bool ok = !timed_out && mbar_wait(&acc_full[buf], (ui >> 1) & 1);
             if (!ok) timed_out = true;
             tc_fence_after();
+            // a share of k: this CTA's 128 rows of it as 32-bit [row][column] in scratch memory
+            float* mine = ksplit > 1 ? scratch + (((size_t)t * ksplit + krank) * 2 + rank) * (size_t)(BN * PBM) : nullptr;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 float v[16];
@@ -207,7 +219,57 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     __syncwarp();
                     if (lane == 0) mbar_arrive_remote(acc_empty_first + (uint32_t)(buf * 8));
                 }
+                if (ksplit > 1) {
+#pragma unroll
+                    for (int i = 0; i < 16; i += 4)
+                        __stcg(reinterpret_cast<float4*>(mine + (size_t)r * BN + c0 + i), make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]));
+                    continue;
+                }
                 emit16<false, EPI, TOut>(v, r, a_row0, b_row0, c0, rows_a, rows_b, bias, out, ldo);
+            }
+            if (ksplit > 1) {
+                // count this share in (a counter a tile and CTA of the pair: each CTA has its own 128 rows); the one
+                // that finds all others counted adds the shares, in their order, and stores.  Nobody waits.
+                __threadfence();
+                asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                if (threadIdx.x == 64) *last_flag = (atomicAdd(&counters[2 * t + (int)rank], 1) == ksplit - 1) ? 1 : 0;
+                asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                const bool last = *last_flag != 0;
+                asm volatile("bar.sync 1, 128;\n" ::: "memory");   // all have read the flag before it is written again
+                if (last) {
+                    __threadfence();
+                    const float* all = scratch + ((size_t)t * ksplit * 2 + rank) * (size_t)(BN * PBM);
+                    const bool live = (a_row0 + r) < rows_a;
+                    // a row a thread, 32 columns at a time: 16-byte loads, those of all shares on their way together
+                    // (a share is [row][column]: with one value a load the merge took longer than the share's products)
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 32) {
+                        if (b_row0 + c0 >= rows_b) break;
+                        float sum[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) sum[i] = 0.f;
+                        if (live) {
+#pragma unroll 4
+                            for (int rk = 0; rk < ksplit; ++rk) {
+                                const float4* src = reinterpret_cast<const float4*>(all + (size_t)rk * 2 * (BN * PBM) + (size_t)r * BN + c0);
+                                float4 part[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) part[i] = __ldcg(src + i);
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    sum[4 * i] += part[i].x;
+                                    sum[4 * i + 1] += part[i].y;
+                                    sum[4 * i + 2] += part[i].z;
+                                    sum[4 * i + 3] += part[i].w;
+                                }
+                            }
+                        }
+                        emit16<false, EPI, TOut>(*reinterpret_cast<float(*)[16]>(&sum[0]), r, a_row0, b_row0, c0, rows_a, rows_b, bias, out, ldo);
+                        if (c0 + 16 < BN)
+                            emit16<false, EPI, TOut>(*reinterpret_cast<float(*)[16]>(&sum[16]), r, a_row0, b_row0, c0 + 16, rows_a, rows_b, bias, out, ldo);
+                    }
+                    if (threadIdx.x == 64) counters[2 * t + (int)rank] = 0;       // ready for the next launch
+                }
             }
         }
     }
@@ -221,11 +283,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 template <int BN, int STAGES, int EPI, typename TOut>
-cudaError_t launch_pair_cfg(const void* x, int m, const void* w, int n, int k, const float* bias, TOut* out, int ldo, int* status,
+cudaError_t launch_pair_cfg(const void* x, int m, const void* w, int n, int k, const float* bias, TOut* out, int ldo,
+                            float* scratch, long long scratch_floats, int* counters, int n_counters, int* status,
                             cudaStream_t stream) {
     CUtensorMap map_a, map_b;
     if (!make_map(&map_a, x, m, k, PBM) || !make_map(&map_b, w, n, k, BN / 2)) return cudaErrorInvalidValue;
-    constexpr int smem = STAGES * (PA_STAGE + (BN / 2) * PBK * 2) + 1024 + 256;
+    constexpr int smem = STAGES * (PA_STAGE + (BN / 2) * PBK * 2) + 1024 + 256;      // (barriers, the slot, the flag: 17 words of 8 bytes at most)
     static std::atomic<unsigned long long> configured{0};
     cudaError_t e = allow_dynamic_smem(gemm_tc_pair_kernel<BN, STAGES, EPI, TOut>, smem, configured);
     if (e != cudaSuccess) return e;
@@ -233,9 +296,20 @@ cudaError_t launch_pair_cfg(const void* x, int m, const void* w, int n, int k, c
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     const int tiles = ((m + 2 * PBM - 1) / (2 * PBM)) * ((n + BN - 1) / BN);
-    const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+    // Half as many tiles as pairs of SMs, or fewer, and a long k: k in two shares, so that twice the pairs work.  Measured
+    // on a B200 (3584 features, k = 18944): 256 to 512 rows 67 to 78 us with two shares against 96 to 98 without; three
+    // shares in two rounds (640 and 768 rows) lost to no shares at all, and so did two shares of a short k (3584: a
+    // share's trip through scratch memory costs about as much as 60 k-blocks).  Two shares also add up to the same
+    // number in either order.
+    int ksplit = 1;
+    const int all_pairs = sms / 2, nkb = (k + PBK - 1) / PBK;
+    if (2 * tiles <= all_pairs && nkb >= 128 && scratch != nullptr && counters != nullptr && 2 * tiles <= n_counters &&
+        (long long)tiles * 2 * 2 * BN * PBM <= scratch_floats)
+        ksplit = 2;
+    const int units = tiles * ksplit;
+    const int pairs = units < all_pairs ? units : all_pairs;
     return launch(gemm_tc_pair_kernel<BN, STAGES, EPI, TOut>, dim3(2 * pairs, 1, 1), dim3(PTHREADS, 1, 1), smem, stream, dim3(2, 1, 1),
-                  map_a, map_b, bias, out, m, n, k, ldo, status);
+                  map_a, map_b, bias, out, m, n, k, ldo, ksplit, scratch, counters, status);
 }
 
 }  // namespace
@@ -243,7 +317,8 @@ cudaError_t launch_pair_cfg(const void* x, int m, const void* w, int n, int k, c
 // bfloat16 out [m, n] (epilogue 0, with bias) or [m, n / 2] (epilogue 1: SiLU(gate) * up over rows of w interleaved
 // in runs of 8).  `bn`: rows of w in a tile: 256, 224 or 192; 0: the one whose rounds of one tile a pair come out best.
 cudaError_t launch_gemm_tc_pair(const void* x, const void* w, const float* bias, void* out, int m, int n, int k, int epilogue,
-                                int bn, int* status, cudaStream_t stream) {
+                                int bn, float* scratch, long long scratch_floats, int* counters, int n_counters, int* status,
+                                cudaStream_t stream) {
     if (m == 0 || n == 0) return cudaSuccess;
     if (k % 8 != 0 || k < 8) return cudaErrorInvalidValue;
     __nv_bfloat16* o = (__nv_bfloat16*)out;
@@ -266,14 +341,14 @@ cudaError_t launch_gemm_tc_pair(const void* x, const void* w, const float* bias,
     }
     if (epilogue == 1) {
         if (n % 16 != 0 || bias != nullptr) return cudaErrorInvalidValue;
-        if (bn == 192) return launch_pair_cfg<192, 7, 1, __nv_bfloat16>(x, m, w, n, k, nullptr, o, n / 2, status, stream);
-        if (bn == 224) return launch_pair_cfg<224, 6, 1, __nv_bfloat16>(x, m, w, n, k, nullptr, o, n / 2, status, stream);
-        return launch_pair_cfg<256, 6, 1, __nv_bfloat16>(x, m, w, n, k, nullptr, o, n / 2, status, stream);
+        if (bn == 192) return launch_pair_cfg<192, 7, 1, __nv_bfloat16>(x, m, w, n, k, nullptr, o, n / 2, scratch, scratch_floats, counters, n_counters, status, stream);
+        if (bn == 224) return launch_pair_cfg<224, 6, 1, __nv_bfloat16>(x, m, w, n, k, nullptr, o, n / 2, scratch, scratch_floats, counters, n_counters, status, stream);
+        return launch_pair_cfg<256, 6, 1, __nv_bfloat16>(x, m, w, n, k, nullptr, o, n / 2, scratch, scratch_floats, counters, n_counters, status, stream);
     }
     if (epilogue != 0) return cudaErrorInvalidValue;
-    if (bn == 192) return launch_pair_cfg<192, 7, 0, __nv_bfloat16>(x, m, w, n, k, bias, o, n, status, stream);
-    if (bn == 224) return launch_pair_cfg<224, 6, 0, __nv_bfloat16>(x, m, w, n, k, bias, o, n, status, stream);
-    return launch_pair_cfg<256, 6, 0, __nv_bfloat16>(x, m, w, n, k, bias, o, n, status, stream);
+    if (bn == 192) return launch_pair_cfg<192, 7, 0, __nv_bfloat16>(x, m, w, n, k, bias, o, n, scratch, scratch_floats, counters, n_counters, status, stream);
+    if (bn == 224) return launch_pair_cfg<224, 6, 0, __nv_bfloat16>(x, m, w, n, k, bias, o, n, scratch, scratch_floats, counters, n_counters, status, stream);
+    return launch_pair_cfg<256, 6, 0, __nv_bfloat16>(x, m, w, n, k, bias, o, n, scratch, scratch_floats, counters, n_counters, status, stream);
 }
 
 }  // namespace vtb

@@ -73,7 +73,8 @@ cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const fl
 // The same product for many rows of x with a tile of 256 rows of x by `bn` (256 or 192) rows of w to a pair of CTAs
 // (tcgen05.mma.cta_group::2): bfloat16 out, epilogue 0 (bias) or 1 (SiLU(gate) * up).
 cudaError_t launch_gemm_tc_pair(const void* x, const void* w, const float* bias, void* out, int m, int n, int k, int epilogue,
-                                int bn, int* status, cudaStream_t stream);
+                                int bn, float* scratch, long long scratch_floats, int* counters, int n_counters, int* status,
+                                cudaStream_t stream);
 
 // Tensor-core attention over the paged cache (bfloat16).  A tile is 16 * warps rows, row r being
 // (token r / group, head r % group); `tiles` lists (sequence, first token) pairs, or is null when
