@@ -657,6 +657,32 @@ def test_pairs_of_ctas_with_k_in_two_shares(m, n, k, epi):
     assert float((out.float() != whole.float()).float().mean()) < 0.2
 
 
+@pytest.mark.parametrize("m,n,k", [(2560, 2048, 8192), (1536, 3584, 8200), (4200, 3584, 8192)])
+def test_pairs_of_ctas_cut_the_tiles_of_a_last_partial_round(m, n, k):
+    """More tiles than pairs of SMs and a last round of few tiles (80 = 74 + 6, 84 = 74 + 10, 238 = 3 * 74 + 16): with
+    scratch memory those tiles' k-blocks are cut into shares for the pairs that would stand idle; the other tiles are
+    as without.  The last case's x is larger than half of L2: its tiles are taken across the rows of w first."""
+    o = ops()
+    torch.manual_seed(20)
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    bias = torch.randn(n, device=DEV)
+    ref = (x.double() @ w.double().t() + bias.double()).cpu()            # a plain 64-bit product (on the device: 40 GFLOP)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    scratch, counters = o._split_workspace(torch.device(DEV))
+    whole = torch.full((m, n), float("nan"), device=DEV, dtype=torch.bfloat16)
+    o.backend().gemm_tc_pair(x, w, bias, whole, 0, 256, status)
+    close(whole, ref, torch.bfloat16, 2)
+    for _ in range(2):
+        out = torch.full((m, n), float("nan"), device=DEV, dtype=torch.bfloat16)
+        o.backend().gemm_tc_pair(x, w, bias, out, 0, 256, status, scratch, counters)
+        close(out, ref, torch.bfloat16, 2)
+        assert int(counters.abs().sum()) == 0 and status.tolist() == [0, 0]
+    changed = (out.float() != whole.float()).float().mean()
+    assert 0 < float(changed) < 0.1                       # only the cut tiles add in another order
+    assert float((out.float() - whole.float()).abs().max()) <= float(ref.abs().max()) / 128
+
+
 def test_products_of_many_rows_go_to_pairs_of_ctas_and_give_the_same_numbers():
     """What the dispatch sends to the kernel of two CTAs a tile (many rows, a long k, a tile for every pair) equals,
     bit for bit, what that kernel gives when called by name; with 32-bit results and for fewer rows the dispatch

@@ -85,7 +85,7 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
 template <int BN, int STAGES, int EPI, typename TOut>
 __global__ void __launch_bounds__(PTHREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo, int ksplit,
+                    const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo, int n_full, int s_tail, int cols_first,
                     float* __restrict__ scratch, int* __restrict__ counters, int* status) {
     static_assert(BN % 32 == 0 && BN <= 256, "each CTA holds half of the tile's rows of w, in whole swizzle groups");
     constexpr int BH = BN / 2;                       // rows of w a CTA loads
@@ -109,9 +109,27 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int a_tiles = (rows_a + 2 * PBM - 1) / (2 * PBM), b_tiles = (rows_b + BN - 1) / BN;
     const int tiles = a_tiles * b_tiles;
     const int nkb = (k + PBK - 1) / PBK;
-    // A unit is (tile, share of k): with fewer tiles than pairs of SMs and a long k, the k-blocks of a tile are cut
-    // into `ksplit` shares for as many pairs; unit u is share u / tiles of tile u % tiles.
-    const int units = tiles * ksplit;
+    // A unit is (tile, share of k).  The first n_full tiles are units by themselves; the k-blocks of each tile after
+    // them are cut into s_tail shares, units of their own (share by share over those tiles).  Two uses: few tiles and a
+    // long k (n_full = 0: every tile in two shares, for twice the pairs), and the tiles of a last, partial round
+    // (n_full = the whole rounds' tiles: the few tiles left over are cut over the pairs that would stand idle).
+    const int tail = tiles - n_full;
+    const int units = n_full + tail * s_tail;
+    // The tiles in the order in which pairs that run together take them: down the rows of x first (they share a tile
+    // of w, and x, if it fits L2, stays there), or across the rows of w first (for an x larger than L2 and a smaller w).
+    auto a_of = [&](int t) { return cols_first ? t / b_tiles : t % a_tiles; };
+    auto b_of = [&](int t) { return cols_first ? t % b_tiles : t / a_tiles; };
+    auto unit_of = [&](int u, int& t, int& krank, int& ks) {
+        if (u < n_full) {
+            t = u;
+            krank = 0;
+            ks = 1;
+        } else {
+            t = n_full + (u - n_full) % tail;
+            krank = (u - n_full) / tail;
+            ks = s_tail;
+        }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -142,9 +160,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int kit = 0;
             bool waited = false;
             for (int u = pair; u < units && !timed_out; u += n_pairs) {
-                const int t = u % tiles, krank = u / tiles;
+                int t, krank, ksplit;
+                unit_of(u, t, krank, ksplit);
                 const int kb0 = (int)((long long)krank * nkb / ksplit), kb1 = (int)((long long)(krank + 1) * nkb / ksplit);
-                const int a_row0 = (t % a_tiles) * 2 * PBM + (int)rank * PBM, b_row0 = (t / a_tiles) * BN + (int)rank * BH;
+                const int a_row0 = a_of(t) * 2 * PBM + (int)rank * PBM, b_row0 = b_of(t) * BN + (int)rank * BH;
                 for (int kb = kb0; kb < kb1; ++kb, ++kit) {
                     const int s = kit % STAGES;
                     if (kit >= STAGES && !mbar_wait(&empty[s], ((kit / STAGES) & 1) ^ 1)) { timed_out = true; break; }
@@ -165,7 +184,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const uint32_t idesc = instr_desc(2 * PBM, BN);
             int kit = 0, ui = 0;
             for (int u = pair; u < units && !timed_out; u += n_pairs, ++ui) {
-                const int krank = u / tiles;
+                int t, krank, ksplit;
+                unit_of(u, t, krank, ksplit);
                 const int kb0 = (int)((long long)krank * nkb / ksplit), kb1 = (int)((long long)(krank + 1) * nkb / ksplit);
                 const int buf = ui & 1;
                 if (ui >= 2 && !mbar_wait(&acc_empty[buf], ((ui >> 1) & 1) ^ 1)) { timed_out = true; break; }
@@ -194,14 +214,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const uint32_t acc_empty_first = in_cta(smem_u32(&acc_empty[0]), 0);
         int ui = 0;
         for (int u = pair; u < units; u += n_pairs, ++ui) {
-            const int t = u % tiles, krank = u / tiles;
-            const int a_row0 = (t % a_tiles) * 2 * PBM + (int)rank * PBM, b_row0 = (t / a_tiles) * BN;
+            int t, krank, ksplit;
+            unit_of(u, t, krank, ksplit);
+            const int cut = t - n_full;                 // index among the tiles that are cut
+            const int a_row0 = a_of(t) * 2 * PBM + (int)rank * PBM, b_row0 = b_of(t) * BN;
             const int buf = ui & 1;
             bool ok = !timed_out && mbar_wait(&acc_full[buf], (ui >> 1) & 1);
             if (!ok) timed_out = true;
             tc_fence_after();
             // a share of k: this CTA's 128 rows of it as 32-bit [row][column] in scratch memory
-            float* mine = ksplit > 1 ? scratch + (((size_t)t * ksplit + krank) * 2 + rank) * (size_t)(BN * PBM) : nullptr;
+            float* mine = ksplit > 1 ? scratch + (((size_t)cut * ksplit + krank) * 2 + rank) * (size_t)(BN * PBM) : nullptr;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 float v[16];
@@ -232,13 +254,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 // that finds all others counted adds the shares, in their order, and stores.  Nobody waits.
                 __threadfence();
                 asm volatile("bar.sync 1, 128;\n" ::: "memory");
-                if (threadIdx.x == 64) *last_flag = (atomicAdd(&counters[2 * t + (int)rank], 1) == ksplit - 1) ? 1 : 0;
+                if (threadIdx.x == 64) *last_flag = (atomicAdd(&counters[2 * cut + (int)rank], 1) == ksplit - 1) ? 1 : 0;
                 asm volatile("bar.sync 1, 128;\n" ::: "memory");
                 const bool last = *last_flag != 0;
                 asm volatile("bar.sync 1, 128;\n" ::: "memory");   // all have read the flag before it is written again
                 if (last) {
                     __threadfence();
-                    const float* all = scratch + ((size_t)t * ksplit * 2 + rank) * (size_t)(BN * PBM);
+                    const float* all = scratch + ((size_t)cut * ksplit * 2 + rank) * (size_t)(BN * PBM);
                     const bool live = (a_row0 + r) < rows_a;
                     // a row a thread, 32 columns at a time: 16-byte loads, those of all shares on their way together
                     // (a share is [row][column]: with one value a load the merge took longer than the share's products)
@@ -268,7 +290,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         if (c0 + 16 < BN)
                             emit16<false, EPI, TOut>(*reinterpret_cast<float(*)[16]>(&sum[16]), r, a_row0, b_row0, c0 + 16, rows_a, rows_b, bias, out, ldo);
                     }
-                    if (threadIdx.x == 64) counters[2 * t + (int)rank] = 0;       // ready for the next launch
+                    if (threadIdx.x == 64) counters[2 * cut + (int)rank] = 0;     // ready for the next launch
                 }
             }
         }
@@ -301,15 +323,36 @@ cudaError_t launch_pair_cfg(const void* x, int m, const void* w, int n, int k, c
     // shares in two rounds (640 and 768 rows) lost to no shares at all, and so did two shares of a short k (3584: a
     // share's trip through scratch memory costs about as much as 60 k-blocks).  Two shares also add up to the same
     // number in either order.
-    int ksplit = 1;
+    // More tiles than pairs, a long k, and a last round that at most half the pairs would take: its tiles are cut
+    // into up to four shares each (added in their order), as many as make units for the idle pairs.
+    int n_full = tiles, s_tail = 1;
     const int all_pairs = sms / 2, nkb = (k + PBK - 1) / PBK;
-    if (2 * tiles <= all_pairs && nkb >= 128 && scratch != nullptr && counters != nullptr && 2 * tiles <= n_counters &&
-        (long long)tiles * 2 * 2 * BN * PBM <= scratch_floats)
-        ksplit = 2;
-    const int units = tiles * ksplit;
+    const bool may_cut = nkb >= 128 && scratch != nullptr && counters != nullptr;
+    if (may_cut && 2 * tiles <= all_pairs && 2 * tiles <= n_counters && (long long)tiles * 2 * 2 * BN * PBM <= scratch_floats) {
+        n_full = 0;
+        s_tail = 2;
+    } else if (may_cut && tiles > all_pairs) {
+        const int rem = tiles % all_pairs;
+        if (rem > 0 && 2 * rem <= all_pairs) {
+            int s = all_pairs / rem;
+            if (s > 4) s = 4;
+            while (s > 1 && nkb / s < 32) --s;
+            if (s > 1 && 2 * rem <= n_counters && (long long)rem * s * 2 * BN * PBM <= scratch_floats) {
+                n_full = tiles - rem;
+                s_tail = s;
+            }
+        }
+    }
+    const int units = n_full + (tiles - n_full) * s_tail;
     const int pairs = units < all_pairs ? units : all_pairs;
+    // x larger than half of L2 and w smaller than x: across the rows of w first (8,192 rows of k = 18944 are 310 MB; with
+    // the rows of x first they would come from HBM again for every column of tiles)
+    int l2 = 0;
+    if (cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev) != cudaSuccess || l2 <= 0) l2 = 64 << 20;
+    const long long x_bytes = (long long)m * k * 2, w_bytes = (long long)n * k * 2;
+    const int cols_first = (x_bytes > l2 / 2 && w_bytes < x_bytes) ? 1 : 0;
     return launch(gemm_tc_pair_kernel<BN, STAGES, EPI, TOut>, dim3(2 * pairs, 1, 1), dim3(PTHREADS, 1, 1), smem, stream, dim3(2, 1, 1),
-                  map_a, map_b, bias, out, m, n, k, ldo, ksplit, scratch, counters, status);
+                  map_a, map_b, bias, out, m, n, k, ldo, n_full, s_tail, cols_first, scratch, counters, status);
 }
 
 }  // namespace
@@ -329,10 +372,15 @@ cudaError_t launch_gemm_tc_pair(const void* x, const void* w, const float* bias,
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
         const int pairs = sms / 2;
-        long best = -1;
+        const int nkb = (k + PBK - 1) / PBK;
+        double best = -1.0;
         for (int cand : {256, 224}) {
             const long t = (long)((m + 2 * PBM - 1) / (2 * PBM)) * ((n + cand - 1) / cand);
-            const long cost = ((t + pairs - 1) / pairs) * (cand + 32 + (256 - cand) / 2);
+            const long rem = t % pairs;
+            // a last round that at most half the pairs would take is cut into shares of k where k is long (launch_pair_cfg)
+            double rounds = (double)(t / pairs);
+            if (rem > 0) rounds += (t > pairs && 2 * rem <= pairs && nkb >= 128 && scratch != nullptr) ? 0.4 : 1.0;
+            const double cost = rounds * (cand + 32 + (256 - cand) / 2);
             if (best < 0 || cost < best) {
                 best = cost;
                 bn = cand;
