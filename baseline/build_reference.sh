@@ -1,7 +1,7 @@
 #!/bin/bash
 # Builds the unmodified vt-transformer v1 engine for sm_100 and links baseline/ref_driver.cpp against it.
 #
-#   baseline/build_reference.sh [REFERENCE_CHECKOUT]      (default /root/reference)
+#   baseline/build_reference.sh [REFERENCE_CHECKOUT]      (default: $VT_REFERENCE_CHECKOUT, else where this build mounts it)
 #
 # The checkout's v1/ tree is copied to baseline/_ref/src (the checkout itself is read-only) and compiled with the
 # flags of its own makefiles (v1/tensortype/Makefile.cuda, v1/tensortype/cuda_kernels/CMakeLists.txt and
@@ -11,7 +11,7 @@
 # reference is changed.  Output: baseline/_ref/ref_driver.
 set -e
 HERE="$(cd "$(dirname "$0")" && pwd)"
-REF="${1:-/root/reference}"
+REF="${1:-${VT_REFERENCE_CHECKOUT:-/root/reference}}"
 OUT="$HERE/_ref"
 CUDA="${CUDA_DIR:-/usr/local/cuda}"
 CUDNN_INC="${CUDNN_INC:-/usr/include/x86_64-linux-gnu}"

@@ -133,7 +133,7 @@ def reference_arm(args) -> int:
     driver = os.path.join(REF_DIR, "ref_driver")
     dag = os.path.join(REF_DIR, "src", "models", "qwen2-7b", "inference_fp16.dag")
     if not os.path.isfile(driver) or not os.path.isfile(dag):
-        if os.path.isdir("/root/reference/v1"):
+        if os.path.isdir(os.path.join(os.environ.get("VT_REFERENCE_CHECKOUT", "/root/reference"), "v1")):
             res = subprocess.run(["bash", os.path.join(ROOT, "baseline", "build_reference.sh")], capture_output=True, text=True)
             if res.returncode != 0:
                 return unavailable("baseline/build_reference.sh failed: " + (res.stderr.strip().splitlines() or ["no message"])[-1][:200])
