@@ -148,15 +148,16 @@ def test_single_token_steps_cut_their_keys_by_the_work_and_fetch_by_boxes_where_
         assert o._decode_plan(64, 16384, dev) == (7, 148, True)
         # a short bound is not cut
         assert o._decode_plan(8, 200, dev) == (1, 0, False)
-        # boxes: where the CTAs run in several rounds (batch 64, any context), or a warp streams many blocks
-        assert o._decode_long_runs(256, 1040, 1, 0, 128, dev) and o._decode_long_runs(256, 1040, 1, 0, 64, dev)
+        # boxes: where a warp streams 16 blocks or more (batch 64 at 4,096 keys), not where it has few, however many CTAs
+        assert not o._decode_long_runs(256, 1040, 1, 0, 128, dev) and o._decode_long_runs(256, 1040, 1, 0, 64, dev)
+        assert o._decode_long_runs(256, 4096, 2, 128, 128, dev) and o._decode_long_runs(256, 2048, 1, 0, 64, dev)
         assert not o._decode_long_runs(32, 2048, 3, 22, 128, dev)
         assert o._decode_long_runs(8, 32768, 1, 0, 128, dev)
-        assert not o._decode_long_runs(256, 1040, 1, 0, 80, dev)          # other head sizes have no boxes
+        assert not o._decode_long_runs(256, 4096, 2, 128, 80, dev)        # other head sizes have no boxes
         old = o.DECODE_BOXES
         try:
             o.DECODE_BOXES = "never"
-            assert not o._decode_long_runs(256, 1040, 1, 0, 128, dev)
+            assert not o._decode_long_runs(256, 4096, 2, 128, 128, dev)
             o.DECODE_BOXES = "always"
             assert o._decode_long_runs(32, 2048, 3, 22, 128, dev) and not o._decode_long_runs(32, 2048, 3, 22, 96, dev)
         finally:

@@ -371,11 +371,9 @@ def test_keys_fetched_as_boxes_give_the_same_bits_as_copies(heads, kv_heads, d, 
         o.DECODE_BOXES = old
     assert not bool(torch.isnan(outs["never"].float()).any())
     assert torch.equal(outs["never"], outs["always"])
-    # and the automatic choice takes boxes here
-    span = min(max(seq_lens), window + 31) if window else max(seq_lens)
-    splits, run, _ = o._decode_plan(T * kv_heads, span, torch.device(DEV))
-    if not window:
-        assert o._decode_long_runs(T * kv_heads, span, splits, run, d, torch.device(DEV))
+    # the automatic choice takes boxes where a warp streams many blocks of a typical sequence (a bound of 8,192 keys)
+    splits, run, _ = o._decode_plan(T * kv_heads, 8192, torch.device(DEV))
+    assert o._decode_long_runs(T * kv_heads, 8192, splits, run, d, torch.device(DEV))
 
 
 @pytest.mark.parametrize("heads,kv_heads,d,page_size,window,rotate", [(28, 4, 128, 16, None, True), (6, 2, 48, 32, 40, True),

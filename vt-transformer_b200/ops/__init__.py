@@ -428,17 +428,22 @@ LONG_RUN_BLOCKS = 16     # blocks of 16 keys a warp from which the boxes pay whe
 def _decode_long_runs(pairs: int, span: int, splits: int, run: int, head_dim: int, device) -> bool:
     """Whether a single-token step's keys and values come as boxes of a tensor map (head sizes 64 and 128):
     a box arrives later than a cp.async copy but costs the warp one instruction, not 32, so it pays where a
-    warp streams many blocks, or where the CTAs run in several rounds and another CTA's work hides the wait; it
-    loses where a warp has a few blocks and the SMs one CTA each."""
+    warp streams many blocks (16 or more: 64 sequences of 4,096 keys, a step of 5.78 against 5.94 ms); it loses
+    where a warp has few, however many CTAs there are (head size 128, 24 to 128 sequences of 1,040 keys: steps 0.2
+    to 1.8 % slower with boxes, measured inside the step)."""
     if head_dim not in (64, 128) or DECODE_BOXES == "never":
         return False
     if DECODE_BOXES == "always":
         return True
     sms = _sm_counts.get(device, 148)
-    if pairs * splits > sms:
+    if head_dim == 64 and pairs * splits > sms:
+        # (blocks of half the bytes: the copies' 16 instructions a lane weigh more; 256 sequences of 512 keys at
+        # 0.5B sizes: a step of 1.84 ms with boxes against 1.97)
         return True
+    warps = 6 if pairs * splits > sms else 8            # the kernel's shape: two CTAs an SM, or one
     blocks = max(1, -(-span // DECODE_BLOCK))
-    return (run if run else blocks) >= LONG_RUN_BLOCKS * 8
+    # (the bound is that of a captured graph: a typical sequence holds half of it, as in _decode_plan)
+    return (run if run else blocks // 2) >= LONG_RUN_BLOCKS * warps
 
 
 def _attention_counters(device, n: int) -> torch.Tensor:
