@@ -743,7 +743,7 @@ def wide_decode_case(folder, name, device, dtype, sequences, decode_steps, runne
                                           f"{len(sequences[i])}) at position {done[i]}: |dlogit| {d:.3e} > {bound:.1e}")
             worst = max(worst, d)
             done[i] += 1
-    keys = sorted(runner._graphs)
+    keys = sorted({k[:2] for k in runner._graphs})      # (batch bucket, bound of the cached lengths)
     for r in rows:
         runner.release(r)
     runner.cache.check()

@@ -146,6 +146,10 @@ def test_single_token_steps_cut_their_keys_by_the_work_and_fetch_by_boxes_where_
         # 32 sequences of 2 KV heads under a bound of 16,384 keys: their lengths may differ by thousands of keys, so
         # up to 7 runs of 148 blocks meet in scratch memory and a short sequence takes one CTA
         assert o._decode_plan(64, 16384, dev) == (7, 148, True)
+        # the same 64 (sequence, KV head) under that bound with lengths alike (all of 4,096 keys or more): the runs stay
+        # the CTAs of a cluster, sized for a typical sequence; one or two sequences of like lengths still meet in scratch
+        assert o._decode_plan(64, 16384, dev, 4096) == (2, 341, False)
+        assert o._decode_plan(4, 32768, dev, 8192) == (37, 32, True)
         # a short bound is not cut
         assert o._decode_plan(8, 200, dev) == (1, 0, False)
         # boxes: where a warp streams 16 blocks or more (batch 64 at 4,096 keys), not where it has few, however many CTAs

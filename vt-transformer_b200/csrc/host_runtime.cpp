@@ -140,11 +140,11 @@ class CacheBook {
     }
 
     // A step of `add` tokens for each of `rows`: extend, all or nothing.  Returns (group, needed, free, longest
-    // length after the step); group -1: done.
+    // length after the step, shortest); group -1: done.
     py::tuple extend_each(const std::vector<int>& rows, int add) {
         std::vector<std::pair<int, long long>> items;
         items.reserve(rows.size());
-        long long longest = 0;
+        long long longest = 0, shortest = -1;
         for (size_t i = 0; i < rows.size(); ++i) {
             check_row(rows[i]);
             for (size_t j = 0; j < i; ++j)
@@ -152,9 +152,10 @@ class CacheBook {
             const long long len = lengths_[rows[i]] + add;
             items.emplace_back(rows[i], len);
             if (len > longest) longest = len;
+            if (shortest < 0 || len < shortest) shortest = len;
         }
         py::tuple r = extend(items);
-        return py::make_tuple(r[0], r[1], r[2], longest);
+        return py::make_tuple(r[0], r[1], r[2], longest, shortest < 0 ? 0 : shortest);
     }
 
     void commit_each(const std::vector<int>& rows, int add) {

@@ -57,6 +57,7 @@ class StepContext:
     want_inverse: Optional[np.ndarray] = None   # set if wanted rows repeat: logits[want_inverse]
     extras: dict = field(default_factory=dict)  # per-step scratch of the kernels' wrappers
     h2d_bytes: int = 0                          # bytes of the description copied to the device
+    min_kv_len: int = 0                         # a lower bound of the cached lengths, if the caller knows one (else 0)
 
 
 def _align4(n: int) -> int:

@@ -37,9 +37,10 @@ def context_bucket(max_kv_len: int) -> int:
 
 
 class DecodeGraph:
-    """One captured step for ``batch`` single-token entries and cached lengths up to ``kv_bound``."""
+    """One captured step for ``batch`` single-token entries and cached lengths up to ``kv_bound``
+    (``like_lengths``: all of them at least a quarter of it)."""
 
-    def __init__(self, runner, batch: int, kv_bound: int):
+    def __init__(self, runner, batch: int, kv_bound: int, like_lengths: bool = False):
         cache, dev = runner.cache, runner.rt.device
         self.runner, self.batch, self.kv_bound = runner, batch, kv_bound
         self.layout = Layout.make(batch, batch, batch, cache.max_pages, len(cache.groups))
@@ -54,6 +55,7 @@ class DecodeGraph:
             fill_host(pinned.numpy(), self.layout, [], [], [], cache)  # all padding: a valid step of nothing
         self.device_buf.copy_(self.ring[0], non_blocking=True)
         self.ctx = context_from(self.device_buf, self.layout, [], 1, kv_bound, runner.status)
+        self.ctx.min_kv_len = kv_bound // 4 if like_lengths else 0
         views = cache.views(self.ctx.block_tables)
         # warm up on a side stream (first calls of kernels set attributes and allocate), then capture
         side = torch.cuda.Stream(device=dev)

@@ -159,14 +159,17 @@ class ModelRunner:
         buffer: they are valid until the next step."""
         from .graphs import DecodeGraph, batch_bucket, context_bucket
         rows = [e.row for e in entries]
-        group, needed, free, max_kv = self.cache.book.extend_each(rows, 1)      # pages for the tokens, all or none
+        group, needed, free, max_kv, min_kv = self.cache.book.extend_each(rows, 1)      # pages for the tokens, all or none
         if group >= 0:
             from ..cache.manager import OutOfPages
             raise OutOfPages(group, needed, free)
-        key = (batch_bucket(len(entries)), context_bucket(max_kv))
+        # a graph a (batch, bound of the cached lengths, whether all lengths are at least a quarter of that bound: the
+        # keys of sequences of like lengths are cut over CTAs in another way than those of very different ones)
+        bound = context_bucket(max_kv)
+        key = (batch_bucket(len(entries)), bound, 4 * min_kv >= bound)
         graph = self._graphs.get(key)
         if graph is None:
-            graph = DecodeGraph(self, *key)
+            graph = DecodeGraph(self, key[0], key[1], like_lengths=key[2])
             self._graphs[key] = graph
         logits = graph.run(entries, carried)
         self.cache.book.commit_each(rows, 1)
