@@ -67,6 +67,38 @@ def test_the_next_step_enqueued_early_changes_no_token(folders, dtype):
     scenarios.overlap_generation_case(folders("B"), "B", DEV, dtype)
 
 
+def test_each_part_knows_which_matrix_streams_next_and_the_hint_changes_no_logit(folders):
+    """Once the weights are loaded the model tells every run's block what the step streams after it: the mixer's
+    last product is followed by the feed-forward's first, the feed-forward's by the next run's first, the last run's
+    by the head's.  With the hints off, a prompt and single-token steps give the same bits."""
+    from vt_transformer_b200 import ops as o
+    from vt_transformer_b200.engine import StepEntry
+    folder = folders("A")
+    ids = helpers.prompts_for("A")[2]
+    logits = {}
+    for n_bytes in (o.LOOK_AHEAD_BYTES or (8 << 20), 0):
+        old, o.LOOK_AHEAD_BYTES = o.LOOK_AHEAD_BYTES, n_bytes
+        try:
+            runner = scenarios.runner_for(folder, DEV, "bfloat16", num_pages=8, max_requests=2)
+            model = runner.model
+            order = model.spec.order
+            for n, run in enumerate(order):
+                block = model.blocks[run.block]
+                after = model.blocks[order[n + 1].block].mixer.w_qkv if n + 1 < len(order) else model.head.weight
+                assert block.mixer.then[0] is block.ffn.w_gate_up and block.mixer.then[1] == 1
+                assert block.ffn.then[0] is after and block.ffn.then[1] == (2 if n + 1 < len(order) else 0)
+            row = runner.admit()
+            got = [runner.step([StepEntry(row, ids[:9], [8])]).clone()]
+            for t in range(9, 14):
+                got.append(runner.step([StepEntry(row, ids[t:t + 1], [0])]).clone())
+            runner.check_status()
+            logits[n_bytes] = torch.cat(got)
+        finally:
+            o.LOOK_AHEAD_BYTES = old
+    with_hints, without = logits.values()
+    assert torch.equal(with_hints, without)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_first_tokens_of_a_sequence(folders, dtype):
     """One token, two tokens, three: the first positions, where the cache is empty and a

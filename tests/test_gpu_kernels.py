@@ -504,6 +504,50 @@ def test_gate_up_product_with_the_activation_in_its_epilogue(m, inter, k):
     close(out32, ref, torch.float32, 40)
 
 
+@pytest.mark.parametrize("m", [1, 8, 33, 64, 200])
+@pytest.mark.parametrize("n,k", [(301, 72), (3584, 3584), (520, 18944)])
+def test_asking_for_the_next_products_weights_changes_no_bit(m, n, k):
+    """A product that is told which matrix streams next asks for its first boxes into L2 while it ends: the same
+    bits with and without, whatever the next matrix is (smaller than a box, with edges that hang over, of another
+    epilogue, far larger than what is asked for), and no status."""
+    o = ops()
+    be = o.backend()
+    torch.manual_seed(23)
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    bias = torch.randn(n, device=DEV)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    scratch, counters = o._split_workspace(torch.device(DEV))
+    nexts = [(torch.zeros(8, 8, device=DEV, dtype=torch.bfloat16), 0), (torch.zeros(130, 72, device=DEV, dtype=torch.bfloat16), 2),
+             (torch.zeros(2 * 1000, 3584, device=DEV, dtype=torch.bfloat16), 1), (torch.zeros(3584, 18944, device=DEV, dtype=torch.bfloat16), 2)]
+    ref = torch.empty(m, n, device=DEV, dtype=torch.float32)
+    be.gemm_tc(x, w, bias, ref, status, scratch, counters)
+    n_shares = be.gemm_tc_shares(m, n, k) if m <= 256 else 0
+    ref_shares = torch.empty(n_shares, m, n, device=DEV, dtype=torch.float32)
+    if n_shares:
+        be.gemm_tc(x, w, bias, ref_shares, status, None, None, 2)
+    for next_w, next_epilogue in nexts:
+        for n_bytes in (16 << 10, 8 << 20, 1 << 30):
+            out = torch.full((m, n), float("nan"), device=DEV, dtype=torch.float32)
+            be.gemm_tc(x, w, bias, out, status, scratch, counters, 0, next_w, next_epilogue, n_bytes)
+            assert torch.equal(out, ref)
+            if n_shares:
+                shares = torch.full((n_shares, m, n), float("nan"), device=DEV, dtype=torch.float32)
+                be.gemm_tc(x, w, bias, shares, status, None, None, 2, next_w, next_epilogue, n_bytes)
+                assert torch.equal(shares, ref_shares)
+    # through ops, with the hint as the parts pass it; a matrix the kernel does not take gives no hint
+    assert o.product_hint(w.float(), "linear") is None and o.product_hint(None, "stream") is None
+    hint = o.product_hint(nexts[2][0], "silu_mul")
+    assert hint[0] is nexts[2][0] and hint[1] == 1
+    out = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    o.linear(x, w, bias, out, status, then=hint)
+    plain_out = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    o.linear(x, w, bias, plain_out, status)
+    assert torch.equal(out, plain_out)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0] and int(counters.abs().sum()) == 0
+
+
 @pytest.mark.parametrize("m", [1, 8, 17, 64, 100, 256])
 @pytest.mark.parametrize("n,k", [(40, 64), (301, 72), (3584, 3584), (520, 18944)])
 def test_tcgen05_product_leaves_its_shares_unadded_and_the_norm_adds_them(m, n, k):

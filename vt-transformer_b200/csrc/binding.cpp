@@ -193,8 +193,22 @@ void gemm_skinny(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, T
                                          stream_of(x)), "gemm_skinny");
 }
 
+// The hint of a product that runs next (kernels.h: NextProduct), from the arguments that carry it.
+vtb::NextProduct next_product(const Tensor& like, const c10::optional<Tensor>& next_w, int64_t next_epilogue, int64_t next_bytes,
+                              const char* who) {
+    vtb::NextProduct next = {nullptr, 0, 0, 0, 0};
+    if (next_w.has_value() && next_bytes > 0) {
+        TORCH_CHECK(next_w->is_cuda() && next_w->scalar_type() == torch::kBFloat16 && next_w->dim() == 2 && next_w->is_contiguous() &&
+                        next_w->device() == like.device() && next_epilogue >= 0 && next_epilogue <= 2,
+                    who, ": next_w must be a contiguous bfloat16 matrix on the same device, next_epilogue 0, 1 or 2");
+        next = {next_w->data_ptr(), (int)next_w->size(0), (int)next_w->size(1), (int)next_epilogue, (long long)next_bytes};
+    }
+    return next;
+}
+
 void gemm_tc(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tensor& out, c10::optional<Tensor> status,
-             c10::optional<Tensor> scratch, c10::optional<Tensor> counters, int64_t epilogue) {
+             c10::optional<Tensor> scratch, c10::optional<Tensor> counters, int64_t epilogue, c10::optional<Tensor> next_w,
+             int64_t next_epilogue, int64_t next_bytes) {
     check_cuda(x, "x"); check_cuda(w, "w"); check_cuda(out, "out");
     TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16, "gemm_tc: x and w must be bfloat16");
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2, "gemm_tc: x and w must be 2-d");
@@ -230,9 +244,11 @@ void gemm_tc(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tenso
         cp = counters->data_ptr<int>();
         cn = counters->numel();
     }
+    const vtb::NextProduct next = next_product(x, next_w, next_epilogue, next_bytes, "gemm_tc");
     c10::cuda::CUDAGuard guard(x.device());
     check_launch(vtb::launch_gemm_tc(dtype_code(out, "out"), x.data_ptr(), w.data_ptr(), bp, out.data_ptr(), m, n, k,
-                                     (int)epilogue, sp, sn, cp, cn, status_ptr(status), stream_of(x)), "gemm_tc");
+                                     (int)epilogue, sp, sn, cp, cn, status_ptr(status), stream_of(x),
+                                     next.w != nullptr ? &next : nullptr), "gemm_tc");
 }
 
 void gemm_tc_pair(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tensor& out, int64_t epilogue, int64_t bn,
@@ -494,7 +510,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("status") = py::none());
     m.def("gemm_skinny", &gemm_skinny, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"));
     m.def("gemm_tc", &gemm_tc, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"), py::arg("status") = py::none(),
-          py::arg("scratch") = py::none(), py::arg("counters") = py::none(), py::arg("epilogue") = 0);
+          py::arg("scratch") = py::none(), py::arg("counters") = py::none(), py::arg("epilogue") = 0,
+          py::arg("next_w") = py::none(), py::arg("next_epilogue") = 0, py::arg("next_bytes") = 0);
     m.def("gemm_tc_pair", &gemm_tc_pair, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("out"), py::arg("epilogue") = 0,
           py::arg("bn") = 256, py::arg("status") = py::none(), py::arg("scratch") = py::none(), py::arg("counters") = py::none());
     m.def("gemm_tc_shares", [](int64_t m, int64_t n, int64_t k) { return (int64_t)vtb::gemm_tc_shares(m, n, k); });

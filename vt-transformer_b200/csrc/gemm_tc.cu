@@ -27,6 +27,7 @@
 #include "gemm_epilogue.cuh"
 #include "kernels.h"
 #include "launch.cuh"
+#include "look_ahead.cuh"
 #include "tc_common.cuh"
 
 namespace vtb {
@@ -42,7 +43,8 @@ template <int BN, int STAGES, bool SWAP, int EPI, typename TOut>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const float* __restrict__ bias, TOut* __restrict__ out, int rows_a, int rows_b, int k, int ldo, int n_full,
-               int s_tail, float* __restrict__ scratch, int* __restrict__ counters, int* status) {
+               int s_tail, float* __restrict__ scratch, int* __restrict__ counters, int* status,
+               const __grid_constant__ CUtensorMap map_ahead, const AheadTiles ahead) {
     constexpr int B_STAGE = BN * BK * 2;
     constexpr int COLS = BN < 32 ? 32 : BN;          // tensor-memory columns of an accumulator
     constexpr int ALLOC = 2 * COLS <= 64 ? 64 : 2 * COLS <= 128 ? 128 : 2 * COLS <= 256 ? 256 : 512;   // a power of two
@@ -131,6 +133,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tma_load_2d(a_s + s * A_STAGE, &map_a, kb * BK, a_row0, &full[s]);
                     tma_load_2d(b_s + s * B_STAGE, &map_b, kb * BK, b_row0, &full[s]);
                 }
+            }
+            // This CTA's last load is on its way: from here to the first loads of the next kernel (the last MMAs, the
+            // epilogue, the end of the grid, the next kernel's set-up and its wait for x) HBM would have nothing to do.
+            // The weights of the product that runs next are written by no kernel: the first k-blocks of its first
+            // units are asked into L2 now.
+            for (int u = blockIdx.x; u < ahead.units && ahead.depth > 0; u += gridDim.x) {
+                int bx, by;
+                for (int i = 0; i < ahead.depth && ahead_box(ahead, u, i, bx, by); ++i) ahead_prefetch(&map_ahead, bx, by);
             }
         }
     } else if (warp == 1) {
@@ -266,9 +276,12 @@ int sm_count() {
 
 template <int BN, int STAGES, bool SWAP, int EPI, typename TOut>
 cudaError_t launch_cfg(const void* a, int rows_a, const void* b, int rows_b, int k, const float* bias, TOut* out, int ldo,
-                       int n_full, int s_tail, float* scratch, int* counters, int* status, cudaStream_t stream) {
-    CUtensorMap map_a, map_b;
+                       int n_full, int s_tail, float* scratch, int* counters, int* status, cudaStream_t stream,
+                       const NextProduct* next) {
+    CUtensorMap map_a, map_b, map_ahead;
     if (!make_map(&map_a, a, rows_a, k, BM) || !make_map(&map_b, b, rows_b, k, BN)) return cudaErrorInvalidValue;
+    AheadTiles ahead = {1, 0, 1, 1, 0};
+    if (!SWAP || !look_ahead(next, rows_b, &map_ahead, &ahead)) map_ahead = map_a;
     constexpr int smem = STAGES * (A_STAGE + BN * BK * 2) + 1024 + 256;
     static std::atomic<unsigned long long> configured{0};
     cudaError_t e = allow_dynamic_smem(gemm_tc_kernel<BN, STAGES, SWAP, EPI, TOut>, smem, configured);
@@ -277,7 +290,7 @@ cudaError_t launch_cfg(const void* a, int rows_a, const void* b, int rows_b, int
     const int units = n_full + (tiles - n_full) * s_tail;
     return launch(gemm_tc_kernel<BN, STAGES, SWAP, EPI, TOut>, dim3(units < sm_count() ? units : sm_count(), 1, 1),
                   dim3(THREADS, 1, 1), smem, stream, map_a, map_b, bias, out, rows_a, rows_b, k, ldo, n_full, s_tail, scratch,
-                  counters, status);
+                  counters, status, map_ahead, ahead);
 }
 
 // Into how many shares k is cut when w is the 128-row operand (small batches).  One CTA fits an SM, so the
@@ -319,7 +332,8 @@ bool swapped_for(int m, int n, int k) {
 
 template <int EPI, typename TOut>
 cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* out, int m, int n, int k, float* scratch,
-                         long long scratch_floats, int* counters, int n_counters, int* status, cudaStream_t stream) {
+                         long long scratch_floats, int* counters, int n_counters, int* status, cudaStream_t stream,
+                         const NextProduct* next) {
     if (swapped_for<EPI>(m, n, k)) {
         // swapped: w is the 128-row operand and every weight is streamed once; the batch rides along as 16 to 256
         // columns.  (At 256 columns a k-block's MMAs take about as long as its 16 KB of weights take to arrive.)
@@ -327,11 +341,11 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
         const bool have_scratch = scratch != nullptr && counters != nullptr;
         const int ksplit = (EPI == 2) ? gemm_tc_shares(m, n, k)
                                       : small_batch_ksplit(n, k, bn, have_scratch, scratch_floats, n_counters);
-        if (bn == 16) return launch_cfg<16, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
-        if (bn == 32) return launch_cfg<32, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
-        if (bn == 64) return launch_cfg<64, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
-        if (bn == 128) return launch_cfg<128, 6, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
-        return launch_cfg<256, 4, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream);
+        if (bn == 16) return launch_cfg<16, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream, next);
+        if (bn == 32) return launch_cfg<32, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream, next);
+        if (bn == 64) return launch_cfg<64, 8, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream, next);
+        if (bn == 128) return launch_cfg<128, 6, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream, next);
+        return launch_cfg<256, 4, true, EPI, TOut>(w, n, x, m, k, bias, out, EPI == 1 ? n / 2 : n, 0, ksplit, scratch, counters, status, stream, next);
     }
     if constexpr (EPI == 2) {
         return cudaErrorInvalidValue;     // shares are left unadded for small batches only
@@ -381,20 +395,44 @@ cudaError_t launch_typed(const void* x, const void* w, const float* bias, TOut* 
         if (s_tail == 1) n_full = tiles;
         const int ldo = EPI == 1 ? n / 2 : n;
         switch (bn) {
-            case 256: return launch_cfg<256, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
-            case 240: return launch_cfg<240, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
-            case 224: return launch_cfg<224, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
-            case 208: return launch_cfg<208, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
-            case 192: return launch_cfg<192, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
-            case 160: return launch_cfg<160, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
-            case 128: if (wide) return launch_cfg<128, 6, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
+            case 256: return launch_cfg<256, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream, next);
+            case 240: return launch_cfg<240, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream, next);
+            case 224: return launch_cfg<224, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream, next);
+            case 208: return launch_cfg<208, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream, next);
+            case 192: return launch_cfg<192, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream, next);
+            case 160: return launch_cfg<160, 5, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream, next);
+            case 128: if (wide) return launch_cfg<128, 6, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream, next);
         }
-        if (bn == 64) return launch_cfg<64, 8, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
-        return launch_cfg<128, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream);
+        if (bn == 64) return launch_cfg<64, 8, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream, next);
+        return launch_cfg<128, 4, false, EPI, TOut>(x, m, w, n, k, bias, out, ldo, n_full, s_tail, scratch, counters, status, stream, next);
     }
 }
 
 }  // namespace
+
+// How the product that runs next over the same m rows will cut its weights, if it runs with w as the 128-row operand;
+// false if there is nothing to ask for.  (It stands on the workspace that the engine gives every product; where the
+// next launch decides otherwise, other boxes of the same matrix are asked for and nothing else changes.)
+bool look_ahead(const NextProduct* next, int m, CUtensorMap* map, AheadTiles* tiles) {
+    if (next == nullptr || next->w == nullptr || next->bytes < A_STAGE || next->k % 8 != 0 || next->k < 8 || next->n < 1 ||
+        ((uintptr_t)next->w & 15) != 0)
+        return false;
+    const int n = next->n, k = next->k;
+    const bool swapped = next->epilogue == 2 ? swapped_for<2>(m, n, k)
+                         : next->epilogue == 1 ? swapped_for<1>(m, n, k) : swapped_for<0>(m, n, k);
+    if (!swapped) return false;
+    const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)));
+    const int ks = next->epilogue == 2 ? gemm_tc_shares(m, n, k) : small_batch_ksplit(n, k, bn, true, 8LL << 20, 4096);
+    tiles->a_tiles = (n + BM - 1) / BM;
+    tiles->s_tail = ks;
+    tiles->nkb = (k + BK - 1) / BK;
+    const int sms = sm_count();
+    tiles->units = tiles->a_tiles * ks < sms ? tiles->a_tiles * ks : sms;
+    const long long boxes = next->bytes / A_STAGE;
+    const long long depth = (boxes + tiles->units - 1) / tiles->units, longest = tiles->nkb / ks + 1;
+    tiles->depth = (int)(depth < longest ? depth : longest);
+    return make_map(map, next->w, n, k, BM);
+}
 
 int gemm_tc_shares(int m, int n, int k) {
     const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)));
@@ -419,7 +457,7 @@ static bool pair_for(int m, int n, int k) {
 
 cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n, int k,
                            int epilogue, float* scratch, long long scratch_floats, int* counters, int n_counters,
-                           int* status, cudaStream_t stream) {
+                           int* status, cudaStream_t stream, const NextProduct* next) {
     if (m == 0 || n == 0) return cudaSuccess;
     if (k % 8 != 0 || k < 8) return cudaErrorInvalidValue;
     if (out_dtype == kBF16 && (epilogue == 0 || epilogue == 1) && pair_for(m, n, k))
@@ -427,19 +465,19 @@ cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const fl
     if (epilogue == 1) {
         if (n % 16 != 0 || bias != nullptr || out_dtype != kBF16) return cudaErrorInvalidValue;
         return launch_typed<1, __nv_bfloat16>(x, w, nullptr, (__nv_bfloat16*)out, m, n, k, scratch, scratch_floats,
-                                              counters, n_counters, status, stream);
+                                              counters, n_counters, status, stream, next);
     }
     if (epilogue == 2) {
         if (out_dtype != kF32 || m > 256) return cudaErrorInvalidValue;
-        return launch_typed<2, float>(x, w, bias, (float*)out, m, n, k, nullptr, 0, nullptr, 0, status, stream);
+        return launch_typed<2, float>(x, w, bias, (float*)out, m, n, k, nullptr, 0, nullptr, 0, status, stream, next);
     }
     if (epilogue != 0) return cudaErrorInvalidValue;
     if (out_dtype == kBF16)
         return launch_typed<0, __nv_bfloat16>(x, w, bias, (__nv_bfloat16*)out, m, n, k, scratch, scratch_floats, counters,
-                                              n_counters, status, stream);
+                                              n_counters, status, stream, next);
     if (out_dtype == kF32)
         return launch_typed<0, float>(x, w, bias, (float*)out, m, n, k, scratch, scratch_floats, counters, n_counters,
-                                      status, stream);
+                                      status, stream, next);
     return cudaErrorInvalidValue;
 }
 

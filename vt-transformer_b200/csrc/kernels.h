@@ -66,10 +66,18 @@ cudaError_t launch_gemm_skinny(int out_dtype, const void* x, const void* w, cons
 // gate and up rows interleaved in runs of 8 (g0..g7, u0..u7, g8.., ...) and out[M, N / 2] = silu(gate) * up.
 // epilogue 2 (float out, M <= 256): k is cut into gemm_tc_shares(M, N, K) shares and out[share, M, N] takes each
 // share's sums as they are (the bias with share 0); the kernel that reads them adds them (launch_rmsnorm).
+// NextProduct: the product that the stream runs after this one (its matrix [n, k] of bfloat16, which no kernel writes, and its
+// epilogue).  A kernel that streams weights for a small batch asks the first `bytes` of what that product will read
+// into L2 once its own last load is on its way, so that HBM has work between the two kernels.  A hint: it changes no result.
+struct NextProduct {
+    const void* w;
+    int n, k, epilogue;
+    long long bytes;
+};
 int gemm_tc_shares(int m, int n, int k);
 cudaError_t launch_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int m, int n, int k,
                            int epilogue, float* scratch, long long scratch_floats, int* counters, int n_counters,
-                           int* status, cudaStream_t stream);
+                           int* status, cudaStream_t stream, const NextProduct* next = nullptr);
 // The same product for many rows of x with a tile of 256 rows of x by `bn` (256 or 192) rows of w to a pair of CTAs
 // (tcgen05.mma.cta_group::2): bfloat16 out, epilogue 0 (bias) or 1 (SiLU(gate) * up).
 cudaError_t launch_gemm_tc_pair(const void* x, const void* w, const float* bias, void* out, int m, int n, int k, int epilogue,

@@ -77,6 +77,15 @@ class DecoderModel:
             part.load(source.get)
         self.rt.loaded.clear()                  # the parts hold what they share; nothing else needs the table
         self.load_info, self.load_warnings = load_report(source, self.rt.notes, aside)
+        self._link_runs()
+
+    def _link_runs(self) -> None:
+        """Tells every run's block which matrix the step streams after it: the first product of the block of the
+        next run, of the head after the last.  (A block that runs twice keeps what follows its last run.)"""
+        runs = self.spec.order
+        for n, run in enumerate(runs):
+            after = self.blocks[runs[n + 1].block] if n + 1 < len(runs) else self.head
+            self.blocks[run.block].link(after.first_product())
 
     def weight_bytes(self, n_tokens: int = 1) -> int:
         """Bytes of weights a step reads: every block's weights once for each of its runs,

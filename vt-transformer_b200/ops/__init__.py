@@ -114,7 +114,27 @@ def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor
         2 * inter, hidden).contiguous()
 
 
-def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, status=None) -> torch.Tensor:
+# Bytes of the next product's weights that a weight-streaming product asks into L2 while it ends (0: none).
+LOOK_AHEAD_BYTES = int(os.environ.get("VTB200_LOOK_AHEAD_BYTES", str(8 << 20)))
+_PRODUCT_KINDS = {"linear": 0, "silu_mul": 1, "stream": 2}
+
+
+def product_hint(w: torch.Tensor, kind: str):
+    """What a part tells the product before one of its own: the matrix ``w`` [N, K] will be streamed next, by
+    ``linear`` ("linear"), ``linear_silu_mul`` ("silu_mul") or ``linear_to_stream`` ("stream").  None for a
+    matrix that the tcgen05 kernel does not take.  Passed as ``then=``; it changes no result."""
+    if w is None or w.dtype != torch.bfloat16 or w.dim() != 2 or not w.is_cuda or not w.is_contiguous():
+        return None
+    return (w, _PRODUCT_KINDS[kind])
+
+
+def _ahead(then) -> dict:
+    if then is None or LOOK_AHEAD_BYTES <= 0:
+        return {}
+    return {"next_w": then[0], "next_epilogue": then[1], "next_bytes": LOOK_AHEAD_BYTES}
+
+
+def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, status=None, then=None) -> torch.Tensor:
     """out[T, I] = silu(x Wg^T) * (x Wu^T) for ``w_gate_up = interleave_gate_up(Wg, Wu)``.  bfloat16: one
     tcgen05 kernel whose epilogue forms the product from the 32-bit sums.  Otherwise the product
     into [T, 2 I] and the elementwise kernel."""
@@ -124,7 +144,7 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
         scratch, counters = _split_workspace(x.device)
         global launches
         launches += 1
-        be.gemm_tc(x, w_gate_up, None, out, status, scratch, counters, 1)
+        be.gemm_tc(x, w_gate_up, None, out, status, scratch, counters, 1, **_ahead(then))
         return out
     gu = torch.empty((x.shape[0], w_gate_up.shape[0]), dtype=x.dtype, device=x.device)
     linear(x, w_gate_up, None, gu, status)
@@ -144,8 +164,10 @@ def rope_store(qkv, positions, cos_sin, k_cache, v_cache, token_seq, block_table
 # --------------------------------------------------------------------------- matrix products
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, status=None) -> torch.Tensor:
-    """out[T, N] = x[T, K] w[N, K]^T (+ bias).  ``out`` is float32 or the dtype of x.
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, status=None,
+           then=None) -> torch.Tensor:
+    """out[T, N] = x[T, K] w[N, K]^T (+ bias).  ``out`` is float32 or the dtype of x.  ``then``: the
+    ``product_hint`` of the product that runs next, if the caller knows it.
 
     float32 x and w: the 32-bit kernel (FFMA in a fixed order, no TF32).  A weight kept in
     32-bit beside bfloat16 activations goes the same way, with x widened.  bfloat16: the
@@ -169,14 +191,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
         be.gemm_skinny(x, w, bias, out)
     else:
         scratch, counters = _split_workspace(x.device)
-        be.gemm_tc(x, w, bias, out, status, scratch, counters)
+        be.gemm_tc(x, w, bias, out, status, scratch, counters, **_ahead(then))
     return out
 
 
 STREAM_SHARES = os.environ.get("VTB200_STREAM_SHARES", "1") != "0"   # False: linear_to_stream always adds the shares itself
 
 
-def linear_to_stream(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], status=None):
+def linear_to_stream(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], status=None, then=None):
     """x w^T (+ bias) for a result that goes straight into the residual stream (``ResidualStream.add``): a
     tensor [T, N] of x's dtype, or, for bfloat16 batches small enough that the kernel cuts the inner dimension
     over CTAs, a ``SplitSum`` of the unadded 32-bit shares, which the next norm adds."""
@@ -191,10 +213,10 @@ def linear_to_stream(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
         shares = torch.empty((be.gemm_tc_shares(m, n, k), m, n), dtype=torch.float32, device=x.device)
         global launches
         launches += 1
-        be.gemm_tc(x, w, bias, shares, status, None, None, 2)
+        be.gemm_tc(x, w, bias, shares, status, None, None, 2, **_ahead(then))
         return SplitSum(shares)
     out = torch.empty((m, w.shape[0]), dtype=x.dtype, device=x.device)
-    return linear(x, w, bias, out, status)
+    return linear(x, w, bias, out, status, then)
 
 
 _workspaces = {}

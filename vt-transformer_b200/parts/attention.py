@@ -71,15 +71,19 @@ class PagedAttention(Mixer):
                 n += b.numel() * b.element_size()
         return n
 
+    def first_product(self):
+        return self.rt.ops.product_hint(self.w_qkv, "stream")
+
     def forward(self, h, ctx, cache):
         s, ops = self.spec, self.rt.ops
         T = h.shape[0]
+        after = ops.product_hint(self.w_o, "stream")
         if ops.single_token_step_is_one_kernel(ctx, h.dtype, s.heads, s.kv_heads, s.head_dim):
-            qkv = ops.linear_to_stream(h, self.w_qkv, self.b_qkv)      # that kernel adds the shares of k itself
+            qkv = ops.linear_to_stream(h, self.w_qkv, self.b_qkv, then=after)      # that kernel adds the shares of k itself
         else:
             qkv = torch.empty((T, self.q_dim + 2 * self.kv_dim), dtype=h.dtype, device=h.device)
-            ops.linear(h, self.w_qkv, self.b_qkv, qkv)
+            ops.linear(h, self.w_qkv, self.b_qkv, qkv, then=after)
         o = torch.empty((T, self.q_dim), dtype=h.dtype, device=h.device)
         ops.rope_attention(qkv, o, self.position.table, cache.k, cache.v, ctx, cache.block_table, s.heads, s.kv_heads,
                            s.head_dim, s.window, self.scale, store=cache.writes, status=ctx.status)
-        return ops.linear_to_stream(o, self.w_o, self.b_o)
+        return ops.linear_to_stream(o, self.w_o, self.b_o, then=self.then)

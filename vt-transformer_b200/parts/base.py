@@ -176,11 +176,19 @@ class Part:
     # memory, so that a captured CUDA graph of it can be replayed for another step.  A part that
     # loops over ``ctx.seqs`` on the host, or allocates by the step's contents, must leave it False.
     graph_safe = False
+    # What the step streams from HBM after this part is done: ``ops.product_hint(...)`` of the first matrix product
+    # of the part that runs next, or None.  The model sets it once the weights are loaded; a part hands it to its own
+    # last product (``then=``), whose kernel asks for the first of those weights while it ends.  A hint only.
+    then = None
 
     def __init__(self, spec, prefix: str, rt: Runtime):
         self.spec = spec
         self.prefix = prefix
         self.rt = rt
+
+    def first_product(self):
+        """``ops.product_hint(...)`` of the matrix product with which this part's ``forward`` begins, or None."""
+        return None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         """Full tensor name -> what is expected under it."""
@@ -242,6 +250,10 @@ class Block(Part):
 
     def cache_spec(self):
         return None
+
+    def link(self, then) -> None:
+        """``then``: the first product of what runs after this block (see ``Part.then``); a block hands it to the
+        part it runs last, and gives the parts before it the first product of their successors."""
 
     def forward(self, stream, ctx, cache):
         raise NotImplementedError

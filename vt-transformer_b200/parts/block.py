@@ -38,6 +38,13 @@ class PreNormBlock(Block):
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in self.parts)
 
+    def first_product(self):
+        return self.mixer.first_product()
+
+    def link(self, then) -> None:
+        self.mixer.then = self.ffn.first_product()
+        self.ffn.then = then
+
     def forward(self, stream, ctx, cache):
         h = stream.normed(self.norm1)
         stream.add(self.mixer.forward(h, ctx, cache))

@@ -56,6 +56,9 @@ class LinearHead(Head):
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size() + self.norm.weight_bytes()
 
+    def first_product(self):
+        return self.rt.ops.product_hint(self.weight, "linear")
+
     def forward(self, stream, ctx):
         s, ops = self.spec, self.rt.ops
         n_want = ctx.want_rows.numel()

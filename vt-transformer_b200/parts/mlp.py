@@ -44,9 +44,12 @@ class GatedMLP(FeedForward):
         return (self.w_gate_up.numel() * self.w_gate_up.element_size()
                 + self.w_down.numel() * self.w_down.element_size())
 
+    def first_product(self):
+        return self.rt.ops.product_hint(self.w_gate_up, "silu_mul")
+
     def forward(self, h, ctx):
         s, ops = self.spec, self.rt.ops
         T = h.shape[0]
         act = torch.empty((T, s.inter), dtype=h.dtype, device=h.device)
-        ops.linear_silu_mul(h, self.w_gate_up, act)
-        return ops.linear_to_stream(act, self.w_down, None)
+        ops.linear_silu_mul(h, self.w_gate_up, act, then=ops.product_hint(self.w_down, "stream"))
+        return ops.linear_to_stream(act, self.w_down, None, then=self.then)
