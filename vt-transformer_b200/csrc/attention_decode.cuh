@@ -68,6 +68,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
     unsigned char* smem_raw = BOXES ? reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023) : smem_dyn;
     __shared__ int last_flag;
     __shared__ __align__(8) uint64_t arrived[DWARPS_MAX][DSTAGES_MAX];      // with boxes: a warp's stage has arrived
+    __shared__ float2 cs_row[D / 2];                                        // the rotation's (cos, sin) of the step's token
     // The kernels before this one in the stream may still be running (programmatic dependent launch).  What
     // the step's description says (lengths, block tables: copied from the host before the step's first kernel)
     // and the keys and values of earlier steps may be read at once; q, and a key or value written in this
@@ -254,6 +255,12 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
 #pragma unroll
     for (int j = 0; j < S - 1; ++j) pages_of(first + j * W, pg_pro[j]);
     pages_of(first + (S - 1) * W, pg_next);
+    // The rotation table is written by no kernel and the token's position is in the step's description: its row is
+    // fetched before the wait (one token a sequence, q as unadded shares: the barrier behind their sum publishes it).
+    const bool cs_staged = p.fuse_rope && p.cos_sin != nullptr && p.qkv_shares != nullptr && ntok == 1 && pos_lo < p.max_pos;
+    if (cs_staged) {
+        for (int i = threadIdx.x; i < D / 2; i += W * 32) cs_row[i] = p.cos_sin[(size_t)pos_lo * (D / 2) + i];
+    }
     int sent = 0;                                     // blocks of the prologue sent for before the wait
 #pragma unroll
     for (int j = 0; j < S - 1; ++j) {
@@ -320,7 +327,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
                 if (tq == 0) set_status(p.status, kStatusBadPosition, pos[i]);
                 continue;
             }
-            const float2* cs = p.cos_sin + (size_t)pos[i] * (D / 2);
+            const float2* cs = cs_staged ? cs_row : p.cos_sin + (size_t)pos[i] * (D / 2);
 #pragma unroll
             for (int u = 0; u < HC; ++u) {
                 const int v = u + HC;
@@ -401,7 +408,7 @@ attention_decode_kernel(const AttnParams p, int* __restrict__ counters, const __
                 }
             }
             const bool rot = p.cos_sin != nullptr && pos_lo < p.max_pos;
-            const float2* cs = p.cos_sin + (size_t)(rot ? pos_lo : 0) * (D / 2);
+            const float2* cs = cs_staged ? cs_row : p.cos_sin + (size_t)(rot ? pos_lo : 0) * (D / 2);
             for (int i = lane; i < D / 2; i += 32) {
                 __nv_bfloat16 ka = value_at(kcol + i), kb2 = value_at(kcol + i + D / 2);
                 const float a = __bfloat162float(ka), b = __bfloat162float(kb2);
