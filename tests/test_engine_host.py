@@ -36,6 +36,28 @@ def test_bad_run_orders_are_refused(fake_backend):
             DecoderModel(replace(spec, order=order), rt)
 
 
+def test_the_model_tells_each_part_which_matrix_streams_next(fake_backend, folders, monkeypatch):
+    """After loading, every run's block knows the first product of what runs after it (the next run's block, the
+    head after the last); the mixer's last product is followed by the feed-forward's first.  A matrix that the
+    tcgen05 kernel does not take (here: 32-bit on the CPU) gives no hint at all."""
+    from vt_transformer_b200 import ops
+    runner = scenarios.runner_for(folders("A"), DEV, DT, num_pages=4, max_requests=1)
+    for block in runner.model.blocks:
+        assert block.mixer.then is None and block.ffn.then is None and block.first_product() is None
+    monkeypatch.setattr(ops, "product_hint", lambda w, kind: (w, kind))
+    model = runner.model
+    model._link_runs()
+    order = model.spec.order
+    assert len(order) >= 2
+    for n, run in enumerate(order):
+        block = model.blocks[run.block]
+        assert block.mixer.then[0] is block.ffn.w_gate_up and block.mixer.then[1] == "silu_mul"
+        if n + 1 < len(order):
+            assert block.ffn.then[0] is model.blocks[order[n + 1].block].mixer.w_qkv and block.ffn.then[1] == "stream"
+        else:
+            assert block.ffn.then[0] is model.head.weight and block.ffn.then[1] == "linear"
+
+
 def test_toy_mixer_with_state_is_registered_built_and_stepped(fake_backend, tmp_path):
     scenarios.toy_state_case(str(tmp_path), DEV, DT)
 
